@@ -1,0 +1,11 @@
+"""B200 (sm_100a) implementation of the NVFP4 quantized-inference hot path:
+fused RMSNorm / add-RMSNorm + NVFP4 quantisation, the NVFP4 block-scaled GEMM
+and the fused NVFP4 MoE, behind the Python call signatures of the operators
+the reference runs.  All compute is in ``lib/libb200fp4.so`` (hand-written
+CUDA, built by ``build.py``); importing this package loads that library and
+fails if it is absent.
+"""
+from . import _lib, layout  # noqa: F401
+from .norm import add_rmsnorm_fp4quant, rmsnorm_fp4quant  # noqa: F401
+
+__all__ = ["rmsnorm_fp4quant", "add_rmsnorm_fp4quant", "layout"]

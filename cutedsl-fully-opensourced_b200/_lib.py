@@ -1,0 +1,69 @@
+"""ctypes binding of libb200fp4.so, the C-ABI in ``include/b200fp4.h``.
+
+There is deliberately no fallback: if the library has not been built the import
+fails, and every failing C call is turned into a Python exception carrying the
+library's own message.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "lib", "libb200fp4.so")
+
+OK, INVALID_ARGUMENT, UNSUPPORTED, CUDA_ERROR, DEVICE_TIMEOUT, NOT_INITIALISED = range(6)
+
+_vp, _i32, _i64, _f32, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
+
+# name -> (restype, argtypes); kept in the order of include/b200fp4.h
+SIGNATURES = {
+    "b200fp4_last_error": (C.c_char_p, []),
+    "b200fp4_version": (_i32, []),
+    "b200fp4_rmsnorm_fp4quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _f32, _i64, _i32, _i64, _i32, _i32, _vp]),
+    "b200fp4_add_rmsnorm_fp4quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _i64, _i32, _i64, _i64,
+                                            _i32, _i32, _vp]),
+}
+
+
+def _load() -> C.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python {os.path.join(_PKG, 'build.py')}` "
+            "(needs nvcc; there is no CPU or JIT fallback)")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)          # AttributeError here = header and library out of sync
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+
+
+class B200Fp4Error(RuntimeError):
+    pass
+
+
+def check(rc: int) -> None:
+    """Raise the Python exception that matches a non-zero status code."""
+    if rc == OK:
+        return
+    msg = (lib.b200fp4_last_error() or b"").decode("utf-8", "replace")
+    if rc == INVALID_ARGUMENT:
+        raise ValueError(msg)
+    if rc == UNSUPPORTED:
+        raise NotImplementedError(msg)
+    raise B200Fp4Error(f"libb200fp4 status {rc}: {msg}")
+
+
+def ptr(t) -> int:
+    """Device pointer of a torch tensor (or of anything with data_ptr()); None -> NULL."""
+    return None if t is None else t.data_ptr()
+
+
+def current_stream_ptr(device=None) -> int:
+    import torch
+
+    return torch.cuda.current_stream(device).cuda_stream

@@ -1,0 +1,61 @@
+// C-ABI of libb200fp4: plain pointers and sizes in, status code out.  The
+// declarations (with the reference interface each entry point stands in for)
+// are in include/b200fp4.h.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "../../include/b200fp4.h"
+#include "common.cuh"
+
+namespace b200fp4 {
+
+static thread_local char g_last_error[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_cuda(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return kOk;
+  return fail(kCudaError, "%s: %s", what, cudaGetErrorString(e));
+}
+
+int norm_fp4quant_launch(const void* x, void* residual, const void* weight, void* y_fp4, void* block_scale,
+                         void* block_scale_unswizzled, const float* global_scale, float eps, int64_t rows,
+                         int hidden, int64_t x_row_stride, int64_t res_row_stride, int dtype, int sf_layout,
+                         cudaStream_t stream);
+
+}  // namespace b200fp4
+
+using namespace b200fp4;
+
+extern "C" {
+
+const char* b200fp4_last_error(void) { return g_last_error; }
+
+int b200fp4_version(void) { return 1; }
+
+int b200fp4_rmsnorm_fp4quant(const void* x, const void* weight, void* y_fp4, void* block_scale,
+                             void* block_scale_unswizzled, const float* global_scale, float eps, int64_t rows,
+                             int hidden, int64_t x_row_stride, int dtype, int sf_layout, void* stream) {
+  return norm_fp4quant_launch(x, nullptr, weight, y_fp4, block_scale, block_scale_unswizzled, global_scale, eps,
+                              rows, hidden, x_row_stride, 0, dtype, sf_layout, static_cast<cudaStream_t>(stream));
+}
+
+int b200fp4_add_rmsnorm_fp4quant(const void* x, void* residual, const void* weight, void* y_fp4,
+                                 void* block_scale, void* block_scale_unswizzled, const float* global_scale,
+                                 float eps, int64_t rows, int hidden, int64_t x_row_stride,
+                                 int64_t residual_row_stride, int dtype, int sf_layout, void* stream) {
+  if (residual == nullptr) return fail(kInvalidArgument, "residual is null");
+  if (residual == x) return fail(kInvalidArgument, "input and residual must not alias");
+  return norm_fp4quant_launch(x, residual, weight, y_fp4, block_scale, block_scale_unswizzled, global_scale, eps,
+                              rows, hidden, x_row_stride, residual_row_stride, dtype, sf_layout,
+                              static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

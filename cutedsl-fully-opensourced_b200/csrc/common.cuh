@@ -1,0 +1,208 @@
+// Shared device helpers for the sm_100a NVFP4 kernels: error plumbing, wide
+// global-memory accesses, scalar-format conversions and the 16-element NVFP4
+// block quantiser whose rounding rules follow the reference's torch golden
+// (tests/python/test_flashinfer_norm_verbatim.py:47-68 and, for the MoE
+// activation packer, tests/python/test_flashinfer_b12x_verbatim.py:28-65).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200fp4 {
+
+// ---------------------------------------------------------------------------
+// host-side error reporting (defined in capi.cu)
+// ---------------------------------------------------------------------------
+enum Status : int {
+  kOk = 0,
+  kInvalidArgument = 1,
+  kUnsupported = 2,
+  kCudaError = 3,
+  kDeviceTimeout = 4,
+  kNotInitialised = 5,
+};
+
+int fail(int code, const char* fmt, ...);
+int check_cuda(cudaError_t e, const char* what);
+
+#define B200_CUDA(call)                                         \
+  do {                                                          \
+    int _rc = ::b200fp4::check_cuda((call), #call);             \
+    if (_rc) return _rc;                                        \
+  } while (0)
+
+// ---------------------------------------------------------------------------
+// 32-byte global accesses (one instruction per 16 half-precision elements)
+// ---------------------------------------------------------------------------
+struct alignas(32) U32x8 {
+  uint32_t v[8];
+};
+
+// read-only, streamed once: bypass L1 allocation
+__device__ __forceinline__ U32x8 ld_stream_32B(const void* p) {
+  U32x8 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]), "=r"(r.v[5]),
+                 "=r"(r.v[6]), "=r"(r.v[7])
+               : "l"(p));
+  return r;
+}
+
+// data that the same kernel writes back later (no .nc)
+__device__ __forceinline__ U32x8 ld_32B(const void* p) {
+  U32x8 r;
+  asm volatile("ld.global.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r.v[0]), "=r"(r.v[1]), "=r"(r.v[2]), "=r"(r.v[3]), "=r"(r.v[4]), "=r"(r.v[5]),
+                 "=r"(r.v[6]), "=r"(r.v[7])
+               : "l"(p)
+               : "memory");
+  return r;
+}
+
+__device__ __forceinline__ void st_32B(void* p, const U32x8& r) {
+  asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(r.v[0]), "r"(r.v[1]),
+               "r"(r.v[2]), "r"(r.v[3]), "r"(r.v[4]), "r"(r.v[5]), "r"(r.v[6]), "r"(r.v[7])
+               : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// 16-bit float pairs <-> f32
+// ---------------------------------------------------------------------------
+template <typename T>
+struct Pair16;
+
+template <>
+struct Pair16<__nv_bfloat16> {
+  static __device__ __forceinline__ float lo(uint32_t u) { return __uint_as_float(u << 16); }
+  static __device__ __forceinline__ float hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+  // two f32 -> packed pair, round-to-nearest-even each
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+    return r;
+  }
+};
+
+template <>
+struct Pair16<__half> {
+  static __device__ __forceinline__ float lo(uint32_t u) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(u & 0xffffu)));
+  }
+  static __device__ __forceinline__ float hi(uint32_t u) {
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(u >> 16)));
+  }
+  static __device__ __forceinline__ uint32_t pack(float a, float b) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+    return r;
+  }
+};
+
+// ---------------------------------------------------------------------------
+// e4m3 scale factors
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t e4m3_encode_rn(float x) {   // 0 <= x <= 448
+  return static_cast<uint32_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
+}
+
+__device__ __forceinline__ float e4m3_decode(uint32_t bits) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw(static_cast<__nv_fp8_storage_t>(bits & 0xffu), __NV_E4M3);
+  return __half2float(__half(h));
+}
+
+// every non-zero code read as 2^(e-7) * (1 + m/8), exponent-0 codes included
+__device__ __forceinline__ float e4m3_decode_implicit_one(uint32_t bits) {
+  bits &= 0x7fu;
+  return bits == 0 ? 0.0f : __uint_as_float((((bits >> 3) + 120u) << 23) | ((bits & 7u) << 20));
+}
+
+// ---------------------------------------------------------------------------
+// e2m1 codes
+// ---------------------------------------------------------------------------
+// Exact code of q = t / s (s > 0): nearest grid value; a value half way
+// between two grid points takes the smaller magnitude; a result of zero is +0.
+// t > c*s  <=>  fl(t/s) > c  for every midpoint c, because c*s is exact in f32.
+__device__ __forceinline__ uint32_t e2m1_code_exact(float t, float s) {
+  const float mag = fabsf(t);
+  uint32_t idx = (mag > 0.25f * s) + (mag > 0.75f * s) + (mag > 1.25f * s) + (mag > 1.75f * s) +
+                 (mag > 2.5f * s) + (mag > 3.5f * s) + (mag > 5.0f * s);
+  return (t < 0.0f && idx != 0) ? (idx | 8u) : idx;
+}
+
+// hardware round-to-nearest-even pair conversion; a -> low nibble, b -> high
+__device__ __forceinline__ uint32_t e2m1x2_hw(float a, float b) {
+  return static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest));
+}
+
+__device__ __forceinline__ uint32_t e2m1x8_hw(const float* u) {
+  return e2m1x2_hw(u[0], u[1]) | (e2m1x2_hw(u[2], u[3]) << 8) | (e2m1x2_hw(u[4], u[5]) << 16) |
+         (e2m1x2_hw(u[6], u[7]) << 24);
+}
+
+// -0 (code 8) -> +0 (code 0) in all eight nibbles
+__device__ __forceinline__ uint32_t e2m1x8_drop_negative_zero(uint32_t x) {
+  const uint32_t nonzero = ((x & 0x77777777u) + 0x77777777u) & 0x88888888u;
+  return x & (0x77777777u | nonzero);
+}
+
+// ---------------------------------------------------------------------------
+// NVFP4 quantisation of one 16-element block held in registers
+//   sf   = min((amax*gs)/6, 448) -> e4m3 (RN-even)
+//   code = nearest_e2m1((v*gs) / sf_q), ties to the smaller magnitude
+// The codes come from the hardware converter applied to two brackets of the
+// quotient, v*k*(1+2^-19) and v*k*(1-2^-19) with k ~ gs/sf_q.  The exact
+// quotient lies strictly between them, so when both brackets convert to the
+// same eight codes that is the exact answer; the rare group where they differ
+// (a value within 2^-18 of a midpoint, exact ties included) is redone with the
+// division-free exact comparison above.
+// kImplicitOne selects the MoE activation packer, which divides by the
+// implicit-one reading of the scale byte instead of its true value.
+// ---------------------------------------------------------------------------
+template <bool kImplicitOne>
+__device__ __forceinline__ void quantize_block16(const float (&v)[16], float gs, uint32_t& codes_lo,
+                                                 uint32_t& codes_hi, uint32_t& sf_bits) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  const float sf = fminf(__fdiv_rn(__fmul_rn(amax, gs), 6.0f), 448.0f);
+  sf_bits = e4m3_encode_rn(sf);
+  const float div = kImplicitOne ? e4m3_decode_implicit_one(sf_bits) : e4m3_decode(sf_bits);
+  const float k = div > 0.0f ? __fmul_rn(gs, __frcp_rn(div)) : 0.0f;
+  const float k_hi = k * 1.0000019073486328125f;   // 1 + 2^-19
+  const float k_lo = k * 0.9999980926513671875f;   // 1 - 2^-19
+  uint32_t out[2];
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    float uh[8], ul[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      uh[i] = v[8 * g + i] * k_hi;
+      ul[i] = v[8 * g + i] * k_lo;
+    }
+    uint32_t ch = e2m1x8_hw(uh);
+    const uint32_t cl = e2m1x8_hw(ul);
+    if (ch != cl) {
+      ch = 0;
+      if (div > 0.0f) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ch |= e2m1_code_exact(__fmul_rn(v[8 * g + i], gs), div) << (4 * i);
+      }
+    }
+    out[g] = e2m1x8_drop_negative_zero(ch);
+  }
+  codes_lo = out[0];
+  codes_hi = out[1];
+}
+
+// offset of scale factor (row m, K-block kb) in the 128x4 tiled layout with rk
+// K-tiles per row tile (python/cutlass_compat/cutlass/utils/blockscaled_layout.py:37-42)
+__device__ __host__ __forceinline__ int64_t sf_swizzled_offset(int64_t m, int kb, int rk) {
+  return (m & 31) * 16 + ((m >> 5) & 3) * 4 + (kb & 3) + static_cast<int64_t>(kb >> 2) * 512 +
+         (m >> 7) * static_cast<int64_t>(rk) * 512;
+}
+
+}  // namespace b200fp4

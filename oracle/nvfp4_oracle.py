@@ -1,0 +1,337 @@
+"""CPU oracle for the NVFP4 quantized-inference hot path.
+
+TEST INFRASTRUCTURE ONLY.  Nothing in the shipped package imports this file;
+it is the checker that the CUDA kernels are compared with (tests, the smoke
+entry and the CPU-baseline leg of the benchmark).  It restates, in numpy plus
+torch-CPU arithmetic, the torch golden functions that the reference keeps in
+its own acceptance tests:
+
+* NVFP4 block quantiser ............ tests/python/test_flashinfer_norm_verbatim.py:47-68
+* rmsnorm_fp4quant golden .......... tests/python/test_flashinfer_norm_verbatim.py:71-81
+* add_rmsnorm_fp4quant golden ...... tests/python/test_flashinfer_norm_verbatim.py:84-99
+* e2m1 / e4m3 decoders ............. tests/python/test_flashinfer_norm_verbatim.py:22-44
+* 128x4 scale-factor layout ........ python/cutlass_compat/cutlass/utils/blockscaled_layout.py:17-42
+                                     tests/python/test_flashinfer_b12x_verbatim.py:68-89
+* block-scaled GEMM golden ......... third_party/cutlass/examples/python/CuTeDSL/cute/blackwell_geforce/
+                                     kernel/blockscaled_gemm/dense_blockscaled_gemm_persistent_cooperative.py:1791-1793
+* MoE "fast" activation quantiser .. tests/python/test_flashinfer_b12x_verbatim.py:28-65
+* routed MoE golden ................ tests/python/test_flashinfer_b12x_verbatim.py:209-219
+
+Parity is PINNED: tests/golden/make_golden.py imports the reference's own
+functions (in the build container, where the reference tree is mounted),
+asserts that every function here returns bit-identical results on the
+reference's test shapes and on the benchmark-shaped cases, and freezes the
+outputs as fixtures that the CPU test-suite replays.  The one unpinned piece is
+the MoE combine for top_k > 1, which the reference never exercises; it is
+defined here as an f32 sum over slots in slot order followed by one rounding.
+
+All float arithmetic is IEEE binary32, one rounding per operation, in the
+order written -- numpy float32 ufuncs and torch-CPU float ops both behave so.
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+F32 = np.float32
+
+# magnitude grid of e2m1 and the midpoints between neighbouring grid points
+E2M1_GRID = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0], dtype=F32)
+E2M1_MIDPOINTS = np.array([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], dtype=F32)
+# signed decode table indexed by the 4-bit code (bit 3 = sign)
+E2M1_DECODE = np.concatenate([E2M1_GRID, -E2M1_GRID]).astype(F32)
+
+SF_BLOCK = 16          # elements that share one scale factor (NVFP4)
+E4M3_MAX = F32(448.0)
+
+
+# --------------------------------------------------------------------------
+# scalar formats
+# --------------------------------------------------------------------------
+def e4m3_encode(x: np.ndarray) -> np.ndarray:
+    """Round non-negative float32 values (<= 448) to e4m3fn bits, RN-even.
+
+    Normal numbers have a 3-bit mantissa and exponent bias 7; values below
+    2**-6 are subnormal with spacing 2**-9, so anything under 2**-10 becomes 0
+    (the decoder of the reference states the same rule,
+    test_flashinfer_norm_verbatim.py:35-44).
+    """
+    x = np.asarray(x, dtype=F32)
+    out = np.zeros(x.shape, dtype=np.uint8)
+    sub = x < F32(2.0 ** -6)
+    # subnormal range: count of 2**-9 steps, ties to even; 8 steps == min normal
+    q_sub = np.rint(x.astype(np.float64) * 512.0).astype(np.int64)
+    # normal range
+    _, ex = np.frexp(np.where(sub, F32(1.0), x))      # x = m * 2**ex, m in [0.5,1)
+    e = ex.astype(np.int64) - 1                        # floor(log2 x)
+    q = np.rint(np.ldexp(np.where(sub, F32(1.0), x).astype(np.float64), 3 - e)).astype(np.int64)
+    carry = q == 16
+    e = np.where(carry, e + 1, e)
+    q = np.where(carry, 8, q)
+    bits_norm = ((e + 7) << 3) | (q - 8)
+    out[...] = np.where(sub, q_sub, bits_norm).astype(np.uint8)
+    return out
+
+
+def e4m3_decode(bits: np.ndarray) -> np.ndarray:
+    """e4m3fn bits -> float32 (sign bit honoured, NaN code not expected)."""
+    b = np.asarray(bits, dtype=np.uint8).astype(np.int32)
+    ex = (b >> 3) & 0xF
+    man = (b & 7).astype(np.float64)
+    mag = np.where(ex == 0, man * 2.0 ** -9, (1.0 + man / 8.0) * np.exp2((ex - 7).astype(np.float64)))
+    return np.where((b >> 7) & 1 == 1, -mag, mag).astype(F32)
+
+
+def e4m3_decode_implicit_one(bits: np.ndarray) -> np.ndarray:
+    """The MoE activation packer's scale decode: every non-zero code is read as
+    2**(e-7) * (1 + m/8), exponent-0 codes included
+    (test_flashinfer_b12x_verbatim.py:28-40)."""
+    b = np.asarray(bits, dtype=np.uint8).astype(np.int32)
+    ex = (b >> 3) & 0xF
+    man = (b & 7).astype(np.float64)
+    val = np.exp2((ex - 7).astype(np.float64)) * (1.0 + man / 8.0)
+    return np.where(b == 0, 0.0, val).astype(F32)
+
+
+def e2m1_nearest_codes(scaled: np.ndarray) -> np.ndarray:
+    """float32 -> 4-bit e2m1 codes by nearest grid value.
+
+    A value exactly half way between two grid points takes the one of smaller
+    magnitude, and anything that lands on zero is encoded as +0 (code 0): that
+    is what an arg-min over the 16-entry table yields, because the first
+    minimal entry wins (test_flashinfer_norm_verbatim.py:47-55).  Magnitudes
+    above 6 saturate.
+    """
+    s = np.asarray(scaled, dtype=F32)
+    mag = np.abs(s)
+    idx = np.zeros(s.shape, dtype=np.uint8)
+    for mid in E2M1_MIDPOINTS:
+        idx += (mag > mid).astype(np.uint8)
+    neg = (s < 0) & (idx > 0)
+    return idx | (neg.astype(np.uint8) << 3)
+
+
+def e2m1_decode(codes: np.ndarray) -> np.ndarray:
+    return E2M1_DECODE[np.asarray(codes, dtype=np.uint8) & 0xF]
+
+
+def pack_e2m1(codes: np.ndarray) -> np.ndarray:
+    """[..., K] codes -> [..., K/2] bytes, even element in the LOW nibble
+    (test_flashinfer_norm_verbatim.py:22-32, test_flashinfer_b12x_verbatim.py:59)."""
+    c = np.asarray(codes, dtype=np.uint8)
+    return (c[..., 0::2] | (c[..., 1::2] << 4)).astype(np.uint8)
+
+
+def unpack_e2m1(packed: np.ndarray) -> np.ndarray:
+    p = np.asarray(packed, dtype=np.uint8)
+    out = np.empty(p.shape[:-1] + (p.shape[-1] * 2,), dtype=np.uint8)
+    out[..., 0::2] = p & 0xF
+    out[..., 1::2] = p >> 4
+    return out
+
+
+# --------------------------------------------------------------------------
+# NVFP4 block quantiser
+# --------------------------------------------------------------------------
+def quantize_nvfp4(values: np.ndarray, global_scale: float, *, implicit_one_packing: bool = False):
+    """Quantise float32 [..., H] (H % 16 == 0) to e2m1 codes + e4m3 SF bits.
+
+    sf      = min((amax * gs) / 6, 448)  -> e4m3 (RN-even)
+    scaled  = (v * gs) / sf_q            (0 where sf_q == 0)
+    code    = nearest e2m1 (ties to the smaller magnitude)
+
+    ``implicit_one_packing`` switches the divisor to the MoE packer's decode of
+    the scale byte (see :func:`e4m3_decode_implicit_one`); the stored byte and
+    the value used to de-quantise stay the true e4m3 number.
+    Returns (codes uint8 [..., H], sf_bits uint8 [..., H/16]).
+    """
+    v = np.ascontiguousarray(values, dtype=F32)
+    gs = F32(global_scale)
+    lead, h = v.shape[:-1], v.shape[-1]
+    if h % SF_BLOCK:
+        raise ValueError("last dimension must be a multiple of 16")
+    blocks = v.reshape(*lead, h // SF_BLOCK, SF_BLOCK)
+    amax = np.abs(blocks).max(axis=-1)
+    sf = np.minimum((amax * gs) / F32(6.0), E4M3_MAX)
+    sf_bits = e4m3_encode(sf)
+    div = e4m3_decode_implicit_one(sf_bits) if implicit_one_packing else e4m3_decode(sf_bits)
+    ok = div > 0
+    safe = np.where(ok, div, F32(1.0))[..., None]
+    scaled = np.where(ok[..., None], (blocks * gs) / safe, F32(0.0)).astype(F32)
+    codes = e2m1_nearest_codes(scaled).reshape(*lead, h)
+    return codes, sf_bits
+
+
+def dequantize_nvfp4(codes: np.ndarray, sf_bits: np.ndarray, global_scale: float = 1.0) -> np.ndarray:
+    """value = grid(code) * sf / gs (test_flashinfer_norm_verbatim.py:110-112)."""
+    c = e2m1_decode(codes)
+    sf = np.repeat(e4m3_decode(sf_bits), SF_BLOCK, axis=-1)
+    return ((c * sf) / F32(global_scale)).astype(F32)
+
+
+# --------------------------------------------------------------------------
+# 128x4 scale-factor layout
+# --------------------------------------------------------------------------
+def sf_swizzled_size(rows: int, k_blocks: int) -> int:
+    return ((rows + 127) // 128) * ((k_blocks + 3) // 4) * 512
+
+
+def sf_swizzled_offsets(rows: int, k_blocks: int) -> np.ndarray:
+    """Byte offset of SF (row m, K-block kb) inside one [rows, k_blocks] matrix:
+    (m%32)*16 + ((m/32)%4)*4 + kb%4 + (kb/4)*512 + (m/128)*rk*512."""
+    rk = (k_blocks + 3) // 4
+    m = np.arange(rows, dtype=np.int64)[:, None]
+    kb = np.arange(k_blocks, dtype=np.int64)[None, :]
+    return (m % 32) * 16 + ((m // 32) % 4) * 4 + (kb % 4) + (kb // 4) * 512 + (m // 128) * rk * 512
+
+
+def swizzle_sf(sf_bits: np.ndarray) -> np.ndarray:
+    """[..., rows, k_blocks] row-major bytes -> [..., tiles*512] swizzled bytes;
+    rows and K-blocks that pad a tile are written as 0."""
+    s = np.asarray(sf_bits, dtype=np.uint8)
+    rows, kb = s.shape[-2:]
+    lead = s.shape[:-2]
+    out = np.zeros(lead + (sf_swizzled_size(rows, kb),), dtype=np.uint8)
+    out[..., sf_swizzled_offsets(rows, kb).reshape(-1)] = s.reshape(*lead, rows * kb)
+    return out
+
+
+def unswizzle_sf(swz: np.ndarray, rows: int, k_blocks: int) -> np.ndarray:
+    s = np.asarray(swz, dtype=np.uint8)
+    lead = s.shape[:-1]
+    return s[..., sf_swizzled_offsets(rows, k_blocks).reshape(-1)].reshape(*lead, rows, k_blocks)
+
+
+# --------------------------------------------------------------------------
+# fused RMSNorm (+ residual add) + NVFP4 quantisation
+# --------------------------------------------------------------------------
+def _inv_rms(h32: torch.Tensor, eps: float) -> torch.Tensor:
+    # mean of squares in f32 with torch's own CPU reduction, then 1/sqrt
+    return torch.rsqrt(h32.square().mean(dim=-1, keepdim=True) + eps)
+
+
+def rmsnorm_fp4quant_ref(x: torch.Tensor, weight: torch.Tensor, eps: float, global_scale: float,
+                         row_chunk: int = 1024):
+    """x [M,H] and weight [H] in fp16/bf16 (CPU).  The product x*w is rounded to
+    the input dtype before the f32 scaling by 1/rms
+    (test_flashinfer_norm_verbatim.py:71-81).
+    Returns (codes [M,H] u8, sf_bits [M,H/16] u8)."""
+    m, h = x.shape
+    codes = np.empty((m, h), dtype=np.uint8)
+    sfb = np.empty((m, h // SF_BLOCK), dtype=np.uint8)
+    for r0 in range(0, m, row_chunk):
+        xs = x[r0:r0 + row_chunk]
+        inv = _inv_rms(xs.float(), eps)
+        q_in = (xs * weight).float() * inv
+        codes[r0:r0 + row_chunk], sfb[r0:r0 + row_chunk] = quantize_nvfp4(q_in.numpy(), global_scale)
+    return codes, sfb
+
+
+def add_rmsnorm_fp4quant_ref(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                             global_scale: float, row_chunk: int = 1024):
+    """h = x + residual in f32; the residual stream keeps h rounded to the input
+    dtype; 1/rms comes from the unrounded h, while the normalised value is the
+    rounded residual times 1/rms times weight, all f32
+    (test_flashinfer_norm_verbatim.py:84-99).
+    Returns (residual_out [M,H] torch, codes, sf_bits)."""
+    m, h = x.shape
+    res_out = torch.empty_like(x)
+    codes = np.empty((m, h), dtype=np.uint8)
+    sfb = np.empty((m, h // SF_BLOCK), dtype=np.uint8)
+    w32 = weight.float()
+    for r0 in range(0, m, row_chunk):
+        acc = x[r0:r0 + row_chunk].float() + residual[r0:r0 + row_chunk].float()
+        rounded = acc.to(x.dtype)
+        res_out[r0:r0 + row_chunk] = rounded
+        q_in = rounded.float() * _inv_rms(acc, eps) * w32
+        codes[r0:r0 + row_chunk], sfb[r0:r0 + row_chunk] = quantize_nvfp4(q_in.numpy(), global_scale)
+    return res_out, codes, sfb
+
+
+def rmsnorm_true(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """Plain f32 RMSNorm, used to derive the per-tensor global scale."""
+    xf = x.float()
+    return xf * _inv_rms(xf, eps) * weight.float()
+
+
+def nvfp4_global_scale(values: torch.Tensor) -> float:
+    """448*6 / amax, as an f32-representable python float."""
+    return float(np.float32(448.0 * 6.0 / float(values.abs().max())))
+
+
+# --------------------------------------------------------------------------
+# NVFP4 block-scaled GEMM
+# --------------------------------------------------------------------------
+def gemm_nvfp4_ref(a_codes, sfa_bits, b_codes, sfb_bits, alpha: float = 1.0) -> torch.Tensor:
+    """C[m,n] = alpha * sum_k (A*SFA)[m,k] * (B*SFB)[n,k]; operands are
+    de-quantised to f32 first and multiplied in f32 (the demo's own check)."""
+    a = torch.from_numpy(e2m1_decode(a_codes) * np.repeat(e4m3_decode(sfa_bits), SF_BLOCK, axis=-1))
+    b = torch.from_numpy(e2m1_decode(b_codes) * np.repeat(e4m3_decode(sfb_bits), SF_BLOCK, axis=-1))
+    c = a @ b.t()
+    return c * alpha if alpha != 1.0 else c
+
+
+def integer_gemm_operands(m: int, n: int, k: int, seed: int = 0):
+    """Exact-test data in the demo's style: values in {-2,-1,0,1}, scale
+    factors in {1,2}; every product and partial sum is an integer that f32
+    holds exactly up to K = 8192."""
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randint(-2, 2, (m, k), generator=g).float().numpy()
+    b = torch.randint(-2, 2, (n, k), generator=g).float().numpy()
+    sfa = torch.randint(1, 3, (m, k // SF_BLOCK), generator=g).float().numpy()
+    sfb = torch.randint(1, 3, (n, k // SF_BLOCK), generator=g).float().numpy()
+    return (e2m1_nearest_codes(a), e4m3_encode(sfa), e2m1_nearest_codes(b), e4m3_encode(sfb))
+
+
+# --------------------------------------------------------------------------
+# routed MoE
+# --------------------------------------------------------------------------
+def route_topk_ref(logits: torch.Tensor, top_k: int, renormalize: bool = True):
+    """softmax over experts -> top-k (descending, lowest index first among
+    equals) -> weights renormalised to sum 1."""
+    p = torch.softmax(logits.float(), dim=-1)
+    # stable sort so that equal probabilities resolve to the lower expert id
+    order = torch.sort(p, dim=-1, descending=True, stable=True).indices[:, :top_k]
+    w = torch.gather(p, 1, order)
+    if renormalize:
+        w = w / w.sum(dim=-1, keepdim=True)
+    return order.to(torch.int32), w
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    return torch.nn.functional.silu(gate) * up
+
+
+def moe_ref(x: torch.Tensor, w1_codes, w1_sf, w2_codes, w2_sf, ids: torch.Tensor, weights: torch.Tensor,
+            w1_alpha=None, w2_alpha=None, fc2_input_scale: float = 1.0) -> torch.Tensor:
+    """Routed NVFP4 MoE on the CPU.
+
+    x bf16 [T,H]; w1_codes [E,2I,H] (rows 0..I-1 = up, I..2I-1 = gate) with
+    w1_sf [E,2I,H/16]; w2_codes [E,H,I] with w2_sf [E,H,I/16]; ids int [T,k];
+    weights f32 [T,k].  Per (token, slot): quantise the token with the MoE
+    packer, FC1, silu(gate)*up in f32, round to bf16, quantise again, FC2;
+    slots are summed in f32 in slot order and rounded once to bf16.
+    """
+    t, h = x.shape
+    e, two_i, _ = w1_codes.shape
+    inter = two_i // 2
+    k = ids.shape[1]
+    a1 = np.ones(e, F32) if w1_alpha is None else np.asarray(w1_alpha, F32)
+    a2 = np.ones(e, F32) if w2_alpha is None else np.asarray(w2_alpha, F32)
+    xc, xs = quantize_nvfp4(x.float().numpy(), 1.0, implicit_one_packing=True)
+    xq = torch.from_numpy(dequantize_nvfp4(xc, xs, 1.0))
+    acc = torch.zeros(t, h, dtype=torch.float32)
+    ids_np = ids.numpy()
+    for slot in range(k):
+        part = torch.zeros(t, h, dtype=torch.float32)
+        for ex in np.unique(ids_np[:, slot]):
+            rows = torch.from_numpy(np.nonzero(ids_np[:, slot] == ex)[0])
+            w1 = torch.from_numpy(dequantize_nvfp4(w1_codes[ex], w1_sf[ex]))
+            w2 = torch.from_numpy(dequantize_nvfp4(w2_codes[ex], w2_sf[ex]))
+            fc1 = (xq[rows] @ w1.t()) * float(a1[ex])
+            act = silu_mul(fc1[:, inter:], fc1[:, :inter]).to(torch.bfloat16).float()
+            ac, asf = quantize_nvfp4(act.numpy(), fc2_input_scale, implicit_one_packing=True)
+            aq = torch.from_numpy(e2m1_decode(ac) * np.repeat(e4m3_decode(asf), SF_BLOCK, axis=-1))
+            part[rows] = (aq @ w2.t()) * float(a2[ex])
+        acc += weights[:, slot:slot + 1].float() * part
+    return acc.to(torch.bfloat16)
