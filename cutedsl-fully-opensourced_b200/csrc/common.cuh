@@ -133,20 +133,44 @@ __device__ __forceinline__ uint32_t e2m1_code_exact(float t, float s) {
   return (t < 0.0f && idx != 0) ? (idx | 8u) : idx;
 }
 
-// hardware round-to-nearest-even pair conversion; a -> low nibble, b -> high
-__device__ __forceinline__ uint32_t e2m1x2_hw(float a, float b) {
-  return static_cast<uint32_t>(__nv_cvt_float2_to_fp4x2(make_float2(a, b), __NV_E2M1, cudaRoundNearest));
-}
-
+// hardware round-to-nearest-even conversion of eight values; element i lands
+// in nibble i (cvt's first source operand goes to the high nibble)
 __device__ __forceinline__ uint32_t e2m1x8_hw(const float* u) {
-  return e2m1x2_hw(u[0], u[1]) | (e2m1x2_hw(u[2], u[3]) << 8) | (e2m1x2_hw(u[4], u[5]) << 16) |
-         (e2m1x2_hw(u[6], u[7]) << 24);
+  uint32_t r;
+  asm("{\n"
+      ".reg .b8 b0, b1, b2, b3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b1, %4, %3;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b2, %6, %5;\n"
+      "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
+      "mov.b32 %0, {b0, b1, b2, b3};\n"
+      "}"
+      : "=r"(r)
+      : "f"(u[0]), "f"(u[1]), "f"(u[2]), "f"(u[3]), "f"(u[4]), "f"(u[5]), "f"(u[6]), "f"(u[7]));
+  return r;
 }
 
 // -0 (code 8) -> +0 (code 0) in all eight nibbles
 __device__ __forceinline__ uint32_t e2m1x8_drop_negative_zero(uint32_t x) {
   const uint32_t nonzero = ((x & 0x77777777u) + 0x77777777u) & 0x88888888u;
   return x & (0x77777777u | nonzero);
+}
+
+// a / 6 rounded to nearest, without the division routine: q = a*c, one exact
+// residual and one correction with c = RN(1/6).  Checked against a/6.0f for
+// every positive float whose quotient is a normal number; for denormal
+// quotients (far below the smallest scale factor) it may be one ulp off,
+// which the e4m3 rounding to zero hides.
+__device__ __forceinline__ float div_by_6(float a) {
+  const float c = 0.16666667163372039794921875f;
+  const float q = __fmul_rn(a, c);
+  return __fmaf_rn(__fmaf_rn(-6.0f, q, a), c, q);
+}
+
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
 }
 
 // ---------------------------------------------------------------------------
@@ -168,10 +192,11 @@ __device__ __forceinline__ void quantize_block16(const float (&v)[16], float gs,
   float amax = 0.0f;
 #pragma unroll
   for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  const float sf = fminf(__fdiv_rn(__fmul_rn(amax, gs), 6.0f), 448.0f);
+  const float sf = fminf(div_by_6(__fmul_rn(amax, gs)), 448.0f);
   sf_bits = e4m3_encode_rn(sf);
   const float div = kImplicitOne ? e4m3_decode_implicit_one(sf_bits) : e4m3_decode(sf_bits);
-  const float k = div > 0.0f ? __fmul_rn(gs, __frcp_rn(div)) : 0.0f;
+  // k only has to be within a few ulp of gs/div: the brackets are 2^-19 wide
+  const float k = div > 0.0f ? gs * rcp_approx(div) : 0.0f;
   const float k_hi = k * 1.0000019073486328125f;   // 1 + 2^-19
   const float k_lo = k * 0.9999980926513671875f;   // 1 - 2^-19
   uint32_t out[2];

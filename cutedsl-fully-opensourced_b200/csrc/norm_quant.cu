@@ -6,19 +6,19 @@
 //
 // One pass over HBM: a row is read once (x, and residual for the add variant),
 // kept in registers across the row reduction, and written once (residual, e2m1
-// codes, e4m3 scale factors).  Each thread owns whole 16-element scale blocks
-// (32 bytes of input = one 256-bit load), so a block's amax, scale factor and
-// eight code bytes never leave the thread; four neighbouring lanes merge their
+// codes, e4m3 scale factors).  Each thread owns kVec adjacent 16-element scale
+// blocks (one 256-bit load per block and tensor), so a block's amax, scale
+// factor and code bytes never leave the thread; neighbouring lanes merge their
 // scale bytes into one 32-bit store, which is contiguous both in the row-major
 // and in the 128x4 tiled scale-factor layout.  The grid is persistent (a
-// multiple of the SM count) so the f32 copy of the weight vector stays in
-// registers across rows.
+// multiple of the SM count); every thread parks the f32 copy of its own slice
+// of the weight vector in shared memory once and re-reads it per row.
 #include "common.cuh"
 
 namespace b200fp4 {
 namespace {
 
-constexpr int kMaxChunksPerThread = 4;   // 16-element chunks per thread per row
+constexpr int kMaxUnitsPerThread = 2;    // strided units per thread per row
 constexpr int kMaxThreads = 512;
 
 struct NormParams {
@@ -51,129 +51,182 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-// kWarpRow: one warp per row (hidden <= 512); otherwise one CTA per row.
-template <typename T, bool kAdd, int kChunks, bool kWarpRow>
+// A "unit" is kVec adjacent 16-element chunks; thread t of a team handles units
+// t, t+team, ... (kUnits of them).  kWarpRow: the team is one warp and a CTA
+// works on one row per warp (hidden <= 512); otherwise the team is the CTA.
+template <typename T, bool kAdd, int kVec, int kUnits, bool kWarpRow>
 __global__ void __launch_bounds__(kMaxThreads) norm_quant_kernel(const NormParams p) {
+  extern __shared__ float4 wsm[];          // per-thread weight slices, f32
+  __shared__ float red[2][kMaxThreads / 32];
+
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int nwarps = blockDim.x >> 5;
   const int nchunks = p.hidden >> 4;
-  const int team = kWarpRow ? 32 : blockDim.x;                 // threads that share a row
+  const int team = kWarpRow ? 32 : blockDim.x;
   const int tid = kWarpRow ? lane : threadIdx.x;
   const int rk = (nchunks + 3) >> 2;
   const float gs = __ldg(p.global_scale);
-  const float inv_n_div = static_cast<float>(p.hidden);
+  const float n_as_float = static_cast<float>(p.hidden);
   const T* __restrict__ xg = static_cast<const T*>(p.x);
   T* rg = static_cast<T*>(p.residual);
   const bool sf_row_vec = (nchunks & 3) == 0;                  // row-major SF rows are 4-byte aligned
+  const bool y_vec16 = ((p.hidden >> 1) & 15) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15) == 0;
+  constexpr int kSlots = kUnits * kVec * 4;                    // float4 slots per thread
+  float4* wmine = wsm + (kWarpRow ? warp * kSlots * 32 : 0) + tid;   // slot s lives at wmine[s * team]
 
-  __shared__ float red[2][kMaxThreads / 32];
-
-  // weight as f32, resident for the whole kernel
-  float wf[kChunks][16];
 #pragma unroll
-  for (int c = 0; c < kChunks; ++c) {
-    const int chunk = tid + c * team;
-    if (chunk < nchunks) {
-      unpack16<T>(ld_stream_32B(static_cast<const T*>(p.weight) + chunk * 16), wf[c]);
-    } else {
+  for (int u = 0; u < kUnits; ++u) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) wf[c][i] = 0.0f;
+    for (int v = 0; v < kVec; ++v) {
+      const int chunk = (tid + u * team) * kVec + v;
+      float wf[16];
+      if (chunk < nchunks) {
+        unpack16<T>(ld_stream_32B(static_cast<const T*>(p.weight) + chunk * 16), wf);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) wf[i] = 0.0f;
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        wmine[((u * kVec + v) * 4 + q) * team] = make_float4(wf[4 * q], wf[4 * q + 1], wf[4 * q + 2], wf[4 * q + 3]);
     }
   }
+  // each thread only ever reads back its own slots: no barrier needed
 
   const int64_t row0 = kWarpRow ? static_cast<int64_t>(blockIdx.x) * nwarps + warp : blockIdx.x;
   const int64_t row_step = kWarpRow ? static_cast<int64_t>(gridDim.x) * nwarps : gridDim.x;
   int parity = 0;
   for (int64_t row = row0; row < p.rows; row += row_step, parity ^= 1) {
     // ---- phase 1: load, (add, round, write residual), sum of squares
-    float h[kChunks][16];
+    float h[kUnits * kVec][16];
     float ssq = 0.0f;
 #pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
-      const int chunk = tid + c * team;
-      if (chunk < nchunks) {
-        const U32x8 xv = ld_stream_32B(xg + row * p.x_row_stride + chunk * 16);
-        if constexpr (kAdd) {
-          T* rptr = rg + row * p.res_row_stride + chunk * 16;
-          const U32x8 rv = ld_32B(rptr);
-          U32x8 outv;
+    for (int u = 0; u < kUnits; ++u) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float a = __fadd_rn(Pair16<T>::lo(xv.v[i]), Pair16<T>::lo(rv.v[i]));
-            const float b = __fadd_rn(Pair16<T>::hi(xv.v[i]), Pair16<T>::hi(rv.v[i]));
-            ssq = fmaf(a, a, ssq);
-            ssq = fmaf(b, b, ssq);
-            outv.v[i] = Pair16<T>::pack(a, b);
-            // the normalised value is built from the ROUNDED residual
-            h[c][2 * i] = Pair16<T>::lo(outv.v[i]);
-            h[c][2 * i + 1] = Pair16<T>::hi(outv.v[i]);
+      for (int v = 0; v < kVec; ++v) {
+        const int c = u * kVec + v;
+        const int chunk = (tid + u * team) * kVec + v;
+        if (chunk < nchunks) {
+          const U32x8 xv = ld_stream_32B(xg + row * p.x_row_stride + chunk * 16);
+          if constexpr (kAdd) {
+            T* rptr = rg + row * p.res_row_stride + chunk * 16;
+            const U32x8 rv = ld_32B(rptr);
+            U32x8 outv;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float a = __fadd_rn(Pair16<T>::lo(xv.v[i]), Pair16<T>::lo(rv.v[i]));
+              const float b = __fadd_rn(Pair16<T>::hi(xv.v[i]), Pair16<T>::hi(rv.v[i]));
+              ssq = fmaf(a, a, ssq);
+              ssq = fmaf(b, b, ssq);
+              outv.v[i] = Pair16<T>::pack(a, b);
+              // the normalised value is built from the ROUNDED residual
+              h[c][2 * i] = Pair16<T>::lo(outv.v[i]);
+              h[c][2 * i + 1] = Pair16<T>::hi(outv.v[i]);
+            }
+            st_32B(rptr, outv);
+          } else {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float4 w4 = wmine[(c * 4 + q) * team];
+              const float wq[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+              for (int j = 0; j < 2; ++j) {
+                const int i = 2 * q + j;
+                const float a = Pair16<T>::lo(xv.v[i]);
+                const float b = Pair16<T>::hi(xv.v[i]);
+                ssq = fmaf(a, a, ssq);
+                ssq = fmaf(b, b, ssq);
+                // x*w is rounded to the input type before the f32 scaling
+                const uint32_t xw = Pair16<T>::pack(__fmul_rn(a, wq[2 * j]), __fmul_rn(b, wq[2 * j + 1]));
+                h[c][2 * i] = Pair16<T>::lo(xw);
+                h[c][2 * i + 1] = Pair16<T>::hi(xw);
+              }
+            }
           }
-          st_32B(rptr, outv);
         } else {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            const float a = Pair16<T>::lo(xv.v[i]);
-            const float b = Pair16<T>::hi(xv.v[i]);
-            ssq = fmaf(a, a, ssq);
-            ssq = fmaf(b, b, ssq);
-            // x*w is rounded to the input type before the f32 scaling
-            const uint32_t xw = Pair16<T>::pack(__fmul_rn(a, wf[c][2 * i]), __fmul_rn(b, wf[c][2 * i + 1]));
-            h[c][2 * i] = Pair16<T>::lo(xw);
-            h[c][2 * i + 1] = Pair16<T>::hi(xw);
-          }
+          for (int i = 0; i < 16; ++i) h[c][i] = 0.0f;
         }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) h[c][i] = 0.0f;
       }
     }
-    // ---- row reduction
+    // ---- row reduction: lanes, then (CTA teams) warps through shared memory
     ssq = warp_sum(ssq);
     if constexpr (!kWarpRow) {
       if (lane == 0) red[parity][warp] = ssq;
       __syncthreads();
-      ssq = 0.0f;
-      for (int i = 0; i < nwarps; ++i) ssq += red[parity][i];
+      ssq = warp_sum(lane < nwarps ? red[parity][lane] : 0.0f);
     }
     // 1/sqrt(mean + eps) with IEEE division and square root
-    const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, inv_n_div), p.eps)));
+    const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, n_as_float), p.eps)));
 
     // ---- phase 2: scale, quantise, store
 #pragma unroll
-    for (int c = 0; c < kChunks; ++c) {
-      const int chunk = tid + c * team;
-      const bool active = chunk < nchunks;
-      float v[16];
+    for (int u = 0; u < kUnits; ++u) {
+      uint32_t codes[kVec][2];
+      uint32_t sfb[kVec];
+      const int chunk0 = (tid + u * team) * kVec;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
+      for (int v = 0; v < kVec; ++v) {
+        const int c = u * kVec + v;
+        float val[16];
         if constexpr (kAdd) {
-          v[i] = __fmul_rn(__fmul_rn(h[c][i], rstd), wf[c][i]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float4 w4 = wmine[(c * 4 + q) * team];
+            val[4 * q + 0] = __fmul_rn(__fmul_rn(h[c][4 * q + 0], rstd), w4.x);
+            val[4 * q + 1] = __fmul_rn(__fmul_rn(h[c][4 * q + 1], rstd), w4.y);
+            val[4 * q + 2] = __fmul_rn(__fmul_rn(h[c][4 * q + 2], rstd), w4.z);
+            val[4 * q + 3] = __fmul_rn(__fmul_rn(h[c][4 * q + 3], rstd), w4.w);
+          }
         } else {
-          v[i] = __fmul_rn(h[c][i], rstd);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) val[i] = __fmul_rn(h[c][i], rstd);
         }
+        quantize_block16<false>(val, gs, codes[v][0], codes[v][1], sfb[v]);
+        if (chunk0 + v >= nchunks) sfb[v] = 0;
       }
-      uint32_t lo, hi, sfb;
-      quantize_block16<false>(v, gs, lo, hi, sfb);
-      if (!active) sfb = 0;
-      if (active) {
-        *reinterpret_cast<uint2*>(p.y + row * (p.hidden >> 1) + chunk * 8) = make_uint2(lo, hi);
+      // codes: kVec * 8 contiguous bytes per thread
+      uint8_t* yrow = p.y + row * (p.hidden >> 1);
+      if constexpr (kVec == 2) {
+        if (chunk0 + 1 < nchunks) {
+          if (y_vec16) {
+            *reinterpret_cast<uint4*>(yrow + chunk0 * 8) =
+                make_uint4(codes[0][0], codes[0][1], codes[1][0], codes[1][1]);
+          } else {
+            *reinterpret_cast<uint2*>(yrow + chunk0 * 8) = make_uint2(codes[0][0], codes[0][1]);
+            *reinterpret_cast<uint2*>(yrow + chunk0 * 8 + 8) = make_uint2(codes[1][0], codes[1][1]);
+          }
+        } else if (chunk0 < nchunks) {
+          *reinterpret_cast<uint2*>(yrow + chunk0 * 8) = make_uint2(codes[0][0], codes[0][1]);
+        }
+      } else {
+        if (chunk0 < nchunks) *reinterpret_cast<uint2*>(yrow + chunk0 * 8) = make_uint2(codes[0][0], codes[0][1]);
       }
-      // gather the scale bytes of four neighbouring chunks into the lane whose chunk % 4 == 0
-      uint32_t quad = sfb;
-      quad |= __shfl_down_sync(0xffffffffu, sfb, 1) << 8;
-      quad |= __shfl_down_sync(0xffffffffu, sfb, 2) << 16;
-      quad |= __shfl_down_sync(0xffffffffu, sfb, 3) << 24;
-      if (active && (lane & 3) == 0) {
+      // scale bytes: the lane whose first chunk is a multiple of 4 collects four K-blocks
+      uint32_t quad;
+      bool leader;
+      if constexpr (kVec == 2) {
+        const uint32_t pair = sfb[0] | (sfb[1] << 8);
+        quad = pair | (__shfl_down_sync(0xffffffffu, pair, 1) << 16);
+        leader = (lane & 1) == 0;
+      } else {
+        quad = sfb[0];
+        quad |= __shfl_down_sync(0xffffffffu, sfb[0], 1) << 8;
+        quad |= __shfl_down_sync(0xffffffffu, sfb[0], 2) << 16;
+        quad |= __shfl_down_sync(0xffffffffu, sfb[0], 3) << 24;
+        leader = (lane & 3) == 0;
+      }
+      if (leader && chunk0 < nchunks) {
         if (p.sf_swizzled != nullptr) {
-          *reinterpret_cast<uint32_t*>(p.sf_swizzled + sf_swizzled_offset(row, chunk, rk)) = quad;
+          *reinterpret_cast<uint32_t*>(p.sf_swizzled + sf_swizzled_offset(row, chunk0, rk)) = quad;
         }
         if (p.sf_rowmajor != nullptr) {
-          uint8_t* dst = p.sf_rowmajor + row * nchunks + chunk;
+          uint8_t* dst = p.sf_rowmajor + row * nchunks + chunk0;
           if (sf_row_vec) {
             *reinterpret_cast<uint32_t*>(dst) = quad;
           } else {
-            for (int j = 0; j < 4 && chunk + j < nchunks; ++j) dst[j] = static_cast<uint8_t>(quad >> (8 * j));
+            for (int j = 0; j < 4 && chunk0 + j < nchunks; ++j) dst[j] = static_cast<uint8_t>(quad >> (8 * j));
           }
         }
       }
@@ -192,33 +245,36 @@ int sm_count() {
   return cached;
 }
 
-template <typename T, bool kAdd, int kChunks, bool kWarpRow>
+template <typename T, bool kAdd, int kVec, int kUnits, bool kWarpRow>
 int launch_one(const NormParams& p, int threads, cudaStream_t stream) {
-  auto kern = norm_quant_kernel<T, kAdd, kChunks, kWarpRow>;
+  auto kern = norm_quant_kernel<T, kAdd, kVec, kUnits, kWarpRow>;
+  const size_t smem = static_cast<size_t>(kUnits) * kVec * 4 * sizeof(float4) * threads;
+  if (smem > 48 * 1024) {
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+  }
   int per_sm = 0;
-  B200_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, 0));
-  if (per_sm < 1) per_sm = 1;
+  B200_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, smem));
+  if (per_sm < 1) return fail(kUnsupported, "norm_quant_kernel does not fit on an SM (%zu bytes of shared memory)", smem);
   const int64_t rows_per_cta = kWarpRow ? threads / 32 : 1;
   const int64_t want = (p.rows + rows_per_cta - 1) / rows_per_cta;
   int64_t grid = static_cast<int64_t>(sm_count()) * per_sm;
   if (grid > want) grid = want;
-  kern<<<static_cast<unsigned>(grid), threads, 0, stream>>>(p);
+  kern<<<static_cast<unsigned>(grid), threads, smem, stream>>>(p);
   return check_cuda(cudaGetLastError(), "norm_quant_kernel launch");
 }
 
 template <typename T, bool kAdd>
 int dispatch(const NormParams& p, cudaStream_t stream) {
   const int nchunks = p.hidden / 16;
-  if (nchunks <= 32) return launch_one<T, kAdd, 1, true>(p, 128, stream);
-  const int chunks = (nchunks + kMaxThreads - 1) / kMaxThreads;
-  const int threads = (((nchunks + chunks - 1) / chunks) + 31) / 32 * 32;
-  switch (chunks) {
-    case 1: return launch_one<T, kAdd, 1, false>(p, threads, stream);
-    case 2: return launch_one<T, kAdd, 2, false>(p, threads, stream);
-    case 3: return launch_one<T, kAdd, 3, false>(p, threads, stream);
-    case 4: return launch_one<T, kAdd, 4, false>(p, threads, stream);
+  if (nchunks <= 32) return launch_one<T, kAdd, 1, 1, true>(p, 128, stream);
+  const int nunits = (nchunks + 1) / 2;                       // two adjacent chunks per unit
+  const int units = (nunits + kMaxThreads - 1) / kMaxThreads;
+  const int threads = (((nunits + units - 1) / units) + 31) / 32 * 32;
+  switch (units) {
+    case 1: return launch_one<T, kAdd, 2, 1, false>(p, threads, stream);
+    case 2: return launch_one<T, kAdd, 2, 2, false>(p, threads, stream);
     default: return fail(kUnsupported, "hidden=%d exceeds the supported maximum of %d", p.hidden,
-                         16 * kMaxThreads * kMaxChunksPerThread);
+                         32 * kMaxThreads * kMaxUnitsPerThread);
   }
 }
 

@@ -103,6 +103,8 @@ def rmsnorm_fp4quant(
     gs = _unit_scale(input.device) if global_scale is None else global_scale
     if gs.dtype != torch.float32 or gs.device != input.device:
         raise ValueError("global_scale must be a float32 tensor on the input's device")
+    if rows == 0:
+        return y_fp4, block_scale
     with torch.cuda.device(input.device):
         _lib.check(_lib.lib.b200fp4_rmsnorm_fp4quant(
             x2.data_ptr(), weight.contiguous().data_ptr(), y_fp4.data_ptr(), block_scale.data_ptr(), None,
@@ -153,6 +155,8 @@ def add_rmsnorm_fp4quant(
     gs = _unit_scale(input.device) if global_scale is None else global_scale
     if gs.dtype != torch.float32 or gs.device != input.device:
         raise ValueError("global_scale must be a float32 tensor on the input's device")
+    if rows == 0:
+        return (y_fp4, block_scale, block_scale_unswizzled) if output_both_sf_layouts else (y_fp4, block_scale)
     with torch.cuda.device(input.device):
         _lib.check(_lib.lib.b200fp4_add_rmsnorm_fp4quant(
             x2.data_ptr(), r2.data_ptr(), weight.contiguous().data_ptr(), y_fp4.data_ptr(), block_scale.data_ptr(),
