@@ -69,6 +69,11 @@ __device__ __forceinline__ void st_32B(void* p, const U32x8& r) {
                : "memory");
 }
 
+// asynchronous L2 prefetch of a contiguous span (address and size multiples of 16 bytes)
+__device__ __forceinline__ void prefetch_l2_bulk(const void* p, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
 // ---------------------------------------------------------------------------
 // 16-bit float pairs <-> f32
 // ---------------------------------------------------------------------------

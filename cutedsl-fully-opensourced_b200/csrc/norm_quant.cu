@@ -97,7 +97,13 @@ __global__ void __launch_bounds__(kMaxThreads) norm_quant_kernel(const NormParam
   const int64_t row0 = kWarpRow ? static_cast<int64_t>(blockIdx.x) * nwarps + warp : blockIdx.x;
   const int64_t row_step = kWarpRow ? static_cast<int64_t>(gridDim.x) * nwarps : gridDim.x;
   int parity = 0;
+  const uint32_t row_bytes = static_cast<uint32_t>(p.hidden) * 2u;
   for (int64_t row = row0; row < p.rows; row += row_step, parity ^= 1) {
+    // pull the row this team will work on next into L2 while the current one is processed
+    if (tid == 0 && row + row_step < p.rows) {
+      prefetch_l2_bulk(xg + (row + row_step) * p.x_row_stride, row_bytes);
+      if constexpr (kAdd) prefetch_l2_bulk(rg + (row + row_step) * p.res_row_stride, row_bytes);
+    }
     // ---- phase 1: load, (add, round, write residual), sum of squares
     float h[kUnits * kVec][16];
     float ssq = 0.0f;
