@@ -6,6 +6,9 @@ CUDA, built by ``build.py``); importing this package loads that library and
 fails if it is absent.
 """
 from . import _lib, layout  # noqa: F401
+from . import gemm  # noqa: F401
+from .gemm import (Sm100BlockScaledGemmKernel, Sm120BlockScaledGemmKernel, nvfp4_gemm)  # noqa: F401
 from .norm import add_rmsnorm_fp4quant, rmsnorm_fp4quant  # noqa: F401
 
-__all__ = ["rmsnorm_fp4quant", "add_rmsnorm_fp4quant", "layout"]
+__all__ = ["rmsnorm_fp4quant", "add_rmsnorm_fp4quant", "nvfp4_gemm", "Sm120BlockScaledGemmKernel",
+           "Sm100BlockScaledGemmKernel", "gemm", "layout"]

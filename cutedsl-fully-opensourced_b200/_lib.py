@@ -23,6 +23,8 @@ SIGNATURES = {
     "b200fp4_rmsnorm_fp4quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _f32, _i64, _i32, _i64, _i32, _i32, _vp]),
     "b200fp4_add_rmsnorm_fp4quant": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f32, _i64, _i32, _i64, _i64,
                                             _i32, _i32, _vp]),
+    "b200fp4_nvfp4_gemm": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "b200fp4_device_status": (_i32, [_vp, C.POINTER(C.c_int), _i32]),
 }
 
 
@@ -56,6 +58,19 @@ def check(rc: int) -> None:
     if rc == UNSUPPORTED:
         raise NotImplementedError(msg)
     raise B200Fp4Error(f"libb200fp4 status {rc}: {msg}")
+
+
+def device_status(clear: bool = True, device=None) -> int:
+    """Synchronise the current stream and return the device status word (0 = healthy)."""
+    out = C.c_int(0)
+    check(lib.b200fp4_device_status(current_stream_ptr(device), C.byref(out), 1 if clear else 0))
+    return out.value
+
+
+def raise_on_device_status(device=None) -> None:
+    st = device_status(True, device)
+    if st:
+        raise B200Fp4Error(f"a device-side wait expired (status bits {st:#x}); results are invalid")
 
 
 def ptr(t) -> int:

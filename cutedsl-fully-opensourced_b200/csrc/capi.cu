@@ -30,6 +30,10 @@ int norm_fp4quant_launch(const void* x, void* residual, const void* weight, void
                          int hidden, int64_t x_row_stride, int64_t res_row_stride, int dtype, int sf_layout,
                          cudaStream_t stream);
 
+int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha, int m, int n,
+               int k, int l, int c_dtype, int tile_n, cudaStream_t stream);
+int device_status_word(int** out);
+
 }  // namespace b200fp4
 
 using namespace b200fp4;
@@ -56,6 +60,23 @@ int b200fp4_add_rmsnorm_fp4quant(const void* x, void* residual, const void* weig
   return norm_fp4quant_launch(x, residual, weight, y_fp4, block_scale, block_scale_unswizzled, global_scale, eps,
                               rows, hidden, x_row_stride, residual_row_stride, dtype, sf_layout,
                               static_cast<cudaStream_t>(stream));
+}
+
+int b200fp4_nvfp4_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha,
+                       int m, int n, int k, int l, int c_dtype, int tile_n, void* stream) {
+  return gemm_dense(a, b, sfa, sfb, c, alpha, m, n, k, l, c_dtype, tile_n, static_cast<cudaStream_t>(stream));
+}
+
+int b200fp4_device_status(void* stream, int* status_out, int clear) {
+  if (status_out == nullptr) return fail(kInvalidArgument, "status_out is null");
+  int* word = nullptr;
+  int rc = device_status_word(&word);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  B200_CUDA(cudaMemcpyAsync(status_out, word, sizeof(int), cudaMemcpyDeviceToHost, s));
+  if (clear) B200_CUDA(cudaMemsetAsync(word, 0, sizeof(int), s));
+  B200_CUDA(cudaStreamSynchronize(s));
+  return kOk;
 }
 
 }  // extern "C"

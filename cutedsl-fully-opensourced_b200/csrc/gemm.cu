@@ -1,0 +1,223 @@
+// Host side of the NVFP4 GEMM family: tensor-map construction, launch
+// configuration and argument checks for the dense block-scaled GEMM and the
+// two grouped GEMMs of the fused MoE.  The device code is in gemm_kernel.cuh.
+#include <mutex>
+
+#include "gemm_kernel.cuh"
+
+namespace b200fp4 {
+
+namespace {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+  });
+  return fn;
+}
+
+// K-major e2m1 operand viewed as bytes: [groups][rows][k/2], boxes of 128 rows x 128 bytes, 128-byte swizzle.
+int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int k, int64_t groups) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (enc == nullptr) return fail(kCudaError, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t row_bytes = static_cast<cuuint64_t>(k) / 2;
+  cuuint64_t dims[3] = {row_bytes, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(groups)};
+  cuuint64_t strides[2] = {row_bytes, row_bytes * static_cast<cuuint64_t>(rows)};
+  cuuint32_t box[3] = {128, 128, 1};
+  cuuint32_t elem[3] = {1, 1, 1};
+  const cuuint32_t rank = groups > 0 ? 3 : 2;
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void*>(base), dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(kCudaError, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  return kOk;
+}
+
+std::mutex g_status_mutex;
+int* g_status_word[64] = {};
+
+}  // namespace
+
+int sm_count_of_current_device() {
+  int dev = 0, n = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  return n > 0 ? n : 148;
+}
+
+// One int per device that kernels OR failure bits into (bounded waits that expired).
+int device_status_word(int** out) {
+  int dev = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(kUnsupported, "device ordinal %d", dev);
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  if (g_status_word[dev] == nullptr) {
+    B200_CUDA(cudaMalloc(&g_status_word[dev], sizeof(int)));
+    B200_CUDA(cudaMemset(g_status_word[dev], 0, sizeof(int)));
+  }
+  *out = g_status_word[dev];
+  return kOk;
+}
+
+template <int kBlockN, bool kSwigluB, typename Epilogue>
+int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, const Epilogue& epi, int max_tiles,
+                cudaStream_t stream) {
+  auto kern = nvfp4_gemm_kernel<kBlockN, kSwigluB, Epilogue>;
+  constexpr SmemLayout L = smem_layout<kBlockN>();
+  static bool configured = false;      // per instantiation
+  if (!configured) {
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L.total)));
+    configured = true;
+  }
+  int grid = sm_count_of_current_device();
+  if (grid > max_tiles) grid = max_tiles;
+  if (grid < 1) return kOk;
+  kern<<<grid, kGemmThreads, L.total, stream>>>(ta, tb, p, epi);
+  return check_cuda(cudaGetLastError(), "nvfp4_gemm_kernel launch");
+}
+
+// ---------------------------------------------------------------------------
+// dense GEMM: C[l][m][n] = alpha * A[l][m][k] . B[l][n][k]^T
+// ---------------------------------------------------------------------------
+template <typename OutT>
+int gemm_dense_typed(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha, int m,
+                     int n, int k, int tile_n, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  int rc = make_operand_map(&ta, a, m, k, 0);
+  if (rc) return rc;
+  rc = make_operand_map(&tb, b, n, k, 1);
+  if (rc) return rc;
+  GemmParams p{};
+  p.sfa = static_cast<const uint8_t*>(sfa);
+  p.sfb = static_cast<const uint8_t*>(sfb);
+  p.m_rows = m;
+  p.n_cols = n;
+  p.k = k;
+  p.rk = (k + 63) / 64;
+  p.num_k_tiles = (k + kBlockK - 1) / kBlockK;
+  p.b_row_tiles = (n + 127) / 128;
+  p.num_m_blocks = (m + kBlockM - 1) / kBlockM;
+  rc = device_status_word(&p.status);
+  if (rc) return rc;
+  EpilogueStore<OutT> epi{static_cast<OutT*>(c), n, alpha, 0};
+  if (tile_n == 256) {
+    p.num_n_blocks = (n + 255) / 256;
+    return launch_gemm<256, false>(ta, tb, p, epi, p.num_m_blocks * p.num_n_blocks, stream);
+  }
+  p.num_n_blocks = (n + 127) / 128;
+  return launch_gemm<128, false>(ta, tb, p, epi, p.num_m_blocks * p.num_n_blocks, stream);
+}
+
+int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha, int m, int n,
+               int k, int l, int c_dtype, int tile_n, cudaStream_t stream) {
+  if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || c == nullptr)
+    return fail(kInvalidArgument, "null pointer argument");
+  if (m <= 0 || n <= 0 || k <= 0 || l <= 0) return fail(kInvalidArgument, "m, n, k, l must be positive");
+  // contiguous dimension of every tensor must cover whole 16-byte units (the reference's
+  // is_valid_tensor_alignment rule): 32 e2m1 elements for A/B, 8 (16-bit) or 4 (f32) for C
+  if (k % 32 != 0) return fail(kInvalidArgument, "Invalid tensor alignment: k=%d is not a multiple of 32", k);
+  if (n % 8 != 0) return fail(kInvalidArgument, "Invalid tensor alignment: n=%d is not a multiple of 8", n);
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(sfa) |
+       reinterpret_cast<uintptr_t>(sfb) | reinterpret_cast<uintptr_t>(c)) & 15)
+    return fail(kInvalidArgument, "Invalid tensor alignment: pointers must be 16-byte aligned");
+  if (c_dtype < 0 || c_dtype > 2) return fail(kUnsupported, "c_dtype code %d (0 fp16, 1 bf16, 2 f32)", c_dtype);
+  if (tile_n != 0 && tile_n != 128 && tile_n != 256) return fail(kInvalidArgument, "tile_n must be 0, 128 or 256");
+  if (tile_n == 0) {
+    // wide tiles halve the operand traffic per flop; keep narrow ones while they are needed to fill the SMs
+    const int64_t tiles256 = static_cast<int64_t>((m + 127) / 128) * ((n + 255) / 256);
+    tile_n = tiles256 >= sm_count_of_current_device() ? 256 : 128;
+  }
+  const int64_t m_tiles = (m + 127) / 128, n_tiles = (n + 127) / 128, rk = (k + 63) / 64;
+  const size_t c_elem = c_dtype == 2 ? 4 : 2;
+  for (int i = 0; i < l; ++i) {
+    const uint8_t* ai = static_cast<const uint8_t*>(a) + static_cast<int64_t>(i) * m * (k / 2);
+    const uint8_t* bi = static_cast<const uint8_t*>(b) + static_cast<int64_t>(i) * n * (k / 2);
+    const uint8_t* sfai = static_cast<const uint8_t*>(sfa) + i * m_tiles * rk * 512;
+    const uint8_t* sfbi = static_cast<const uint8_t*>(sfb) + i * n_tiles * rk * 512;
+    uint8_t* ci = static_cast<uint8_t*>(c) + static_cast<int64_t>(i) * m * n * c_elem;
+    int rc;
+    if (c_dtype == 0) rc = gemm_dense_typed<__half>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, stream);
+    else if (c_dtype == 1) rc = gemm_dense_typed<__nv_bfloat16>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, stream);
+    else rc = gemm_dense_typed<float>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, stream);
+    if (rc) return rc;
+  }
+  return kOk;
+}
+
+// ---------------------------------------------------------------------------
+// grouped GEMMs of the MoE (rows are expert-major, every 128-row block belongs to one expert)
+// ---------------------------------------------------------------------------
+// FC1: act = quant(bf16(silu(gate) * up)) with [up | gate] = Xq . W1[e]^T * w1_alpha[e]
+int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* w1_sf, void* act_codes, void* act_sf,
+                 const float* w1_alpha, const float* fc2_input_scale, const int* num_m_blocks_dev,
+                 const int* m_block_expert, int max_m_blocks, int hidden, int inter, int experts,
+                 cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  int rc = make_operand_map(&ta, xq, static_cast<int64_t>(max_m_blocks) * 128, hidden, 0);
+  if (rc) return rc;
+  rc = make_operand_map(&tb, w1, 2 * inter, hidden, experts);
+  if (rc) return rc;
+  GemmParams p{};
+  p.sfa = static_cast<const uint8_t*>(xq_sf);
+  p.sfb = static_cast<const uint8_t*>(w1_sf);
+  p.m_rows = max_m_blocks * 128;
+  p.n_cols = inter;
+  p.k = hidden;
+  p.rk = (hidden + 63) / 64;
+  p.num_k_tiles = (hidden + kBlockK - 1) / kBlockK;
+  p.num_n_blocks = inter / 128;
+  p.b_row_tiles = (2 * inter) / 128;
+  p.gate_row_offset = inter;
+  p.num_m_blocks_dev = num_m_blocks_dev;
+  p.num_m_blocks = max_m_blocks;
+  p.m_block_group = m_block_expert;
+  rc = device_status_word(&p.status);
+  if (rc) return rc;
+  EpilogueSwiglu epi{static_cast<uint8_t*>(act_codes), static_cast<uint8_t*>(act_sf), w1_alpha, fc2_input_scale, inter};
+  return launch_gemm<256, true>(ta, tb, p, epi, max_m_blocks * p.num_n_blocks, stream);
+}
+
+// FC2: partial[row][h] = (Actq . W2[e]^T) * w2_alpha[e], f32
+int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, float* partial,
+                 const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert, int max_m_blocks,
+                 int hidden, int inter, int experts, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  int rc = make_operand_map(&ta, act_codes, static_cast<int64_t>(max_m_blocks) * 128, inter, 0);
+  if (rc) return rc;
+  rc = make_operand_map(&tb, w2, hidden, inter, experts);
+  if (rc) return rc;
+  GemmParams p{};
+  p.sfa = static_cast<const uint8_t*>(act_sf);
+  p.sfb = static_cast<const uint8_t*>(w2_sf);
+  p.m_rows = max_m_blocks * 128;
+  p.n_cols = hidden;
+  p.k = inter;
+  p.rk = (inter + 63) / 64;
+  p.num_k_tiles = (inter + kBlockK - 1) / kBlockK;
+  p.b_row_tiles = (hidden + 127) / 128;
+  p.num_m_blocks_dev = num_m_blocks_dev;
+  p.num_m_blocks = max_m_blocks;
+  p.m_block_group = m_block_expert;
+  rc = device_status_word(&p.status);
+  if (rc) return rc;
+  EpilogueStore<float> epi{partial, hidden, w2_alpha, 1};
+  if (hidden % 256 == 0) {
+    p.num_n_blocks = hidden / 256;
+    return launch_gemm<256, false>(ta, tb, p, epi, max_m_blocks * p.num_n_blocks, stream);
+  }
+  p.num_n_blocks = (hidden + 127) / 128;
+  return launch_gemm<128, false>(ta, tb, p, epi, max_m_blocks * p.num_n_blocks, stream);
+}
+
+}  // namespace b200fp4

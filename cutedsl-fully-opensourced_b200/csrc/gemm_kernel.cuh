@@ -1,0 +1,399 @@
+// NVFP4 block-scaled GEMM mainloop for sm_100a, shared by the dense GEMM and
+// the two grouped MoE GEMMs.
+//
+//   C[m, n] = sum_k (A[m,k] * SFA[m,k/16]) * (B[n,k] * SFB[n,k/16])
+//
+// A and B are e2m1, two per byte, K-major; SFA / SFB are e4m3 bytes in the
+// 128x4 tiled layout.  The reference computes this with warp-level mma.sync on
+// sm_120 (third_party/cutlass/examples/python/CuTeDSL/cute/blackwell_geforce/
+// kernel/blockscaled_gemm/dense_blockscaled_gemm_persistent_cooperative.py:443-1185);
+// here one CTA per SM runs a warp-specialised persistent loop:
+//
+//   warp 0  TMA producer: per 256-wide K tile, one tiled copy of A (128 rows x
+//           128 bytes, 128-byte swizzle), one per 128-row piece of B, and plain
+//           bulk copies of the scale-factor slabs (2 KB per 128 rows: four
+//           512-byte 128x4 tiles are contiguous in the tiled layout)
+//   warp 1  MMA issuer: tcgen05.cp moves the scale slabs into tensor memory,
+//           then four tcgen05.mma kind::mxf4nvf4 (K = 64 each) accumulate into
+//           a TMEM accumulator; tcgen05.commit releases the stage
+//   warps 2-5  epilogue: tcgen05.ld the accumulator (each warp its own 32-lane
+//           quarter), apply the epilogue functor, store
+//
+// No cluster launch and no multicast anywhere.  Every wait is bounded: on
+// expiry the kernel raises a flag in the status word and all roles leave.
+#pragma once
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace b200fp4 {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 256;                 // e2m1 elements per stage = 128 bytes per row
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+constexpr long long kWaitLimitCycles = 4000000000LL;   // ~2 s at 2 GHz
+
+enum GemmStatusBits : int {
+  kStatusTimeoutProducer = 1,
+  kStatusTimeoutMma = 2,
+  kStatusTimeoutEpilogue = 4,
+};
+
+struct GemmParams {
+  const uint8_t* sfa;          // tiled scale factors of A: [m_tiles][rk][512]
+  const uint8_t* sfb;          // tiled scale factors of B: [groups][b_row_tiles][rk][512]
+  int m_rows;                  // rows of A that exist (TMA zero-fills beyond); grouped: padded total
+  int n_cols;                  // output columns per row
+  int k;                       // reduction length in elements
+  int rk;                      // ceil(k / 64): scale-factor K-tiles per row tile
+  int num_k_tiles;             // ceil(k / 256)
+  int num_n_blocks;
+  int b_row_tiles;             // 128-row tiles of B per group (scale-factor addressing)
+  int gate_row_offset;         // SwiGLU epilogue: first row of the gate half inside B
+  // tile list: plain GEMM uses ceil(m_rows/128) row blocks of one group; the grouped GEMMs
+  // read the number of row blocks and the group of every row block from device memory
+  const int* num_m_blocks_dev; // null -> num_m_blocks
+  int num_m_blocks;
+  const int* m_block_group;    // null -> group 0
+  int* status;                 // device status word (bits of GemmStatusBits)
+};
+
+struct SmemLayout {
+  int stages;
+  uint32_t a_bytes, b_bytes, sfa_bytes, sfb_bytes, stage_bytes, total;
+};
+
+template <int kBlockN>
+__host__ __device__ constexpr SmemLayout smem_layout() {
+  SmemLayout s{};
+  s.a_bytes = kBlockM * 128;
+  s.b_bytes = kBlockN * 128;
+  s.sfa_bytes = 2048;
+  s.sfb_bytes = (kBlockN / 128) * 2048;
+  s.stage_bytes = s.a_bytes + s.b_bytes + s.sfa_bytes + s.sfb_bytes;
+  s.stages = kBlockN == 256 ? 4 : 6;
+  s.total = s.stages * s.stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  return s;
+}
+
+struct PipeState {
+  int stage = 0;
+  uint32_t phase = 0;
+  __device__ __forceinline__ void advance(int n) {
+    if (++stage == n) {
+      stage = 0;
+      phase ^= 1;
+    }
+  }
+};
+
+// Poll an mbarrier phase; gives up when another role raised the abort flag or the cycle budget ran out.
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t it = 1;; ++it) {
+    if (ptx::mbar_try_wait(bar, parity)) return true;
+    if ((it & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Epilogue functors.  operator() is called by the 128 epilogue threads once per
+// tile; `row` is the accumulator row (TMEM lane) of the calling thread.
+// load(c0, regs) fetches 32 accumulator columns starting at c0.
+// ----------------------------------------------------------------------------
+template <typename OutT>
+struct EpilogueStore {
+  OutT* c;
+  int64_t ldc;                  // elements
+  const float* alpha;           // one scale, or one per group (alpha_per_group); null = 1
+  int alpha_per_group;
+
+  template <int kBlockN, typename Loader>
+  __device__ __forceinline__ void operator()(const GemmParams& p, int m_blk, int n_blk, int group, int row,
+                                             Loader&& load) const {
+    const float scale = alpha == nullptr ? 1.0f : __ldg(alpha + (alpha_per_group ? group : 0));
+    const int64_t grow = static_cast<int64_t>(m_blk) * kBlockM + row;
+    const bool row_ok = grow < p.m_rows;
+    OutT* crow = c + grow * ldc + static_cast<int64_t>(n_blk) * kBlockN;
+    const int cols_left = p.n_cols - n_blk * kBlockN;
+#pragma unroll 1
+    for (int c0 = 0; c0 < kBlockN; c0 += 32) {
+      uint32_t r[32];
+      load(c0, r);                 // warp-collective: every lane takes part, stores are predicated
+      if (!row_ok) continue;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {          // 8 columns per group
+        if (c0 + 8 * g < cols_left) {        // n_cols is a multiple of 8
+          float f[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[8 * g + i]) * scale;
+          if constexpr (sizeof(OutT) == 4) {
+            float4* dst = reinterpret_cast<float4*>(crow + c0 + 8 * g);
+            dst[0] = make_float4(f[0], f[1], f[2], f[3]);
+            dst[1] = make_float4(f[4], f[5], f[6], f[7]);
+          } else {
+            uint4 v;
+            v.x = Pair16<OutT>::pack(f[0], f[1]);
+            v.y = Pair16<OutT>::pack(f[2], f[3]);
+            v.z = Pair16<OutT>::pack(f[4], f[5]);
+            v.w = Pair16<OutT>::pack(f[6], f[7]);
+            *reinterpret_cast<uint4*>(crow + c0 + 8 * g) = v;
+          }
+        }
+      }
+    }
+  }
+};
+
+// FC1 of the MoE: the 256 accumulator columns are [up j0..j0+127 | gate j0..j0+127];
+// act = bf16(silu(gate) * up), re-quantised to NVFP4 with the MoE activation packer
+// (tests/python/test_flashinfer_b12x_verbatim.py:214-218) and written as the A operand of FC2.
+struct EpilogueSwiglu {
+  uint8_t* act_codes;           // [m_rows, inter/2]
+  uint8_t* act_sf;              // tiled [m_tiles][rk2][512], rk2 = ceil(inter/64)
+  const float* w1_alpha;        // per group
+  const float* fc2_input_scale; // one f32 (global scale of the activation quantiser)
+  int inter;                    // activation columns per row
+
+  template <int kBlockN, typename Loader>
+  __device__ __forceinline__ void operator()(const GemmParams& p, int m_blk, int n_blk, int group, int row,
+                                             Loader&& load) const {
+    static_assert(kBlockN == 256, "the SwiGLU epilogue pairs two 128-column halves");
+    const float a1 = w1_alpha == nullptr ? 1.0f : __ldg(w1_alpha + group);
+    const float gs = fc2_input_scale == nullptr ? 1.0f : __ldg(fc2_input_scale);
+    const int64_t grow = static_cast<int64_t>(m_blk) * kBlockM + row;
+    const int j0 = n_blk * 128;
+    const int rk2 = (inter + 63) >> 6;
+    uint8_t* sf_tile = act_sf + static_cast<int64_t>(m_blk) * rk2 * 512 + (row & 31) * 16 + (row >> 5) * 4;
+#pragma unroll 1
+    for (int c0 = 0; c0 < 128; c0 += 32) {
+      uint32_t up[32], gate[32];
+      load(c0, up);
+      load(128 + c0, gate);
+      if (j0 + c0 >= inter) continue;
+      uint32_t sfpair = 0;
+      uint32_t codes[4];
+#pragma unroll
+      for (int b = 0; b < 2; ++b) {
+        float v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float u = __uint_as_float(up[16 * b + i]) * a1;
+          const float g = __uint_as_float(gate[16 * b + i]) * a1;
+          const float s = __fdiv_rn(g, 1.0f + expf(-g));          // silu, f32
+          v[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(s, u)));
+        }
+        uint32_t sfb;
+        quantize_block16<true>(v, gs, codes[2 * b], codes[2 * b + 1], sfb);
+        sfpair |= sfb << (8 * b);
+      }
+      *reinterpret_cast<uint4*>(act_codes + grow * (inter >> 1) + ((j0 + c0) >> 1)) =
+          make_uint4(codes[0], codes[1], codes[2], codes[3]);
+      const int kb = (j0 + c0) >> 4;          // even
+      *reinterpret_cast<uint16_t*>(sf_tile + (kb & 3) + (kb >> 2) * 512) = static_cast<uint16_t>(sfpair);
+    }
+  }
+};
+
+// ----------------------------------------------------------------------------
+// kSwigluB: B tile = two 128-row pieces (up rows, gate rows); otherwise kBlockN/128 consecutive pieces.
+// ----------------------------------------------------------------------------
+template <int kBlockN, bool kSwigluB, typename Epilogue>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                  const GemmParams p, const Epilogue epi) {
+  constexpr SmemLayout L = smem_layout<kBlockN>();
+  constexpr int kStages = L.stages;
+  constexpr int kAccStages = kBlockN == 256 ? 1 : 2;
+  constexpr int kBPieces = kBlockN / 128;
+  constexpr uint32_t kSfaCol = kAccStages * kBlockN;            // TMEM columns: accumulators first
+  constexpr uint32_t kSfbCol = kSfaCol + 16;
+  constexpr uint32_t kIdesc = ptx::idesc_mxf4nvf4(kBlockN);
+  static_assert(kSfbCol + 4 * (kBlockN / 32) <= kTmemCols, "TMEM budget");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + kStages * L.stage_bytes;
+  // barrier slots (8 bytes each): full[kStages], empty[kStages], acc_full[2], acc_empty[2]; then tmem ptr, abort flag
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto acc_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
+  auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 2 + s); };
+  uint8_t* tail_gen = smem_gen + kStages * L.stage_bytes + 8 * (2 * kStages + 4);
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(tail_gen);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail_gen + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(acc_full_bar(s), 1);
+      ptx::mbar_init(acc_empty_bar(s), 128);
+    }
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 0) {
+    __syncwarp();
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const int num_m_blocks = p.num_m_blocks_dev != nullptr ? __ldg(p.num_m_blocks_dev) : p.num_m_blocks;
+  const int num_tiles = num_m_blocks * p.num_n_blocks;
+
+  if (warp == 0) {
+    // =============================== TMA producer ===============================
+    if (lane == 0) {
+      PipeState st;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m_blk = tile % num_m_blocks;
+        const int n_blk = tile / num_m_blocks;
+        const int group = p.m_block_group != nullptr ? __ldg(p.m_block_group + m_blk) : 0;
+        int b_row[kBPieces];
+        if constexpr (kSwigluB) {
+          b_row[0] = n_blk * 128;
+          b_row[1] = p.gate_row_offset + n_blk * 128;
+        } else {
+#pragma unroll
+          for (int i = 0; i < kBPieces; ++i) b_row[i] = n_blk * kBlockN + 128 * i;
+        }
+        for (int kt = 0; kt < p.num_k_tiles; ++kt) {
+          if (!wait_bounded(empty_bar(st.stage), st.phase ^ 1u, abort_flag)) {
+            atomicOr(p.status, kStatusTimeoutProducer);
+            ok = false;
+            break;
+          }
+          const uint32_t sa = smem_base + st.stage * L.stage_bytes;
+          const uint32_t sb = sa + L.a_bytes;
+          const uint32_t ssfa = sb + L.b_bytes;
+          const uint32_t ssfb = ssfa + L.sfa_bytes;
+          const int k_sf_tiles = min(4, p.rk - 4 * kt);                 // 512-byte scale tiles in this stage
+          const uint32_t sf_bytes = static_cast<uint32_t>(k_sf_tiles) * 512u;
+          const uint32_t bar = full_bar(st.stage);
+          ptx::mbar_expect_tx(bar, L.a_bytes + L.b_bytes + sf_bytes * (1 + kBPieces));
+          ptx::tma_load_2d(sa, &tmap_a, kt * 128, m_blk * kBlockM, bar);
+#pragma unroll
+          for (int i = 0; i < kBPieces; ++i) ptx::tma_load_3d(sb + i * 128 * 128, &tmap_b, kt * 128, b_row[i], group, bar);
+          ptx::bulk_load(ssfa, p.sfa + (static_cast<int64_t>(m_blk) * p.rk + 4 * kt) * 512, sf_bytes, bar);
+#pragma unroll
+          for (int i = 0; i < kBPieces; ++i) {
+            const int64_t tile_idx = static_cast<int64_t>(group) * p.b_row_tiles + (b_row[i] >> 7);
+            ptx::bulk_load(ssfb + i * 2048, p.sfb + (tile_idx * p.rk + 4 * kt) * 512, sf_bytes, bar);
+          }
+          st.advance(kStages);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // =============================== MMA issuer ===============================
+    if (lane == 0) {
+      PipeState st;
+      PipeState acc;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!wait_bounded(acc_empty_bar(acc.stage), acc.phase ^ 1u, abort_flag)) {
+          atomicOr(p.status, kStatusTimeoutMma);
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc.stage * kBlockN;
+        for (int kt = 0; kt < p.num_k_tiles; ++kt) {
+          if (!wait_bounded(full_bar(st.stage), st.phase, abort_flag)) {
+            atomicOr(p.status, kStatusTimeoutMma);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t sa = smem_base + st.stage * L.stage_bytes;
+          const uint32_t sb = sa + L.a_bytes;
+          const uint32_t ssfa = sb + L.b_bytes;
+          const uint32_t ssfb = ssfa + L.sfa_bytes;
+          const int kblocks = min(4, (p.k - kt * kBlockK + 63) >> 6);   // 64-wide MMA steps with data
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+            if (kb < kblocks) {
+              ptx::tmem_cp_sf(tmem_base + kSfaCol + 4 * kb, ptx::smem_desc_sf(ssfa + 512 * kb));
+#pragma unroll
+              for (int i = 0; i < kBPieces; ++i) {
+                ptx::tmem_cp_sf(tmem_base + kSfbCol + (kBlockN / 32) * kb + 4 * i,
+                                ptx::smem_desc_sf(ssfb + 2048 * i + 512 * kb));
+              }
+            }
+          }
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+            if (kb < kblocks) {
+              ptx::mma_mxf4nvf4(d_tmem, ptx::smem_desc_sw128(sa + 32 * kb), ptx::smem_desc_sw128(sb + 32 * kb), kIdesc,
+                                tmem_base + kSfaCol + 4 * kb, tmem_base + kSfbCol + (kBlockN / 32) * kb,
+                                (kt | kb) != 0 ? 1u : 0u);
+            }
+          }
+          ptx::tc_commit(empty_bar(st.stage));        // stage reusable once these MMAs have read it
+          st.advance(kStages);
+        }
+        if (ok) ptx::tc_commit(acc_full_bar(acc.stage));
+        acc.advance(kAccStages);
+      }
+    }
+  } else {
+    // =============================== epilogue ===============================
+    const int quarter = warp & 3;                      // TMEM lanes this warp may touch
+    const int row = quarter * 32 + lane;
+    PipeState acc;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int m_blk = tile % num_m_blocks;
+      const int n_blk = tile / num_m_blocks;
+      const int group = p.m_block_group != nullptr ? __ldg(p.m_block_group + m_blk) : 0;
+      if (!wait_bounded(acc_full_bar(acc.stage), acc.phase, abort_flag)) {
+        if (lane == 0) atomicOr(p.status, kStatusTimeoutEpilogue);
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc.stage * kBlockN;
+      epi.template operator()<kBlockN>(p, m_blk, n_blk, group, row, [&](int c0, uint32_t (&r)[32]) {
+        ptx::tmem_ld_32x32(t_acc + c0, r);
+        ptx::tmem_ld_wait();
+      });
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(acc_empty_bar(acc.stage));
+      acc.advance(kAccStages);
+    }
+  }
+
+  // ---- teardown: everybody meets, then the allocating warp frees tensor memory
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) {
+    if (*abort_flag) {
+      // a role gave up: let copies that are still in flight land before the CTA's memory is reused
+      for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    __syncwarp();
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace b200fp4

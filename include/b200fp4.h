@@ -58,6 +58,24 @@ int b200fp4_add_rmsnorm_fp4quant(const void* x, void* residual, const void* weig
                                  float eps, int64_t rows, int hidden, int64_t x_row_stride,
                                  int64_t residual_row_stride, int dtype, int sf_layout, void* stream);
 
+/* NVFP4 block-scaled dense GEMM, C[l][m][n] = alpha * sum_k (A*SFA)[l][m][k] * (B*SFB)[l][n][k].
+ * A [l][m][k/2] and B [l][n][k/2]: e2m1 codes, two per byte (lower k in the low nibble), K contiguous.
+ * SFA / SFB: e4m3 bytes, one per 16 K-elements, in 128x4 tiles [l][ceil(rows/128)][ceil(k/64)][32][4][4]
+ * (padding bytes zero).  C row-major, c_dtype 0 = fp16, 1 = bf16, 2 = f32; f32 accumulation.
+ * alpha: one f32 in device memory, or NULL for 1.  tile_n: 0 = choose, 128 or 256.
+ * Stands in for Sm120BlockScaledGemmKernel.__call__ and its kernel:
+ *   third_party/cutlass/examples/python/CuTeDSL/cute/blackwell_geforce/kernel/blockscaled_gemm/
+ *   dense_blockscaled_gemm_persistent_cooperative.py:281-439 (host), :443-1185 (device),
+ *   alignment rule :1461-1511 (k % 32, n % 8, else "Invalid tensor alignment"). */
+int b200fp4_nvfp4_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha,
+                       int m, int n, int k, int l, int c_dtype, int tile_n, void* stream);
+
+/* Kernels never trap: a device-side wait that exceeds its bound ORs a bit into a per-device
+ * status word and the kernel returns.  This call synchronises the stream and copies the word
+ * to *status_out (0 = healthy; 1/2/4 = GEMM producer / MMA / epilogue wait expired), clearing
+ * it when clear != 0.  No counterpart in the reference, whose kernels wait without bounds. */
+int b200fp4_device_status(void* stream, int* status_out, int clear);
+
 #ifdef __cplusplus
 }
 #endif
