@@ -119,10 +119,21 @@ class AddRmsNormWorkload:
     rows, hidden = 8192, 7168
     bytes_per_element = 2 + 2 + 2 + 0.5 + 0.0625      # x in, residual in+out, codes, scale bytes
     kernel = "norm_quant_kernel<bf16, add>"
+    bound = "hbm"
 
     def __init__(self, rank: int):
         self.rank = rank
         self.alg_bytes = int(self.rows * self.hidden * self.bytes_per_element)
+
+    @property
+    def work(self):                 # units of the metric per step: bytes
+        return float(self.alg_bytes)
+
+    def config(self, world):
+        return {"workload": self.name, "rows_per_gpu": self.rows, "hidden": self.hidden,
+                "sf_layout": "swizzled_128x4", "parallelism": f"rows x{world}",
+                "l2": "working set 385 MB per step exceeds the 126 MB L2; the in-place residual is "
+                      "restored by an untimed 117 MB copy between steps"}
 
     def host_inputs(self, rows=None):
         import torch
@@ -199,7 +210,90 @@ class AddRmsNormWorkload:
             f"{rows} of {self.rows} rows x {self.hidden}, oracle port (numpy+torch), {threads} threads"
 
 
-WORKLOADS = {"add_rmsnorm": AddRmsNormWorkload}
+class GemmWorkload:
+    """NVFP4 block-scaled GEMM M=N=K=8192: A, B ~ N(0,1) quantised to e2m1 with e4m3 scale factors per
+    16 K-elements and a per-tensor global scale, f32 accumulate, bf16 output, alpha = 1/(gs_A*gs_B)."""
+    metric = "NVFP4 GEMM TFLOP/s"
+    unit = "TFLOP/s"
+    dtype = "nvfp4 (e2m1 x e2m1, ue4m3 scales, f32 accumulate)"
+    kernel = "nvfp4_gemm_kernel<256>"
+    bound = "tensor"
+    launches_per_step = 1
+    sets = 3                      # rotating operand sets so no step finds its operands in L2
+    FP4_NOMINAL_TFLOPS = 9000.0   # dense FP4 peak of a B200 (nominal; no measured FP4 peak exists)
+
+    def __init__(self, rank: int, m: int = 8192, n: int = 8192, k: int = 8192):
+        self.rank, self.m, self.n, self.k = rank, m, n, k
+        self.rows, self.hidden = m, k
+        self.name = f"nvfp4_gemm_{m}x{n}x{k}_bf16out"
+        self.work = 2.0 * m * n * k
+        self.alg_bytes = m * k // 2 + n * k // 2 + (m + n) * k // 16 + 2 * m * n
+
+    def setup(self, pkg):
+        import torch
+        self.pkg = pkg
+        self.ops = []
+        for i in range(self.sets):
+            g = torch.Generator(device="cuda").manual_seed(100 * self.rank + i)
+            a = torch.randn(self.m, self.k, generator=g, device="cuda")
+            b = torch.randn(self.n, self.k, generator=g, device="cuda")
+            aq, sfa, gsa = pkg.gemm.quantize_operand(a)
+            del a
+            bq, sfb, gsb = pkg.gemm.quantize_operand(b)
+            del b
+            alpha = torch.tensor([1.0 / (gsa * gsb)], device="cuda")
+            c = torch.empty(self.m, self.n, dtype=torch.bfloat16, device="cuda")
+            self.ops.append((aq, bq, sfa, sfb, alpha, c))
+        self.i = 0
+
+    def restore(self):
+        pass
+
+    def step(self):
+        aq, bq, sfa, sfb, alpha, c = self.ops[self.i % self.sets]
+        self.i += 1
+        self.pkg.nvfp4_gemm(aq, bq, sfa, sfb, alpha=alpha, out=c, tile_n=self.tile_n)
+
+    tile_n = 0
+
+    def config(self, world):
+        return {"workload": self.name, "m_per_gpu": self.m, "n": self.n, "k": self.k,
+                "parallelism": f"rows of A/C x{world}, B replicated",
+                "l2": f"{self.sets} rotating operand sets of 72 MB + 134 MB output each, so a step never "
+                      "finds its operands in the 126 MB L2"}
+
+    def setup_e2e(self):
+        import torch
+        aq, bq, sfa, sfb, alpha, c = self.ops[0]
+        self.h = [t.cpu().pin_memory() for t in (aq, bq, sfa, sfb)]
+        self.hc = torch.empty(c.shape, dtype=c.dtype).pin_memory()
+        self.h2d = sum(t.numel() * t.element_size() for t in self.h)
+        self.d2h = self.hc.numel() * 2
+
+    def step_e2e(self):
+        aq, bq, sfa, sfb, alpha, c = self.ops[0]
+        for d, h in zip((aq, bq, sfa, sfb), self.h):
+            d.copy_(h, non_blocking=True)
+        self.pkg.nvfp4_gemm(aq, bq, sfa, sfb, alpha=alpha, out=c, tile_n=self.tile_n)
+        self.hc.copy_(c, non_blocking=True)
+
+    def cpu_run(self, threads: int):
+        import numpy as np
+        import torch
+        from oracle import nvfp4_oracle as O
+        m, n, k = min(self.m, 1024), min(self.n, 1024), self.k
+        torch.set_num_threads(threads)
+        g = torch.Generator().manual_seed(0)
+        ac, sfa = O.quantize_nvfp4(torch.randn(m, k, generator=g).numpy(), 500.0)
+        bc, sfb = O.quantize_nvfp4(torch.randn(n, k, generator=g).numpy(), 500.0)
+        t0 = time.perf_counter()
+        O.gemm_nvfp4_ref(ac, sfa, bc, sfb, alpha=1.0 / 250000.0)
+        dt = time.perf_counter() - t0
+        return 2.0 * m * n * k / dt / 1e12, dt, \
+            f"{m}x{n}x{k} block of the {self.m}x{self.n}x{self.k} problem: de-quantise + f32 matmul, {threads} threads"
+
+
+WORKLOADS = {"add_rmsnorm": AddRmsNormWorkload, "gemm": GemmWorkload}
 
 
 # ---------------------------------------------------------------------------
@@ -244,13 +338,21 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU arm inside the GPU run")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--rows", type=int, default=None, help="override the row count (small profiling cases)")
+    ap.add_argument("--m", type=int, default=None, help="gemm: override M (M-sweep 128 / 1024 / 8192)")
+    ap.add_argument("--nk", type=int, default=None, help="gemm: override N = K (small profiling cases)")
+    ap.add_argument("--tile-n", type=int, default=0, help="gemm: force the 128- or 256-wide tile")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    wl = WORKLOADS[args.workload](rank)
-    if args.rows:
+    if args.workload == "gemm":
+        nk = args.nk or 8192
+        wl = GemmWorkload(rank, args.m or 8192, nk, nk)
+        wl.tile_n = args.tile_n
+    else:
+        wl = WORKLOADS[args.workload](rank)
+    if args.rows and args.workload == "add_rmsnorm":
         wl.rows = args.rows
         wl.name += f"_rows{args.rows}"
         wl.alg_bytes = int(wl.rows * wl.hidden * wl.bytes_per_element)
@@ -329,26 +431,28 @@ def main():
 
     if rank == 0:
         ms_per_step = total_ms / steps
-        value = wl.alg_bytes * world / (ms_per_step * 1e-3) / 1e9
-        e2e_value = wl.alg_bytes * world / (e2e_ms / e2e_steps * 1e-3) / 1e9
+        scale = 1e9 if wl.unit == "GB/s" else 1e12
+        value = wl.work * world / (ms_per_step * 1e-3) / scale
+        e2e_value = wl.work * world / (e2e_ms / e2e_steps * 1e-3) / scale
         # roofline of the dominant kernel: rank 0's own launches, averaged over the timed region
         k_ms = statistics.mean(step_ms)
-        achieved = wl.alg_bytes / (k_ms * 1e-3) / 1e9
+        achieved = wl.work / (k_ms * 1e-3) / scale
+        if wl.bound == "hbm":
+            peak, peak_src = peaks["hbm_gbs"], peaks["source"]
+        else:
+            peak, peak_src = wl.FP4_NOMINAL_TFLOPS, "nominal dense FP4 (no measured FP4 peak; 4x measured bf16 burst = %.0f)" % (4 * peaks["bf16_tflops"])
         line = {
             "metric": wl.metric, "value": round(value, 2), "unit": wl.unit, "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-            "config": {"workload": wl.name, "rows_per_gpu": wl.rows, "hidden": wl.hidden,
-                       "sf_layout": "swizzled_128x4", "parallelism": f"rows x{world}",
-                       "l2": "working set 385 MB per step exceeds the 126 MB L2; the in-place residual is "
-                             "restored by an untimed 117 MB copy between steps"},
+            "config": wl.config(world),
             "e2e": None if args.no_e2e else {
                 "value": round(e2e_value, 3), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d * world,
                 "d2h_bytes_per_step": wl.d2h * world, "steps": e2e_steps},
             "gpu_launches": wl.launches_per_step * steps * world,
-            "roofline": {"bound": "hbm", "kernel": wl.kernel, "achieved": round(achieved, 1),
-                         "peak": peaks["hbm_gbs"], "peak_source": peaks["source"], "unit": "GB/s",
-                         "frac": round(achieved / peaks["hbm_gbs"], 4), "traffic": None,
+            "roofline": {"bound": wl.bound, "kernel": wl.kernel, "achieved": round(achieved, 1),
+                         "peak": peak, "peak_source": peak_src, "unit": wl.unit,
+                         "frac": round(achieved / peak, 4), "traffic": None,
                          "algorithmic_bytes_per_launch": wl.alg_bytes,
                          "kernel_us": round(k_ms * 1e3, 2), "kernel_us_min": round(min(step_ms) * 1e3, 2)},
             "clocks": clocks,
