@@ -33,6 +33,13 @@ int norm_fp4quant_launch(const void* x, void* residual, const void* weight, void
 int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha, int m, int n,
                int k, int l, int c_dtype, int tile_n, cudaStream_t stream);
 int device_status_word(int** out);
+int route_topk(const float* logits, int* ids, float* weights, int tokens, int experts, int top_k, int renormalize,
+               cudaStream_t stream);
+size_t moe_workspace_bytes(int64_t tokens, int hidden, int inter, int experts, int top_k);
+int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, const void* w2_sf, const int* ids,
+              const float* route_w, const float* w1_alpha, const float* w2_alpha, const float* fc2_input_scale,
+              void* out, int64_t tokens, int hidden, int inter, int experts, int top_k, int expert_lo,
+              int accumulate, void* workspace, size_t workspace_bytes, cudaStream_t stream);
 
 }  // namespace b200fp4
 
@@ -65,6 +72,26 @@ int b200fp4_add_rmsnorm_fp4quant(const void* x, void* residual, const void* weig
 int b200fp4_nvfp4_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha,
                        int m, int n, int k, int l, int c_dtype, int tile_n, void* stream) {
   return gemm_dense(a, b, sfa, sfb, c, alpha, m, n, k, l, c_dtype, tile_n, static_cast<cudaStream_t>(stream));
+}
+
+int b200fp4_topk_route(const float* logits, int* ids, float* weights, int tokens, int experts, int top_k,
+                       int renormalize, void* stream) {
+  return route_topk(logits, ids, weights, tokens, experts, top_k, renormalize, static_cast<cudaStream_t>(stream));
+}
+
+size_t b200fp4_moe_workspace_bytes(int64_t tokens, int hidden, int intermediate, int local_experts, int top_k) {
+  if (tokens < 0 || hidden <= 0 || intermediate <= 0 || local_experts <= 0 || top_k <= 0) return 0;
+  return moe_workspace_bytes(tokens, hidden, intermediate, local_experts, top_k);
+}
+
+int b200fp4_moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, const void* w2_sf,
+                      const int* token_selected_experts, const float* token_final_scales, const float* w1_alpha,
+                      const float* w2_alpha, const float* fc2_input_scale, void* out, int64_t tokens, int hidden,
+                      int intermediate, int local_experts, int top_k, int local_expert_offset, int accumulate,
+                      void* workspace, size_t workspace_bytes, void* stream) {
+  return moe_fused(x, w1, w1_sf, w2, w2_sf, token_selected_experts, token_final_scales, w1_alpha, w2_alpha,
+                   fc2_input_scale, out, tokens, hidden, intermediate, local_experts, top_k, local_expert_offset,
+                   accumulate, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int b200fp4_device_status(void* stream, int* status_out, int clear) {

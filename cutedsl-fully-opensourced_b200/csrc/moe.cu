@@ -1,0 +1,337 @@
+// Fused NVFP4 MoE for sm_100a: the stages around the two grouped GEMMs.
+//
+// Stands in for flashinfer's b12x_fused_moe as the reference calls it
+// (tests/python/test_flashinfer_b12x_verbatim.py:99-116); arithmetic contract is
+// the reference's routed golden (same file, lines 28-65 and 209-219):
+//
+//   route (optional)   softmax over expert logits -> top-k -> renormalise
+//   count / scan       rows per local expert; every expert's segment is padded to whole 128-row
+//                      blocks so that a GEMM tile never straddles two experts
+//   scatter + quant    each token is quantised ONCE to NVFP4 with the activation packer and its
+//                      codes / scale bytes are written to the row of every (token, slot) pair
+//   FC1 grouped GEMM   [up | gate] = Xq . W1[e]^T, epilogue silu(gate)*up -> bf16 -> NVFP4   (gemm.cu)
+//   FC2 grouped GEMM   partial = Actq . W2[e]^T * w2_alpha[e]                               (gemm.cu)
+//   combine            out[t] = bf16( sum_j weight[t,j] * partial[row(t,j)] ), f32, slot order
+//
+// All intermediate buffers live in a caller-provided workspace.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace b200fp4 {
+
+int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* w1_sf, void* act_codes, void* act_sf,
+                 const float* w1_alpha, const float* fc2_input_scale, const int* num_m_blocks_dev,
+                 const int* m_block_expert, int max_m_blocks, int hidden, int inter, int experts, cudaStream_t stream);
+int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, float* partial,
+                 const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert, int max_m_blocks,
+                 int hidden, int inter, int experts, cudaStream_t stream);
+
+namespace {
+
+constexpr int kRouteMaxPerLane = 32;       // experts <= 1024
+
+// ---------------------------------------------------------------------------
+// route: one warp per token
+// ---------------------------------------------------------------------------
+__global__ void route_topk_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ weights,
+                                  int tokens, int experts, int top_k, int renormalize) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= tokens) return;
+  const float* row = logits + static_cast<int64_t>(warp) * experts;
+  float v[kRouteMaxPerLane];
+  const int per_lane = (experts + 31) >> 5;
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kRouteMaxPerLane; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = (i < per_lane && e < experts) ? row[e] : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kRouteMaxPerLane; ++i) {
+    v[i] = (i < per_lane && lane + 32 * i < experts) ? expf(v[i] - mx) : -1.0f;   // -1 = absent / already taken
+    if (v[i] > 0.0f) sum += v[i];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  const float inv = 1.0f / sum;
+  float picked = 0.0f;
+  float my_w = 0.0f;
+  int my_id = 0;
+  for (int j = 0; j < top_k; ++j) {
+    // lane-local best (lowest index among equals), then the warp's best
+    float best = -1.0f;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kRouteMaxPerLane; ++i) {
+      if (i < per_lane && v[i] > best) {
+        best = v[i];
+        best_e = lane + 32 * i;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) {
+        best = ob;
+        best_e = oe;
+      }
+    }
+    if ((best_e & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < kRouteMaxPerLane; ++i)
+        if (i == (best_e >> 5)) v[i] = -1.0f;
+    }
+    const float prob = best * inv;
+    picked += prob;
+    if (lane == j) {
+      my_w = prob;
+      my_id = best_e;
+    }
+  }
+  if (lane < top_k) {
+    ids[static_cast<int64_t>(warp) * top_k + lane] = my_id;
+    weights[static_cast<int64_t>(warp) * top_k + lane] = renormalize ? my_w / picked : my_w;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// bookkeeping header at the start of the workspace
+// ---------------------------------------------------------------------------
+struct MoeHeader {           // all int32, contiguous
+  int* counts;               // [experts]     rows routed to each local expert
+  int* cursor;               // [experts]     next free row inside the expert's segment
+  int* offsets;              // [experts + 1] first row of each expert's padded segment
+  int* num_m_blocks;         // [1]
+  int* m_block_expert;       // [max_m_blocks]
+  int* slot_row;             // [tokens * top_k] row of every (token, slot), -1 if the expert is not local
+};
+
+__global__ void moe_count_kernel(const int* __restrict__ ids, int n_slots, int expert_lo, int experts, int* counts) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_slots) return;
+  const int e = ids[i] - expert_lo;
+  if (e >= 0 && e < experts) atomicAdd(counts + e, 1);
+}
+
+// single CTA: padded exclusive scan over experts and the block -> expert table
+__global__ void moe_scan_kernel(MoeHeader h, int experts, int max_m_blocks) {
+  __shared__ int s_blocks[1024];
+  const int t = threadIdx.x;
+  int blocks = 0;
+  if (t < experts) blocks = (h.counts[t] + 127) >> 7;
+  s_blocks[t] = blocks;
+  __syncthreads();
+  // Hillis-Steele inclusive scan over up to 1024 experts
+  for (int o = 1; o < 1024; o <<= 1) {
+    const int add = t >= o ? s_blocks[t - o] : 0;
+    __syncthreads();
+    s_blocks[t] += add;
+    __syncthreads();
+  }
+  const int incl = s_blocks[t];
+  const int excl = incl - blocks;
+  if (t < experts) {
+    h.offsets[t] = excl * 128;
+    h.cursor[t] = 0;
+    for (int b = 0; b < blocks; ++b)
+      if (excl + b < max_m_blocks) h.m_block_expert[excl + b] = t;
+  }
+  if (t == experts - 1) {
+    h.offsets[experts] = incl * 128;
+    *h.num_m_blocks = min(incl, max_m_blocks);
+  }
+}
+
+// one CTA per token: quantise the row once, then write it to the row of every local slot
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads)
+moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids, MoeHeader h, uint8_t* xq,
+                         uint8_t* xq_sf, int hidden, int top_k, int expert_lo, int experts, int max_rows) {
+  __shared__ int s_rows[64];
+  const int token = blockIdx.x;
+  if (threadIdx.x < top_k) {
+    const int e = ids[static_cast<int64_t>(token) * top_k + threadIdx.x] - expert_lo;
+    int row = -1;
+    if (e >= 0 && e < experts) {
+      row = h.offsets[e] + atomicAdd(h.cursor + e, 1);
+      if (row >= max_rows) row = -1;
+    }
+    s_rows[threadIdx.x] = row;
+    h.slot_row[static_cast<int64_t>(token) * top_k + threadIdx.x] = row;
+  }
+  __syncthreads();
+  const int nchunks = hidden >> 4;
+  const int rk = (nchunks + 3) >> 2;
+  for (int chunk = threadIdx.x; chunk < nchunks; chunk += kThreads) {
+    const U32x8 raw = ld_stream_32B(x + static_cast<int64_t>(token) * hidden + chunk * 16);
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[2 * i] = Pair16<__nv_bfloat16>::lo(raw.v[i]);
+      v[2 * i + 1] = Pair16<__nv_bfloat16>::hi(raw.v[i]);
+    }
+    uint32_t lo, hi, sfb;
+    quantize_block16<true>(v, 1.0f, lo, hi, sfb);
+    for (int j = 0; j < top_k; ++j) {
+      const int row = s_rows[j];
+      if (row < 0) continue;
+      *reinterpret_cast<uint2*>(xq + static_cast<int64_t>(row) * (hidden >> 1) + chunk * 8) = make_uint2(lo, hi);
+      xq_sf[sf_swizzled_offset(row, chunk, rk)] = static_cast<uint8_t>(sfb);
+    }
+  }
+}
+
+// one CTA per token; every thread owns 4 output columns at a time
+__global__ void moe_combine_kernel(const float* __restrict__ partial, const int* __restrict__ slot_row,
+                                   const float* __restrict__ weights, __nv_bfloat16* __restrict__ out, int hidden,
+                                   int top_k, int accumulate) {
+  __shared__ int s_rows[64];
+  __shared__ float s_w[64];
+  const int token = blockIdx.x;
+  if (threadIdx.x < top_k) {
+    s_rows[threadIdx.x] = slot_row[static_cast<int64_t>(token) * top_k + threadIdx.x];
+    s_w[threadIdx.x] = weights[static_cast<int64_t>(token) * top_k + threadIdx.x];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < top_k; ++j) {
+      const int row = s_rows[j];
+      if (row < 0) continue;
+      const float4 pv = *reinterpret_cast<const float4*>(partial + static_cast<int64_t>(row) * hidden + c);
+      const float w = s_w[j];
+      acc.x = __fadd_rn(acc.x, __fmul_rn(w, pv.x));
+      acc.y = __fadd_rn(acc.y, __fmul_rn(w, pv.y));
+      acc.z = __fadd_rn(acc.z, __fmul_rn(w, pv.z));
+      acc.w = __fadd_rn(acc.w, __fmul_rn(w, pv.w));
+    }
+    __nv_bfloat16* o = out + static_cast<int64_t>(token) * hidden + c;
+    if (accumulate) {
+      acc.x += __bfloat162float(o[0]);
+      acc.y += __bfloat162float(o[1]);
+      acc.z += __bfloat162float(o[2]);
+      acc.w += __bfloat162float(o[3]);
+    }
+    uint2 packed;
+    packed.x = Pair16<__nv_bfloat16>::pack(acc.x, acc.y);
+    packed.y = Pair16<__nv_bfloat16>::pack(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(o) = packed;
+  }
+}
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct MoeWorkspace {
+  MoeHeader h;
+  uint8_t* xq;
+  uint8_t* xq_sf;
+  uint8_t* act;
+  uint8_t* act_sf;
+  float* partial;
+  size_t header_bytes;     // counts .. slot_row
+  size_t xq_sf_bytes;
+  size_t total;
+  int max_m_blocks;
+};
+
+MoeWorkspace carve(void* base, int64_t tokens, int hidden, int inter, int experts, int top_k) {
+  MoeWorkspace w{};
+  const int64_t slots = tokens * top_k;
+  const int64_t blocks = std::min<int64_t>(experts, slots) + slots / 128;
+  w.max_m_blocks = static_cast<int>(blocks);
+  const int64_t rows = blocks * 128;
+  uint8_t* p = static_cast<uint8_t*>(base);
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    uint8_t* r = p == nullptr ? nullptr : p + off;
+    off = align_up(off + bytes, 256);
+    return r;
+  };
+  w.h.counts = reinterpret_cast<int*>(take(sizeof(int) * experts));
+  w.h.cursor = reinterpret_cast<int*>(take(sizeof(int) * experts));
+  w.h.offsets = reinterpret_cast<int*>(take(sizeof(int) * (experts + 1)));
+  w.h.num_m_blocks = reinterpret_cast<int*>(take(sizeof(int)));
+  w.h.m_block_expert = reinterpret_cast<int*>(take(sizeof(int) * blocks));
+  w.h.slot_row = reinterpret_cast<int*>(take(sizeof(int) * slots));
+  w.header_bytes = off;
+  w.xq_sf_bytes = static_cast<size_t>(blocks) * ((hidden + 63) / 64) * 512;
+  w.xq_sf = take(w.xq_sf_bytes);
+  w.xq = take(static_cast<size_t>(rows) * (hidden / 2));
+  w.act_sf = take(static_cast<size_t>(blocks) * ((inter + 63) / 64) * 512);
+  w.act = take(static_cast<size_t>(rows) * (inter / 2));
+  w.partial = reinterpret_cast<float*>(take(static_cast<size_t>(rows) * hidden * sizeof(float)));
+  w.total = off;
+  return w;
+}
+
+}  // namespace
+
+int route_topk(const float* logits, int* ids, float* weights, int tokens, int experts, int top_k, int renormalize,
+               cudaStream_t stream) {
+  if (logits == nullptr || ids == nullptr || weights == nullptr) return fail(kInvalidArgument, "null pointer argument");
+  if (tokens < 0 || experts < 1 || top_k < 1 || top_k > 32 || top_k > experts)
+    return fail(kInvalidArgument, "tokens=%d experts=%d top_k=%d", tokens, experts, top_k);
+  if (experts > 32 * kRouteMaxPerLane) return fail(kUnsupported, "experts=%d exceeds %d", experts, 32 * kRouteMaxPerLane);
+  if (tokens == 0) return kOk;
+  const int warps_per_cta = 4;
+  route_topk_kernel<<<(tokens + warps_per_cta - 1) / warps_per_cta, 32 * warps_per_cta, 0, stream>>>(
+      logits, ids, weights, tokens, experts, top_k, renormalize);
+  return check_cuda(cudaGetLastError(), "route_topk_kernel launch");
+}
+
+size_t moe_workspace_bytes(int64_t tokens, int hidden, int inter, int experts, int top_k) {
+  return carve(nullptr, tokens, hidden, inter, experts, top_k).total;
+}
+
+// experts = number of LOCAL experts (w1/w2/alphas hold exactly those); token_selected_experts holds global
+// ids, of which [expert_lo, expert_lo + experts) are served here.  accumulate != 0 adds into `out`.
+int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, const void* w2_sf, const int* ids,
+              const float* route_w, const float* w1_alpha, const float* w2_alpha, const float* fc2_input_scale,
+              void* out, int64_t tokens, int hidden, int inter, int experts, int top_k, int expert_lo,
+              int accumulate, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  if (x == nullptr || w1 == nullptr || w1_sf == nullptr || w2 == nullptr || w2_sf == nullptr || ids == nullptr ||
+      route_w == nullptr || out == nullptr || workspace == nullptr)
+    return fail(kInvalidArgument, "null pointer argument");
+  if (tokens < 0 || top_k < 1 || top_k > 64 || experts < 1 || experts > 1024)
+    return fail(kInvalidArgument, "tokens=%lld top_k=%d experts=%d", static_cast<long long>(tokens), top_k, experts);
+  if (hidden % 64 != 0 || hidden < 64) return fail(kUnsupported, "hidden=%d must be a multiple of 64", hidden);
+  if (inter % 128 != 0 || inter < 128) return fail(kUnsupported, "intermediate=%d must be a multiple of 128", inter);
+  if ((reinterpret_cast<uintptr_t>(x) & 31) || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
+      ((reinterpret_cast<uintptr_t>(w1) | reinterpret_cast<uintptr_t>(w2) | reinterpret_cast<uintptr_t>(w1_sf) |
+        reinterpret_cast<uintptr_t>(w2_sf)) & 15) || (reinterpret_cast<uintptr_t>(out) & 7))
+    return fail(kInvalidArgument, "misaligned pointer (x 32 B, weights 16 B, workspace 256 B, out 8 B)");
+  if (tokens * top_k > (1ll << 30)) return fail(kUnsupported, "too many routed rows");
+  if (tokens == 0) return kOk;
+  MoeWorkspace ws = carve(workspace, tokens, hidden, inter, experts, top_k);
+  if (workspace_bytes < ws.total)
+    return fail(kInvalidArgument, "workspace holds %zu bytes, %zu needed", workspace_bytes, ws.total);
+  const int slots = static_cast<int>(tokens * top_k);
+  const int max_rows = ws.max_m_blocks * 128;
+
+  B200_CUDA(cudaMemsetAsync(ws.h.counts, 0, sizeof(int) * experts, stream));
+  B200_CUDA(cudaMemsetAsync(ws.xq_sf, 0, ws.xq_sf_bytes, stream));      // rows that only pad a block read as zero
+  moe_count_kernel<<<(slots + 255) / 256, 256, 0, stream>>>(ids, slots, expert_lo, experts, ws.h.counts);
+  moe_scan_kernel<<<1, 1024, 0, stream>>>(ws.h, experts, ws.max_m_blocks);
+  moe_scatter_quant_kernel<128><<<static_cast<unsigned>(tokens), 128, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), ids, ws.h, ws.xq, ws.xq_sf, hidden, top_k, expert_lo, experts, max_rows);
+  B200_CUDA(cudaGetLastError());
+  int rc = gemm_moe_fc1(ws.xq, ws.xq_sf, w1, w1_sf, ws.act, ws.act_sf, w1_alpha, fc2_input_scale, ws.h.num_m_blocks,
+                        ws.h.m_block_expert, ws.max_m_blocks, hidden, inter, experts, stream);
+  if (rc) return rc;
+  rc = gemm_moe_fc2(ws.act, ws.act_sf, w2, w2_sf, ws.partial, w2_alpha, ws.h.num_m_blocks, ws.h.m_block_expert,
+                    ws.max_m_blocks, hidden, inter, experts, stream);
+  if (rc) return rc;
+  const int threads = hidden / 4 >= 256 ? 256 : 128;
+  moe_combine_kernel<<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
+      ws.partial, ws.h.slot_row, route_w, static_cast<__nv_bfloat16*>(out), hidden, top_k, accumulate);
+  return check_cuda(cudaGetLastError(), "moe_combine_kernel launch");
+}
+
+}  // namespace b200fp4

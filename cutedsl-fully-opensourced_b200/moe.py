@@ -1,0 +1,140 @@
+"""Drop-in ``b12x_fused_moe`` (NVFP4 weights, bf16 tokens) and the router.
+
+Call signature of flashinfer's ``fused_moe.cute_dsl.b12x_moe.b12x_fused_moe`` as
+the reference calls it (tests/python/test_flashinfer_b12x_verbatim.py:99-116,
+tools/perf/bench_flashinfer_b12x.py:77-81).  One call = a fixed sequence of CUDA
+kernels on the current stream inside ``b200fp4_moe_fused``: count / scan,
+quantise + scatter, grouped FC1 with SwiGLU and re-quantisation, grouped FC2,
+weighted combine.  Scratch memory comes from a per-device buffer that only
+grows; pass ``workspace=`` to control it.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .layout import six_mode_to_storage
+
+_WORKSPACES = {}
+
+
+def moe_workspace_bytes(tokens: int, hidden: int, intermediate: int, local_experts: int, top_k: int) -> int:
+    return int(_lib.lib.b200fp4_moe_workspace_bytes(tokens, hidden, intermediate, local_experts, top_k))
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    key = (device.type, device.index)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def _sf_storage(sf: torch.Tensor, experts: int, rows: int, k: int, name: str) -> torch.Tensor:
+    """Accept the six-mode view (32,4,m_tiles,4,k_tiles,E) or already-flat tiled bytes [E, tiles*512]."""
+    need = -(-rows // 128) * -(-(k // 16) // 4) * 512
+    if sf.dim() == 6:
+        st = six_mode_to_storage(sf)
+    else:
+        st = sf.contiguous().view(torch.uint8).reshape(experts, -1)
+    if st.shape[0] != experts or st.shape[1] != need:
+        raise ValueError(f"{name}: expected {experts} x {need} scale bytes in 128x4 tiles, got {tuple(st.shape)}")
+    return st
+
+
+def topk_route(router_logits: torch.Tensor, top_k: int, renormalize: bool = True):
+    """softmax -> top-k -> (renormalised) weights on the GPU; returns (ids int32, weights float32)."""
+    if not router_logits.is_cuda or router_logits.dtype != torch.float32 or router_logits.dim() != 2:
+        raise ValueError("router_logits must be a float32 CUDA tensor [tokens, experts]")
+    logits = router_logits.contiguous()
+    t, e = logits.shape
+    ids = torch.empty(t, top_k, dtype=torch.int32, device=logits.device)
+    w = torch.empty(t, top_k, dtype=torch.float32, device=logits.device)
+    with torch.cuda.device(logits.device):
+        _lib.check(_lib.lib.b200fp4_topk_route(logits.data_ptr(), ids.data_ptr(), w.data_ptr(), t, e, top_k,
+                                               1 if renormalize else 0, _lib.current_stream_ptr(logits.device)))
+    return ids, w
+
+
+def b12x_fused_moe(
+    x: torch.Tensor,
+    w1_weight: torch.Tensor,
+    w1_weight_sf: torch.Tensor,
+    w2_weight: torch.Tensor,
+    w2_weight_sf: torch.Tensor,
+    token_selected_experts: torch.Tensor,
+    token_final_scales: torch.Tensor,
+    num_experts: int,
+    top_k: int,
+    *,
+    w1_alpha: Optional[torch.Tensor] = None,
+    w2_alpha: Optional[torch.Tensor] = None,
+    fc2_input_scale: Optional[torch.Tensor] = None,
+    quant_mode: str = "nvfp4",
+    num_local_experts: Optional[int] = None,
+    local_expert_offset: int = 0,
+    output: Optional[torch.Tensor] = None,
+    output_dtype: torch.dtype = torch.bfloat16,
+    activation: str = "silu",
+    activation_precision: Optional[str] = None,
+    accumulate: bool = False,
+    workspace: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """out[t] = sum_j scale[t,j] * FC2_e(quant(silu(gate) * up)),  [up|gate] = FC1_e(quant(x[t])), e = expert[t,j].
+
+    ``w1_weight`` [E_local, 2I, H/2] uint8 holds the up rows first, then the gate rows; scale tensors are the
+    six-mode e4m3 views the reference builds.  With ``num_local_experts`` / ``local_expert_offset`` only the experts
+    of this rank are computed and other slots contribute zero."""
+    if quant_mode != "nvfp4" or activation_precision not in (None, "fp4", "nvfp4"):
+        raise NotImplementedError("only NVFP4 weights with NVFP4 activations are implemented")
+    if activation not in ("silu", "swiglu"):
+        raise NotImplementedError(f"activation {activation!r}: only silu (SwiGLU) is implemented")
+    if output_dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
+        raise NotImplementedError("tokens and output must be bfloat16")
+    if not x.is_cuda:
+        raise ValueError("x must be a CUDA tensor (there is no CPU implementation)")
+    if x.dim() != 2 or not x.is_contiguous():
+        raise ValueError("x must be contiguous [tokens, hidden]")
+    tokens, hidden = x.shape
+    local = num_experts if num_local_experts is None else num_local_experts
+    w1 = w1_weight.view(torch.uint8)
+    w2 = w2_weight.view(torch.uint8)
+    if w1.dim() != 3 or w1.shape[0] != local or w1.shape[2] * 2 != hidden or not w1.is_contiguous():
+        raise ValueError(f"w1_weight must be contiguous [{local}, 2*I, {hidden // 2}]")
+    inter = w1.shape[1] // 2
+    if tuple(w2.shape) != (local, hidden, inter // 2) or not w2.is_contiguous():
+        raise ValueError(f"w2_weight must be contiguous [{local}, {hidden}, {inter // 2}]")
+    ids, scales = token_selected_experts, token_final_scales
+    if ids.dtype != torch.int32 or tuple(ids.shape) != (tokens, top_k) or not ids.is_contiguous():
+        raise ValueError("token_selected_experts must be contiguous int32 [tokens, top_k]")
+    if scales.dtype != torch.float32 or tuple(scales.shape) != (tokens, top_k) or not scales.is_contiguous():
+        raise ValueError("token_final_scales must be contiguous float32 [tokens, top_k]")
+    s1 = _sf_storage(w1_weight_sf, local, 2 * inter, hidden, "w1_weight_sf")
+    s2 = _sf_storage(w2_weight_sf, local, hidden, inter, "w2_weight_sf")
+    for name, a in (("w1_alpha", w1_alpha), ("w2_alpha", w2_alpha)):
+        if a is not None and (a.dtype != torch.float32 or a.numel() != local or not a.is_contiguous()):
+            raise ValueError(f"{name} must be float32 [{local}]")
+    if fc2_input_scale is not None and (fc2_input_scale.dtype != torch.float32 or fc2_input_scale.numel() != 1):
+        raise ValueError("fc2_input_scale must be one float32")
+    if output is None:
+        output = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=x.device)
+        if accumulate:
+            output.zero_()
+    elif tuple(output.shape) != (tokens, hidden) or output.dtype != torch.bfloat16 or not output.is_contiguous():
+        raise ValueError("output must be contiguous bfloat16 [tokens, hidden]")
+    if tokens == 0:
+        return output
+    need = moe_workspace_bytes(tokens, hidden, inter, local, top_k)
+    ws = _workspace(x.device, need) if workspace is None else workspace
+    if ws.numel() * ws.element_size() < need:
+        raise ValueError(f"workspace too small: {need} bytes needed")
+    with torch.cuda.device(x.device):
+        _lib.check(_lib.lib.b200fp4_moe_fused(
+            x.data_ptr(), w1.data_ptr(), s1.data_ptr(), w2.data_ptr(), s2.data_ptr(), ids.data_ptr(),
+            scales.data_ptr(), _lib.ptr(w1_alpha), _lib.ptr(w2_alpha), _lib.ptr(fc2_input_scale), output.data_ptr(),
+            tokens, hidden, inter, local, top_k, int(local_expert_offset), 1 if accumulate else 0, ws.data_ptr(),
+            ws.numel() * ws.element_size(), _lib.current_stream_ptr(x.device)))
+    return output

@@ -70,6 +70,36 @@ int b200fp4_add_rmsnorm_fp4quant(const void* x, void* residual, const void* weig
 int b200fp4_nvfp4_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha,
                        int m, int n, int k, int l, int c_dtype, int tile_n, void* stream);
 
+/* Router: softmax over `experts` logits per token, the top_k largest probabilities (lowest index
+ * first among equals), optionally renormalised to sum 1.  logits f32 [tokens, experts] ->
+ * ids i32 [tokens, top_k], weights f32 [tokens, top_k].
+ * The reference op takes ids and weights as inputs and its harness draws them on the host
+ * (tests/python/test_flashinfer_b12x_verbatim.py:142-143, tools/perf/bench_flashinfer_b12x.py:70-74);
+ * this entry puts that step on the GPU. */
+int b200fp4_topk_route(const float* logits, int* ids, float* weights, int tokens, int experts, int top_k,
+                       int renormalize, void* stream);
+
+/* Bytes of scratch that b200fp4_moe_fused needs for this problem size (0 on bad arguments). */
+size_t b200fp4_moe_workspace_bytes(int64_t tokens, int hidden, int intermediate, int local_experts, int top_k);
+
+/* Fused NVFP4 MoE: quantise tokens (NVFP4, in kernel), route by the given expert ids, FC1 [2I,H] per
+ * expert, silu(gate)*up -> bf16 -> NVFP4, FC2 [H,I], times the routing weight, summed per token -> bf16.
+ * Stands in for flashinfer's b12x_fused_moe as the reference calls it:
+ *   tests/python/test_flashinfer_b12x_verbatim.py:99-116, tools/perf/bench_flashinfer_b12x.py:77-81
+ * Arithmetic contract: tests/python/test_flashinfer_b12x_verbatim.py:28-65,209-219.
+ * x bf16 [tokens, hidden]; w1 u8 [local_experts, 2I, hidden/2] (rows 0..I-1 = up, I..2I-1 = gate);
+ * w2 u8 [local_experts, hidden, I/2]; w1_sf / w2_sf e4m3 bytes in 128x4 tiles
+ * [local_experts][rows/128][K/64][32][4][4]; ids i32 and scales f32 [tokens, top_k]; alphas f32
+ * [local_experts] or NULL; fc2_input_scale one f32 or NULL; out bf16 [tokens, hidden].
+ * Expert ids are global: those in [local_expert_offset, local_expert_offset + local_experts) are
+ * computed, the others contribute nothing (expert parallelism).  accumulate != 0 adds into out.
+ * workspace: 256-byte aligned device scratch of b200fp4_moe_workspace_bytes(...) bytes. */
+int b200fp4_moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, const void* w2_sf,
+                      const int* token_selected_experts, const float* token_final_scales, const float* w1_alpha,
+                      const float* w2_alpha, const float* fc2_input_scale, void* out, int64_t tokens, int hidden,
+                      int intermediate, int local_experts, int top_k, int local_expert_offset, int accumulate,
+                      void* workspace, size_t workspace_bytes, void* stream);
+
 /* Kernels never trap: a device-side wait that exceeds its bound ORs a bit into a per-device
  * status word and the kernel returns.  This call synchronises the stream and copies the word
  * to *status_out (0 = healthy; 1/2/4 = GEMM producer / MMA / epilogue wait expired), clearing

@@ -1,0 +1,189 @@
+"""GPU parity of the fused NVFP4 MoE and the router (through the C-ABI).
+
+Bars: the reference's constant-weight routing cases must match BIT-EXACTLY; random weights are
+compared with the CPU oracle at rel-L2 <= 1e-2 (the stated tolerance; observed ~1e-3, caused by f32
+summation order flipping a few bf16 roundings of the activation) and with the reference's own
+acceptance statistics.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import nvfp4_oracle as O
+from conftest import golden
+
+pytestmark = pytest.mark.gpu
+
+
+def six_mode(sf_logical: np.ndarray) -> torch.Tensor:
+    """[E, rows, K/16] scale bytes -> the (32,4,m_tiles,4,k_tiles,E) e4m3 view the operator takes."""
+    e, rows, kb = sf_logical.shape
+    swz = torch.from_numpy(O.swizzle_sf(sf_logical)).cuda()
+    st = swz.view(e, (rows + 127) // 128, (kb + 3) // 4, 32, 4, 4)
+    return st.view(torch.float8_e4m3fn).permute(3, 4, 1, 5, 2, 0)
+
+
+def random_weights(rng, e, hidden, inter):
+    w1c = rng.integers(0, 16, size=(e, 2 * inter, hidden), dtype=np.uint8)
+    w2c = rng.integers(0, 16, size=(e, hidden, inter), dtype=np.uint8)
+    w1s = rng.integers(0x18, 0x30, size=(e, 2 * inter, hidden // 16), dtype=np.uint8)   # 2^-4 .. 2^-1
+    w2s = rng.integers(0x18, 0x30, size=(e, hidden, inter // 16), dtype=np.uint8)
+    return w1c, w1s, w2c, w2s
+
+
+def run_gpu(b200, x, w1c, w1s, w2c, w2s, ids, wts, **kw):
+    e = w1c.shape[0]
+    out = b200.b12x_fused_moe(
+        x.cuda(), torch.from_numpy(O.pack_e2m1(w1c)).cuda(), six_mode(w1s), torch.from_numpy(O.pack_e2m1(w2c)).cuda(),
+        six_mode(w2s), ids.cuda(), wts.cuda(), kw.pop("num_experts", e), ids.shape[1], **kw)
+    torch.cuda.synchronize()
+    assert b200._lib.device_status() == 0, "a device-side wait expired"
+    return out.cpu()
+
+
+def rel_l2(a, b):
+    return float(torch.linalg.vector_norm(a.float() - b.float()) / torch.linalg.vector_norm(b.float()))
+
+
+@pytest.mark.parametrize("tokens", [8, 64, 256, 641])
+def test_uniform_routing_exact(b200, tokens):
+    """tests/python/test_flashinfer_b12x_verbatim.py:125-185: x = 0.1, weight codes 0x11 / 0x22, scales 2^-6."""
+    expected = torch.from_numpy(golden("moe.npz")["uniform_expected"].copy()).view(torch.bfloat16)
+    experts, hidden, inter = 2, 256, 128
+    x = torch.full((tokens, hidden), 0.1, dtype=torch.bfloat16)
+    w1c = np.broadcast_to(np.array([1, 2], np.uint8)[:, None, None], (experts, 2 * inter, hidden)).copy()
+    w2c = np.broadcast_to(np.array([1, 2], np.uint8)[:, None, None], (experts, hidden, inter)).copy()
+    sfb = O.e4m3_encode(np.float32(0.015625))
+    w1s = np.full((experts, 2 * inter, hidden // 16), sfb, np.uint8)
+    w2s = np.full((experts, hidden, inter // 16), sfb, np.uint8)
+    ids = (torch.arange(tokens, dtype=torch.int32) % experts)[:, None].contiguous()
+    ones = torch.ones(experts)
+    out = run_gpu(b200, x, w1c, w1s, w2c, w2s, ids, torch.ones(tokens, 1), w1_alpha=ones.cuda(), w2_alpha=ones.cuda(),
+                  fc2_input_scale=torch.ones(1).cuda(), quant_mode="nvfp4")
+    assert torch.equal(out, expected[ids[:, 0].long(), None].expand_as(out))
+
+
+def test_reference_random_case(b200):
+    """tests/python/test_flashinfer_b12x_verbatim.py:188-237 replayed from the frozen fixture."""
+    g = golden("moe.npz")
+    x = torch.from_numpy(g["rand_x"].copy()).view(torch.bfloat16)
+    w1c, w2c = O.unpack_e2m1(g["rand_w1"]), O.unpack_e2m1(g["rand_w2"])
+    out = run_gpu(b200, x, w1c, g["rand_w1_sf"], w2c, g["rand_w2_sf"], torch.from_numpy(g["rand_ids"]),
+                  torch.from_numpy(g["rand_routes"]))
+    oracle = torch.from_numpy(g["rand_oracle"].copy()).view(torch.bfloat16)
+    assert rel_l2(out, oracle) <= 1e-2
+    ref = torch.from_numpy(g["rand_ref_f32"])
+    actual = out.float()
+    diff = (actual - ref).abs()
+    rel = diff / (ref.abs() + 1e-6)
+    assert diff.mean() <= 0.02
+    assert torch.linalg.vector_norm(diff) / torch.linalg.vector_norm(ref) <= 0.10
+    assert torch.nn.functional.cosine_similarity(actual.reshape(1, -1), ref.reshape(1, -1)).item() >= 0.995
+    assert ((diff <= 0.05) | (rel <= 0.25)).float().mean() >= 0.985
+
+
+@pytest.mark.parametrize("tokens,experts,hidden,inter,top_k", [
+    (1, 4, 256, 128, 2), (37, 8, 512, 256, 4), (300, 8, 512, 256, 2), (130, 16, 1024, 384, 8)])
+def test_topk_random_against_oracle(b200, tokens, experts, hidden, inter, top_k):
+    rng = np.random.default_rng(tokens + experts)
+    torch.manual_seed(tokens)
+    w1c, w1s, w2c, w2s = random_weights(rng, experts, hidden, inter)
+    x = torch.randn(tokens, hidden).to(torch.bfloat16)
+    ids, wts = O.route_topk_ref(torch.randn(tokens, experts), top_k)
+    a1 = torch.tensor(rng.uniform(0.01, 0.03, experts), dtype=torch.float32)
+    a2 = torch.tensor(rng.uniform(0.5, 2.0, experts), dtype=torch.float32)
+    gs2 = 3.0
+    ref = O.moe_ref(x, w1c, w1s, w2c, w2s, ids, wts, a1.numpy(), a2.numpy(), gs2)
+    out = run_gpu(b200, x, w1c, w1s, w2c, w2s, ids, wts.contiguous(), w1_alpha=a1.cuda(), w2_alpha=a2.cuda(),
+                  fc2_input_scale=torch.tensor([gs2]).cuda())
+    assert rel_l2(out, ref) <= 1e-2
+
+
+def test_hot_expert_and_expert_parallel_split(b200):
+    """All tokens share one hot expert (several 128-row blocks of one expert), and the same problem computed as two
+    expert-parallel halves accumulated into one output."""
+    rng = np.random.default_rng(5)
+    torch.manual_seed(5)
+    tokens, experts, hidden, inter, top_k = 400, 8, 256, 128, 2
+    w1c, w1s, w2c, w2s = random_weights(rng, experts, hidden, inter)
+    x = torch.randn(tokens, hidden).to(torch.bfloat16)
+    logits = torch.randn(tokens, experts)
+    logits[:, 3] += 1e4
+    ids, wts = O.route_topk_ref(logits, top_k)
+    assert bool((ids[:, 0] == 3).all())
+    a1 = torch.full((experts,), 0.02)
+    ref = O.moe_ref(x, w1c, w1s, w2c, w2s, ids, wts, a1.numpy())
+    out = run_gpu(b200, x, w1c, w1s, w2c, w2s, ids, wts.contiguous(), w1_alpha=a1.cuda())
+    assert rel_l2(out, ref) <= 1e-2
+    # two "ranks" with four experts each
+    acc = torch.zeros(tokens, hidden, dtype=torch.bfloat16, device="cuda")
+    for lo in (0, 4):
+        sl = slice(lo, lo + 4)
+        b200.b12x_fused_moe(
+            x.cuda(), torch.from_numpy(O.pack_e2m1(w1c[sl])).cuda(), six_mode(w1s[sl]),
+            torch.from_numpy(O.pack_e2m1(w2c[sl])).cuda(), six_mode(w2s[sl]), ids.cuda(), wts.contiguous().cuda(),
+            experts, top_k, w1_alpha=a1[sl].contiguous().cuda(), num_local_experts=4, local_expert_offset=lo,
+            output=acc, accumulate=True)
+    torch.cuda.synchronize()
+    assert rel_l2(acc.cpu(), ref) <= 1e-2
+
+
+def test_router_matches_oracle(b200):
+    torch.manual_seed(0)
+    for tokens, experts, k in [(1, 8, 2), (64, 128, 8), (333, 256, 8), (50, 40, 5)]:
+        logits = torch.randn(tokens, experts)
+        ids_ref, w_ref = O.route_topk_ref(logits, k)
+        ids, w = b200.topk_route(logits.cuda(), k)
+        torch.cuda.synchronize()
+        assert torch.equal(ids.cpu(), ids_ref)
+        assert torch.allclose(w.cpu(), w_ref, rtol=1e-5, atol=1e-7)
+        ids2, w2 = b200.topk_route(logits.cuda(), k, renormalize=False)
+        assert torch.allclose(w2.cpu().sum(-1), torch.softmax(logits, -1).gather(1, ids_ref.long()).sum(-1), rtol=1e-5)
+    # equal logits resolve to the lowest expert ids
+    ids, w = b200.topk_route(torch.zeros(3, 16).cuda(), 4)
+    assert torch.equal(ids.cpu(), torch.arange(4, dtype=torch.int32).expand(3, 4))
+
+
+def test_empty_and_argument_errors(b200):
+    rng = np.random.default_rng(1)
+    w1c, w1s, w2c, w2s = random_weights(rng, 2, 256, 128)
+    args = (torch.from_numpy(O.pack_e2m1(w1c)).cuda(), six_mode(w1s), torch.from_numpy(O.pack_e2m1(w2c)).cuda(),
+            six_mode(w2s))
+    x0 = torch.empty(0, 256, dtype=torch.bfloat16, device="cuda")
+    out = b200.b12x_fused_moe(x0, *args, torch.empty(0, 1, dtype=torch.int32, device="cuda"),
+                              torch.empty(0, 1, device="cuda"), 2, 1)
+    assert out.shape == (0, 256)
+    x = torch.zeros(4, 256, dtype=torch.bfloat16, device="cuda")
+    ids = torch.zeros(4, 1, dtype=torch.int32, device="cuda")
+    w = torch.ones(4, 1, device="cuda")
+    with pytest.raises(NotImplementedError):
+        b200.b12x_fused_moe(x, *args, ids, w, 2, 1, quant_mode="mxfp8")
+    with pytest.raises(NotImplementedError):
+        b200.b12x_fused_moe(x, *args, ids, w, 2, 1, activation="relu2")
+    with pytest.raises(ValueError):
+        b200.b12x_fused_moe(x, *args, ids.long(), w, 2, 1)
+    with pytest.raises(ValueError):
+        b200.b12x_fused_moe(x.cpu(), *args, ids, w, 2, 1)
+
+
+def test_prefill_config_sampled_tokens(b200):
+    """Benchmark prefill shape (4096 tokens, hidden 2048, 128 experts, top-8, intermediate 768): a sample of
+    tokens against the oracle, every output finite, and idempotence (same inputs, same bits)."""
+    tokens, experts, hidden, inter, top_k = 4096, 128, 2048, 768, 8
+    rng = np.random.default_rng(0)
+    torch.manual_seed(0)
+    w1c, w1s, w2c, w2s = random_weights(rng, experts, hidden, inter)
+    x = torch.randn(tokens, hidden).to(torch.bfloat16)
+    ids, wts = O.route_topk_ref(torch.randn(tokens, experts), top_k)
+    a1 = torch.full((experts,), 0.01)
+    dev = (torch.from_numpy(O.pack_e2m1(w1c)).cuda(), six_mode(w1s), torch.from_numpy(O.pack_e2m1(w2c)).cuda(),
+           six_mode(w2s))
+    out = b200.b12x_fused_moe(x.cuda(), *dev, ids.cuda(), wts.contiguous().cuda(), experts, top_k, w1_alpha=a1.cuda())
+    out2 = b200.b12x_fused_moe(x.cuda(), *dev, ids.cuda(), wts.contiguous().cuda(), experts, top_k, w1_alpha=a1.cuda())
+    torch.cuda.synchronize()
+    assert b200._lib.device_status() == 0
+    assert torch.equal(out, out2)
+    assert bool(torch.isfinite(out.float()).all())
+    sample = torch.arange(0, tokens, 171)[:24]
+    ref = O.moe_ref(x[sample], w1c, w1s, w2c, w2s, ids[sample], wts[sample], a1.numpy())
+    assert rel_l2(out.cpu()[sample], ref) <= 1e-2
