@@ -293,7 +293,119 @@ class GemmWorkload:
             f"{m}x{n}x{k} block of the {self.m}x{self.n}x{self.k} problem: de-quantise + f32 matmul, {threads} threads"
 
 
-WORKLOADS = {"add_rmsnorm": AddRmsNormWorkload, "gemm": GemmWorkload}
+class MoeWorkload:
+    """Fused NVFP4 MoE.  prefill: 4096 tokens, hidden 2048, 128 experts, top-8, intermediate 768.
+    decode: T tokens, hidden 7168, 256 experts, top-8, intermediate 2048, 1% of rows forced onto expert 0.
+    Tokens bf16 ~ N(0,1); expert weights N(0, 0.02) quantised to NVFP4 per expert (global scale
+    448*6/amax folded into w1_alpha / w2_alpha); router logits ~ N(0,1), softmax top-k renormalised.
+    A step = router kernel + the fused MoE call."""
+    metric = "MoE tokens/s"
+    unit = "tokens/s"
+    dtype = "nvfp4 weights and activations, bf16 tokens, f32 accumulate"
+    kernel = "nvfp4_gemm_kernel<256, swiglu> + nvfp4_gemm_kernel<256> (grouped FC1 / FC2)"
+    bound = "hbm"
+    launches_per_step = 8      # route, count, scan, scatter-quant, FC1, FC2, combine (+ 2 memsets not counted) 
+
+    def __init__(self, rank, kind="prefill", tokens=None):
+        self.rank, self.kind = rank, kind
+        if kind == "prefill":
+            self.tokens, self.hidden, self.experts, self.top_k, self.inter = tokens or 4096, 2048, 128, 8, 768
+        else:
+            self.tokens, self.hidden, self.experts, self.top_k, self.inter = tokens or 64, 7168, 256, 8, 2048
+        self.rows = self.tokens
+        self.name = f"moe_{kind}_T{self.tokens}_H{self.hidden}_E{self.experts}_k{self.top_k}_I{self.inter}"
+        self.work = float(self.tokens)
+        self.expert_bytes = 3 * self.hidden * self.inter // 2 + 3 * self.hidden * self.inter // 16
+
+    def _quant_experts(self, pkg, rows, k, seed):
+        import torch
+        from cutedsl_fully_opensourced_b200.layout import swizzled_sf_numel
+        e = self.experts
+        codes = torch.empty(e, rows, k // 2, dtype=torch.uint8, device="cuda")
+        sf = torch.empty(e, swizzled_sf_numel(rows, k // 16), dtype=torch.uint8, device="cuda")
+        inv_gs = torch.empty(e, dtype=torch.float32, device="cuda")
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        for i in range(e):
+            w = 0.02 * torch.randn(rows, k, generator=g, device="cuda")
+            c, s, gs = pkg.gemm.quantize_operand(w)
+            codes[i], sf[i], inv_gs[i] = c, s, 1.0 / gs
+        return codes, sf, inv_gs
+
+    def setup(self, pkg):
+        import torch
+        self.pkg = pkg
+        t, h, e, k, i = self.tokens, self.hidden, self.experts, self.top_k, self.inter
+        self.w1, self.w1_sf, self.a1 = self._quant_experts(pkg, 2 * i, h, 11)
+        self.w2, self.w2_sf, self.a2 = self._quant_experts(pkg, h, i, 12)
+        g = torch.Generator(device="cuda").manual_seed(1000 + self.rank)
+        self.x = torch.randn(t, h, generator=g, device="cuda").to(torch.bfloat16)
+        self.logits = torch.randn(t, e, generator=g, device="cuda")
+        if self.kind == "decode":
+            n_hot = max(1, -(-t // 100))
+            self.logits[:n_hot, 0] += 1e4
+        self.out = torch.empty(t, h, dtype=torch.bfloat16, device="cuda")
+        self.fc2_scale = torch.ones(1, device="cuda")
+        ids, _ = pkg.topk_route(self.logits, k)
+        active = int(torch.unique(ids).numel())
+        self.active_experts = active
+        self.alg_bytes = active * self.expert_bytes + 2 * t * h * 2
+        # L2 flush buffer: the weights of the prefill case (340 MB) exceed L2 by themselves; the decode
+        # cases touch as little as 0.2 GB, so a 256 MB buffer is rewritten between steps (untimed)
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if self.alg_bytes < (400 << 20) else None
+
+    def restore(self):
+        if self.flush is not None:
+            self.flush.zero_()
+
+    def step(self):
+        ids, wts = self.pkg.topk_route(self.logits, self.top_k)
+        self.pkg.b12x_fused_moe(self.x, self.w1, self.w1_sf, self.w2, self.w2_sf, ids, wts, self.experts, self.top_k,
+                                w1_alpha=self.a1, w2_alpha=self.a2, fc2_input_scale=self.fc2_scale, output=self.out)
+
+    def config(self, world):
+        return {"workload": self.name, "tokens": self.tokens, "hidden": self.hidden, "experts": self.experts,
+                "top_k": self.top_k, "intermediate": self.inter, "active_experts": self.active_experts,
+                "parallelism": f"experts x{world}",
+                "l2": "weights streamed per step exceed the 126 MB L2" if self.flush is None else
+                      "a 256 MB buffer is rewritten (untimed) between steps to flush the 126 MB L2"}
+
+    def setup_e2e(self):
+        import torch
+        self.hx = self.x.cpu().pin_memory()
+        self.hl = self.logits.cpu().pin_memory()
+        self.ho = torch.empty(self.out.shape, dtype=torch.bfloat16).pin_memory()
+        self.h2d = self.hx.numel() * 2 + self.hl.numel() * 4
+        self.d2h = self.ho.numel() * 2
+
+    def step_e2e(self):
+        self.x.copy_(self.hx, non_blocking=True)
+        self.logits.copy_(self.hl, non_blocking=True)
+        self.step()
+        self.ho.copy_(self.out, non_blocking=True)
+
+    def cpu_run(self, threads: int):
+        import numpy as np
+        import torch
+        from oracle import nvfp4_oracle as O
+        torch.set_num_threads(threads)
+        t = min(self.tokens, 64)
+        e = 8                                   # a bounded sample: 64 tokens routed over 8 experts of the same shape
+        rng = np.random.default_rng(0)
+        w1c = rng.integers(0, 16, size=(e, 2 * self.inter, self.hidden), dtype=np.uint8)
+        w2c = rng.integers(0, 16, size=(e, self.hidden, self.inter), dtype=np.uint8)
+        w1s = rng.integers(0x18, 0x30, size=(e, 2 * self.inter, self.hidden // 16), dtype=np.uint8)
+        w2s = rng.integers(0x18, 0x30, size=(e, self.hidden, self.inter // 16), dtype=np.uint8)
+        x = torch.randn(t, self.hidden).to(torch.bfloat16)
+        ids, wts = O.route_topk_ref(torch.randn(t, e), min(self.top_k, e))
+        t0 = time.perf_counter()
+        O.moe_ref(x, w1c, w1s, w2c, w2s, ids, wts)
+        dt = time.perf_counter() - t0
+        return t / dt, dt, (f"{t} tokens over {e} experts of this shape, top-{min(self.top_k, e)}: oracle port "
+                            f"(numpy+torch), {threads} threads")
+
+
+WORKLOADS = {"add_rmsnorm": AddRmsNormWorkload, "gemm": GemmWorkload, "moe_prefill": MoeWorkload,
+             "moe_decode": MoeWorkload}
 
 
 # ---------------------------------------------------------------------------
@@ -341,6 +453,7 @@ def main():
     ap.add_argument("--m", type=int, default=None, help="gemm: override M (M-sweep 128 / 1024 / 8192)")
     ap.add_argument("--nk", type=int, default=None, help="gemm: override N = K (small profiling cases)")
     ap.add_argument("--tile-n", type=int, default=0, help="gemm: force the 128- or 256-wide tile")
+    ap.add_argument("--tokens", type=int, default=None, help="moe: override the token count (decode: 1 / 8 / 64)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -350,6 +463,8 @@ def main():
         nk = args.nk or 8192
         wl = GemmWorkload(rank, args.m or 8192, nk, nk)
         wl.tile_n = args.tile_n
+    elif args.workload.startswith("moe_"):
+        wl = MoeWorkload(rank, args.workload[4:], args.tokens)
     else:
         wl = WORKLOADS[args.workload](rank)
     if args.rows and args.workload == "add_rmsnorm":
@@ -431,12 +546,15 @@ def main():
 
     if rank == 0:
         ms_per_step = total_ms / steps
-        scale = 1e9 if wl.unit == "GB/s" else 1e12
+        scale = {"GB/s": 1e9, "TFLOP/s": 1e12}.get(wl.unit, 1.0)
         value = wl.work * world / (ms_per_step * 1e-3) / scale
         e2e_value = wl.work * world / (e2e_ms / e2e_steps * 1e-3) / scale
         # roofline of the dominant kernel: rank 0's own launches, averaged over the timed region
         k_ms = statistics.mean(step_ms)
         achieved = wl.work / (k_ms * 1e-3) / scale
+        roof_unit = wl.unit
+        if wl.unit == "tokens/s":          # roofline of the whole step in bytes streamed from HBM
+            achieved, roof_unit = wl.alg_bytes / (k_ms * 1e-3) / 1e9, "GB/s"
         if wl.bound == "hbm":
             peak, peak_src = peaks["hbm_gbs"], peaks["source"]
         else:
@@ -451,7 +569,7 @@ def main():
                 "d2h_bytes_per_step": wl.d2h * world, "steps": e2e_steps},
             "gpu_launches": wl.launches_per_step * steps * world,
             "roofline": {"bound": wl.bound, "kernel": wl.kernel, "achieved": round(achieved, 1),
-                         "peak": peak, "peak_source": peak_src, "unit": wl.unit,
+                         "peak": peak, "peak_source": peak_src, "unit": roof_unit,
                          "frac": round(achieved / peak, 4), "traffic": None,
                          "algorithmic_bytes_per_launch": wl.alg_bytes,
                          "kernel_us": round(k_ms * 1e3, 2), "kernel_us_min": round(min(step_ms) * 1e3, 2)},
