@@ -22,10 +22,11 @@ namespace b200fp4 {
 
 int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* w1_sf, void* act_codes, void* act_sf,
                  const float* w1_alpha, const float* fc2_input_scale, const int* num_m_blocks_dev,
-                 const int* m_block_expert, int max_m_blocks, int hidden, int inter, int experts, cudaStream_t stream);
+                 const int* m_block_expert, int max_m_blocks, int hidden, int inter, int experts, int* status,
+                 cudaStream_t stream);
 int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, float* partial,
                  const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert, int max_m_blocks,
-                 int hidden, int inter, int experts, cudaStream_t stream);
+                 int hidden, int inter, int experts, int* status, cudaStream_t stream);
 
 namespace {
 
@@ -290,14 +291,15 @@ size_t moe_workspace_bytes(int64_t tokens, int hidden, int inter, int experts, i
   return carve(nullptr, tokens, hidden, inter, experts, top_k).total;
 }
 
+// status: device word that the GEMM kernels OR failure bits into.
 // experts = number of LOCAL experts (w1/w2/alphas hold exactly those); token_selected_experts holds global
 // ids, of which [expert_lo, expert_lo + experts) are served here.  accumulate != 0 adds into `out`.
 int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, const void* w2_sf, const int* ids,
               const float* route_w, const float* w1_alpha, const float* w2_alpha, const float* fc2_input_scale,
               void* out, int64_t tokens, int hidden, int inter, int experts, int top_k, int expert_lo,
-              int accumulate, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+              int accumulate, void* workspace, size_t workspace_bytes, int* status, cudaStream_t stream) {
   if (x == nullptr || w1 == nullptr || w1_sf == nullptr || w2 == nullptr || w2_sf == nullptr || ids == nullptr ||
-      route_w == nullptr || out == nullptr || workspace == nullptr)
+      route_w == nullptr || out == nullptr || workspace == nullptr || status == nullptr)
     return fail(kInvalidArgument, "null pointer argument");
   if (tokens < 0 || top_k < 1 || top_k > 64 || experts < 1 || experts > 1024)
     return fail(kInvalidArgument, "tokens=%lld top_k=%d experts=%d", static_cast<long long>(tokens), top_k, experts);
@@ -323,10 +325,10 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
       static_cast<const __nv_bfloat16*>(x), ids, ws.h, ws.xq, ws.xq_sf, hidden, top_k, expert_lo, experts, max_rows);
   B200_CUDA(cudaGetLastError());
   int rc = gemm_moe_fc1(ws.xq, ws.xq_sf, w1, w1_sf, ws.act, ws.act_sf, w1_alpha, fc2_input_scale, ws.h.num_m_blocks,
-                        ws.h.m_block_expert, ws.max_m_blocks, hidden, inter, experts, stream);
+                        ws.h.m_block_expert, ws.max_m_blocks, hidden, inter, experts, status, stream);
   if (rc) return rc;
   rc = gemm_moe_fc2(ws.act, ws.act_sf, w2, w2_sf, ws.partial, w2_alpha, ws.h.num_m_blocks, ws.h.m_block_expert,
-                    ws.max_m_blocks, hidden, inter, experts, stream);
+                    ws.max_m_blocks, hidden, inter, experts, status, stream);
   if (rc) return rc;
   const int threads = hidden / 4 >= 256 ? 256 : 128;
   moe_combine_kernel<<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
