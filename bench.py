@@ -120,6 +120,9 @@ class AddRmsNormWorkload:
     bytes_per_element = 2 + 2 + 2 + 0.5 + 0.0625      # x in, residual in+out, codes, scale bytes
     kernel = "norm_quant_kernel<bf16, add>"
     bound = "hbm"
+    # DRAM bytes inside the kernel window per element, from the ncu capture summarised in
+    # profiles/norm_quant_add_bf16.md (reads equal the algorithmic reads; most writes drain from L2 later)
+    traffic_per_element = (117496064 + 26109440) / (4096 * 7168)
 
     def __init__(self, rank: int):
         self.rank = rank
@@ -570,7 +573,9 @@ def main():
             "gpu_launches": wl.launches_per_step * steps * world,
             "roofline": {"bound": wl.bound, "kernel": wl.kernel, "achieved": round(achieved, 1),
                          "peak": peak, "peak_source": peak_src, "unit": roof_unit,
-                         "frac": round(achieved / peak, 4), "traffic": None,
+                         "frac": round(achieved / peak, 4),
+                         "traffic": (int(wl.traffic_per_element * wl.rows * wl.hidden)
+                                     if hasattr(wl, "traffic_per_element") else None),
                          "algorithmic_bytes_per_launch": wl.alg_bytes,
                          "kernel_us": round(k_ms * 1e3, 2), "kernel_us_min": round(min(step_ms) * 1e3, 2)},
             "clocks": clocks,
