@@ -100,6 +100,21 @@ int b200fp4_moe_fused(const void* x, const void* w1, const void* w1_sf, const vo
                       int intermediate, int local_experts, int top_k, int local_expert_offset, int accumulate,
                       void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same fused MoE for callers that cannot allocate device memory (engines that forbid cudaMalloc after
+ * start-up, plugins that only receive raw pointers, latency-critical loops).  It has no counterpart in the
+ * reference; it exists only in this library.  Arguments as b200fp4_moe_fused, without the workspace: the
+ * scratch is a fixed 32 MiB array inside the library's device image (held by every GPU that loads the
+ * library until the process ends).  Problems whose b200fp4_moe_workspace_bytes(...) exceeds 32 MiB are
+ * refused with B200FP4_UNSUPPORTED.  status_word: a caller-owned int in device memory, zeroed by the
+ * caller, into which the kernels OR the bits described at b200fp4_device_status.
+ * The first call on each device looks up the array's device address; make it before any stream capture.
+ * All calls on a GPU share the array: calls whose kernels overlap on the same GPU race, serialise them. */
+int b200fp4_moe_fused_noalloc(const void* x, const void* w1, const void* w1_sf, const void* w2, const void* w2_sf,
+                              const int* token_selected_experts, const float* token_final_scales,
+                              const float* w1_alpha, const float* w2_alpha, const float* fc2_input_scale, void* out,
+                              int64_t tokens, int hidden, int intermediate, int local_experts, int top_k,
+                              int local_expert_offset, int accumulate, int* status_word, void* stream);
+
 /* Kernels never trap: a device-side wait that exceeds its bound ORs a bit into a per-device
  * status word and the kernel returns.  This call synchronises the stream and copies the word
  * to *status_out (0 = healthy; 1/2/4 = GEMM producer / MMA / epilogue wait expired), clearing
