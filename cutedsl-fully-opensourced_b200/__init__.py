@@ -8,7 +8,7 @@ fails if it is absent.
 from . import _lib, layout  # noqa: F401
 from . import gemm  # noqa: F401
 from .gemm import (Sm100BlockScaledGemmKernel, Sm120BlockScaledGemmKernel, nvfp4_gemm)  # noqa: F401
-from . import moe  # noqa: F401
+from . import moe, parallel  # noqa: F401
 from .moe import b12x_fused_moe, topk_route  # noqa: F401
 from .norm import add_rmsnorm_fp4quant, rmsnorm_fp4quant  # noqa: F401
 

@@ -190,8 +190,9 @@ moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, const int* __restr
 }
 
 // one CTA per token; every thread owns 4 output columns at a time
+template <typename OutT>
 __global__ void moe_combine_kernel(const float* __restrict__ partial, const int* __restrict__ slot_row,
-                                   const float* __restrict__ weights, __nv_bfloat16* __restrict__ out, int hidden,
+                                   const float* __restrict__ weights, OutT* __restrict__ out, int hidden,
                                    int top_k, int accumulate) {
   __shared__ int s_rows[64];
   __shared__ float s_w[64];
@@ -213,17 +214,28 @@ __global__ void moe_combine_kernel(const float* __restrict__ partial, const int*
       acc.z = __fadd_rn(acc.z, __fmul_rn(w, pv.z));
       acc.w = __fadd_rn(acc.w, __fmul_rn(w, pv.w));
     }
-    __nv_bfloat16* o = out + static_cast<int64_t>(token) * hidden + c;
-    if (accumulate) {
-      acc.x += __bfloat162float(o[0]);
-      acc.y += __bfloat162float(o[1]);
-      acc.z += __bfloat162float(o[2]);
-      acc.w += __bfloat162float(o[3]);
+    OutT* o = out + static_cast<int64_t>(token) * hidden + c;
+    if constexpr (sizeof(OutT) == 4) {
+      if (accumulate) {
+        const float4 prev = *reinterpret_cast<const float4*>(o);
+        acc.x += prev.x;
+        acc.y += prev.y;
+        acc.z += prev.z;
+        acc.w += prev.w;
+      }
+      *reinterpret_cast<float4*>(o) = acc;
+    } else {
+      if (accumulate) {
+        acc.x += __bfloat162float(o[0]);
+        acc.y += __bfloat162float(o[1]);
+        acc.z += __bfloat162float(o[2]);
+        acc.w += __bfloat162float(o[3]);
+      }
+      uint2 packed;
+      packed.x = Pair16<__nv_bfloat16>::pack(acc.x, acc.y);
+      packed.y = Pair16<__nv_bfloat16>::pack(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(o) = packed;
     }
-    uint2 packed;
-    packed.x = Pair16<__nv_bfloat16>::pack(acc.x, acc.y);
-    packed.y = Pair16<__nv_bfloat16>::pack(acc.z, acc.w);
-    *reinterpret_cast<uint2*>(o) = packed;
   }
 }
 
@@ -297,7 +309,9 @@ size_t moe_workspace_bytes(int64_t tokens, int hidden, int inter, int experts, i
 int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, const void* w2_sf, const int* ids,
               const float* route_w, const float* w1_alpha, const float* w2_alpha, const float* fc2_input_scale,
               void* out, int64_t tokens, int hidden, int inter, int experts, int top_k, int expert_lo,
-              int accumulate, void* workspace, size_t workspace_bytes, int* status, cudaStream_t stream) {
+              int accumulate, int out_dtype, void* workspace, size_t workspace_bytes, int* status,
+              cudaStream_t stream) {
+  if (out_dtype != 1 && out_dtype != 2) return fail(kUnsupported, "out_dtype code %d (1 bf16, 2 f32)", out_dtype);
   if (x == nullptr || w1 == nullptr || w1_sf == nullptr || w2 == nullptr || w2_sf == nullptr || ids == nullptr ||
       route_w == nullptr || out == nullptr || workspace == nullptr || status == nullptr)
     return fail(kInvalidArgument, "null pointer argument");
@@ -307,8 +321,8 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
   if (inter % 128 != 0 || inter < 128) return fail(kUnsupported, "intermediate=%d must be a multiple of 128", inter);
   if ((reinterpret_cast<uintptr_t>(x) & 31) || (reinterpret_cast<uintptr_t>(workspace) & 255) ||
       ((reinterpret_cast<uintptr_t>(w1) | reinterpret_cast<uintptr_t>(w2) | reinterpret_cast<uintptr_t>(w1_sf) |
-        reinterpret_cast<uintptr_t>(w2_sf)) & 15) || (reinterpret_cast<uintptr_t>(out) & 7))
-    return fail(kInvalidArgument, "misaligned pointer (x 32 B, weights 16 B, workspace 256 B, out 8 B)");
+        reinterpret_cast<uintptr_t>(w2_sf)) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+    return fail(kInvalidArgument, "misaligned pointer (x 32 B, weights 16 B, workspace 256 B, out 16 B)");
   if (tokens * top_k > (1ll << 30)) return fail(kUnsupported, "too many routed rows");
   if (tokens == 0) return kOk;
   MoeWorkspace ws = carve(workspace, tokens, hidden, inter, experts, top_k);
@@ -331,8 +345,13 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
                     ws.max_m_blocks, hidden, inter, experts, status, stream);
   if (rc) return rc;
   const int threads = hidden / 4 >= 256 ? 256 : 128;
-  moe_combine_kernel<<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
-      ws.partial, ws.h.slot_row, route_w, static_cast<__nv_bfloat16*>(out), hidden, top_k, accumulate);
+  if (out_dtype == 2) {
+    moe_combine_kernel<float><<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
+        ws.partial, ws.h.slot_row, route_w, static_cast<float*>(out), hidden, top_k, accumulate);
+  } else {
+    moe_combine_kernel<__nv_bfloat16><<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
+        ws.partial, ws.h.slot_row, route_w, static_cast<__nv_bfloat16*>(out), hidden, top_k, accumulate);
+  }
   return check_cuda(cudaGetLastError(), "moe_combine_kernel launch");
 }
 

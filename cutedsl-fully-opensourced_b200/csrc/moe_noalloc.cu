@@ -27,7 +27,8 @@ size_t moe_workspace_bytes(int64_t tokens, int hidden, int inter, int experts, i
 int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, const void* w2_sf, const int* ids,
               const float* route_w, const float* w1_alpha, const float* w2_alpha, const float* fc2_input_scale,
               void* out, int64_t tokens, int hidden, int inter, int experts, int top_k, int expert_lo,
-              int accumulate, void* workspace, size_t workspace_bytes, int* status, cudaStream_t stream);
+              int accumulate, int out_dtype, void* workspace, size_t workspace_bytes, int* status,
+              cudaStream_t stream);
 
 namespace {
 
@@ -77,5 +78,6 @@ extern "C" int b200fp4_moe_fused_noalloc(const void* x, const void* w1, const vo
   if (rc) return rc;
   return moe_fused(x, w1, w1_sf, w2, w2_sf, token_selected_experts, token_final_scales, w1_alpha, w2_alpha,
                    fc2_input_scale, out, tokens, hidden, intermediate, local_experts, top_k, local_expert_offset,
-                   accumulate, scratch, kBuiltinScratchBytes, status_word, static_cast<cudaStream_t>(stream));
+                   accumulate, /*out_dtype=bf16*/ 1, scratch, kBuiltinScratchBytes, status_word,
+                   static_cast<cudaStream_t>(stream));
 }

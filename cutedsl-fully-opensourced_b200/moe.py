@@ -92,8 +92,8 @@ def b12x_fused_moe(
         raise NotImplementedError("only NVFP4 weights with NVFP4 activations are implemented")
     if activation not in ("silu", "swiglu"):
         raise NotImplementedError(f"activation {activation!r}: only silu (SwiGLU) is implemented")
-    if output_dtype != torch.bfloat16 or x.dtype != torch.bfloat16:
-        raise NotImplementedError("tokens and output must be bfloat16")
+    if output_dtype not in (torch.bfloat16, torch.float32) or x.dtype != torch.bfloat16:
+        raise NotImplementedError("tokens must be bfloat16 and the output bfloat16 (or float32 partial sums)")
     if not x.is_cuda:
         raise ValueError("x must be a CUDA tensor (there is no CPU implementation)")
     if x.dim() != 2 or not x.is_contiguous():
@@ -120,11 +120,12 @@ def b12x_fused_moe(
     if fc2_input_scale is not None and (fc2_input_scale.dtype != torch.float32 or fc2_input_scale.numel() != 1):
         raise ValueError("fc2_input_scale must be one float32")
     if output is None:
-        output = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=x.device)
+        output = torch.empty(tokens, hidden, dtype=output_dtype, device=x.device)
         if accumulate:
             output.zero_()
-    elif tuple(output.shape) != (tokens, hidden) or output.dtype != torch.bfloat16 or not output.is_contiguous():
-        raise ValueError("output must be contiguous bfloat16 [tokens, hidden]")
+    elif (tuple(output.shape) != (tokens, hidden) or output.dtype not in (torch.bfloat16, torch.float32)
+          or not output.is_contiguous()):
+        raise ValueError("output must be contiguous bfloat16 or float32 [tokens, hidden]")
     if tokens == 0:
         return output
     need = moe_workspace_bytes(tokens, hidden, inter, local, top_k)
@@ -135,6 +136,7 @@ def b12x_fused_moe(
         _lib.check(_lib.lib.b200fp4_moe_fused(
             x.data_ptr(), w1.data_ptr(), s1.data_ptr(), w2.data_ptr(), s2.data_ptr(), ids.data_ptr(),
             scales.data_ptr(), _lib.ptr(w1_alpha), _lib.ptr(w2_alpha), _lib.ptr(fc2_input_scale), output.data_ptr(),
-            tokens, hidden, inter, local, top_k, int(local_expert_offset), 1 if accumulate else 0, ws.data_ptr(),
+            tokens, hidden, inter, local, top_k, int(local_expert_offset), 1 if accumulate else 0,
+            2 if output.dtype == torch.float32 else 1, ws.data_ptr(),
             ws.numel() * ws.element_size(), _lib.current_stream_ptr(x.device)))
     return output

@@ -90,7 +90,8 @@ size_t b200fp4_moe_workspace_bytes(int64_t tokens, int hidden, int intermediate,
  * x bf16 [tokens, hidden]; w1 u8 [local_experts, 2I, hidden/2] (rows 0..I-1 = up, I..2I-1 = gate);
  * w2 u8 [local_experts, hidden, I/2]; w1_sf / w2_sf e4m3 bytes in 128x4 tiles
  * [local_experts][rows/128][K/64][32][4][4]; ids i32 and scales f32 [tokens, top_k]; alphas f32
- * [local_experts] or NULL; fc2_input_scale one f32 or NULL; out bf16 [tokens, hidden].
+ * [local_experts] or NULL; fc2_input_scale one f32 or NULL; out [tokens, hidden], bf16 (out_dtype 1) or
+ * f32 (out_dtype 2, what expert-parallel ranks reduce across GPUs).
  * Expert ids are global: those in [local_expert_offset, local_expert_offset + local_experts) are
  * computed, the others contribute nothing (expert parallelism).  accumulate != 0 adds into out.
  * workspace: 256-byte aligned device scratch of b200fp4_moe_workspace_bytes(...) bytes. */
@@ -98,7 +99,7 @@ int b200fp4_moe_fused(const void* x, const void* w1, const void* w1_sf, const vo
                       const int* token_selected_experts, const float* token_final_scales, const float* w1_alpha,
                       const float* w2_alpha, const float* fc2_input_scale, void* out, int64_t tokens, int hidden,
                       int intermediate, int local_experts, int top_k, int local_expert_offset, int accumulate,
-                      void* workspace, size_t workspace_bytes, void* stream);
+                      int out_dtype, void* workspace, size_t workspace_bytes, void* stream);
 
 /* The same fused MoE for callers that cannot allocate device memory (engines that forbid cudaMalloc after
  * start-up, plugins that only receive raw pointers, latency-critical loops).  It has no counterpart in the

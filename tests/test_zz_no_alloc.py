@@ -48,7 +48,7 @@ def _call_regular(lib, d, out, tokens, hidden, inter, experts, top_k, stream):
     return lib.b200fp4_moe_fused(
         d["x"].data_ptr(), d["w1"].data_ptr(), d["s1"].data_ptr(), d["w2"].data_ptr(), d["s2"].data_ptr(),
         d["ids"].data_ptr(), d["wts"].data_ptr(), d["a1"].data_ptr(), None, None, out.data_ptr(), tokens, hidden,
-        inter, experts, top_k, 0, 0, ws.data_ptr(), need, stream), ws
+        inter, experts, top_k, 0, 0, 1, ws.data_ptr(), need, stream), ws
 
 
 def _call_noalloc(lib, d, out, status, tokens, hidden, inter, experts, top_k, stream):
