@@ -309,26 +309,33 @@ class MoeWorkload:
     bound = "hbm"
     launches_per_step = 8      # route, count, scan, scatter-quant, FC1, FC2, combine (+ 2 memsets not counted) 
 
-    def __init__(self, rank, kind="prefill", tokens=None):
-        self.rank, self.kind = rank, kind
+    scaling = "strong"         # the token batch is fixed; more GPUs split it (and the experts)
+
+    def __init__(self, rank, kind="prefill", tokens=None, world=1):
+        self.rank, self.kind, self.world = rank, kind, world
         if kind == "prefill":
             self.tokens, self.hidden, self.experts, self.top_k, self.inter = tokens or 4096, 2048, 128, 8, 768
         else:
             self.tokens, self.hidden, self.experts, self.top_k, self.inter = tokens or 64, 7168, 256, 8, 2048
         self.rows = self.tokens
         self.name = f"moe_{kind}_T{self.tokens}_H{self.hidden}_E{self.experts}_k{self.top_k}_I{self.inter}"
-        self.work = float(self.tokens)
+        if self.tokens % world or self.experts % world:
+            raise SystemExit(f"{self.tokens} tokens / {self.experts} experts do not divide over {world} ranks")
+        self.local_tokens = self.tokens // world
+        self.local_experts = self.experts // world
+        self.expert_lo = rank * self.local_experts
+        self.work = float(self.local_tokens)      # per rank; the bench multiplies by the world size
         self.expert_bytes = 3 * self.hidden * self.inter // 2 + 3 * self.hidden * self.inter // 16
 
     def _quant_experts(self, pkg, rows, k, seed):
         import torch
         from cutedsl_fully_opensourced_b200.layout import swizzled_sf_numel
-        e = self.experts
+        e = self.local_experts                   # this rank's experts only; they never move
         codes = torch.empty(e, rows, k // 2, dtype=torch.uint8, device="cuda")
         sf = torch.empty(e, swizzled_sf_numel(rows, k // 16), dtype=torch.uint8, device="cuda")
         inv_gs = torch.empty(e, dtype=torch.float32, device="cuda")
-        g = torch.Generator(device="cuda").manual_seed(seed)
         for i in range(e):
+            g = torch.Generator(device="cuda").manual_seed(seed * 100003 + self.expert_lo + i)
             w = 0.02 * torch.randn(rows, k, generator=g, device="cuda")
             c, s, gs = pkg.gemm.quantize_operand(w)
             codes[i], sf[i], inv_gs[i] = c, s, 1.0 / gs
@@ -337,21 +344,26 @@ class MoeWorkload:
     def setup(self, pkg):
         import torch
         self.pkg = pkg
-        t, h, e, k, i = self.tokens, self.hidden, self.experts, self.top_k, self.inter
+        t, h, e, k, i = self.local_tokens, self.hidden, self.experts, self.top_k, self.inter
         self.w1, self.w1_sf, self.a1 = self._quant_experts(pkg, 2 * i, h, 11)
         self.w2, self.w2_sf, self.a2 = self._quant_experts(pkg, h, i, 12)
         g = torch.Generator(device="cuda").manual_seed(1000 + self.rank)
         self.x = torch.randn(t, h, generator=g, device="cuda").to(torch.bfloat16)
         self.logits = torch.randn(t, e, generator=g, device="cuda")
-        if self.kind == "decode":
-            n_hot = max(1, -(-t // 100))
+        if self.kind == "decode" and self.rank == 0:
+            n_hot = max(1, -(-self.tokens // 100))
             self.logits[:n_hot, 0] += 1e4
         self.out = torch.empty(t, h, dtype=torch.bfloat16, device="cuda")
         self.fc2_scale = torch.ones(1, device="cuda")
         ids, _ = pkg.topk_route(self.logits, k)
         active = int(torch.unique(ids).numel())
         self.active_experts = active
-        self.alg_bytes = active * self.expert_bytes + 2 * t * h * 2
+        self.alg_bytes = min(active, self.local_experts) * self.expert_bytes + 2 * t * h * 2
+        self.ep = None
+        if self.world > 1:
+            self.ep = pkg.parallel.ExpertParallelMoE(e, k)
+            self.weights = {"w1": self.w1, "w1_sf": self.w1_sf, "w2": self.w2, "w2_sf": self.w2_sf,
+                            "w1_alpha": self.a1, "w2_alpha": self.a2, "fc2_input_scale": self.fc2_scale}
         # L2 flush buffer: the weights of the prefill case (340 MB) exceed L2 by themselves; the decode
         # cases touch as little as 0.2 GB, so a 256 MB buffer is rewritten between steps (untimed)
         self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if self.alg_bytes < (400 << 20) else None
@@ -362,13 +374,17 @@ class MoeWorkload:
 
     def step(self):
         ids, wts = self.pkg.topk_route(self.logits, self.top_k)
+        if self.ep is not None:
+            self.ep.forward(self.x, ids, wts, self.weights, out=self.out)
+            return
         self.pkg.b12x_fused_moe(self.x, self.w1, self.w1_sf, self.w2, self.w2_sf, ids, wts, self.experts, self.top_k,
                                 w1_alpha=self.a1, w2_alpha=self.a2, fc2_input_scale=self.fc2_scale, output=self.out)
 
     def config(self, world):
         return {"workload": self.name, "tokens": self.tokens, "hidden": self.hidden, "experts": self.experts,
                 "top_k": self.top_k, "intermediate": self.inter, "active_experts": self.active_experts,
-                "parallelism": f"experts x{world}",
+                "parallelism": (f"experts x{world}, tokens x{world}; NCCL all-gather of tokens + routing, "
+                                "reduce-scatter of f32 partial outputs") if world > 1 else "single GPU",
                 "l2": "weights streamed per step exceed the 126 MB L2" if self.flush is None else
                       "a 256 MB buffer is rewritten (untimed) between steps to flush the 126 MB L2"}
 
@@ -467,7 +483,7 @@ def main():
         wl = GemmWorkload(rank, args.m or 8192, nk, nk)
         wl.tile_n = args.tile_n
     elif args.workload.startswith("moe_"):
-        wl = MoeWorkload(rank, args.workload[4:], args.tokens)
+        wl = MoeWorkload(rank, args.workload[4:], args.tokens, world)
     else:
         wl = WORKLOADS[args.workload](rank)
     if args.rows and args.workload == "add_rmsnorm":
@@ -564,7 +580,8 @@ def main():
             peak, peak_src = wl.FP4_NOMINAL_TFLOPS, "nominal dense FP4 (no measured FP4 peak; 4x measured bf16 burst = %.0f)" % (4 * peaks["bf16_tflops"])
         line = {
             "metric": wl.metric, "value": round(value, 2), "unit": wl.unit, "n_gpus": world, "steps": steps,
-            "warmup": warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak",
+            "warmup": warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
+            "scaling": getattr(wl, "scaling", "weak"),
             "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
             "config": wl.config(world),
             "e2e": None if args.no_e2e else {

@@ -1,0 +1,70 @@
+"""Expert-parallel MoE on two GPUs (one process per GPU, NCCL) against the single-GPU operator.
+Needs two devices; on a one-GPU box it reports a skip with that reason."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import nvfp4_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _problem():
+    rng = np.random.default_rng(11)
+    torch.manual_seed(11)
+    experts, hidden, inter, top_k, tokens = 8, 512, 256, 4, 96
+    w1c = rng.integers(0, 16, size=(experts, 2 * inter, hidden), dtype=np.uint8)
+    w2c = rng.integers(0, 16, size=(experts, hidden, inter), dtype=np.uint8)
+    w1s = rng.integers(0x18, 0x30, size=(experts, 2 * inter, hidden // 16), dtype=np.uint8)
+    w2s = rng.integers(0x18, 0x30, size=(experts, hidden, inter // 16), dtype=np.uint8)
+    x = torch.randn(tokens, hidden).to(torch.bfloat16)
+    ids, wts = O.route_topk_ref(torch.randn(tokens, experts), top_k)
+    return (w1c, w1s, w2c, w2s), x, ids, wts.contiguous(), experts, top_k
+
+
+def _dev_weights(w1c, w1s, w2c, w2s, sl, dev):
+    return {"w1": torch.from_numpy(O.pack_e2m1(w1c[sl])).to(dev), "w1_sf": torch.from_numpy(O.swizzle_sf(w1s[sl])).to(dev),
+            "w2": torch.from_numpy(O.pack_e2m1(w2c[sl])).to(dev), "w2_sf": torch.from_numpy(O.swizzle_sf(w2s[sl])).to(dev),
+            "w1_alpha": torch.full((sl.stop - sl.start,), 0.02, device=dev)}
+
+
+def _worker(rank, world, port, result_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import cutedsl_fully_opensourced_b200 as b200
+        (w1c, w1s, w2c, w2s), x, ids, wts, experts, top_k = _problem()
+        ep = b200.parallel.ExpertParallelMoE(experts, top_k)
+        sl = slice(ep.expert_lo, ep.expert_lo + ep.local_experts)
+        dev = torch.device("cuda", rank)
+        t = x.shape[0] // world
+        mine = slice(rank * t, (rank + 1) * t)
+        for _ in range(2):          # twice: buffers are reused across steps
+            out = ep.forward(x[mine].to(dev), ids[mine].to(dev), wts[mine].to(dev), _dev_weights(w1c, w1s, w2c, w2s, sl, dev))
+        torch.cuda.synchronize()
+        assert b200._lib.device_status() == 0
+        torch.save(out.cpu(), os.path.join(result_dir, f"out{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_two_gpus_matches_single_gpu(b200, tmp_path):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs (run under `gpurun --gpus 2`)")
+    import torch.multiprocessing as mp
+    world, port = 2, 29600 + os.getpid() % 2000
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    (w1c, w1s, w2c, w2s), x, ids, wts, experts, top_k = _problem()
+    w = _dev_weights(w1c, w1s, w2c, w2s, slice(0, experts), "cuda")
+    single = b200.b12x_fused_moe(x.cuda(), w["w1"], w["w1_sf"], w["w2"], w["w2_sf"], ids.cuda(), wts.cuda(), experts,
+                                 top_k, w1_alpha=w["w1_alpha"]).cpu()
+    got = torch.cat([torch.load(os.path.join(tmp_path, f"out{r}.pt")) for r in range(world)])
+    # same per-slot partial sums; only the f32 summation order across ranks differs from slot order
+    err = torch.linalg.vector_norm(got.float() - single.float()) / torch.linalg.vector_norm(single.float())
+    assert err <= 2e-3, float(err)
+    ref = O.moe_ref(x, w1c, w1s, w2c, w2s, ids, wts, np.full(experts, 0.02, np.float32))
+    assert torch.linalg.vector_norm(got.float() - ref.float()) / torch.linalg.vector_norm(ref.float()) <= 1e-2
