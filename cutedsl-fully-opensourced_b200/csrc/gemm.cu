@@ -83,7 +83,7 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
   int grid = sm_count_of_current_device();
   if (grid > max_tiles) grid = max_tiles;
   if (grid < 1) return kOk;
-  kern<<<grid, kGemmThreads, L.total, stream>>>(ta, tb, p, epi);
+  kern<<<grid, gemm_threads(kBlockN), L.total, stream>>>(ta, tb, p, epi);
   return check_cuda(cudaGetLastError(), "nvfp4_gemm_kernel launch");
 }
 
@@ -161,8 +161,8 @@ int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, v
 // FC1: act = quant(bf16(silu(gate) * up)) with [up | gate] = Xq . W1[e]^T * w1_alpha[e]
 int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* w1_sf, void* act_codes, void* act_sf,
                  const float* w1_alpha, const float* fc2_input_scale, const int* num_m_blocks_dev,
-                 const int* m_block_expert, int max_m_blocks, int hidden, int inter, int experts, int* status,
-                 cudaStream_t stream) {
+                 const int* m_block_expert, const int* m_block_rows, int max_m_blocks, int hidden, int inter,
+                 int experts, int* status, cudaStream_t stream) {
   CUtensorMap ta, tb;
   int rc = make_operand_map(&ta, xq, static_cast<int64_t>(max_m_blocks) * 128, hidden, 0);
   if (rc) return rc;
@@ -182,6 +182,7 @@ int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* 
   p.num_m_blocks_dev = num_m_blocks_dev;
   p.num_m_blocks = max_m_blocks;
   p.m_block_group = m_block_expert;
+  p.m_block_rows = m_block_rows;
   p.status = status;
   EpilogueSwiglu epi{static_cast<uint8_t*>(act_codes), static_cast<uint8_t*>(act_sf), w1_alpha, fc2_input_scale, inter};
   return launch_gemm<256, true>(ta, tb, p, epi, max_m_blocks * p.num_n_blocks, stream);
@@ -189,8 +190,9 @@ int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* 
 
 // FC2: partial[row][h] = (Actq . W2[e]^T) * w2_alpha[e], f32
 int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, float* partial,
-                 const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert, int max_m_blocks,
-                 int hidden, int inter, int experts, int* status, cudaStream_t stream) {
+                 const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
+                 const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int* status,
+                 cudaStream_t stream) {
   CUtensorMap ta, tb;
   int rc = make_operand_map(&ta, act_codes, static_cast<int64_t>(max_m_blocks) * 128, inter, 0);
   if (rc) return rc;
@@ -208,6 +210,7 @@ int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, cons
   p.num_m_blocks_dev = num_m_blocks_dev;
   p.num_m_blocks = max_m_blocks;
   p.m_block_group = m_block_expert;
+  p.m_block_rows = m_block_rows;
   p.status = status;
   EpilogueStore<float> epi{partial, hidden, w2_alpha, 1};
   if (hidden % 256 == 0) {

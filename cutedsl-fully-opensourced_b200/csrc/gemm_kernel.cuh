@@ -16,8 +16,9 @@
 //   warp 1  MMA issuer: tcgen05.cp moves the scale slabs into tensor memory,
 //           then four tcgen05.mma kind::mxf4nvf4 (K = 64 each) accumulate into
 //           a TMEM accumulator; tcgen05.commit releases the stage
-//   warps 2-5  epilogue: tcgen05.ld the accumulator (each warp its own 32-lane
-//           quarter), apply the epilogue functor, store
+//   warps 2..  epilogue (4 warps for 128-wide tiles, 8 for 256-wide ones): tcgen05.ld the
+//           accumulator (each warp its own 32-lane quarter; with 8 warps two warps share a
+//           quarter and split the columns), apply the epilogue functor, store
 //
 // No cluster launch and no multicast anywhere.  Every wait is bounded: on
 // expiry the kernel raises a flag in the status word and all roles leave.
@@ -30,7 +31,10 @@ namespace b200fp4 {
 
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 256;                 // e2m1 elements per stage = 128 bytes per row
-constexpr int kGemmThreads = 192;
+// two single-thread roles (TMA, MMA) + the epilogue warps: four for 128-wide tiles (the second
+// accumulator hides the epilogue), eight for 256-wide tiles (one accumulator: drain it twice as fast)
+__host__ __device__ constexpr int epilogue_warps(int block_n) { return block_n == 256 ? 8 : 4; }
+__host__ __device__ constexpr int gemm_threads(int block_n) { return 64 + 32 * epilogue_warps(block_n); }
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitLimitCycles = 4000000000LL;   // ~2 s at 2 GHz
 
@@ -56,6 +60,7 @@ struct GemmParams {
   const int* num_m_blocks_dev; // null -> num_m_blocks
   int num_m_blocks;
   const int* m_block_group;    // null -> group 0
+  const int* m_block_rows;     // null -> all 128 rows of a block hold data; else rows of the block that do
   int* status;                 // device status word (bits of GemmStatusBits)
 };
 
@@ -116,16 +121,18 @@ struct EpilogueStore {
   const float* alpha;           // one scale, or one per group (alpha_per_group); null = 1
   int alpha_per_group;
 
+  // part / parts: which share of the tile's columns this warp drains (two warps per TMEM quarter when parts == 2)
   template <int kBlockN, typename Loader>
   __device__ __forceinline__ void operator()(const GemmParams& p, int m_blk, int n_blk, int group, int row,
-                                             Loader&& load) const {
+                                             int rows_valid, int part, int parts, Loader&& load) const {
     const float scale = alpha == nullptr ? 1.0f : __ldg(alpha + (alpha_per_group ? group : 0));
     const int64_t grow = static_cast<int64_t>(m_blk) * kBlockM + row;
-    const bool row_ok = grow < p.m_rows;
+    const bool row_ok = grow < p.m_rows && row < rows_valid;
     OutT* crow = c + grow * ldc + static_cast<int64_t>(n_blk) * kBlockN;
     const int cols_left = p.n_cols - n_blk * kBlockN;
+    const int span = kBlockN / parts;
 #pragma unroll 1
-    for (int c0 = 0; c0 < kBlockN; c0 += 32) {
+    for (int c0 = part * span; c0 < (part + 1) * span; c0 += 32) {
       uint32_t r[32];
       load(c0, r);                 // warp-collective: every lane takes part, stores are predicated
       if (!row_ok) continue;
@@ -165,7 +172,7 @@ struct EpilogueSwiglu {
 
   template <int kBlockN, typename Loader>
   __device__ __forceinline__ void operator()(const GemmParams& p, int m_blk, int n_blk, int group, int row,
-                                             Loader&& load) const {
+                                             int rows_valid, int part, int parts, Loader&& load) const {
     static_assert(kBlockN == 256, "the SwiGLU epilogue pairs two 128-column halves");
     const float a1 = w1_alpha == nullptr ? 1.0f : __ldg(w1_alpha + group);
     const float gs = fc2_input_scale == nullptr ? 1.0f : __ldg(fc2_input_scale);
@@ -173,8 +180,9 @@ struct EpilogueSwiglu {
     const int j0 = n_blk * 128;
     const int rk2 = (inter + 63) >> 6;
     uint8_t* sf_tile = act_sf + static_cast<int64_t>(m_blk) * rk2 * 512 + (row & 31) * 16 + (row >> 5) * 4;
+    const int span = 128 / parts;
 #pragma unroll 1
-    for (int c0 = 0; c0 < 128; c0 += 32) {
+    for (int c0 = part * span; c0 < (part + 1) * span; c0 += 32) {
       uint32_t up[32], gate[32];
       load(c0, up);
       load(128 + c0, gate);
@@ -188,7 +196,7 @@ struct EpilogueSwiglu {
         for (int i = 0; i < 16; ++i) {
           const float u = __uint_as_float(up[16 * b + i]) * a1;
           const float g = __uint_as_float(gate[16 * b + i]) * a1;
-          const float s = __fdiv_rn(g, 1.0f + expf(-g));          // silu, f32
+          const float s = __fdividef(g, 1.0f + __expf(-g));       // silu in f32 (a few ulp; rounded to bf16 next)
           v[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(s, u)));
         }
         uint32_t sfb;
@@ -207,7 +215,7 @@ struct EpilogueSwiglu {
 // kSwigluB: B tile = two 128-row pieces (up rows, gate rows); otherwise kBlockN/128 consecutive pieces.
 // ----------------------------------------------------------------------------
 template <int kBlockN, bool kSwigluB, typename Epilogue>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(gemm_threads(kBlockN), 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const GemmParams p, const Epilogue epi) {
   constexpr SmemLayout L = smem_layout<kBlockN>();
@@ -242,7 +250,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(acc_full_bar(s), 1);
-      ptx::mbar_init(acc_empty_bar(s), 128);
+      ptx::mbar_init(acc_empty_bar(s), 32 * epilogue_warps(kBlockN));
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
@@ -359,7 +367,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
   } else {
     // =============================== epilogue ===============================
+    constexpr int kParts = epilogue_warps(kBlockN) / 4;
     const int quarter = warp & 3;                      // TMEM lanes this warp may touch
+    const int part = (warp - 2) >> 2;                  // which share of the columns (two warps per quarter)
     const int row = quarter * 32 + lane;
     PipeState acc;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
@@ -372,10 +382,14 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       }
       ptx::tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc.stage * kBlockN;
-      epi.template operator()<kBlockN>(p, m_blk, n_blk, group, row, [&](int c0, uint32_t (&r)[32]) {
-        ptx::tmem_ld_32x32(t_acc + c0, r);
-        ptx::tmem_ld_wait();
-      });
+      const int rows_valid = p.m_block_rows != nullptr ? __ldg(p.m_block_rows + m_blk) : kBlockM;
+      if (quarter * 32 < rows_valid) {                 // a warp whose 32 rows only pad the block has nothing to do
+        epi.template operator()<kBlockN>(p, m_blk, n_blk, group, row, rows_valid, part, kParts,
+                                         [&](int c0, uint32_t (&r)[32]) {
+                                           ptx::tmem_ld_32x32(t_acc + c0, r);
+                                           ptx::tmem_ld_wait();
+                                         });
+      }
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(acc_empty_bar(acc.stage));
       acc.advance(kAccStages);

@@ -22,11 +22,12 @@ namespace b200fp4 {
 
 int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* w1_sf, void* act_codes, void* act_sf,
                  const float* w1_alpha, const float* fc2_input_scale, const int* num_m_blocks_dev,
-                 const int* m_block_expert, int max_m_blocks, int hidden, int inter, int experts, int* status,
-                 cudaStream_t stream);
+                 const int* m_block_expert, const int* m_block_rows, int max_m_blocks, int hidden, int inter,
+                 int experts, int* status, cudaStream_t stream);
 int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, float* partial,
-                 const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert, int max_m_blocks,
-                 int hidden, int inter, int experts, int* status, cudaStream_t stream);
+                 const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
+                 const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int* status,
+                 cudaStream_t stream);
 
 namespace {
 
@@ -111,6 +112,7 @@ struct MoeHeader {           // all int32, contiguous
   int* offsets;              // [experts + 1] first row of each expert's padded segment
   int* num_m_blocks;         // [1]
   int* m_block_expert;       // [max_m_blocks]
+  int* m_block_rows;         // [max_m_blocks] rows of the block that hold data (the rest pads it to 128)
   int* slot_row;             // [tokens * top_k] row of every (token, slot), -1 if the expert is not local
 };
 
@@ -141,8 +143,13 @@ __global__ void moe_scan_kernel(MoeHeader h, int experts, int max_m_blocks) {
   if (t < experts) {
     h.offsets[t] = excl * 128;
     h.cursor[t] = 0;
-    for (int b = 0; b < blocks; ++b)
-      if (excl + b < max_m_blocks) h.m_block_expert[excl + b] = t;
+    const int count = h.counts[t];
+    for (int b = 0; b < blocks; ++b) {
+      if (excl + b < max_m_blocks) {
+        h.m_block_expert[excl + b] = t;
+        h.m_block_rows[excl + b] = min(128, count - 128 * b);
+      }
+    }
   }
   if (t == experts - 1) {
     h.offsets[experts] = incl * 128;
@@ -272,6 +279,7 @@ MoeWorkspace carve(void* base, int64_t tokens, int hidden, int inter, int expert
   w.h.offsets = reinterpret_cast<int*>(take(sizeof(int) * (experts + 1)));
   w.h.num_m_blocks = reinterpret_cast<int*>(take(sizeof(int)));
   w.h.m_block_expert = reinterpret_cast<int*>(take(sizeof(int) * blocks));
+  w.h.m_block_rows = reinterpret_cast<int*>(take(sizeof(int) * blocks));
   w.h.slot_row = reinterpret_cast<int*>(take(sizeof(int) * slots));
   w.header_bytes = off;
   w.xq_sf_bytes = static_cast<size_t>(blocks) * ((hidden + 63) / 64) * 512;
@@ -339,10 +347,10 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
       static_cast<const __nv_bfloat16*>(x), ids, ws.h, ws.xq, ws.xq_sf, hidden, top_k, expert_lo, experts, max_rows);
   B200_CUDA(cudaGetLastError());
   int rc = gemm_moe_fc1(ws.xq, ws.xq_sf, w1, w1_sf, ws.act, ws.act_sf, w1_alpha, fc2_input_scale, ws.h.num_m_blocks,
-                        ws.h.m_block_expert, ws.max_m_blocks, hidden, inter, experts, status, stream);
+                        ws.h.m_block_expert, ws.h.m_block_rows, ws.max_m_blocks, hidden, inter, experts, status, stream);
   if (rc) return rc;
   rc = gemm_moe_fc2(ws.act, ws.act_sf, w2, w2_sf, ws.partial, w2_alpha, ws.h.num_m_blocks, ws.h.m_block_expert,
-                    ws.max_m_blocks, hidden, inter, experts, status, stream);
+                    ws.h.m_block_rows, ws.max_m_blocks, hidden, inter, experts, status, stream);
   if (rc) return rc;
   const int threads = hidden / 4 >= 256 ? 256 : 128;
   if (out_dtype == 2) {
