@@ -107,6 +107,47 @@ struct Pair16<__half> {
   }
 };
 
+// both halves of a packed 16-bit pair as one f32x2 register pair (defined after f32x2_pack)
+template <typename T>
+__device__ __forceinline__ uint64_t pair16_to_f32x2(uint32_t u);
+
+// ---------------------------------------------------------------------------
+// packed f32x2 arithmetic (sm_100): two IEEE round-to-nearest f32 operations per instruction,
+// operands are register pairs viewed as one 64-bit value {lo, hi}
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t f32x2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ float f32x2_lo(uint64_t v) { return __uint_as_float(static_cast<uint32_t>(v)); }
+__device__ __forceinline__ float f32x2_hi(uint64_t v) { return __uint_as_float(static_cast<uint32_t>(v >> 32)); }
+__device__ __forceinline__ uint64_t f32x2_mul(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f32x2_add(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t f32x2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
+template <typename T>
+__device__ __forceinline__ uint64_t pair16_to_f32x2(uint32_t u) {
+  return f32x2_pack(Pair16<T>::lo(u), Pair16<T>::hi(u));
+}
+// f32x2 -> packed 16-bit pair, round-to-nearest-even each
+template <typename T>
+__device__ __forceinline__ uint32_t f32x2_to_pair16(uint64_t v) {
+  return Pair16<T>::pack(f32x2_lo(v), f32x2_hi(v));
+}
+
 // ---------------------------------------------------------------------------
 // e4m3 scale factors
 // ---------------------------------------------------------------------------
@@ -191,12 +232,14 @@ __device__ __forceinline__ float rcp_approx(float x) {
 // kImplicitOne selects the MoE activation packer, which divides by the
 // implicit-one reading of the scale byte instead of its true value.
 // ---------------------------------------------------------------------------
+// The arithmetic runs on the packed f32x2 instructions of sm_100 (two IEEE round-to-nearest f32
+// operations per instruction): a block is eight register pairs.
 template <bool kImplicitOne>
-__device__ __forceinline__ void quantize_block16(const float (&v)[16], float gs, uint32_t& codes_lo,
+__device__ __forceinline__ void quantize_block16(const uint64_t (&v2)[8], float gs, uint32_t& codes_lo,
                                                  uint32_t& codes_hi, uint32_t& sf_bits) {
   float amax = 0.0f;
 #pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  for (int i = 0; i < 8; ++i) amax = fmaxf(fmaxf(amax, fabsf(f32x2_lo(v2[i]))), fabsf(f32x2_hi(v2[i])));
   const float sf = fminf(div_by_6(__fmul_rn(amax, gs)), 448.0f);
   sf_bits = e4m3_encode_rn(sf);
   const float div = kImplicitOne ? e4m3_decode_implicit_one(sf_bits) : e4m3_decode(sf_bits);
@@ -204,14 +247,20 @@ __device__ __forceinline__ void quantize_block16(const float (&v)[16], float gs,
   const float k = div > 0.0f ? gs * rcp_approx(div) : 0.0f;
   const float k_hi = k * 1.0000019073486328125f;   // 1 + 2^-19
   const float k_lo = k * 0.9999980926513671875f;   // 1 - 2^-19
+  const uint64_t k_hi2 = f32x2_pack(k_hi, k_hi);
+  const uint64_t k_lo2 = f32x2_pack(k_lo, k_lo);
   uint32_t out[2];
 #pragma unroll
   for (int g = 0; g < 2; ++g) {
     float uh[8], ul[8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      uh[i] = v[8 * g + i] * k_hi;
-      ul[i] = v[8 * g + i] * k_lo;
+    for (int i = 0; i < 4; ++i) {
+      const uint64_t h = f32x2_mul(v2[4 * g + i], k_hi2);
+      const uint64_t l = f32x2_mul(v2[4 * g + i], k_lo2);
+      uh[2 * i] = f32x2_lo(h);
+      uh[2 * i + 1] = f32x2_hi(h);
+      ul[2 * i] = f32x2_lo(l);
+      ul[2 * i + 1] = f32x2_hi(l);
     }
     uint32_t ch = e2m1x8_hw(uh);
     const uint32_t cl = e2m1x8_hw(ul);
@@ -219,13 +268,26 @@ __device__ __forceinline__ void quantize_block16(const float (&v)[16], float gs,
       ch = 0;
       if (div > 0.0f) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) ch |= e2m1_code_exact(__fmul_rn(v[8 * g + i], gs), div) << (4 * i);
+        for (int i = 0; i < 4; ++i) {
+          ch |= e2m1_code_exact(__fmul_rn(f32x2_lo(v2[4 * g + i]), gs), div) << (8 * i);
+          ch |= e2m1_code_exact(__fmul_rn(f32x2_hi(v2[4 * g + i]), gs), div) << (8 * i + 4);
+        }
       }
     }
     out[g] = e2m1x8_drop_negative_zero(ch);
   }
   codes_lo = out[0];
   codes_hi = out[1];
+}
+
+// the same for sixteen scalars
+template <bool kImplicitOne>
+__device__ __forceinline__ void quantize_block16(const float (&v)[16], float gs, uint32_t& codes_lo,
+                                                 uint32_t& codes_hi, uint32_t& sf_bits) {
+  uint64_t v2[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v2[i] = f32x2_pack(v[2 * i], v[2 * i + 1]);
+  quantize_block16<kImplicitOne>(v2, gs, codes_lo, codes_hi, sf_bits);
 }
 
 // offset of scale factor (row m, K-block kb) in the 128x4 tiled layout with rk

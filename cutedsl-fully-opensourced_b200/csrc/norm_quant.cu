@@ -54,8 +54,10 @@ __device__ __forceinline__ float warp_sum(float v) {
 // A "unit" is kVec adjacent 16-element chunks; thread t of a team handles units
 // t, t+team, ... (kUnits of them).  kWarpRow: the team is one warp and a CTA
 // works on one row per warp (hidden <= 512); otherwise the team is the CTA.
-template <typename T, bool kAdd, int kVec, int kUnits, bool kWarpRow>
-__global__ void __launch_bounds__(kMaxThreads) norm_quant_kernel(const NormParams p) {
+// kCap: upper bound of the block size of this instantiation; small blocks ask the compiler for a
+// register budget that lets five of them share an SM.
+template <typename T, bool kAdd, int kVec, int kUnits, bool kWarpRow, int kCap>
+__global__ void __launch_bounds__(kCap, kCap <= 256 ? 5 : 2) norm_quant_kernel(const NormParams p) {
   extern __shared__ float4 wsm[];          // per-thread weight slices, f32
   __shared__ float red[2][kMaxThreads / 32];
 
@@ -104,9 +106,10 @@ __global__ void __launch_bounds__(kMaxThreads) norm_quant_kernel(const NormParam
       prefetch_l2_bulk(xg + (row + row_step) * p.x_row_stride, row_bytes);
       if constexpr (kAdd) prefetch_l2_bulk(rg + (row + row_step) * p.res_row_stride, row_bytes);
     }
-    // ---- phase 1: load, (add, round, write residual), sum of squares
-    float h[kUnits * kVec][16];
-    float ssq = 0.0f;
+    // ---- phase 1: load, (add, round, write residual), sum of squares; all f32 math on register pairs
+    // what phase 2 normalises, kept as packed 16-bit pairs so that few registers live across the row reduction
+    uint32_t h[kUnits * kVec][8];
+    uint64_t ssq2 = 0;                       // {0.0f, 0.0f}
 #pragma unroll
     for (int u = 0; u < kUnits; ++u) {
 #pragma unroll
@@ -121,41 +124,33 @@ __global__ void __launch_bounds__(kMaxThreads) norm_quant_kernel(const NormParam
             U32x8 outv;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-              const float a = __fadd_rn(Pair16<T>::lo(xv.v[i]), Pair16<T>::lo(rv.v[i]));
-              const float b = __fadd_rn(Pair16<T>::hi(xv.v[i]), Pair16<T>::hi(rv.v[i]));
-              ssq = fmaf(a, a, ssq);
-              ssq = fmaf(b, b, ssq);
-              outv.v[i] = Pair16<T>::pack(a, b);
-              // the normalised value is built from the ROUNDED residual
-              h[c][2 * i] = Pair16<T>::lo(outv.v[i]);
-              h[c][2 * i + 1] = Pair16<T>::hi(outv.v[i]);
+              const uint64_t s2 = f32x2_add(pair16_to_f32x2<T>(xv.v[i]), pair16_to_f32x2<T>(rv.v[i]));
+              ssq2 = f32x2_fma(s2, s2, ssq2);
+              outv.v[i] = f32x2_to_pair16<T>(s2);
+              h[c][i] = outv.v[i];                         // the normalised value is built from the ROUNDED residual
             }
             st_32B(rptr, outv);
           } else {
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const float4 w4 = wmine[(c * 4 + q) * team];
-              const float wq[4] = {w4.x, w4.y, w4.z, w4.w};
-#pragma unroll
-              for (int j = 0; j < 2; ++j) {
-                const int i = 2 * q + j;
-                const float a = Pair16<T>::lo(xv.v[i]);
-                const float b = Pair16<T>::hi(xv.v[i]);
-                ssq = fmaf(a, a, ssq);
-                ssq = fmaf(b, b, ssq);
-                // x*w is rounded to the input type before the f32 scaling
-                const uint32_t xw = Pair16<T>::pack(__fmul_rn(a, wq[2 * j]), __fmul_rn(b, wq[2 * j + 1]));
-                h[c][2 * i] = Pair16<T>::lo(xw);
-                h[c][2 * i + 1] = Pair16<T>::hi(xw);
-              }
+              const uint64_t x0 = pair16_to_f32x2<T>(xv.v[2 * q]);
+              const uint64_t x1 = pair16_to_f32x2<T>(xv.v[2 * q + 1]);
+              ssq2 = f32x2_fma(x0, x0, ssq2);
+              ssq2 = f32x2_fma(x1, x1, ssq2);
+              // x*w is rounded to the input type before the f32 scaling
+              h[c][2 * q] = f32x2_to_pair16<T>(f32x2_mul(x0, f32x2_pack(w4.x, w4.y)));
+              h[c][2 * q + 1] = f32x2_to_pair16<T>(f32x2_mul(x1, f32x2_pack(w4.z, w4.w)));
             }
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) h[c][i] = 0.0f;
+          for (int i = 0; i < 8; ++i) h[c][i] = 0;
         }
       }
     }
+    float ssq = __fadd_rn(f32x2_lo(ssq2), f32x2_hi(ssq2));
+
     // ---- row reduction: lanes, then (CTA teams) warps through shared memory
     ssq = warp_sum(ssq);
     if constexpr (!kWarpRow) {
@@ -165,6 +160,7 @@ __global__ void __launch_bounds__(kMaxThreads) norm_quant_kernel(const NormParam
     }
     // 1/sqrt(mean + eps) with IEEE division and square root
     const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ssq, n_as_float), p.eps)));
+    const uint64_t rstd2 = f32x2_pack(rstd, rstd);
 
     // ---- phase 2: scale, quantise, store
 #pragma unroll
@@ -175,19 +171,18 @@ __global__ void __launch_bounds__(kMaxThreads) norm_quant_kernel(const NormParam
 #pragma unroll
       for (int v = 0; v < kVec; ++v) {
         const int c = u * kVec + v;
-        float val[16];
+        uint64_t val[8];
         if constexpr (kAdd) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const float4 w4 = wmine[(c * 4 + q) * team];
-            val[4 * q + 0] = __fmul_rn(__fmul_rn(h[c][4 * q + 0], rstd), w4.x);
-            val[4 * q + 1] = __fmul_rn(__fmul_rn(h[c][4 * q + 1], rstd), w4.y);
-            val[4 * q + 2] = __fmul_rn(__fmul_rn(h[c][4 * q + 2], rstd), w4.z);
-            val[4 * q + 3] = __fmul_rn(__fmul_rn(h[c][4 * q + 3], rstd), w4.w);
+            val[2 * q] = f32x2_mul(f32x2_mul(pair16_to_f32x2<T>(h[c][2 * q]), rstd2), f32x2_pack(w4.x, w4.y));
+            val[2 * q + 1] =
+                f32x2_mul(f32x2_mul(pair16_to_f32x2<T>(h[c][2 * q + 1]), rstd2), f32x2_pack(w4.z, w4.w));
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 16; ++i) val[i] = __fmul_rn(h[c][i], rstd);
+          for (int i = 0; i < 8; ++i) val[i] = f32x2_mul(pair16_to_f32x2<T>(h[c][i]), rstd2);
         }
         quantize_block16<false>(val, gs, codes[v][0], codes[v][1], sfb[v]);
         if (chunk0 + v >= nchunks) sfb[v] = 0;
@@ -251,9 +246,9 @@ int sm_count() {
   return cached;
 }
 
-template <typename T, bool kAdd, int kVec, int kUnits, bool kWarpRow>
+template <typename T, bool kAdd, int kVec, int kUnits, bool kWarpRow, int kCap>
 int launch_one(const NormParams& p, int threads, cudaStream_t stream) {
-  auto kern = norm_quant_kernel<T, kAdd, kVec, kUnits, kWarpRow>;
+  auto kern = norm_quant_kernel<T, kAdd, kVec, kUnits, kWarpRow, kCap>;
   const size_t smem = static_cast<size_t>(kUnits) * kVec * 4 * sizeof(float4) * threads;
   if (smem > 48 * 1024) {
     B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
@@ -261,6 +256,9 @@ int launch_one(const NormParams& p, int threads, cudaStream_t stream) {
   int per_sm = 0;
   B200_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, smem));
   if (per_sm < 1) return fail(kUnsupported, "norm_quant_kernel does not fit on an SM (%zu bytes of shared memory)", smem);
+  // the residual-add variant is DRAM-bound with four resident CTAs per SM already; more of them only
+  // lengthen the last wave (measured on B200: 70 us with 4, 74 us with 6 at [8192, 7168])
+  if (kAdd && !kWarpRow && per_sm > 4) per_sm = 4;
   const int64_t rows_per_cta = kWarpRow ? threads / 32 : 1;
   const int64_t want = (p.rows + rows_per_cta - 1) / rows_per_cta;
   int64_t grid = static_cast<int64_t>(sm_count()) * per_sm;
@@ -272,13 +270,15 @@ int launch_one(const NormParams& p, int threads, cudaStream_t stream) {
 template <typename T, bool kAdd>
 int dispatch(const NormParams& p, cudaStream_t stream) {
   const int nchunks = p.hidden / 16;
-  if (nchunks <= 32) return launch_one<T, kAdd, 1, 1, true>(p, 128, stream);
+  if (nchunks <= 32) return launch_one<T, kAdd, 1, 1, true, 128>(p, 128, stream);
   const int nunits = (nchunks + 1) / 2;                       // two adjacent chunks per unit
   const int units = (nunits + kMaxThreads - 1) / kMaxThreads;
   const int threads = (((nunits + units - 1) / units) + 31) / 32 * 32;
   switch (units) {
-    case 1: return launch_one<T, kAdd, 2, 1, false>(p, threads, stream);
-    case 2: return launch_one<T, kAdd, 2, 2, false>(p, threads, stream);
+    case 1:
+      return threads <= 256 ? launch_one<T, kAdd, 2, 1, false, 256>(p, threads, stream)
+                            : launch_one<T, kAdd, 2, 1, false, kMaxThreads>(p, threads, stream);
+    case 2: return launch_one<T, kAdd, 2, 2, false, kMaxThreads>(p, threads, stream);
     default: return fail(kUnsupported, "hidden=%d exceeds the supported maximum of %d", p.hidden,
                          32 * kMaxThreads * kMaxUnitsPerThread);
   }
