@@ -3,6 +3,7 @@
 // two grouped GEMMs of the fused MoE.  The device code is in gemm_kernel.cuh.
 #include <mutex>
 
+#include "gemm2cta_kernel.cuh"
 #include "gemm_kernel.cuh"
 
 namespace b200fp4 {
@@ -41,6 +42,22 @@ int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int k, in
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(kCudaError, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  return kOk;
+}
+
+// Tiled scale-factor storage viewed as rows of 256 bytes; a box of 8 rows is the 2 KB slab of one
+// 128-row tile and four 64-wide K tiles.  Rows past the end read as zero.
+int make_sf_map(CUtensorMap* map, const void* base, int64_t total_bytes) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (enc == nullptr) return fail(kCudaError, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {256, static_cast<cuuint64_t>(total_bytes / 256)};
+  cuuint64_t strides[1] = {256};
+  cuuint32_t box[2] = {256, 8};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(kCudaError, "cuTensorMapEncodeTiled (scale factors) failed with CUresult %d", static_cast<int>(r));
   return kOk;
 }
 
@@ -87,12 +104,62 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
   return check_cuda(cudaGetLastError(), "nvfp4_gemm_kernel launch");
 }
 
+// CTA-pair variant: 256 x 256 tiles on 2-CTA clusters
+template <typename OutT>
+int gemm_dense_pair(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha, int m,
+                    int n, int k, cudaStream_t stream) {
+  CUtensorMap ta, tb, tsa, tsb;
+  int rc = make_operand_map(&ta, a, m, k, 0);
+  if (rc) return rc;
+  rc = make_operand_map(&tb, b, n, k, 1);
+  if (rc) return rc;
+  const int64_t rk = (k + 63) / 64;
+  rc = make_sf_map(&tsa, sfa, static_cast<int64_t>((m + 127) / 128) * rk * 512);
+  if (rc) return rc;
+  rc = make_sf_map(&tsb, sfb, static_cast<int64_t>((n + 127) / 128) * rk * 512);
+  if (rc) return rc;
+  GemmParams p{};
+  p.m_rows = m;
+  p.n_cols = n;
+  p.k = k;
+  p.rk = static_cast<int>(rk);
+  p.num_k_tiles = (k + kBlockK - 1) / kBlockK;
+  p.num_m_blocks = (m + 255) / 256;
+  p.num_n_blocks = (n + 255) / 256;
+  rc = device_status_word(&p.status);
+  if (rc) return rc;
+  EpilogueStore<OutT> epi{static_cast<OutT*>(c), n, alpha, 0};
+  auto kern = nvfp4_gemm_pair_kernel<EpilogueStore<OutT>>;
+  static bool configured = false;
+  if (!configured) {
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kPairSmemBytes)));
+    configured = true;
+  }
+  int pairs = sm_count_of_current_device() / 2;
+  const int tiles = p.num_m_blocks * p.num_n_blocks;
+  if (pairs > tiles) pairs = tiles;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(kPairThreads, 1, 1);
+  cfg.dynamicSmemBytes = kPairSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return check_cuda(cudaLaunchKernelEx(&cfg, kern, ta, tb, tsa, tsb, p, epi), "nvfp4_gemm_pair_kernel launch");
+}
+
 // ---------------------------------------------------------------------------
 // dense GEMM: C[l][m][n] = alpha * A[l][m][k] . B[l][n][k]^T
 // ---------------------------------------------------------------------------
 template <typename OutT>
 int gemm_dense_typed(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha, int m,
                      int n, int k, int tile_n, cudaStream_t stream) {
+  if (tile_n == 512) return gemm_dense_pair<OutT>(a, b, sfa, sfb, c, alpha, m, n, k, stream);
   CUtensorMap ta, tb;
   int rc = make_operand_map(&ta, a, m, k, 0);
   if (rc) return rc;
@@ -132,7 +199,8 @@ int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, v
        reinterpret_cast<uintptr_t>(sfb) | reinterpret_cast<uintptr_t>(c)) & 15)
     return fail(kInvalidArgument, "Invalid tensor alignment: pointers must be 16-byte aligned");
   if (c_dtype < 0 || c_dtype > 2) return fail(kUnsupported, "c_dtype code %d (0 fp16, 1 bf16, 2 f32)", c_dtype);
-  if (tile_n != 0 && tile_n != 128 && tile_n != 256) return fail(kInvalidArgument, "tile_n must be 0, 128 or 256");
+  if (tile_n != 0 && tile_n != 128 && tile_n != 256 && tile_n != 512)
+    return fail(kInvalidArgument, "tile_n must be 0, 128, 256 or 512 (512 = 256 x 256 tiles on CTA pairs)");
   if (tile_n == 0) {
     // wide tiles halve the operand traffic per flop; keep narrow ones while they are needed to fill the SMs
     const int64_t tiles256 = static_cast<int64_t>((m + 127) / 128) * ((n + 255) / 256);

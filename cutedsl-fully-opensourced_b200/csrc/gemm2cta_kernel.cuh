@@ -1,0 +1,201 @@
+// NVFP4 block-scaled dense GEMM on CTA pairs (tcgen05 cta_group::2) for sm_100a.
+//
+// The single-CTA kernel (gemm_kernel.cuh) is bound by the bytes each SM pulls through its
+// L2 port: a 128 x 256 tile needs 54 KB of operands per 256-wide K step.  Here two CTAs of a
+// 2-CTA cluster share one 256 x 256 tile: each loads its own 128 rows of A, its own 128 of
+// the 256 B rows and the scale factors, 38 KB per K step for the same flops per SM, and the
+// even CTA issues 256-row MMAs that read B from both CTAs' shared memory.  Every CTA keeps
+// its 128 x 256 half of the accumulator in its own tensor memory and drains it itself.
+//
+// Per CTA: warp 0 lane 0 = TMA producer (loads credit the full-barrier of the even CTA),
+// warp 1 lane 0 of the even CTA = MMA issuer (tcgen05.commit with a CTA mask releases the
+// stage in both CTAs), warps 2-9 = epilogue.  No TMA multicast is used anywhere: every tile
+// is fetched by the CTA that needs it.  All waits are bounded as in the single-CTA kernel.
+#pragma once
+
+#include "gemm_kernel.cuh"
+
+namespace b200fp4 {
+
+constexpr int kPairStages = 5;
+constexpr uint32_t kPairStageBytes = 16384 + 16384 + 2048 + 4096;    // A, B half, SFA, SFB (both halves)
+constexpr uint32_t kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 256;
+constexpr int kPairThreads = 64 + 8 * 32;
+
+template <typename Epilogue>
+__global__ void __launch_bounds__(kPairThreads, 1)
+nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                       const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
+                       const GemmParams p, const Epilogue epi) {
+  constexpr int kStages = kPairStages;
+  constexpr int kBlockN = 256;
+  constexpr uint32_t kSfaCol = 256;
+  constexpr uint32_t kSfbCol = kSfaCol + 16;
+  constexpr uint32_t kIdesc = ptx::idesc_mxf4nvf4_m256(kBlockN);
+  constexpr uint32_t kABytes = 16384, kBBytes = 16384, kSfaBytes = 2048;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  const uint32_t bar_base = smem_base + kStages * kPairStageBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  const uint32_t acc_full_bar = bar_base + 8u * (2 * kStages);
+  const uint32_t acc_empty_bar = bar_base + 8u * (2 * kStages + 1);
+  uint8_t* tail_gen = smem_gen + kStages * kPairStageBytes + 8 * (2 * kStages + 2);
+  volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(tail_gen);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tail_gen + 4);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();          // 0 = even CTA (issues the MMAs), 1 = its peer
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);                    // the even CTA's expect_tx arrival (+ both CTAs' bytes)
+      ptx::mbar_init(empty_bar(s), 1);                   // one commit per use, delivered to both CTAs
+    }
+    ptx::mbar_init(acc_full_bar, 1);
+    ptx::mbar_init(acc_empty_bar, 2 * 8 * 32);           // the epilogue threads of both CTAs
+    *abort_flag = 0;
+    ptx::fence_mbar_init();
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+    ptx::prefetch_tensormap(&tmap_sfa);
+    ptx::prefetch_tensormap(&tmap_sfb);
+  }
+  if (warp == 0) {
+    __syncwarp();
+    ptx::tmem2_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_ptr_smem)), kTmemCols);
+    ptx::tmem2_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::cluster_sync();                                   // both CTAs' barriers exist before anyone signals them
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_ptr_smem;
+
+  const int num_tiles = p.num_m_blocks * p.num_n_blocks; // num_m_blocks counts 256-row blocks here
+
+  if (warp == 0) {
+    // =============================== TMA producer (both CTAs) ===============================
+    if (lane == 0) {
+      PipeState st;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int m2 = tile % p.num_m_blocks;
+        const int n_blk = tile / p.num_m_blocks;
+        const int m_tile = 2 * m2 + static_cast<int>(rank);          // 128-row tile of A owned by this CTA
+        for (int kt = 0; kt < p.num_k_tiles; ++kt) {
+          if (!wait_bounded(empty_bar(st.stage), st.phase ^ 1u, abort_flag)) {
+            atomicOr(p.status, kStatusTimeoutProducer);
+            ok = false;
+            break;
+          }
+          const uint32_t sa = smem_base + st.stage * kPairStageBytes;
+          const uint32_t sb = sa + kABytes;
+          const uint32_t ssfa = sb + kBBytes;
+          const uint32_t ssfb = ssfa + kSfaBytes;
+          const uint32_t bar = full_bar(st.stage) & ptx::kPeerBitMask;   // always the even CTA's barrier
+          if (rank == 0) ptx::mbar_expect_tx(full_bar(st.stage), 2 * kPairStageBytes);
+          ptx::tma2_load_2d(sa, &tmap_a, kt * 128, m_tile * 128, bar);
+          ptx::tma2_load_3d(sb, &tmap_b, kt * 128, n_blk * 256 + static_cast<int>(rank) * 128, 0, bar);
+          ptx::tma2_load_2d(ssfa, &tmap_sfa, 0, (m_tile * p.rk + 4 * kt) * 2, bar);
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+            ptx::tma2_load_2d(ssfb + i * 2048, &tmap_sfb, 0, ((n_blk * 2 + i) * p.rk + 4 * kt) * 2, bar);
+          st.advance(kStages);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // =============================== MMA issuer (even CTA only) ===============================
+    if (lane == 0 && rank == 0) {
+      PipeState st;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        if (!wait_bounded(acc_empty_bar, acc_phase ^ 1u, abort_flag)) {
+          atomicOr(p.status, kStatusTimeoutMma);
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        for (int kt = 0; kt < p.num_k_tiles; ++kt) {
+          if (!wait_bounded(full_bar(st.stage), st.phase, abort_flag)) {
+            atomicOr(p.status, kStatusTimeoutMma);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t sa = smem_base + st.stage * kPairStageBytes;
+          const uint32_t sb = sa + kABytes;
+          const uint32_t ssfa = sb + kBBytes;
+          const uint32_t ssfb = ssfa + kSfaBytes;
+          const int kblocks = min(4, (p.k - kt * kBlockK + 63) >> 6);
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+            if (kb < kblocks) {
+              ptx::tmem2_cp_sf(tmem_base + kSfaCol + 4 * kb, ptx::smem_desc_sf(ssfa + 512 * kb));
+#pragma unroll
+              for (int i = 0; i < 2; ++i)
+                ptx::tmem2_cp_sf(tmem_base + kSfbCol + 8 * kb + 4 * i, ptx::smem_desc_sf(ssfb + 2048 * i + 512 * kb));
+            }
+          }
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+            if (kb < kblocks) {
+              ptx::mma2_mxf4nvf4(tmem_base, ptx::smem_desc_sw128(sa + 32 * kb), ptx::smem_desc_sw128(sb + 32 * kb),
+                                 kIdesc, tmem_base + kSfaCol + 4 * kb, tmem_base + kSfbCol + 8 * kb,
+                                 (kt | kb) != 0 ? 1u : 0u);
+            }
+          }
+          ptx::tc2_commit_mcast(empty_bar(st.stage), 3);      // frees the stage in both CTAs
+          st.advance(kStages);
+        }
+        if (ok) ptx::tc2_commit_mcast(acc_full_bar, 3);       // accumulators of both CTAs are complete
+        acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // =============================== epilogue (both CTAs) ===============================
+    const int quarter = warp & 3;
+    const int part = (warp - 2) >> 2;
+    const int row = quarter * 32 + lane;
+    uint32_t acc_phase = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs) {
+      const int m2 = tile % p.num_m_blocks;
+      const int n_blk = tile / p.num_m_blocks;
+      if (!wait_bounded(acc_full_bar, acc_phase, abort_flag)) {
+        if (lane == 0) atomicOr(p.status, kStatusTimeoutEpilogue);
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      epi.template operator()<kBlockN>(p, 2 * m2 + static_cast<int>(rank), n_blk, 0, row, kBlockM, part, 2,
+                                       [&](int c0, uint32_t (&r)[32]) {
+                                         ptx::tmem_ld_32x32(t_acc + c0, r);
+                                         ptx::tmem_ld_wait();
+                                       });
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive_cluster(acc_empty_bar & ptx::kPeerBitMask);
+      acc_phase ^= 1u;
+    }
+  }
+
+  // ---- teardown: nobody leaves while the peer may still signal this CTA or read its memory
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::cluster_sync();
+  if (warp == 0) {
+    if (*abort_flag) {
+      for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    __syncwarp();
+    ptx::tc_fence_after_sync();
+    ptx::tmem2_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace b200fp4
