@@ -115,6 +115,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     if (lane == 0 && rank == 0) {
       PipeState st;
       uint32_t acc_phase = 0;
+      uint32_t sf_set = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         if (!wait_bounded(acc_empty_bar, acc_phase ^ 1u, abort_flag)) {
@@ -134,21 +135,18 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           const uint32_t ssfa = sb + kBBytes;
           const uint32_t ssfb = ssfa + kSfaBytes;
           const int kblocks = min(4, (p.k - kt * kBlockK + 63) >> 6);
+          const uint32_t sfa_t = tmem_base + kSfaCol + (sf_set ? 48u : 0u);   // two alternating sets of slab columns
+          const uint32_t sfb_t = tmem_base + kSfbCol + (sf_set ? 48u : 0u);
+          sf_set ^= 1u;
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb) {
             if (kb < kblocks) {
-              ptx::tmem2_cp_sf(tmem_base + kSfaCol + 4 * kb, ptx::smem_desc_sf(ssfa + 512 * kb));
+              ptx::tmem2_cp_sf(sfa_t + 4 * kb, ptx::smem_desc_sf(ssfa + 512 * kb));
 #pragma unroll
               for (int i = 0; i < 2; ++i)
-                ptx::tmem2_cp_sf(tmem_base + kSfbCol + 8 * kb + 4 * i, ptx::smem_desc_sf(ssfb + 2048 * i + 512 * kb));
-            }
-          }
-#pragma unroll
-          for (int kb = 0; kb < 4; ++kb) {
-            if (kb < kblocks) {
+                ptx::tmem2_cp_sf(sfb_t + 8 * kb + 4 * i, ptx::smem_desc_sf(ssfb + 2048 * i + 512 * kb));
               ptx::mma2_mxf4nvf4(tmem_base, ptx::smem_desc_sw128(sa + 32 * kb), ptx::smem_desc_sw128(sb + 32 * kb),
-                                 kIdesc, tmem_base + kSfaCol + 4 * kb, tmem_base + kSfbCol + 8 * kb,
-                                 (kt | kb) != 0 ? 1u : 0u);
+                                 kIdesc, sfa_t + 4 * kb, sfb_t + 8 * kb, (kt | kb) != 0 ? 1u : 0u);
             }
           }
           ptx::tc2_commit_mcast(empty_bar(st.stage), 3);      // frees the stage in both CTAs

@@ -224,8 +224,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   constexpr int kBPieces = kBlockN / 128;
   constexpr uint32_t kSfaCol = kAccStages * kBlockN;            // TMEM columns: accumulators first
   constexpr uint32_t kSfbCol = kSfaCol + 16;
+  constexpr uint32_t kSfSetCols = 16 + 4 * (kBlockN / 32);      // columns of one set of scale slabs (SFA + SFB)
   constexpr uint32_t kIdesc = ptx::idesc_mxf4nvf4(kBlockN);
-  static_assert(kSfbCol + 4 * (kBlockN / 32) <= kTmemCols, "TMEM budget");
+  static_assert(kSfaCol + 2 * kSfSetCols <= kTmemCols, "TMEM budget");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -300,6 +301,11 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const int k_sf_tiles = min(4, p.rk - 4 * kt);                 // 512-byte scale tiles in this stage
           const uint32_t sf_bytes = static_cast<uint32_t>(k_sf_tiles) * 512u;
           const uint32_t bar = full_bar(st.stage);
+#ifdef B200_EXPERIMENT_NO_LOADS
+          ptx::mbar_arrive(bar);
+          st.advance(kStages);
+          continue;
+#endif
           ptx::mbar_expect_tx(bar, L.a_bytes + L.b_bytes + sf_bytes * (1 + kBPieces));
           ptx::tma_load_2d(sa, &tmap_a, kt * 128, m_blk * kBlockM, bar);
 #pragma unroll
@@ -319,6 +325,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     if (lane == 0) {
       PipeState st;
       PipeState acc;
+      uint32_t sf_set = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         if (!wait_bounded(acc_empty_bar(acc.stage), acc.phase ^ 1u, abort_flag)) {
@@ -339,23 +346,27 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const uint32_t ssfa = sb + L.b_bytes;
           const uint32_t ssfb = ssfa + L.sfa_bytes;
           const int kblocks = min(4, (p.k - kt * kBlockK + 63) >> 6);   // 64-wide MMA steps with data
+          // scale slabs -> TMEM right before the MMA that reads them; the slab columns alternate between two
+          // sets from one K tile to the next, so these copies never wait for the previous tile's MMAs
+          const uint32_t sfa_t = tmem_base + kSfaCol + (sf_set ? kSfSetCols : 0u);
+          const uint32_t sfb_t = tmem_base + kSfbCol + (sf_set ? kSfSetCols : 0u);
+          sf_set ^= 1u;
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb) {
             if (kb < kblocks) {
-              ptx::tmem_cp_sf(tmem_base + kSfaCol + 4 * kb, ptx::smem_desc_sf(ssfa + 512 * kb));
+#ifdef B200_EXPERIMENT_SKIP_SF
+              if (kt == 0) {
+#else
+              {
+#endif
+                ptx::tmem_cp_sf(sfa_t + 4 * kb, ptx::smem_desc_sf(ssfa + 512 * kb));
 #pragma unroll
-              for (int i = 0; i < kBPieces; ++i) {
-                ptx::tmem_cp_sf(tmem_base + kSfbCol + (kBlockN / 32) * kb + 4 * i,
-                                ptx::smem_desc_sf(ssfb + 2048 * i + 512 * kb));
+                for (int i = 0; i < kBPieces; ++i) {
+                  ptx::tmem_cp_sf(sfb_t + (kBlockN / 32) * kb + 4 * i, ptx::smem_desc_sf(ssfb + 2048 * i + 512 * kb));
+                }
               }
-            }
-          }
-#pragma unroll
-          for (int kb = 0; kb < 4; ++kb) {
-            if (kb < kblocks) {
               ptx::mma_mxf4nvf4(d_tmem, ptx::smem_desc_sw128(sa + 32 * kb), ptx::smem_desc_sw128(sb + 32 * kb), kIdesc,
-                                tmem_base + kSfaCol + 4 * kb, tmem_base + kSfbCol + (kBlockN / 32) * kb,
-                                (kt | kb) != 0 ? 1u : 0u);
+                                sfa_t + 4 * kb, sfb_t + (kBlockN / 32) * kb, (kt | kb) != 0 ? 1u : 0u);
             }
           }
           ptx::tc_commit(empty_bar(st.stage));        // stage reusable once these MMAs have read it
