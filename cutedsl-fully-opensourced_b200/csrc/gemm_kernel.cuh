@@ -13,9 +13,11 @@
 //           128 bytes, 128-byte swizzle), one per 128-row piece of B, and plain
 //           bulk copies of the scale-factor slabs (2 KB per 128 rows: four
 //           512-byte 128x4 tiles are contiguous in the tiled layout)
-//   warp 1  MMA issuer: tcgen05.cp moves the scale slabs into tensor memory,
-//           then four tcgen05.mma kind::mxf4nvf4 (K = 64 each) accumulate into
-//           a TMEM accumulator; tcgen05.commit releases the stage
+//   warp 1  MMA issuer: four tcgen05.mma kind::mxf4nvf4 (K = 64 each) per stage accumulate
+//           into a TMEM accumulator; tcgen05.commit releases the stage
+//   last 4 warps  scale-slab movers: shared memory -> registers -> tensor memory (tcgen05.st),
+//           one set of slab columns per stage.  tcgen05.cp would do the same copy, but it runs
+//           in the MMA pipe: twelve copies per stage cost a third of the kernel's time there
 //   warps 2..  epilogue (4 warps for 128-wide tiles, 8 for 256-wide ones): tcgen05.ld the
 //           accumulator (each warp its own 32-lane quarter; with 8 warps two warps share a
 //           quarter and split the columns), apply the epilogue functor, store
@@ -34,7 +36,9 @@ constexpr int kBlockK = 256;                 // e2m1 elements per stage = 128 by
 // two single-thread roles (TMA, MMA) + the epilogue warps: four for 128-wide tiles (the second
 // accumulator hides the epilogue), eight for 256-wide tiles (one accumulator: drain it twice as fast)
 __host__ __device__ constexpr int epilogue_warps(int block_n) { return block_n == 256 ? 8 : 4; }
-__host__ __device__ constexpr int gemm_threads(int block_n) { return 64 + 32 * epilogue_warps(block_n); }
+// ... + four warps (one per 32-lane quarter of tensor memory) that move the scale slabs of every K
+// tile from shared memory into tensor memory
+__host__ __device__ constexpr int gemm_threads(int block_n) { return 64 + 32 * epilogue_warps(block_n) + 128; }
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitLimitCycles = 4000000000LL;   // ~2 s at 2 GHz
 
@@ -223,10 +227,10 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   constexpr int kAccStages = kBlockN == 256 ? 1 : 2;
   constexpr int kBPieces = kBlockN / 128;
   constexpr uint32_t kSfaCol = kAccStages * kBlockN;            // TMEM columns: accumulators first
-  constexpr uint32_t kSfbCol = kSfaCol + 16;
   constexpr uint32_t kSfSetCols = 16 + 4 * (kBlockN / 32);      // columns of one set of scale slabs (SFA + SFB)
   constexpr uint32_t kIdesc = ptx::idesc_mxf4nvf4(kBlockN);
-  static_assert(kSfaCol + 2 * kSfSetCols <= kTmemCols, "TMEM budget");
+  constexpr int kFirstSfWarp = 2 + epilogue_warps(kBlockN);
+  static_assert(kSfaCol + kStages * kSfSetCols <= kTmemCols, "TMEM budget: one set of slab columns per stage");
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -237,7 +241,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto acc_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
   auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 2 + s); };
-  uint8_t* tail_gen = smem_gen + kStages * L.stage_bytes + 8 * (2 * kStages + 4);
+  auto sf_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 4 + s); };
+  uint8_t* tail_gen = smem_gen + kStages * L.stage_bytes + 8 * (3 * kStages + 4);
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(tail_gen);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail_gen + 4);
 
@@ -248,6 +253,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(full_bar(s), 1);
       ptx::mbar_init(empty_bar(s), 1);
+      ptx::mbar_init(sf_full_bar(s), 4);                 // one arrival per slab-mover warp
     }
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(acc_full_bar(s), 1);
@@ -325,7 +331,6 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     if (lane == 0) {
       PipeState st;
       PipeState acc;
-      uint32_t sf_set = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         if (!wait_bounded(acc_empty_bar(acc.stage), acc.phase ^ 1u, abort_flag)) {
@@ -343,28 +348,19 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           ptx::tc_fence_after_sync();
           const uint32_t sa = smem_base + st.stage * L.stage_bytes;
           const uint32_t sb = sa + L.a_bytes;
-          const uint32_t ssfa = sb + L.b_bytes;
-          const uint32_t ssfb = ssfa + L.sfa_bytes;
           const int kblocks = min(4, (p.k - kt * kBlockK + 63) >> 6);   // 64-wide MMA steps with data
-          // scale slabs -> TMEM right before the MMA that reads them; the slab columns alternate between two
-          // sets from one K tile to the next, so these copies never wait for the previous tile's MMAs
-          const uint32_t sfa_t = tmem_base + kSfaCol + (sf_set ? kSfSetCols : 0u);
-          const uint32_t sfb_t = tmem_base + kSfbCol + (sf_set ? kSfSetCols : 0u);
-          sf_set ^= 1u;
+          // the slab movers have put this stage's scale factors into its set of TMEM columns
+          if (!wait_bounded(sf_full_bar(st.stage), st.phase, abort_flag)) {
+            atomicOr(p.status, kStatusTimeoutMma);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t sfa_t = tmem_base + kSfaCol + st.stage * kSfSetCols;
+          const uint32_t sfb_t = sfa_t + 16;
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb) {
             if (kb < kblocks) {
-#ifdef B200_EXPERIMENT_SKIP_SF
-              if (kt == 0) {
-#else
-              {
-#endif
-                ptx::tmem_cp_sf(sfa_t + 4 * kb, ptx::smem_desc_sf(ssfa + 512 * kb));
-#pragma unroll
-                for (int i = 0; i < kBPieces; ++i) {
-                  ptx::tmem_cp_sf(sfb_t + (kBlockN / 32) * kb + 4 * i, ptx::smem_desc_sf(ssfb + 2048 * i + 512 * kb));
-                }
-              }
               ptx::mma_mxf4nvf4(d_tmem, ptx::smem_desc_sw128(sa + 32 * kb), ptx::smem_desc_sw128(sb + 32 * kb), kIdesc,
                                 sfa_t + 4 * kb, sfb_t + (kBlockN / 32) * kb, (kt | kb) != 0 ? 1u : 0u);
             }
@@ -374,6 +370,59 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
         if (ok) ptx::tc_commit(acc_full_bar(acc.stage));
         acc.advance(kAccStages);
+      }
+    }
+  } else if (warp >= kFirstSfWarp) {
+    // =============================== scale-slab movers ===============================
+    // Lane l of every quarter needs the 16 bytes of slab row l per 64-wide K block: 4 columns of SFA
+    // (row groups 0-3 of the 128-row tile) and 4 per 128 rows of B.  All four warps write the same
+    // values, each into its own 32 lanes: the MMA expects the slab replicated in every quarter.
+    const int quarter = warp & 3;
+    PipeState st;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int kt = 0; kt < p.num_k_tiles; ++kt) {
+        if (!wait_bounded(full_bar(st.stage), st.phase, abort_flag)) {
+          if (lane == 0) atomicOr(p.status, kStatusTimeoutMma);
+          ok = false;
+          break;
+        }
+        const uint8_t* slab = smem_gen + st.stage * L.stage_bytes + L.a_bytes + L.b_bytes + lane * 16;
+        const uint32_t t_sf = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kSfaCol + st.stage * kSfSetCols;
+        uint32_t ra[16];
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+          const uint4 v = *reinterpret_cast<const uint4*>(slab + 512 * kb);
+          ra[4 * kb] = v.x, ra[4 * kb + 1] = v.y, ra[4 * kb + 2] = v.z, ra[4 * kb + 3] = v.w;
+        }
+        ptx::tmem_st_32x16(t_sf, ra);
+        const uint8_t* slab_b = slab + L.sfa_bytes;
+        if constexpr (kBPieces == 2) {
+          uint32_t rb[32];
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const uint4 v = *reinterpret_cast<const uint4*>(slab_b + 2048 * i + 512 * kb);
+              rb[8 * kb + 4 * i] = v.x, rb[8 * kb + 4 * i + 1] = v.y, rb[8 * kb + 4 * i + 2] = v.z,
+                          rb[8 * kb + 4 * i + 3] = v.w;
+            }
+          }
+          ptx::tmem_st_32x32(t_sf + 16, rb);
+        } else {
+          uint32_t rb[16];
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+            const uint4 v = *reinterpret_cast<const uint4*>(slab_b + 512 * kb);
+            rb[4 * kb] = v.x, rb[4 * kb + 1] = v.y, rb[4 * kb + 2] = v.z, rb[4 * kb + 3] = v.w;
+          }
+          ptx::tmem_st_32x16(t_sf + 16, rb);
+        }
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(sf_full_bar(st.stage));
+        st.advance(kStages);
       }
     }
   } else {
