@@ -9,7 +9,8 @@
 //
 // Per CTA: warp 0 lane 0 = TMA producer (loads credit the full-barrier of the even CTA),
 // warp 1 lane 0 of the even CTA = MMA issuer (tcgen05.commit with a CTA mask releases the
-// stage in both CTAs), warps 2-9 = epilogue.  No TMA multicast is used anywhere: every tile
+// stage in both CTAs), warps 2-9 = epilogue, warps 10-13 = scale-slab movers (shared memory ->
+// tensor memory with tcgen05.st, each CTA for itself; they report to the even CTA).  No TMA multicast is used anywhere: every tile
 // is fetched by the CTA that needs it.  All waits are bounded as in the single-CTA kernel.
 #pragma once
 
@@ -20,7 +21,7 @@ namespace b200fp4 {
 constexpr int kPairStages = 5;
 constexpr uint32_t kPairStageBytes = 16384 + 16384 + 2048 + 4096;    // A, B half, SFA, SFB (both halves)
 constexpr uint32_t kPairSmemBytes = kPairStages * kPairStageBytes + 1024 + 256;
-constexpr int kPairThreads = 64 + 8 * 32;
+constexpr int kPairThreads = 64 + 8 * 32 + 128;     // TMA, MMA, 8 epilogue warps, 4 scale-slab movers
 
 template <typename Epilogue>
 __global__ void __launch_bounds__(kPairThreads, 1)
@@ -30,7 +31,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
   constexpr int kStages = kPairStages;
   constexpr int kBlockN = 256;
   constexpr uint32_t kSfaCol = 256;
-  constexpr uint32_t kSfbCol = kSfaCol + 16;
+  constexpr uint32_t kSfSetCols = 48;                    // 16 columns of SFA + 32 of SFB per stage
+  static_assert(kSfaCol + kPairStages * kSfSetCols <= kTmemCols, "TMEM budget");
   constexpr uint32_t kIdesc = ptx::idesc_mxf4nvf4_m256(kBlockN);
   constexpr uint32_t kABytes = 16384, kBBytes = 16384, kSfaBytes = 2048;
 
@@ -42,7 +44,9 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   const uint32_t acc_full_bar = bar_base + 8u * (2 * kStages);
   const uint32_t acc_empty_bar = bar_base + 8u * (2 * kStages + 1);
-  uint8_t* tail_gen = smem_gen + kStages * kPairStageBytes + 8 * (2 * kStages + 2);
+  auto sf_loaded_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 2 + s); };   // own slabs have landed
+  auto sf_full_bar = [&](int s) { return bar_base + 8u * (3 * kStages + 2 + s); };     // both CTAs' slabs are in TMEM
+  uint8_t* tail_gen = smem_gen + kStages * kPairStageBytes + 8 * (4 * kStages + 2);
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(tail_gen);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail_gen + 4);
 
@@ -56,6 +60,8 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(full_bar(s), 1);                    // the even CTA's expect_tx arrival (+ both CTAs' bytes)
       ptx::mbar_init(empty_bar(s), 1);                   // one commit per use, delivered to both CTAs
+      ptx::mbar_init(sf_loaded_bar(s), 1);
+      ptx::mbar_init(sf_full_bar(s), 8);                 // four mover warps in each CTA
     }
     ptx::mbar_init(acc_full_bar, 1);
     ptx::mbar_init(acc_empty_bar, 2 * 8 * 32);           // the epilogue threads of both CTAs
@@ -99,13 +105,16 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           const uint32_t ssfa = sb + kBBytes;
           const uint32_t ssfb = ssfa + kSfaBytes;
           const uint32_t bar = full_bar(st.stage) & ptx::kPeerBitMask;   // always the even CTA's barrier
-          if (rank == 0) ptx::mbar_expect_tx(full_bar(st.stage), 2 * kPairStageBytes);
+          if (rank == 0) ptx::mbar_expect_tx(full_bar(st.stage), 2 * (kABytes + kBBytes));
           ptx::tma2_load_2d(sa, &tmap_a, kt * 128, m_tile * 128, bar);
           ptx::tma2_load_3d(sb, &tmap_b, kt * 128, n_blk * 256 + static_cast<int>(rank) * 128, 0, bar);
-          ptx::tma2_load_2d(ssfa, &tmap_sfa, 0, (m_tile * p.rk + 4 * kt) * 2, bar);
+          // the scale slabs are consumed by this CTA's own mover warps: they report to a local barrier
+          const uint32_t sbar = sf_loaded_bar(st.stage);
+          ptx::mbar_expect_tx(sbar, kSfaBytes + 4096);
+          ptx::tma_load_2d(ssfa, &tmap_sfa, 0, (m_tile * p.rk + 4 * kt) * 2, sbar);
 #pragma unroll
           for (int i = 0; i < 2; ++i)
-            ptx::tma2_load_2d(ssfb + i * 2048, &tmap_sfb, 0, ((n_blk * 2 + i) * p.rk + 4 * kt) * 2, bar);
+            ptx::tma_load_2d(ssfb + i * 2048, &tmap_sfb, 0, ((n_blk * 2 + i) * p.rk + 4 * kt) * 2, sbar);
           st.advance(kStages);
         }
       }
@@ -115,7 +124,6 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     if (lane == 0 && rank == 0) {
       PipeState st;
       uint32_t acc_phase = 0;
-      uint32_t sf_set = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         if (!wait_bounded(acc_empty_bar, acc_phase ^ 1u, abort_flag)) {
@@ -132,19 +140,18 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           ptx::tc_fence_after_sync();
           const uint32_t sa = smem_base + st.stage * kPairStageBytes;
           const uint32_t sb = sa + kABytes;
-          const uint32_t ssfa = sb + kBBytes;
-          const uint32_t ssfb = ssfa + kSfaBytes;
           const int kblocks = min(4, (p.k - kt * kBlockK + 63) >> 6);
-          const uint32_t sfa_t = tmem_base + kSfaCol + (sf_set ? 48u : 0u);   // two alternating sets of slab columns
-          const uint32_t sfb_t = tmem_base + kSfbCol + (sf_set ? 48u : 0u);
-          sf_set ^= 1u;
+          if (!wait_bounded(sf_full_bar(st.stage), st.phase, abort_flag)) {
+            atomicOr(p.status, kStatusTimeoutMma);
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t sfa_t = tmem_base + kSfaCol + st.stage * kSfSetCols;
+          const uint32_t sfb_t = sfa_t + 16;
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb) {
             if (kb < kblocks) {
-              ptx::tmem2_cp_sf(sfa_t + 4 * kb, ptx::smem_desc_sf(ssfa + 512 * kb));
-#pragma unroll
-              for (int i = 0; i < 2; ++i)
-                ptx::tmem2_cp_sf(sfb_t + 8 * kb + 4 * i, ptx::smem_desc_sf(ssfb + 2048 * i + 512 * kb));
               ptx::mma2_mxf4nvf4(tmem_base, ptx::smem_desc_sw128(sa + 32 * kb), ptx::smem_desc_sw128(sb + 32 * kb),
                                  kIdesc, sfa_t + 4 * kb, sfb_t + 8 * kb, (kt | kb) != 0 ? 1u : 0u);
             }
@@ -154,6 +161,45 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         }
         if (ok) ptx::tc2_commit_mcast(acc_full_bar, 3);       // accumulators of both CTAs are complete
         acc_phase ^= 1u;
+      }
+    }
+  } else if (warp >= 10) {
+    // =============================== scale-slab movers (both CTAs) ===============================
+    const int quarter = warp & 3;
+    PipeState st;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      for (int kt = 0; kt < p.num_k_tiles; ++kt) {
+        if (!wait_bounded(sf_loaded_bar(st.stage), st.phase, abort_flag)) {
+          if (lane == 0) atomicOr(p.status, kStatusTimeoutMma);
+          ok = false;
+          break;
+        }
+        const uint8_t* slab = smem_gen + st.stage * kPairStageBytes + kABytes + kBBytes + lane * 16;
+        const uint32_t t_sf = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kSfaCol + st.stage * kSfSetCols;
+        uint32_t ra[16];
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+          const uint4 v = *reinterpret_cast<const uint4*>(slab + 512 * kb);
+          ra[4 * kb] = v.x, ra[4 * kb + 1] = v.y, ra[4 * kb + 2] = v.z, ra[4 * kb + 3] = v.w;
+        }
+        ptx::tmem_st_32x16(t_sf, ra);
+        uint32_t rb[32];
+#pragma unroll
+        for (int kb = 0; kb < 4; ++kb) {
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            const uint4 v = *reinterpret_cast<const uint4*>(slab + kSfaBytes + 2048 * i + 512 * kb);
+            rb[8 * kb + 4 * i] = v.x, rb[8 * kb + 4 * i + 1] = v.y, rb[8 * kb + 4 * i + 2] = v.z,
+                        rb[8 * kb + 4 * i + 3] = v.w;
+          }
+        }
+        ptx::tmem_st_32x32(t_sf + 16, rb);
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(sf_full_bar(st.stage) & ptx::kPeerBitMask);
+        st.advance(kStages);
       }
     }
   } else {

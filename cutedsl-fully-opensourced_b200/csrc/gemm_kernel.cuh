@@ -307,11 +307,6 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const int k_sf_tiles = min(4, p.rk - 4 * kt);                 // 512-byte scale tiles in this stage
           const uint32_t sf_bytes = static_cast<uint32_t>(k_sf_tiles) * 512u;
           const uint32_t bar = full_bar(st.stage);
-#ifdef B200_EXPERIMENT_NO_LOADS
-          ptx::mbar_arrive(bar);
-          st.advance(kStages);
-          continue;
-#endif
           ptx::mbar_expect_tx(bar, L.a_bytes + L.b_bytes + sf_bytes * (1 + kBPieces));
           ptx::tma_load_2d(sa, &tmap_a, kt * 128, m_blk * kBlockM, bar);
 #pragma unroll
