@@ -281,7 +281,9 @@ int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, cons
   p.m_block_rows = m_block_rows;
   p.status = status;
   EpilogueStore<float> epi{partial, hidden, w2_alpha, 1};
-  if (hidden % 256 == 0) {
+  // Short reductions (few K tiles) spend more time draining the accumulator than filling it; the
+  // 128-wide tile has two accumulators, so its epilogue overlaps the next tile's MMAs.
+  if (hidden % 256 == 0 && p.num_k_tiles > 4) {
     p.num_n_blocks = hidden / 256;
     return launch_gemm<256, false>(ta, tb, p, epi, max_m_blocks * p.num_n_blocks, stream);
   }

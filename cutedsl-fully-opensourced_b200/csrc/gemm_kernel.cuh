@@ -140,23 +140,40 @@ struct EpilogueStore {
       uint32_t r[32];
       load(c0, r);                 // warp-collective: every lane takes part, stores are predicated
       if (!row_ok) continue;
+      if constexpr (sizeof(OutT) == 4) {
+        // 32-byte stores: every lane writes another row, so a store instruction costs one L1 wavefront per
+        // lane whatever its width -- wider stores halve the wavefronts per tile
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {          // 8 columns per group
-        if (c0 + 8 * g < cols_left) {        // n_cols is a multiple of 8
-          float f[8];
+        for (int g = 0; g < 4; ++g) {          // 8 columns = 32 bytes per store; n_cols is a multiple of 8
+          if (c0 + 8 * g < cols_left) {
+            U32x8 v;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[8 * g + i]) * scale;
-          if constexpr (sizeof(OutT) == 4) {
-            float4* dst = reinterpret_cast<float4*>(crow + c0 + 8 * g);
-            dst[0] = make_float4(f[0], f[1], f[2], f[3]);
-            dst[1] = make_float4(f[4], f[5], f[6], f[7]);
+            for (int i = 0; i < 8; ++i) v.v[i] = __float_as_uint(__uint_as_float(r[8 * g + i]) * scale);
+            if ((reinterpret_cast<uintptr_t>(crow) & 31) == 0) {
+              st_32B(crow + c0 + 8 * g, v);
+            } else {
+              uint4* dst = reinterpret_cast<uint4*>(crow + c0 + 8 * g);
+              dst[0] = make_uint4(v.v[0], v.v[1], v.v[2], v.v[3]);
+              dst[1] = make_uint4(v.v[4], v.v[5], v.v[6], v.v[7]);
+            }
+          }
+        }
+      } else {
+        const bool wide = (reinterpret_cast<uintptr_t>(crow) & 31) == 0 && (ldc & 15) == 0;
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {          // 16 columns = 32 bytes per store when rows are 32-byte aligned
+          U32x8 v;
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            v.v[i] = Pair16<OutT>::pack(__uint_as_float(r[16 * g + 2 * i]) * scale,
+                                        __uint_as_float(r[16 * g + 2 * i + 1]) * scale);
+          if (wide && c0 + 16 * g + 8 < cols_left) {
+            st_32B(crow + c0 + 16 * g, v);
           } else {
-            uint4 v;
-            v.x = Pair16<OutT>::pack(f[0], f[1]);
-            v.y = Pair16<OutT>::pack(f[2], f[3]);
-            v.z = Pair16<OutT>::pack(f[4], f[5]);
-            v.w = Pair16<OutT>::pack(f[6], f[7]);
-            *reinterpret_cast<uint4*>(crow + c0 + 8 * g) = v;
+            if (c0 + 16 * g < cols_left)
+              *reinterpret_cast<uint4*>(crow + c0 + 16 * g) = make_uint4(v.v[0], v.v[1], v.v[2], v.v[3]);
+            if (c0 + 16 * g + 8 < cols_left)
+              *reinterpret_cast<uint4*>(crow + c0 + 16 * g + 8) = make_uint4(v.v[4], v.v[5], v.v[6], v.v[7]);
           }
         }
       }
