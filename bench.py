@@ -373,7 +373,10 @@ class MoeWorkload:
         self.alg_bytes = min(active, self.local_experts) * self.expert_bytes + 2 * t * h * 2
         self.ep = None
         if self.world > 1:
-            self.ep = pkg.parallel.ExpertParallelMoE(e, k)
+            if os.environ.get("B200FP4_EP", "peer") == "collective":
+                self.ep = pkg.parallel.ExpertParallelMoE(e, k)
+            else:
+                self.ep = pkg.parallel.PeerExpertParallelMoE(e, k, t, h, i)
             self.weights = {"w1": self.w1, "w1_sf": self.w1_sf, "w2": self.w2, "w2_sf": self.w2_sf,
                             "w1_alpha": self.a1, "w2_alpha": self.a2, "fc2_input_scale": self.fc2_scale}
         # L2 flush buffer: the weights of the prefill case (340 MB) exceed L2 by themselves; the decode
@@ -395,8 +398,11 @@ class MoeWorkload:
     def config(self, world):
         return {"workload": self.name, "tokens": self.tokens, "hidden": self.hidden, "experts": self.experts,
                 "top_k": self.top_k, "intermediate": self.inter, "active_experts": self.active_experts,
-                "parallelism": (f"experts x{world}, tokens x{world}; NCCL all-gather of tokens + routing, "
-                                "reduce-scatter of f32 partial outputs") if world > 1 else "single GPU",
+                "parallelism": (f"experts x{world}, tokens x{world}; " + (
+                    "NCCL all-gather of tokens + routing, reduce-scatter of f32 partial outputs"
+                    if os.environ.get("B200FP4_EP", "peer") == "collective" else
+                    "dispatch / combine as NVLink peer loads inside the kernels, two barriers per step")
+                ) if world > 1 else "single GPU",
                 "l2": "weights streamed per step exceed the 126 MB L2" if self.flush is None else
                       "a 256 MB buffer is rewritten (untimed) between steps to flush the 126 MB L2"}
 

@@ -28,6 +28,10 @@ SIGNATURES = {
     "b200fp4_moe_workspace_bytes": (_sz, [_i64, _i32, _i32, _i32, _i32]),
     "b200fp4_moe_fused": (_i32, [_vp] * 11 + [_i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
     "b200fp4_moe_fused_noalloc": (_i32, [_vp] * 11 + [_i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "b200fp4_moe_ep_buffer_bytes": (_sz, [_i64, _i32, _i32, _i32, _i32, _i32]),
+    "b200fp4_moe_ep_stage": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "b200fp4_moe_ep_compute": (_i32, [_vp, _i32, _i32] + [_vp] * 7 + [_i64, _i32, _i32, _i32, _i32, _vp]),
+    "b200fp4_moe_ep_combine": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp]),
     "b200fp4_device_status": (_i32, [_vp, C.POINTER(C.c_int), _i32]),
 }
 

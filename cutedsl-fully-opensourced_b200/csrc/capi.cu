@@ -42,6 +42,17 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
               int accumulate, int out_dtype, void* workspace, size_t workspace_bytes, int* status,
               cudaStream_t stream);
 
+size_t moe_ep_buffer_bytes(int64_t tokens_local, int hidden, int inter, int experts_local, int top_k, int world);
+int moe_ep_stage(const void* x, const int* ids, void* own_buffer, int64_t tokens_local, int hidden, int inter,
+                 int experts_local, int top_k, int world, cudaStream_t stream);
+int moe_ep_compute(const void* const* peer_buffers, int rank, int world, const void* w1, const void* w1_sf,
+                   const void* w2, const void* w2_sf, const float* w1_alpha, const float* w2_alpha,
+                   const float* fc2_input_scale, int64_t tokens_local, int hidden, int inter, int experts_local,
+                   int top_k, int* status, cudaStream_t stream);
+int moe_ep_combine(const void* const* peer_buffers, int rank, int world, const int* ids, const float* weights,
+                   void* out, int64_t tokens_local, int hidden, int inter, int experts_local, int top_k,
+                   cudaStream_t stream);
+
 }  // namespace b200fp4
 
 using namespace b200fp4;
@@ -96,6 +107,37 @@ int b200fp4_moe_fused(const void* x, const void* w1, const void* w1_sf, const vo
   return moe_fused(x, w1, w1_sf, w2, w2_sf, token_selected_experts, token_final_scales, w1_alpha, w2_alpha,
                    fc2_input_scale, out, tokens, hidden, intermediate, local_experts, top_k, local_expert_offset,
                    accumulate, out_dtype, workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+size_t b200fp4_moe_ep_buffer_bytes(int64_t tokens_local, int hidden, int intermediate, int local_experts, int top_k,
+                                   int world) {
+  if (tokens_local < 0 || hidden <= 0 || intermediate <= 0 || local_experts <= 0 || top_k <= 0 || world <= 0) return 0;
+  return moe_ep_buffer_bytes(tokens_local, hidden, intermediate, local_experts, top_k, world);
+}
+
+int b200fp4_moe_ep_stage(const void* x, const int* token_selected_experts, void* own_buffer, int64_t tokens_local,
+                         int hidden, int intermediate, int local_experts, int top_k, int world, void* stream) {
+  return moe_ep_stage(x, token_selected_experts, own_buffer, tokens_local, hidden, intermediate, local_experts, top_k,
+                      world, static_cast<cudaStream_t>(stream));
+}
+
+int b200fp4_moe_ep_compute(const void* const* peer_buffers, int rank, int world, const void* w1, const void* w1_sf,
+                           const void* w2, const void* w2_sf, const float* w1_alpha, const float* w2_alpha,
+                           const float* fc2_input_scale, int64_t tokens_local, int hidden, int intermediate,
+                           int local_experts, int top_k, void* stream) {
+  int* status = nullptr;
+  int rc = device_status_word(&status);
+  if (rc) return rc;
+  return moe_ep_compute(peer_buffers, rank, world, w1, w1_sf, w2, w2_sf, w1_alpha, w2_alpha, fc2_input_scale,
+                        tokens_local, hidden, intermediate, local_experts, top_k, status,
+                        static_cast<cudaStream_t>(stream));
+}
+
+int b200fp4_moe_ep_combine(const void* const* peer_buffers, int rank, int world, const int* token_selected_experts,
+                           const float* token_final_scales, void* out, int64_t tokens_local, int hidden,
+                           int intermediate, int local_experts, int top_k, void* stream) {
+  return moe_ep_combine(peer_buffers, rank, world, token_selected_experts, token_final_scales, out, tokens_local,
+                        hidden, intermediate, local_experts, top_k, static_cast<cudaStream_t>(stream));
 }
 
 int b200fp4_device_status(void* stream, int* status_out, int clear) {

@@ -364,3 +364,291 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
 }
 
 }  // namespace b200fp4
+
+// =============================================================================================
+// Expert parallelism over peer memory.
+//
+// Every rank owns a slice of the token batch and a contiguous range of experts.  All ranks hold a
+// buffer of identical layout that the others can address (peer pointers: NVLink loads, no
+// multimem, no TMA from peer memory).  One step is three launches per rank, separated by two
+// cross-rank barriers that the caller provides:
+//
+//   stage      quantise the local tokens ONCE to NVFP4 and publish codes, scale bytes and expert
+//              ids in the own buffer                                                   -- barrier --
+//   compute    count the slots of ALL ranks' tokens that hit local experts, lay the rows out,
+//              pull the quantised rows over NVLink straight into the expert-major GEMM operand
+//              (4.5 bits per element cross the wire instead of 16), FC1, FC2; publish the
+//              per-slot output rows and the slot -> row table                          -- barrier --
+//   combine    every rank sums, for its own tokens, the k output rows from wherever they were
+//              computed (peer loads fused into the weighted sum), one bf16 rounding
+//
+// The reference has no multi-GPU path; this is the dispatch / combine all-to-all of an
+// expert-parallel MoE written as kernels over peer memory.
+// =============================================================================================
+namespace b200fp4 {
+namespace {
+
+constexpr int kMaxPeers = 16;
+struct PeerPtrs {
+  uint8_t* p[kMaxPeers];
+};
+
+struct EpLayout {
+  // published for peers
+  size_t tok_codes, tok_sf, tok_ids, slot_row, partial;
+  // private to the rank
+  size_t counts, cursor, offsets, num_m_blocks, m_block_expert, m_block_rows, xq_sf, xq, act_sf, act;
+  size_t xq_sf_bytes, total;
+  int max_m_blocks;
+};
+
+EpLayout ep_layout(int64_t tokens_local, int hidden, int inter, int experts_local, int top_k, int world) {
+  EpLayout L{};
+  const int64_t slots = tokens_local * world * top_k;
+  const int64_t blocks = std::min<int64_t>(experts_local, slots) + slots / 128;
+  L.max_m_blocks = static_cast<int>(blocks);
+  const int64_t rows = blocks * 128;
+  size_t off = 0;
+  auto take = [&](size_t bytes) {
+    const size_t r = off;
+    off = align_up(off + bytes, 256);
+    return r;
+  };
+  L.tok_codes = take(static_cast<size_t>(tokens_local) * (hidden / 2));
+  L.tok_sf = take(static_cast<size_t>(tokens_local) * (hidden / 16));
+  L.tok_ids = take(sizeof(int) * tokens_local * top_k);
+  L.slot_row = take(sizeof(int) * slots);
+  L.partial = take(static_cast<size_t>(rows) * hidden * sizeof(float));
+  L.counts = take(sizeof(int) * experts_local);
+  L.cursor = take(sizeof(int) * experts_local);
+  L.offsets = take(sizeof(int) * (experts_local + 1));
+  L.num_m_blocks = take(sizeof(int));
+  L.m_block_expert = take(sizeof(int) * blocks);
+  L.m_block_rows = take(sizeof(int) * blocks);
+  L.xq_sf_bytes = static_cast<size_t>(blocks) * ((hidden + 63) / 64) * 512;
+  L.xq_sf = take(L.xq_sf_bytes);
+  L.xq = take(static_cast<size_t>(rows) * (hidden / 2));
+  L.act_sf = take(static_cast<size_t>(blocks) * ((inter + 63) / 64) * 512);
+  L.act = take(static_cast<size_t>(rows) * (inter / 2));
+  L.total = off;
+  return L;
+}
+
+// one CTA per local token: NVFP4 codes + row-major scale bytes + the token's expert ids
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads)
+ep_stage_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids, uint8_t* tok_codes, uint8_t* tok_sf,
+                int* tok_ids, int hidden, int top_k) {
+  const int token = blockIdx.x;
+  if (threadIdx.x < top_k)
+    tok_ids[static_cast<int64_t>(token) * top_k + threadIdx.x] = ids[static_cast<int64_t>(token) * top_k + threadIdx.x];
+  const int nchunks = hidden >> 4;
+  for (int chunk = threadIdx.x; chunk < nchunks; chunk += kThreads) {
+    const U32x8 raw = ld_stream_32B(x + static_cast<int64_t>(token) * hidden + chunk * 16);
+    uint64_t v2[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v2[i] = pair16_to_f32x2<__nv_bfloat16>(raw.v[i]);
+    uint32_t lo, hi, sfb;
+    quantize_block16<true>(v2, 1.0f, lo, hi, sfb);
+    *reinterpret_cast<uint2*>(tok_codes + static_cast<int64_t>(token) * (hidden >> 1) + chunk * 8) = make_uint2(lo, hi);
+    tok_sf[static_cast<int64_t>(token) * nchunks + chunk] = static_cast<uint8_t>(sfb);
+  }
+}
+
+__global__ void ep_count_kernel(PeerPtrs peers, size_t tok_ids_off, int slots_per_rank, int world, int expert_lo,
+                                int experts, int* counts) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= slots_per_rank * world) return;
+  const int src = i / slots_per_rank;
+  const int* ids = reinterpret_cast<const int*>(peers.p[src] + tok_ids_off);
+  const int e = ids[i - src * slots_per_rank] - expert_lo;
+  if (e >= 0 && e < experts) atomicAdd(counts + e, 1);
+}
+
+// one CTA per token of ANY rank: rows for its local slots, then the quantised row is pulled from its owner
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads)
+ep_gather_kernel(PeerPtrs peers, EpLayout L, MoeHeader h, uint8_t* xq, uint8_t* xq_sf, int tokens_local, int hidden,
+                 int top_k, int expert_lo, int experts, int max_rows) {
+  __shared__ int s_rows[64];
+  __shared__ int s_any;
+  const int g = blockIdx.x;                        // global token index
+  const int src = g / tokens_local;
+  const int t = g - src * tokens_local;
+  const uint8_t* peer = peers.p[src];
+  if (threadIdx.x == 0) s_any = 0;
+  __syncthreads();
+  if (threadIdx.x < top_k) {
+    const int e = reinterpret_cast<const int*>(peer + L.tok_ids)[static_cast<int64_t>(t) * top_k + threadIdx.x] - expert_lo;
+    int row = -1;
+    if (e >= 0 && e < experts) {
+      row = h.offsets[e] + atomicAdd(h.cursor + e, 1);
+      if (row >= max_rows) row = -1;
+    }
+    s_rows[threadIdx.x] = row;
+    h.slot_row[static_cast<int64_t>(g) * top_k + threadIdx.x] = row;
+    if (row >= 0) s_any = 1;
+  }
+  __syncthreads();
+  if (!s_any) return;
+  const int nchunks = hidden >> 4;
+  const int rk = (nchunks + 3) >> 2;
+  const uint8_t* codes = peer + L.tok_codes + static_cast<int64_t>(t) * (hidden >> 1);
+  const uint8_t* sf = peer + L.tok_sf + static_cast<int64_t>(t) * nchunks;
+  for (int chunk = threadIdx.x; chunk < nchunks; chunk += kThreads) {
+    const uint2 c = *reinterpret_cast<const uint2*>(codes + chunk * 8);
+    const uint8_t s = sf[chunk];
+    for (int j = 0; j < top_k; ++j) {
+      const int row = s_rows[j];
+      if (row < 0) continue;
+      *reinterpret_cast<uint2*>(xq + static_cast<int64_t>(row) * (hidden >> 1) + chunk * 8) = c;
+      xq_sf[sf_swizzled_offset(row, chunk, rk)] = s;
+    }
+  }
+}
+
+// one CTA per local token: the k output rows come from the ranks that own the experts
+__global__ void ep_combine_kernel(PeerPtrs peers, EpLayout L, const int* __restrict__ ids,
+                                  const float* __restrict__ weights, __nv_bfloat16* __restrict__ out, int rank,
+                                  int tokens_local, int hidden, int top_k, int experts_local) {
+  __shared__ const float* s_src[64];
+  __shared__ float s_w[64];
+  const int t = blockIdx.x;
+  const int64_t g = static_cast<int64_t>(rank) * tokens_local + t;
+  if (threadIdx.x < top_k) {
+    const int e = ids[static_cast<int64_t>(t) * top_k + threadIdx.x];
+    const int owner = e / experts_local;
+    const uint8_t* peer = peers.p[owner];
+    const int row = reinterpret_cast<const int*>(peer + L.slot_row)[g * top_k + threadIdx.x];
+    s_src[threadIdx.x] =
+        row < 0 ? nullptr : reinterpret_cast<const float*>(peer + L.partial) + static_cast<int64_t>(row) * hidden;
+    s_w[threadIdx.x] = weights[static_cast<int64_t>(t) * top_k + threadIdx.x];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < top_k; ++j) {
+      const float* src = s_src[j];
+      if (src == nullptr) continue;
+      const float4 pv = *reinterpret_cast<const float4*>(src + c);
+      const float w = s_w[j];
+      acc.x = __fadd_rn(acc.x, __fmul_rn(w, pv.x));
+      acc.y = __fadd_rn(acc.y, __fmul_rn(w, pv.y));
+      acc.z = __fadd_rn(acc.z, __fmul_rn(w, pv.z));
+      acc.w = __fadd_rn(acc.w, __fmul_rn(w, pv.w));
+    }
+    uint2 packed;
+    packed.x = Pair16<__nv_bfloat16>::pack(acc.x, acc.y);
+    packed.y = Pair16<__nv_bfloat16>::pack(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(out + static_cast<int64_t>(t) * hidden + c) = packed;
+  }
+}
+
+int ep_check(int64_t tokens_local, int hidden, int inter, int experts_local, int top_k, int world, int rank) {
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
+    return fail(kInvalidArgument, "world=%d rank=%d (at most %d ranks)", world, rank, kMaxPeers);
+  if (tokens_local < 0 || top_k < 1 || top_k > 64 || experts_local < 1 || experts_local > 1024)
+    return fail(kInvalidArgument, "tokens=%lld top_k=%d experts=%d", static_cast<long long>(tokens_local), top_k,
+                experts_local);
+  if (hidden % 64 != 0 || hidden < 64) return fail(kUnsupported, "hidden=%d must be a multiple of 64", hidden);
+  if (inter % 128 != 0 || inter < 128) return fail(kUnsupported, "intermediate=%d must be a multiple of 128", inter);
+  if (tokens_local * world * top_k > (1ll << 30)) return fail(kUnsupported, "too many routed rows");
+  return kOk;
+}
+
+int ep_peers(const void* const* peer_buffers, int world, PeerPtrs* out) {
+  if (peer_buffers == nullptr) return fail(kInvalidArgument, "peer_buffers is null");
+  for (int i = 0; i < kMaxPeers; ++i) out->p[i] = nullptr;
+  for (int i = 0; i < world; ++i) {
+    if (peer_buffers[i] == nullptr || (reinterpret_cast<uintptr_t>(peer_buffers[i]) & 255))
+      return fail(kInvalidArgument, "peer buffer %d is null or not 256-byte aligned", i);
+    out->p[i] = static_cast<uint8_t*>(const_cast<void*>(peer_buffers[i]));
+  }
+  return kOk;
+}
+
+}  // namespace
+
+size_t moe_ep_buffer_bytes(int64_t tokens_local, int hidden, int inter, int experts_local, int top_k, int world) {
+  return ep_layout(tokens_local, hidden, inter, experts_local, top_k, world).total;
+}
+
+int moe_ep_stage(const void* x, const int* ids, void* own_buffer, int64_t tokens_local, int hidden, int inter,
+                 int experts_local, int top_k, int world, cudaStream_t stream) {
+  int rc = ep_check(tokens_local, hidden, inter, experts_local, top_k, world, 0);
+  if (rc) return rc;
+  if (x == nullptr || ids == nullptr || own_buffer == nullptr) return fail(kInvalidArgument, "null pointer argument");
+  if ((reinterpret_cast<uintptr_t>(x) & 31) || (reinterpret_cast<uintptr_t>(own_buffer) & 255))
+    return fail(kInvalidArgument, "x must be 32-byte and the buffer 256-byte aligned");
+  if (tokens_local == 0) return kOk;
+  const EpLayout L = ep_layout(tokens_local, hidden, inter, experts_local, top_k, world);
+  uint8_t* b = static_cast<uint8_t*>(own_buffer);
+  ep_stage_kernel<128><<<static_cast<unsigned>(tokens_local), 128, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), ids, b + L.tok_codes, b + L.tok_sf, reinterpret_cast<int*>(b + L.tok_ids),
+      hidden, top_k);
+  return check_cuda(cudaGetLastError(), "ep_stage_kernel launch");
+}
+
+int moe_ep_compute(const void* const* peer_buffers, int rank, int world, const void* w1, const void* w1_sf,
+                   const void* w2, const void* w2_sf, const float* w1_alpha, const float* w2_alpha,
+                   const float* fc2_input_scale, int64_t tokens_local, int hidden, int inter, int experts_local,
+                   int top_k, int* status, cudaStream_t stream) {
+  int rc = ep_check(tokens_local, hidden, inter, experts_local, top_k, world, rank);
+  if (rc) return rc;
+  if (w1 == nullptr || w1_sf == nullptr || w2 == nullptr || w2_sf == nullptr || status == nullptr)
+    return fail(kInvalidArgument, "null pointer argument");
+  PeerPtrs peers;
+  rc = ep_peers(peer_buffers, world, &peers);
+  if (rc) return rc;
+  if (tokens_local == 0) return kOk;
+  const EpLayout L = ep_layout(tokens_local, hidden, inter, experts_local, top_k, world);
+  uint8_t* b = peers.p[rank];
+  MoeHeader h{};
+  h.counts = reinterpret_cast<int*>(b + L.counts);
+  h.cursor = reinterpret_cast<int*>(b + L.cursor);
+  h.offsets = reinterpret_cast<int*>(b + L.offsets);
+  h.num_m_blocks = reinterpret_cast<int*>(b + L.num_m_blocks);
+  h.m_block_expert = reinterpret_cast<int*>(b + L.m_block_expert);
+  h.m_block_rows = reinterpret_cast<int*>(b + L.m_block_rows);
+  h.slot_row = reinterpret_cast<int*>(b + L.slot_row);
+  const int expert_lo = rank * experts_local;
+  const int slots_per_rank = static_cast<int>(tokens_local * top_k);
+  const int total_slots = slots_per_rank * world;
+  const int max_rows = L.max_m_blocks * 128;
+  B200_CUDA(cudaMemsetAsync(h.counts, 0, sizeof(int) * experts_local, stream));
+  B200_CUDA(cudaMemsetAsync(b + L.xq_sf, 0, L.xq_sf_bytes, stream));
+  ep_count_kernel<<<(total_slots + 255) / 256, 256, 0, stream>>>(peers, L.tok_ids, slots_per_rank, world, expert_lo,
+                                                                experts_local, h.counts);
+  moe_scan_kernel<<<1, 1024, 0, stream>>>(h, experts_local, L.max_m_blocks);
+  ep_gather_kernel<128><<<static_cast<unsigned>(tokens_local * world), 128, 0, stream>>>(
+      peers, L, h, b + L.xq, b + L.xq_sf, static_cast<int>(tokens_local), hidden, top_k, expert_lo, experts_local,
+      max_rows);
+  B200_CUDA(cudaGetLastError());
+  rc = gemm_moe_fc1(b + L.xq, b + L.xq_sf, w1, w1_sf, b + L.act, b + L.act_sf, w1_alpha, fc2_input_scale,
+                    h.num_m_blocks, h.m_block_expert, h.m_block_rows, L.max_m_blocks, hidden, inter, experts_local,
+                    status, stream);
+  if (rc) return rc;
+  return gemm_moe_fc2(b + L.act, b + L.act_sf, w2, w2_sf, reinterpret_cast<float*>(b + L.partial), w2_alpha,
+                      h.num_m_blocks, h.m_block_expert, h.m_block_rows, L.max_m_blocks, hidden, inter, experts_local,
+                      status, stream);
+}
+
+int moe_ep_combine(const void* const* peer_buffers, int rank, int world, const int* ids, const float* weights,
+                   void* out, int64_t tokens_local, int hidden, int inter, int experts_local, int top_k,
+                   cudaStream_t stream) {
+  int rc = ep_check(tokens_local, hidden, inter, experts_local, top_k, world, rank);
+  if (rc) return rc;
+  if (ids == nullptr || weights == nullptr || out == nullptr) return fail(kInvalidArgument, "null pointer argument");
+  PeerPtrs peers;
+  rc = ep_peers(peer_buffers, world, &peers);
+  if (rc) return rc;
+  if (tokens_local == 0) return kOk;
+  const EpLayout L = ep_layout(tokens_local, hidden, inter, experts_local, top_k, world);
+  const int threads = hidden / 4 >= 256 ? 256 : 128;
+  ep_combine_kernel<<<static_cast<unsigned>(tokens_local), threads, 0, stream>>>(
+      peers, L, ids, weights, static_cast<__nv_bfloat16*>(out), rank, static_cast<int>(tokens_local), hidden, top_k,
+      experts_local);
+  return check_cuda(cudaGetLastError(), "ep_combine_kernel launch");
+}
+
+}  // namespace b200fp4

@@ -10,6 +10,11 @@
   top_k >= world size nearly every token visits every rank, so this moves the same bytes as a dispatch /
   combine all-to-all while letting NVSwitch do the reduction.
 
+  ``PeerExpertParallelMoE`` is the same partition with the exchange inside the kernels: every rank publishes its
+  quantised tokens in a buffer that the others address directly (NVLink peer loads over torch symmetric memory),
+  expert owners pull the rows they need, and the combine kernel reads the output rows from wherever they were
+  computed.  Two stream-ordered cross-rank barriers per step replace the collectives.
+
 The reference itself is single-GPU (it has no collective anywhere); this layer is new.
 """
 from __future__ import annotations
@@ -103,4 +108,72 @@ class ExpertParallelMoE:
         if out is None:
             out = torch.empty(t, h, dtype=torch.bfloat16, device=x.device)
         out.copy_(res)
+        return out
+
+
+class PeerExpertParallelMoE:
+    """Expert-parallel fused MoE whose dispatch and combine are peer-memory loads inside the kernels.
+
+    Per step and rank: ``b200fp4_moe_ep_stage`` (quantise own tokens, publish), barrier,
+    ``b200fp4_moe_ep_compute`` (gather rows of local experts from all ranks, FC1, FC2), barrier,
+    ``b200fp4_moe_ep_combine`` (weighted sum of rows read from their owners).  The exchange buffer comes from
+    ``torch.distributed._symmetric_memory``; the barriers are its signal-pad barrier on the current stream.
+    Shapes are fixed at construction: every rank passes ``tokens_local`` tokens per call.
+    """
+
+    def __init__(self, num_experts: int, top_k: int, tokens_local: int, hidden: int, intermediate: int,
+                 group: Optional[dist.ProcessGroup] = None, device: Optional[torch.device] = None):
+        import ctypes
+
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _lib
+        self._lib = _lib
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.num_experts, self.top_k = num_experts, top_k
+        self.tokens_local, self.hidden, self.inter = tokens_local, hidden, intermediate
+        self.expert_lo, self.local_experts = shard_experts(num_experts, self.world, self.rank)
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        nbytes = int(_lib.lib.b200fp4_moe_ep_buffer_bytes(tokens_local, hidden, intermediate, self.local_experts, top_k,
+                                                          self.world))
+        if nbytes == 0:
+            raise ValueError("bad expert-parallel MoE shape")
+        self.buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+        self.handle = symm_mem.rendezvous(self.buffer, self.group)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self._peer_array = (ctypes.c_void_p * self.world)(*ptrs)
+        self._own_ptr = ptrs[self.rank]
+        self.handle.barrier()
+
+    def forward(self, x: torch.Tensor, ids: torch.Tensor, scales: torch.Tensor, weights: dict,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        lib, chk = self._lib.lib, self._lib.check
+        t, h = x.shape
+        if (t, h) != (self.tokens_local, self.hidden) or x.dtype != torch.bfloat16 or not x.is_contiguous():
+            raise ValueError(f"x must be contiguous bfloat16 [{self.tokens_local}, {self.hidden}]")
+        if ids.dtype != torch.int32 or tuple(ids.shape) != (t, self.top_k) or not ids.is_contiguous():
+            raise ValueError("ids must be contiguous int32 [tokens, top_k]")
+        if scales.dtype != torch.float32 or tuple(scales.shape) != (t, self.top_k) or not scales.is_contiguous():
+            raise ValueError("scales must be contiguous float32 [tokens, top_k]")
+        from .moe import _sf_storage
+        w1 = weights["w1"].view(torch.uint8)
+        w2 = weights["w2"].view(torch.uint8)
+        s1 = _sf_storage(weights["w1_sf"], self.local_experts, 2 * self.inter, h, "w1_sf")
+        s2 = _sf_storage(weights["w2_sf"], self.local_experts, h, self.inter, "w2_sf")
+        if out is None:
+            out = torch.empty(t, h, dtype=torch.bfloat16, device=x.device)
+        stream = self._lib.current_stream_ptr(x.device)
+        args = (t, h, self.inter, self.local_experts, self.top_k)
+        with torch.cuda.device(x.device):
+            chk(lib.b200fp4_moe_ep_stage(x.data_ptr(), ids.data_ptr(), self._own_ptr, *args, self.world, stream))
+            self.handle.barrier()
+            chk(lib.b200fp4_moe_ep_compute(
+                self._peer_array, self.rank, self.world, w1.data_ptr(), s1.data_ptr(), w2.data_ptr(), s2.data_ptr(),
+                self._lib.ptr(weights.get("w1_alpha")), self._lib.ptr(weights.get("w2_alpha")),
+                self._lib.ptr(weights.get("fc2_input_scale")), *args, stream))
+            self.handle.barrier()
+            chk(lib.b200fp4_moe_ep_combine(self._peer_array, self.rank, self.world, ids.data_ptr(), scales.data_ptr(),
+                                           out.data_ptr(), *args, stream))
         return out

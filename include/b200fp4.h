@@ -116,6 +116,30 @@ int b200fp4_moe_fused_noalloc(const void* x, const void* w1, const void* w1_sf, 
                               int64_t tokens, int hidden, int intermediate, int local_experts, int top_k,
                               int local_expert_offset, int accumulate, int* status_word, void* stream);
 
+/* Expert-parallel MoE over peer memory: one process per GPU, every rank owns tokens_local tokens and
+ * local_experts consecutive experts (rank r: experts r*local_experts ...), and every rank holds a
+ * buffer of b200fp4_moe_ep_buffer_bytes(...) bytes that all ranks can address (peer_buffers[i] is
+ * rank i's buffer as seen from the calling process, e.g. CUDA IPC or symmetric memory; 256-byte
+ * aligned).  One step = stage, <cross-rank barrier>, compute, <cross-rank barrier>, combine, all
+ * stream-ordered; the barriers are the caller's (any stream-ordered barrier across the ranks).
+ *   stage    quantise the rank's tokens once to NVFP4 and publish them with their expert ids;
+ *   compute  pull the rows routed to local experts from their owners, FC1 / SwiGLU / FC2;
+ *   combine  out[t] = bf16(sum_j scale[t,j] * row_j), rows read from the ranks that computed them.
+ * Arguments as b200fp4_moe_fused (ids are global).  The reference is single-GPU and has no
+ * counterpart; these entry points are the dispatch / combine of an expert-parallel deployment of
+ * the same operator (tests/python/test_flashinfer_b12x_verbatim.py:99-116). */
+size_t b200fp4_moe_ep_buffer_bytes(int64_t tokens_local, int hidden, int intermediate, int local_experts, int top_k,
+                                   int world);
+int b200fp4_moe_ep_stage(const void* x, const int* token_selected_experts, void* own_buffer, int64_t tokens_local,
+                         int hidden, int intermediate, int local_experts, int top_k, int world, void* stream);
+int b200fp4_moe_ep_compute(const void* const* peer_buffers, int rank, int world, const void* w1, const void* w1_sf,
+                           const void* w2, const void* w2_sf, const float* w1_alpha, const float* w2_alpha,
+                           const float* fc2_input_scale, int64_t tokens_local, int hidden, int intermediate,
+                           int local_experts, int top_k, void* stream);
+int b200fp4_moe_ep_combine(const void* const* peer_buffers, int rank, int world, const int* token_selected_experts,
+                           const float* token_final_scales, void* out, int64_t tokens_local, int hidden,
+                           int intermediate, int local_experts, int top_k, void* stream);
+
 /* Kernels never trap: a device-side wait that exceeds its bound ORs a bit into a per-device
  * status word and the kernel returns.  This call synchronises the stream and copies the word
  * to *status_out (0 = healthy; 1/2/4 = GEMM producer / MMA / epilogue wait expired), clearing

@@ -38,16 +38,21 @@ def _worker(rank, world, port, result_dir):
     try:
         import cutedsl_fully_opensourced_b200 as b200
         (w1c, w1s, w2c, w2s), x, ids, wts, experts, top_k = _problem()
-        ep = b200.parallel.ExpertParallelMoE(experts, top_k)
-        sl = slice(ep.expert_lo, ep.expert_lo + ep.local_experts)
         dev = torch.device("cuda", rank)
         t = x.shape[0] // world
         mine = slice(rank * t, (rank + 1) * t)
-        for _ in range(2):          # twice: buffers are reused across steps
-            out = ep.forward(x[mine].to(dev), ids[mine].to(dev), wts[mine].to(dev), _dev_weights(w1c, w1s, w2c, w2s, sl, dev))
-        torch.cuda.synchronize()
-        assert b200._lib.device_status() == 0
-        torch.save(out.cpu(), os.path.join(result_dir, f"out{rank}.pt"))
+        for kind in ("collective", "peer"):
+            if kind == "collective":
+                ep = b200.parallel.ExpertParallelMoE(experts, top_k)
+            else:
+                ep = b200.parallel.PeerExpertParallelMoE(experts, top_k, t, x.shape[1], w2c.shape[2])
+            sl = slice(ep.expert_lo, ep.expert_lo + ep.local_experts)
+            w = _dev_weights(w1c, w1s, w2c, w2s, sl, dev)
+            for _ in range(3):          # several steps: buffers are reused
+                out = ep.forward(x[mine].to(dev), ids[mine].to(dev), wts[mine].to(dev), w)
+            torch.cuda.synchronize()
+            assert b200._lib.device_status() == 0
+            torch.save(out.cpu(), os.path.join(result_dir, f"out_{kind}{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
@@ -62,9 +67,14 @@ def test_expert_parallel_two_gpus_matches_single_gpu(b200, tmp_path):
     w = _dev_weights(w1c, w1s, w2c, w2s, slice(0, experts), "cuda")
     single = b200.b12x_fused_moe(x.cuda(), w["w1"], w["w1_sf"], w["w2"], w["w2_sf"], ids.cuda(), wts.cuda(), experts,
                                  top_k, w1_alpha=w["w1_alpha"]).cpu()
-    got = torch.cat([torch.load(os.path.join(tmp_path, f"out{r}.pt")) for r in range(world)])
-    # same per-slot partial sums; only the f32 summation order across ranks differs from slot order
-    err = torch.linalg.vector_norm(got.float() - single.float()) / torch.linalg.vector_norm(single.float())
-    assert err <= 2e-3, float(err)
     ref = O.moe_ref(x, w1c, w1s, w2c, w2s, ids, wts, np.full(experts, 0.02, np.float32))
-    assert torch.linalg.vector_norm(got.float() - ref.float()) / torch.linalg.vector_norm(ref.float()) <= 1e-2
+    for kind in ("collective", "peer"):
+        got = torch.cat([torch.load(os.path.join(tmp_path, f"out_{kind}{r}.pt")) for r in range(world)])
+        if kind == "peer":
+            # same rows, same slot order, same single rounding as on one GPU
+            assert torch.equal(got, single), "peer-memory expert parallelism differs from the single-GPU result"
+        else:
+            # same per-slot rows; only the f32 summation order across ranks differs from slot order
+            err = torch.linalg.vector_norm(got.float() - single.float()) / torch.linalg.vector_norm(single.float())
+            assert err <= 2e-3, float(err)
+        assert torch.linalg.vector_norm(got.float() - ref.float()) / torch.linalg.vector_norm(ref.float()) <= 1e-2
