@@ -544,7 +544,8 @@ def main():
         wl.restore()
         wl.step()
     step_fn = wl.step
-    if args.cuda_graph and args.workload.startswith("moe_") and world == 1:
+    if args.cuda_graph and args.workload.startswith("moe_") and (
+            world == 1 or os.environ.get("B200FP4_EP", "peer") != "collective"):
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
