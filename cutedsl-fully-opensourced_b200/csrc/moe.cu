@@ -377,10 +377,12 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
 //              ids in the own buffer                                                   -- barrier --
 //   compute    count the slots of ALL ranks' tokens that hit local experts, lay the rows out,
 //              pull the quantised rows over NVLink straight into the expert-major GEMM operand
-//              (4.5 bits per element cross the wire instead of 16), FC1, FC2; publish the
-//              per-slot output rows and the slot -> row table                          -- barrier --
-//   combine    every rank sums, for its own tokens, the k output rows from wherever they were
-//              computed (peer loads fused into the weighted sum), one bf16 rounding
+//              (4.5 bits per element cross the wire instead of 16), FC1, FC2, then send every
+//              output row home: whole 8 KB rows written into the buffer of the rank that owns the
+//              token (coalesced peer stores; row-strided 32-byte stores from inside the GEMM
+//              epilogue were measured 2x slower end to end)                            -- barrier --
+//   combine    every rank sums the k rows that arrived for each of its tokens (local memory),
+//              one bf16 rounding
 //
 // The reference has no multi-GPU path; this is the dispatch / combine all-to-all of an
 // expert-parallel MoE written as kernels over peer memory.
@@ -394,10 +396,10 @@ struct PeerPtrs {
 };
 
 struct EpLayout {
-  // published for peers
-  size_t tok_codes, tok_sf, tok_ids, slot_row, partial;
+  // published for peers: the rank's quantised tokens, and the landing zone of its tokens' output rows
+  size_t tok_codes, tok_sf, tok_ids, recv;
   // private to the rank
-  size_t counts, cursor, offsets, num_m_blocks, m_block_expert, m_block_rows, xq_sf, xq, act_sf, act;
+  size_t partial, row_dst, counts, cursor, offsets, num_m_blocks, m_block_expert, m_block_rows, xq_sf, xq, act_sf, act;
   size_t xq_sf_bytes, total;
   int max_m_blocks;
 };
@@ -417,8 +419,9 @@ EpLayout ep_layout(int64_t tokens_local, int hidden, int inter, int experts_loca
   L.tok_codes = take(static_cast<size_t>(tokens_local) * (hidden / 2));
   L.tok_sf = take(static_cast<size_t>(tokens_local) * (hidden / 16));
   L.tok_ids = take(sizeof(int) * tokens_local * top_k);
-  L.slot_row = take(sizeof(int) * slots);
+  L.recv = take(static_cast<size_t>(tokens_local) * top_k * hidden * sizeof(float));
   L.partial = take(static_cast<size_t>(rows) * hidden * sizeof(float));
+  L.row_dst = take(sizeof(float*) * rows);
   L.counts = take(sizeof(int) * experts_local);
   L.cursor = take(sizeof(int) * experts_local);
   L.offsets = take(sizeof(int) * (experts_local + 1));
@@ -468,8 +471,8 @@ __global__ void ep_count_kernel(PeerPtrs peers, size_t tok_ids_off, int slots_pe
 // one CTA per token of ANY rank: rows for its local slots, then the quantised row is pulled from its owner
 template <int kThreads>
 __global__ void __launch_bounds__(kThreads)
-ep_gather_kernel(PeerPtrs peers, EpLayout L, MoeHeader h, uint8_t* xq, uint8_t* xq_sf, int tokens_local, int hidden,
-                 int top_k, int expert_lo, int experts, int max_rows) {
+ep_gather_kernel(PeerPtrs peers, EpLayout L, MoeHeader h, float** row_dst, uint8_t* xq, uint8_t* xq_sf,
+                 int tokens_local, int hidden, int top_k, int expert_lo, int experts, int max_rows) {
   __shared__ int s_rows[64];
   __shared__ int s_any;
   const int g = blockIdx.x;                        // global token index
@@ -486,8 +489,12 @@ ep_gather_kernel(PeerPtrs peers, EpLayout L, MoeHeader h, uint8_t* xq, uint8_t* 
       if (row >= max_rows) row = -1;
     }
     s_rows[threadIdx.x] = row;
-    h.slot_row[static_cast<int64_t>(g) * top_k + threadIdx.x] = row;
-    if (row >= 0) s_any = 1;
+    if (row >= 0) {
+      s_any = 1;
+      // the output row of this slot goes home: slot (t, j) of rank src
+      row_dst[row] = reinterpret_cast<float*>(peers.p[src] + L.recv) +
+                     (static_cast<int64_t>(t) * top_k + threadIdx.x) * hidden;
+    }
   }
   __syncthreads();
   if (!s_any) return;
@@ -507,30 +514,31 @@ ep_gather_kernel(PeerPtrs peers, EpLayout L, MoeHeader h, uint8_t* xq, uint8_t* 
   }
 }
 
-// one CTA per local token: the k output rows come from the ranks that own the experts
-__global__ void ep_combine_kernel(PeerPtrs peers, EpLayout L, const int* __restrict__ ids,
-                                  const float* __restrict__ weights, __nv_bfloat16* __restrict__ out, int rank,
-                                  int tokens_local, int hidden, int top_k, int experts_local) {
-  __shared__ const float* s_src[64];
+// one CTA per row of the expert-major output: copy it to the landing zone of the token's rank
+__global__ void ep_return_rows_kernel(const float* __restrict__ partial, float* const* __restrict__ row_dst,
+                                      const int* __restrict__ num_m_blocks, const int* __restrict__ m_block_rows,
+                                      int hidden) {
+  const int blk = blockIdx.x >> 7;
+  const int r = blockIdx.x & 127;
+  if (blk >= __ldg(num_m_blocks) || r >= __ldg(m_block_rows + blk)) return;
+  const int64_t row = blockIdx.x;
+  const float4* src = reinterpret_cast<const float4*>(partial + row * hidden);
+  float4* dst = reinterpret_cast<float4*>(row_dst[row]);
+  for (int i = threadIdx.x; i < hidden / 4; i += blockDim.x) dst[i] = src[i];
+}
+
+// one CTA per local token: its k output rows have been delivered into this rank's own buffer
+__global__ void ep_combine_kernel(const float* __restrict__ recv, const float* __restrict__ weights,
+                                  __nv_bfloat16* __restrict__ out, int hidden, int top_k) {
   __shared__ float s_w[64];
   const int t = blockIdx.x;
-  const int64_t g = static_cast<int64_t>(rank) * tokens_local + t;
-  if (threadIdx.x < top_k) {
-    const int e = ids[static_cast<int64_t>(t) * top_k + threadIdx.x];
-    const int owner = e / experts_local;
-    const uint8_t* peer = peers.p[owner];
-    const int row = reinterpret_cast<const int*>(peer + L.slot_row)[g * top_k + threadIdx.x];
-    s_src[threadIdx.x] =
-        row < 0 ? nullptr : reinterpret_cast<const float*>(peer + L.partial) + static_cast<int64_t>(row) * hidden;
-    s_w[threadIdx.x] = weights[static_cast<int64_t>(t) * top_k + threadIdx.x];
-  }
+  if (threadIdx.x < top_k) s_w[threadIdx.x] = weights[static_cast<int64_t>(t) * top_k + threadIdx.x];
   __syncthreads();
+  const float* rows = recv + static_cast<int64_t>(t) * top_k * hidden;
   for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int j = 0; j < top_k; ++j) {
-      const float* src = s_src[j];
-      if (src == nullptr) continue;
-      const float4 pv = *reinterpret_cast<const float4*>(src + c);
+      const float4 pv = *reinterpret_cast<const float4*>(rows + static_cast<int64_t>(j) * hidden + c);
       const float w = s_w[j];
       acc.x = __fadd_rn(acc.x, __fmul_rn(w, pv.x));
       acc.y = __fadd_rn(acc.y, __fmul_rn(w, pv.y));
@@ -610,7 +618,8 @@ int moe_ep_compute(const void* const* peer_buffers, int rank, int world, const v
   h.num_m_blocks = reinterpret_cast<int*>(b + L.num_m_blocks);
   h.m_block_expert = reinterpret_cast<int*>(b + L.m_block_expert);
   h.m_block_rows = reinterpret_cast<int*>(b + L.m_block_rows);
-  h.slot_row = reinterpret_cast<int*>(b + L.slot_row);
+  h.slot_row = nullptr;
+  float** row_dst = reinterpret_cast<float**>(b + L.row_dst);
   const int expert_lo = rank * experts_local;
   const int slots_per_rank = static_cast<int>(tokens_local * top_k);
   const int total_slots = slots_per_rank * world;
@@ -621,16 +630,20 @@ int moe_ep_compute(const void* const* peer_buffers, int rank, int world, const v
                                                                 experts_local, h.counts);
   moe_scan_kernel<<<1, 1024, 0, stream>>>(h, experts_local, L.max_m_blocks);
   ep_gather_kernel<128><<<static_cast<unsigned>(tokens_local * world), 128, 0, stream>>>(
-      peers, L, h, b + L.xq, b + L.xq_sf, static_cast<int>(tokens_local), hidden, top_k, expert_lo, experts_local,
-      max_rows);
+      peers, L, h, row_dst, b + L.xq, b + L.xq_sf, static_cast<int>(tokens_local), hidden, top_k, expert_lo,
+      experts_local, max_rows);
   B200_CUDA(cudaGetLastError());
   rc = gemm_moe_fc1(b + L.xq, b + L.xq_sf, w1, w1_sf, b + L.act, b + L.act_sf, w1_alpha, fc2_input_scale,
                     h.num_m_blocks, h.m_block_expert, h.m_block_rows, L.max_m_blocks, hidden, inter, experts_local,
                     status, stream);
   if (rc) return rc;
-  return gemm_moe_fc2(b + L.act, b + L.act_sf, w2, w2_sf, reinterpret_cast<float*>(b + L.partial), w2_alpha,
-                      h.num_m_blocks, h.m_block_expert, h.m_block_rows, L.max_m_blocks, hidden, inter, experts_local,
-                      status, stream);
+  rc = gemm_moe_fc2(b + L.act, b + L.act_sf, w2, w2_sf, reinterpret_cast<float*>(b + L.partial), w2_alpha,
+                    h.num_m_blocks, h.m_block_expert, h.m_block_rows, L.max_m_blocks, hidden, inter, experts_local,
+                    status, stream);
+  if (rc) return rc;
+  ep_return_rows_kernel<<<static_cast<unsigned>(max_rows), 256, 0, stream>>>(
+      reinterpret_cast<const float*>(b + L.partial), row_dst, h.num_m_blocks, h.m_block_rows, hidden);
+  return check_cuda(cudaGetLastError(), "ep_return_rows_kernel launch");
 }
 
 int moe_ep_combine(const void* const* peer_buffers, int rank, int world, const int* ids, const float* weights,
@@ -645,9 +658,9 @@ int moe_ep_combine(const void* const* peer_buffers, int rank, int world, const i
   if (tokens_local == 0) return kOk;
   const EpLayout L = ep_layout(tokens_local, hidden, inter, experts_local, top_k, world);
   const int threads = hidden / 4 >= 256 ? 256 : 128;
+  (void)ids;
   ep_combine_kernel<<<static_cast<unsigned>(tokens_local), threads, 0, stream>>>(
-      peers, L, ids, weights, static_cast<__nv_bfloat16*>(out), rank, static_cast<int>(tokens_local), hidden, top_k,
-      experts_local);
+      reinterpret_cast<const float*>(peers.p[rank] + L.recv), weights, static_cast<__nv_bfloat16*>(out), hidden, top_k);
   return check_cuda(cudaGetLastError(), "ep_combine_kernel launch");
 }
 
