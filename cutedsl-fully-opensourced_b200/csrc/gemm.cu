@@ -29,13 +29,13 @@ EncodeTiledFn encode_tiled_fn() {
 }
 
 // K-major e2m1 operand viewed as bytes: [groups][rows][k/2], boxes of 128 rows x 128 bytes, 128-byte swizzle.
-int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int k, int64_t groups) {
+int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int k, int64_t groups, int box_rows = 128) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (enc == nullptr) return fail(kCudaError, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t row_bytes = static_cast<cuuint64_t>(k) / 2;
   cuuint64_t dims[3] = {row_bytes, static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(groups)};
   cuuint64_t strides[2] = {row_bytes, row_bytes * static_cast<cuuint64_t>(rows)};
-  cuuint32_t box[3] = {128, 128, 1};
+  cuuint32_t box[3] = {128, static_cast<cuuint32_t>(box_rows), 1};
   cuuint32_t elem[3] = {1, 1, 1};
   const cuuint32_t rank = groups > 0 ? 3 : 2;
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, rank, const_cast<void*>(base), dims, strides, box, elem,
@@ -163,7 +163,7 @@ int gemm_dense_typed(const void* a, const void* b, const void* sfa, const void* 
   CUtensorMap ta, tb;
   int rc = make_operand_map(&ta, a, m, k, 0);
   if (rc) return rc;
-  rc = make_operand_map(&tb, b, n, k, 1);
+  rc = make_operand_map(&tb, b, n, k, 1, tile_n == 64 ? 64 : 128);
   if (rc) return rc;
   GemmParams p{};
   p.sfa = static_cast<const uint8_t*>(sfa);
@@ -182,6 +182,10 @@ int gemm_dense_typed(const void* a, const void* b, const void* sfa, const void* 
     p.num_n_blocks = (n + 255) / 256;
     return launch_gemm<256, false>(ta, tb, p, epi, p.num_m_blocks * p.num_n_blocks, stream);
   }
+  if (tile_n == 64) {
+    p.num_n_blocks = (n + 63) / 64;
+    return launch_gemm<64, false>(ta, tb, p, epi, p.num_m_blocks * p.num_n_blocks, stream);
+  }
   p.num_n_blocks = (n + 127) / 128;
   return launch_gemm<128, false>(ta, tb, p, epi, p.num_m_blocks * p.num_n_blocks, stream);
 }
@@ -199,12 +203,15 @@ int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, v
        reinterpret_cast<uintptr_t>(sfb) | reinterpret_cast<uintptr_t>(c)) & 15)
     return fail(kInvalidArgument, "Invalid tensor alignment: pointers must be 16-byte aligned");
   if (c_dtype < 0 || c_dtype > 2) return fail(kUnsupported, "c_dtype code %d (0 fp16, 1 bf16, 2 f32)", c_dtype);
-  if (tile_n != 0 && tile_n != 128 && tile_n != 256 && tile_n != 512)
-    return fail(kInvalidArgument, "tile_n must be 0, 128, 256 or 512 (512 = 256 x 256 tiles on CTA pairs)");
+  if (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 256 && tile_n != 512)
+    return fail(kInvalidArgument, "tile_n must be 0, 64, 128, 256 or 512 (512 = 256 x 256 tiles on CTA pairs)");
   if (tile_n == 0) {
     // wide tiles halve the operand traffic per flop; keep narrow ones while they are needed to fill the SMs
-    const int64_t tiles256 = static_cast<int64_t>((m + 127) / 128) * ((n + 255) / 256);
-    tile_n = tiles256 >= sm_count_of_current_device() ? 256 : 128;
+    const int sms = sm_count_of_current_device();
+    const int64_t m_blocks = (m + 127) / 128;
+    if (m_blocks * ((n + 255) / 256) >= sms) tile_n = 256;
+    else if (m_blocks * ((n + 127) / 128) >= sms) tile_n = 128;
+    else tile_n = 64;            // few rows (weight streaming): narrow tiles put more SMs on the stream of B
   }
   const int64_t m_tiles = (m + 127) / 128, n_tiles = (n + 127) / 128, rk = (k + 63) / 64;
   const size_t c_elem = c_dtype == 2 ? 4 : 2;

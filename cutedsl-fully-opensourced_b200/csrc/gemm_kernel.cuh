@@ -79,9 +79,9 @@ __host__ __device__ constexpr SmemLayout smem_layout() {
   s.a_bytes = kBlockM * 128;
   s.b_bytes = kBlockN * 128;
   s.sfa_bytes = 2048;
-  s.sfb_bytes = (kBlockN / 128) * 2048;
+  s.sfb_bytes = (kBlockN >= 128 ? kBlockN / 128 : 1) * 2048;    // whole 128-row slabs, also for 64-wide tiles
   s.stage_bytes = s.a_bytes + s.b_bytes + s.sfa_bytes + s.sfb_bytes;
-  s.stages = kBlockN == 256 ? 4 : 6;
+  s.stages = kBlockN == 256 ? 4 : (kBlockN == 128 ? 6 : 7);
   s.total = s.stages * s.stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
   return s;
 }
@@ -242,9 +242,11 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   constexpr SmemLayout L = smem_layout<kBlockN>();
   constexpr int kStages = L.stages;
   constexpr int kAccStages = kBlockN == 256 ? 1 : 2;
-  constexpr int kBPieces = kBlockN / 128;
+  constexpr int kBPieces = kBlockN >= 128 ? kBlockN / 128 : 1;
+  constexpr int kBPieceRows = kBlockN >= 128 ? 128 : kBlockN;   // rows per TMA box of B
+  constexpr uint32_t kSfbColsPerKb = 4 * kBPieces;              // slab columns per 64-wide K block
   constexpr uint32_t kSfaCol = kAccStages * kBlockN;            // TMEM columns: accumulators first
-  constexpr uint32_t kSfSetCols = 16 + 4 * (kBlockN / 32);      // columns of one set of scale slabs (SFA + SFB)
+  constexpr uint32_t kSfSetCols = 16 + 4 * kSfbColsPerKb;       // columns of one set of scale slabs (SFA + SFB)
   constexpr uint32_t kIdesc = ptx::idesc_mxf4nvf4(kBlockN);
   constexpr int kFirstSfWarp = 2 + epilogue_warps(kBlockN);
   static_assert(kSfaCol + kStages * kSfSetCols <= kTmemCols, "TMEM budget: one set of slab columns per stage");
@@ -309,7 +311,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           b_row[1] = p.gate_row_offset + n_blk * 128;
         } else {
 #pragma unroll
-          for (int i = 0; i < kBPieces; ++i) b_row[i] = n_blk * kBlockN + 128 * i;
+          for (int i = 0; i < kBPieces; ++i) b_row[i] = n_blk * kBlockN + kBPieceRows * i;
         }
         for (int kt = 0; kt < p.num_k_tiles; ++kt) {
           if (!wait_bounded(empty_bar(st.stage), st.phase ^ 1u, abort_flag)) {
@@ -327,7 +329,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           ptx::mbar_expect_tx(bar, L.a_bytes + L.b_bytes + sf_bytes * (1 + kBPieces));
           ptx::tma_load_2d(sa, &tmap_a, kt * 128, m_blk * kBlockM, bar);
 #pragma unroll
-          for (int i = 0; i < kBPieces; ++i) ptx::tma_load_3d(sb + i * 128 * 128, &tmap_b, kt * 128, b_row[i], group, bar);
+          for (int i = 0; i < kBPieces; ++i) ptx::tma_load_3d(sb + i * kBPieceRows * 128, &tmap_b, kt * 128, b_row[i], group, bar);
           ptx::bulk_load(ssfa, p.sfa + (static_cast<int64_t>(m_blk) * p.rk + 4 * kt) * 512, sf_bytes, bar);
 #pragma unroll
           for (int i = 0; i < kBPieces; ++i) {
@@ -351,6 +353,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc.stage * kBlockN;
+        // a 64-wide tile uses half of a 128-row slab of B scale factors: its row groups start at column 0 or 2
+        const uint32_t sfb_shift = kBlockN >= 128 ? 0u : static_cast<uint32_t>(((tile / num_m_blocks) * kBlockN & 127) >> 5);
         for (int kt = 0; kt < p.num_k_tiles; ++kt) {
           if (!wait_bounded(full_bar(st.stage), st.phase, abort_flag)) {
             atomicOr(p.status, kStatusTimeoutMma);
@@ -374,7 +378,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           for (int kb = 0; kb < 4; ++kb) {
             if (kb < kblocks) {
               ptx::mma_mxf4nvf4(d_tmem, ptx::smem_desc_sw128(sa + 32 * kb), ptx::smem_desc_sw128(sb + 32 * kb), kIdesc,
-                                sfa_t + 4 * kb, sfb_t + (kBlockN / 32) * kb, (kt | kb) != 0 ? 1u : 0u);
+                                sfa_t + 4 * kb, sfb_t + kSfbColsPerKb * kb + sfb_shift, (kt | kb) != 0 ? 1u : 0u);
             }
           }
           ptx::tc_commit(empty_bar(st.stage));        // stage reusable once these MMAs have read it

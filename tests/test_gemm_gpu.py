@@ -31,7 +31,7 @@ def _check_status(b200):
 
 @pytest.mark.parametrize("m,n,k,tile_n", [
     (128, 128, 128, 128), (128, 128, 256, 128), (128, 256, 256, 256), (256, 384, 512, 128),
-    (256, 512, 1024, 256), (1024, 1024, 1024, 0), (256, 256, 64, 512), (512, 768, 1024, 512), (128, 128, 128, 512),
+    (256, 512, 1024, 256), (1024, 1024, 1024, 0), (256, 256, 64, 512), (512, 768, 1024, 512), (128, 128, 128, 512), (128, 192, 512, 64), (256, 64, 128, 64),
 ])
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16, torch.float16])
 def test_integer_operands_exact(b200, m, n, k, tile_n, out_dtype):
@@ -45,7 +45,7 @@ def test_integer_operands_exact(b200, m, n, k, tile_n, out_dtype):
 
 
 @pytest.mark.parametrize("m,n,k", [(128, 128, 64), (200, 264, 96), (130, 8, 32), (1, 136, 416), (333, 520, 1280)])
-@pytest.mark.parametrize("tile_n", [128, 256, 512])
+@pytest.mark.parametrize("tile_n", [64, 128, 256, 512])
 def test_ragged_shapes_random_codes(b200, m, n, k, tile_n):
     rng = np.random.default_rng(m * 7 + n * 3 + k)
     ac = rng.integers(0, 16, size=(m, k), dtype=np.uint8)
