@@ -317,7 +317,7 @@ class MoeWorkload:
     metric = "MoE tokens/s"
     unit = "tokens/s"
     dtype = "nvfp4 weights and activations, bf16 tokens, f32 accumulate"
-    kernel = "nvfp4_gemm_kernel<256, swiglu> + nvfp4_gemm_kernel<256> (grouped FC1 / FC2)"
+    kernel = "nvfp4_gemm_kernel<swiglu> + nvfp4_gemm_kernel (grouped FC1 / FC2)"
     bound = "hbm"
     launches_per_step = 8      # route, count, scan, scatter-quant, FC1, FC2, combine (+ 2 memsets not counted) 
 
@@ -367,6 +367,8 @@ class MoeWorkload:
             self.logits[:n_hot, 0] += 1e4
         self.out = torch.empty(t, h, dtype=torch.bfloat16, device="cuda")
         self.fc2_scale = torch.ones(1, device="cuda")
+        # per-expert output rows between FC2 and the weighted f32 sum: bf16 (default) or f32
+        self.slot_rows = torch.float32 if os.environ.get("B200FP4_SLOT_ROWS", "bf16") == "f32" else torch.bfloat16
         ids, _ = pkg.topk_route(self.logits, k)
         active = int(torch.unique(ids).numel())
         self.active_experts = active
@@ -393,11 +395,14 @@ class MoeWorkload:
             self.ep.forward(self.x, ids, wts, self.weights, out=self.out)
             return
         self.pkg.b12x_fused_moe(self.x, self.w1, self.w1_sf, self.w2, self.w2_sf, ids, wts, self.experts, self.top_k,
-                                w1_alpha=self.a1, w2_alpha=self.a2, fc2_input_scale=self.fc2_scale, output=self.out)
+                                w1_alpha=self.a1, w2_alpha=self.a2, fc2_input_scale=self.fc2_scale, output=self.out,
+                                slot_rows_dtype=self.slot_rows)
 
     def config(self, world):
         return {"workload": self.name, "tokens": self.tokens, "hidden": self.hidden, "experts": self.experts,
                 "top_k": self.top_k, "intermediate": self.inter, "active_experts": self.active_experts,
+                "slot_rows": "bf16" if world > 1 or self.slot_rows is not None and "bfloat16" in str(self.slot_rows)
+                else "f32",
                 "parallelism": (f"experts x{world}, tokens x{world}; " + (
                     "NCCL all-gather of tokens + routing, reduce-scatter of f32 partial outputs"
                     if os.environ.get("B200FP4_EP", "peer") == "collective" else

@@ -1,6 +1,7 @@
 // Host side of the NVFP4 GEMM family: tensor-map construction, launch
 // configuration and argument checks for the dense block-scaled GEMM and the
 // two grouped GEMMs of the fused MoE.  The device code is in gemm_kernel.cuh.
+#include <cstdlib>
 #include <mutex>
 
 #include "gemm2cta_kernel.cuh"
@@ -91,7 +92,7 @@ template <int kBlockN, bool kSwigluB, typename Epilogue>
 int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, const Epilogue& epi, int max_tiles,
                 cudaStream_t stream) {
   auto kern = nvfp4_gemm_kernel<kBlockN, kSwigluB, Epilogue>;
-  constexpr SmemLayout L = smem_layout<kBlockN>();
+  constexpr SmemLayout L = smem_layout<kBlockN, kSwigluB>();
   static bool configured = false;      // per instantiation
   if (!configured) {
     B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L.total)));
@@ -100,7 +101,7 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& 
   int grid = sm_count_of_current_device();
   if (grid > max_tiles) grid = max_tiles;
   if (grid < 1) return kOk;
-  kern<<<grid, gemm_threads(kBlockN), L.total, stream>>>(ta, tb, p, epi);
+  kern<<<grid, gemm_threads(kBlockN, kSwigluB), L.total, stream>>>(ta, tb, p, epi);
   return check_cuda(cudaGetLastError(), "nvfp4_gemm_kernel launch");
 }
 
@@ -238,10 +239,19 @@ int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* 
                  const float* w1_alpha, const float* fc2_input_scale, const int* num_m_blocks_dev,
                  const int* m_block_expert, const int* m_block_rows, int max_m_blocks, int hidden, int inter,
                  int experts, int* status, cudaStream_t stream) {
+  // Tile width: [up 64 | gate 64] tiles have two accumulators, so the SwiGLU + re-quantisation epilogue of one
+  // tile runs under the MMAs of the next; [up 128 | gate 128] tiles have one accumulator but half the MMAs per
+  // flop.  The epilogue costs the same per output column either way, the MMAs scale with the reduction length:
+  // narrow tiles win while the epilogue is a large share (short reductions).  B200FP4_FC1_TILE=128|256 overrides.
+  static const int forced_tile = [] {
+    const char* e = getenv("B200FP4_FC1_TILE");
+    return e != nullptr ? atoi(e) : 0;
+  }();
+  const bool narrow = forced_tile == 128 || (forced_tile != 256 && hidden <= 4096);
   CUtensorMap ta, tb;
   int rc = make_operand_map(&ta, xq, static_cast<int64_t>(max_m_blocks) * 128, hidden, 0);
   if (rc) return rc;
-  rc = make_operand_map(&tb, w1, 2 * inter, hidden, experts);
+  rc = make_operand_map(&tb, w1, 2 * inter, hidden, experts, narrow ? 64 : 128);
   if (rc) return rc;
   GemmParams p{};
   p.sfa = static_cast<const uint8_t*>(xq_sf);
@@ -260,14 +270,21 @@ int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* 
   p.m_block_rows = m_block_rows;
   p.status = status;
   EpilogueSwiglu epi{static_cast<uint8_t*>(act_codes), static_cast<uint8_t*>(act_sf), w1_alpha, fc2_input_scale, inter};
+  if (narrow) {
+    p.num_n_blocks = inter / 64;
+    return launch_gemm<128, true>(ta, tb, p, epi, max_m_blocks * p.num_n_blocks, stream);
+  }
   return launch_gemm<256, true>(ta, tb, p, epi, max_m_blocks * p.num_n_blocks, stream);
 }
 
-// FC2: partial[row][h] = (Actq . W2[e]^T) * w2_alpha[e], f32
-int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, float* partial,
-                 const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
-                 const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int* status,
-                 cudaStream_t stream) {
+// FC2: partial[row][h] = (Actq . W2[e]^T) * w2_alpha[e], stored as f32 or (rows_bf16) rounded to bf16.
+// The kernel is bound by what its epilogue can store (an SM writes some 16 bytes per cycle), so the
+// 16-bit rows nearly halve its time and the combine's.
+template <typename RowT>
+int gemm_moe_fc2_typed(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, RowT* partial,
+                       const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
+                       const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int* status,
+                       cudaStream_t stream) {
   CUtensorMap ta, tb;
   int rc = make_operand_map(&ta, act_codes, static_cast<int64_t>(max_m_blocks) * 128, inter, 0);
   if (rc) return rc;
@@ -287,10 +304,11 @@ int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, cons
   p.m_block_group = m_block_expert;
   p.m_block_rows = m_block_rows;
   p.status = status;
-  EpilogueStore<float> epi{partial, hidden, w2_alpha, 1};
+  EpilogueStore<RowT> epi{partial, hidden, w2_alpha, 1};
   // Short reductions (few K tiles) spend more time draining the accumulator than filling it; the
   // 128-wide tile has two accumulators, so its epilogue overlaps the next tile's MMAs.
-  if (hidden % 256 == 0 && p.num_k_tiles > 4) {
+  const bool wide = hidden % 256 == 0 && p.num_k_tiles > 4;
+  if (wide) {
     p.num_n_blocks = hidden / 256;
     return launch_gemm<256, false>(ta, tb, p, epi, max_m_blocks * p.num_n_blocks, stream);
   }
@@ -298,4 +316,17 @@ int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, cons
   return launch_gemm<128, false>(ta, tb, p, epi, max_m_blocks * p.num_n_blocks, stream);
 }
 
+int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, void* partial,
+                 int rows_bf16, const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
+                 const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int* status,
+                 cudaStream_t stream) {
+  if (rows_bf16)
+    return gemm_moe_fc2_typed(act_codes, act_sf, w2, w2_sf, static_cast<__nv_bfloat16*>(partial), w2_alpha,
+                              num_m_blocks_dev, m_block_expert, m_block_rows, max_m_blocks, hidden, inter, experts,
+                              status, stream);
+  return gemm_moe_fc2_typed(act_codes, act_sf, w2, w2_sf, static_cast<float*>(partial), w2_alpha, num_m_blocks_dev,
+                            m_block_expert, m_block_rows, max_m_blocks, hidden, inter, experts, status, stream);
+}
+
 }  // namespace b200fp4
+

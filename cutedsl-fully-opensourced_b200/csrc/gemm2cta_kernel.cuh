@@ -12,11 +12,16 @@
 // stage in both CTAs), warps 2-9 = epilogue, warps 10-13 = scale-slab movers (shared memory ->
 // tensor memory with tcgen05.st, each CTA for itself; they report to the even CTA).  No TMA multicast is used anywhere: every tile
 // is fetched by the CTA that needs it.  All waits are bounded as in the single-CTA kernel.
+//
+// Measured: no faster than the single-CTA kernel.  The B half that each tensor core reads from its peer's
+// shared memory appears to come through the same SM ingest path as the TMA loads (38 KB + 16 KB per K step
+// again), so without multicast loads the pair saves nothing; the kernel is kept as the tile_n = 512 option.
 #pragma once
 
 #include "gemm_kernel.cuh"
 
 namespace b200fp4 {
+
 
 constexpr int kPairStages = 5;
 constexpr uint32_t kPairStageBytes = 16384 + 16384 + 2048 + 4096;    // A, B half, SFA, SFB (both halves)
@@ -64,7 +69,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       ptx::mbar_init(sf_full_bar(s), 8);                 // four mover warps in each CTA
     }
     ptx::mbar_init(acc_full_bar, 1);
-    ptx::mbar_init(acc_empty_bar, 2 * 8 * 32);           // the epilogue threads of both CTAs
+    ptx::mbar_init(acc_empty_bar, 2 * 8);                // the epilogue warps of both CTAs
     *abort_flag = 0;
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmap_a);
@@ -198,7 +203,13 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
         ptx::tmem_st_wait();
         ptx::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive_cluster(sf_full_bar(st.stage) & ptx::kPeerBitMask);
+        // The slabs are in tensor memory (tcgen05.wait::st returned) before the arrive is issued.  The odd CTA
+        // signals with a relaxed arrive: one with cluster-scope release stalls its thread for 300 to 2000
+        // cycles under load, and there is no memory write here for a release to order.
+        if (lane == 0) {
+          if (rank == 0) ptx::mbar_arrive(sf_full_bar(st.stage));
+          else ptx::mbar_arrive_cluster_relaxed(sf_full_bar(st.stage) & ptx::kPeerBitMask);
+        }
         st.advance(kStages);
       }
     }
@@ -223,7 +234,11 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                                          ptx::tmem_ld_wait();
                                        });
       ptx::tc_fence_before_sync();
-      ptx::mbar_arrive_cluster(acc_empty_bar & ptx::kPeerBitMask);
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) ptx::mbar_arrive(acc_empty_bar);
+        else ptx::mbar_arrive_cluster_relaxed(acc_empty_bar & ptx::kPeerBitMask);   // tcgen05.wait::ld has returned
+      }
       acc_phase ^= 1u;
     }
   }

@@ -13,8 +13,11 @@
 //           128 bytes, 128-byte swizzle), one per 128-row piece of B, and plain
 //           bulk copies of the scale-factor slabs (2 KB per 128 rows: four
 //           512-byte 128x4 tiles are contiguous in the tiled layout)
-//   warp 1  MMA issuer: four tcgen05.mma kind::mxf4nvf4 (K = 64 each) per stage accumulate
-//           into a TMEM accumulator; tcgen05.commit releases the stage
+//   warp 1 and the last warp  MMA issuers: per stage each issues four tcgen05.mma kind::mxf4nvf4
+//           (K = 64 each) for its half of the tile's columns into its half of a TMEM accumulator;
+//           tcgen05.commit releases the stage.  One thread cannot keep the tensor pipe busy with
+//           block-scaled MMAs (about 160 cycles between its instructions whatever their width, against
+//           128 cycles of pipe time for 128 x 256 x 64); two threads with half-width instructions do
 //   last 4 warps  scale-slab movers: shared memory -> registers -> tensor memory (tcgen05.st),
 //           one set of slab columns per stage.  tcgen05.cp would do the same copy, but it runs
 //           in the MMA pipe: twelve copies per stage cost a third of the kernel's time there
@@ -35,10 +38,17 @@ constexpr int kBlockM = 128;
 constexpr int kBlockK = 256;                 // e2m1 elements per stage = 128 bytes per row
 // two single-thread roles (TMA, MMA) + the epilogue warps: four for 128-wide tiles (the second
 // accumulator hides the epilogue), eight for 256-wide tiles (one accumulator: drain it twice as fast)
-__host__ __device__ constexpr int epilogue_warps(int block_n) { return block_n == 256 ? 8 : 4; }
+// (the SwiGLU epilogue is arithmetic-heavy: eight warps at either width)
+__host__ __device__ constexpr int epilogue_warps(int block_n, bool swiglu = false) {
+  return (block_n == 256 || swiglu) ? 8 : 4;
+}
 // ... + four warps (one per 32-lane quarter of tensor memory) that move the scale slabs of every K
 // tile from shared memory into tensor memory
-__host__ __device__ constexpr int gemm_threads(int block_n) { return 64 + 32 * epilogue_warps(block_n) + 128; }
+// ... + the second MMA issuer (tiles of 128 columns and more)
+__host__ __device__ constexpr int mma_issuers(int block_n) { return 1; }
+__host__ __device__ constexpr int gemm_threads(int block_n, bool swiglu = false) {
+  return 64 + 32 * epilogue_warps(block_n, swiglu) + 128 + (mma_issuers(block_n) == 2 ? 32 : 0);
+}
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitLimitCycles = 4000000000LL;   // ~2 s at 2 GHz
 
@@ -73,16 +83,17 @@ struct SmemLayout {
   uint32_t a_bytes, b_bytes, sfa_bytes, sfb_bytes, stage_bytes, total;
 };
 
-template <int kBlockN>
+template <int kBlockN, bool kSwigluB = false>
 __host__ __device__ constexpr SmemLayout smem_layout() {
   SmemLayout s{};
   s.a_bytes = kBlockM * 128;
   s.b_bytes = kBlockN * 128;
   s.sfa_bytes = 2048;
-  s.sfb_bytes = (kBlockN >= 128 ? kBlockN / 128 : 1) * 2048;    // whole 128-row slabs, also for 64-wide tiles
+  // whole 128-row slabs, also for 64-row pieces; the up and gate pieces of a SwiGLU tile sit in different slabs
+  s.sfb_bytes = (kSwigluB ? 2 : (kBlockN >= 128 ? kBlockN / 128 : 1)) * 2048;
   s.stage_bytes = s.a_bytes + s.b_bytes + s.sfa_bytes + s.sfb_bytes;
-  s.stages = kBlockN == 256 ? 4 : (kBlockN == 128 ? 6 : 7);
-  s.total = s.stages * s.stage_bytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  s.stages = kBlockN == 256 ? 4 : (kBlockN == 128 ? (kSwigluB ? 5 : 6) : 7);
+  s.total = s.stages * s.stage_bytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
   return s;
 }
 
@@ -98,11 +109,15 @@ struct PipeState {
 };
 
 // Poll an mbarrier phase; gives up when another role raised the abort flag or the cycle budget ran out.
+// kBackoffNs > 0: sleep between polls.  Warps that spin take issue slots from the warps on the critical
+// path (MMA issuer, slab movers); roles that can afford some wake-up latency back off.
+template <int kBackoffNs = 0>
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
     if (ptx::mbar_try_wait(bar, parity)) return true;
+    if constexpr (kBackoffNs > 0) __nanosleep(kBackoffNs);
     if ((it & 255u) == 0) {
       if (*abort_flag) return false;
       if (clock64() - t0 > kWaitLimitCycles) {
@@ -181,7 +196,7 @@ struct EpilogueStore {
   }
 };
 
-// FC1 of the MoE: the 256 accumulator columns are [up j0..j0+127 | gate j0..j0+127];
+// FC1 of the MoE: the accumulator columns are [up j0..j0+h-1 | gate j0..j0+h-1], h = half the tile width;
 // act = bf16(silu(gate) * up), re-quantised to NVFP4 with the MoE activation packer
 // (tests/python/test_flashinfer_b12x_verbatim.py:214-218) and written as the A operand of FC2.
 struct EpilogueSwiglu {
@@ -194,19 +209,20 @@ struct EpilogueSwiglu {
   template <int kBlockN, typename Loader>
   __device__ __forceinline__ void operator()(const GemmParams& p, int m_blk, int n_blk, int group, int row,
                                              int rows_valid, int part, int parts, Loader&& load) const {
-    static_assert(kBlockN == 256, "the SwiGLU epilogue pairs two 128-column halves");
+    constexpr int kHalf = kBlockN / 2;
+    static_assert(kHalf % 64 == 0, "the SwiGLU epilogue pairs two halves of whole 32-column groups per warp");
     const float a1 = w1_alpha == nullptr ? 1.0f : __ldg(w1_alpha + group);
     const float gs = fc2_input_scale == nullptr ? 1.0f : __ldg(fc2_input_scale);
     const int64_t grow = static_cast<int64_t>(m_blk) * kBlockM + row;
-    const int j0 = n_blk * 128;
+    const int j0 = n_blk * kHalf;
     const int rk2 = (inter + 63) >> 6;
     uint8_t* sf_tile = act_sf + static_cast<int64_t>(m_blk) * rk2 * 512 + (row & 31) * 16 + (row >> 5) * 4;
-    const int span = 128 / parts;
+    const int span = kHalf / parts;
 #pragma unroll 1
     for (int c0 = part * span; c0 < (part + 1) * span; c0 += 32) {
       uint32_t up[32], gate[32];
       load(c0, up);
-      load(128 + c0, gate);
+      load(kHalf + c0, gate);
       if (j0 + c0 >= inter) continue;
       uint32_t sfpair = 0;
       uint32_t codes[4];
@@ -233,22 +249,29 @@ struct EpilogueSwiglu {
 };
 
 // ----------------------------------------------------------------------------
-// kSwigluB: B tile = two 128-row pieces (up rows, gate rows); otherwise kBlockN/128 consecutive pieces.
+// kSwigluB: B tile = two pieces of kBlockN/2 rows (up rows, gate rows); otherwise consecutive 128-row pieces
+// (one 64-row piece for 64-wide tiles).
 // ----------------------------------------------------------------------------
 template <int kBlockN, bool kSwigluB, typename Epilogue>
-__global__ void __launch_bounds__(gemm_threads(kBlockN), 1)
+__global__ void __launch_bounds__(gemm_threads(kBlockN, kSwigluB), 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const GemmParams p, const Epilogue epi) {
-  constexpr SmemLayout L = smem_layout<kBlockN>();
+  constexpr SmemLayout L = smem_layout<kBlockN, kSwigluB>();
   constexpr int kStages = L.stages;
   constexpr int kAccStages = kBlockN == 256 ? 1 : 2;
-  constexpr int kBPieces = kBlockN >= 128 ? kBlockN / 128 : 1;
-  constexpr int kBPieceRows = kBlockN >= 128 ? 128 : kBlockN;   // rows per TMA box of B
-  constexpr uint32_t kSfbColsPerKb = 4 * kBPieces;              // slab columns per 64-wide K block
+  constexpr int kBPieces = kSwigluB ? 2 : (kBlockN >= 128 ? kBlockN / 128 : 1);
+  constexpr int kBPieceRows = kBlockN / kBPieces;               // rows per TMA box of B
+  constexpr bool kHalfSlabPieces = kSwigluB && kBPieceRows == 64;   // two 64-row pieces: half a slab each
+  constexpr int kEpiWarps = epilogue_warps(kBlockN, kSwigluB);
+  // slab columns per 64-wide K block: one per 32 rows of the tile (64-wide tiles keep their whole slab)
+  constexpr uint32_t kSfbColsPerKb = kBlockN >= 128 ? kBlockN / 32 : 4;
   constexpr uint32_t kSfaCol = kAccStages * kBlockN;            // TMEM columns: accumulators first
   constexpr uint32_t kSfSetCols = 16 + 4 * kSfbColsPerKb;       // columns of one set of scale slabs (SFA + SFB)
-  constexpr uint32_t kIdesc = ptx::idesc_mxf4nvf4(kBlockN);
-  constexpr int kFirstSfWarp = 2 + epilogue_warps(kBlockN);
+  constexpr int kIssuers = mma_issuers(kBlockN);
+  constexpr int kIssueN = kBlockN / kIssuers;                   // columns per MMA instruction
+  constexpr uint32_t kIdesc = ptx::idesc_mxf4nvf4(kIssueN);
+  constexpr int kFirstSfWarp = 2 + kEpiWarps;
+  constexpr int kSecondMmaWarp = kFirstSfWarp + 4;
   static_assert(kSfaCol + kStages * kSfSetCols <= kTmemCols, "TMEM budget: one set of slab columns per stage");
 
   extern __shared__ uint8_t smem_raw[];
@@ -261,7 +284,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   auto acc_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
   auto acc_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 2 + s); };
   auto sf_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + 4 + s); };
-  uint8_t* tail_gen = smem_gen + kStages * L.stage_bytes + 8 * (3 * kStages + 4);
+  auto sf_loaded_bar = [&](int s) { return bar_base + 8u * (3 * kStages + 4 + s); };
+  uint8_t* tail_gen = smem_gen + kStages * L.stage_bytes + 8 * (4 * kStages + 4);
   volatile uint32_t* tmem_ptr_smem = reinterpret_cast<volatile uint32_t*>(tail_gen);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tail_gen + 4);
 
@@ -271,12 +295,13 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(full_bar(s), 1);
-      ptx::mbar_init(empty_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), kIssuers);              // one commit per MMA issuer
       ptx::mbar_init(sf_full_bar(s), 4);                 // one arrival per slab-mover warp
+      ptx::mbar_init(sf_loaded_bar(s), 1);
     }
     for (int s = 0; s < 2; ++s) {
-      ptx::mbar_init(acc_full_bar(s), 1);
-      ptx::mbar_init(acc_empty_bar(s), 32 * epilogue_warps(kBlockN));
+      ptx::mbar_init(acc_full_bar(s), kIssuers);
+      ptx::mbar_init(acc_empty_bar(s), 32 * kEpiWarps);
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
@@ -307,8 +332,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const int group = p.m_block_group != nullptr ? __ldg(p.m_block_group + m_blk) : 0;
         int b_row[kBPieces];
         if constexpr (kSwigluB) {
-          b_row[0] = n_blk * 128;
-          b_row[1] = p.gate_row_offset + n_blk * 128;
+          b_row[0] = n_blk * kBPieceRows;
+          b_row[1] = p.gate_row_offset + n_blk * kBPieceRows;
         } else {
 #pragma unroll
           for (int i = 0; i < kBPieces; ++i) b_row[i] = n_blk * kBlockN + kBPieceRows * i;
@@ -325,61 +350,69 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const uint32_t ssfb = ssfa + L.sfa_bytes;
           const int k_sf_tiles = min(4, p.rk - 4 * kt);                 // 512-byte scale tiles in this stage
           const uint32_t sf_bytes = static_cast<uint32_t>(k_sf_tiles) * 512u;
-          const uint32_t bar = full_bar(st.stage);
-          ptx::mbar_expect_tx(bar, L.a_bytes + L.b_bytes + sf_bytes * (1 + kBPieces));
-          ptx::tma_load_2d(sa, &tmap_a, kt * 128, m_blk * kBlockM, bar);
-#pragma unroll
-          for (int i = 0; i < kBPieces; ++i) ptx::tma_load_3d(sb + i * kBPieceRows * 128, &tmap_b, kt * 128, b_row[i], group, bar);
-          ptx::bulk_load(ssfa, p.sfa + (static_cast<int64_t>(m_blk) * p.rk + 4 * kt) * 512, sf_bytes, bar);
+          // the scale slabs go first and report to their own barrier: the movers carry them into tensor
+          // memory while the operand tiles are still on their way
+          const uint32_t sbar = sf_loaded_bar(st.stage);
+          ptx::mbar_expect_tx(sbar, sf_bytes * (1 + kBPieces));
+          ptx::bulk_load(ssfa, p.sfa + (static_cast<int64_t>(m_blk) * p.rk + 4 * kt) * 512, sf_bytes, sbar);
 #pragma unroll
           for (int i = 0; i < kBPieces; ++i) {
             const int64_t tile_idx = static_cast<int64_t>(group) * p.b_row_tiles + (b_row[i] >> 7);
-            ptx::bulk_load(ssfb + i * 2048, p.sfb + (tile_idx * p.rk + 4 * kt) * 512, sf_bytes, bar);
+            ptx::bulk_load(ssfb + i * 2048, p.sfb + (tile_idx * p.rk + 4 * kt) * 512, sf_bytes, sbar);
           }
+          const uint32_t bar = full_bar(st.stage);
+          ptx::mbar_expect_tx(bar, L.a_bytes + L.b_bytes);
+          ptx::tma_load_2d(sa, &tmap_a, kt * 128, m_blk * kBlockM, bar);
+#pragma unroll
+          for (int i = 0; i < kBPieces; ++i) ptx::tma_load_3d(sb + i * kBPieceRows * 128, &tmap_b, kt * 128, b_row[i], group, bar);
           st.advance(kStages);
         }
       }
     }
-  } else if (warp == 1) {
-    // =============================== MMA issuer ===============================
+  } else if (warp == 1 || (kIssuers == 2 && warp == kSecondMmaWarp)) {
+    // =============================== MMA issuers ===============================
     if (lane == 0) {
+      const uint32_t half = warp == 1 ? 0u : 1u;        // which half of the tile's columns (rows of B)
       PipeState st;
       PipeState acc;
       bool ok = true;
+      // Everything this thread does between two MMAs delays the next one once the tensor pipe's short queue
+      // has drained, so the loop is kept short: two barrier waits per K tile (operands landed, scale slabs in
+      // tensor memory) and descriptors that advance by additions.
+      const uint64_t a_desc0 = ptx::smem_desc_sw128(smem_base);
+      const uint64_t b_desc0 = ptx::smem_desc_sw128(smem_base + L.a_bytes + half * (kIssueN * 128));
+      const int last_kblocks = ((p.k - (p.num_k_tiles - 1) * kBlockK) + 63) >> 6;   // 64-wide steps of the last K tile
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         if (!wait_bounded(acc_empty_bar(acc.stage), acc.phase ^ 1u, abort_flag)) {
           atomicOr(p.status, kStatusTimeoutMma);
           break;
         }
         ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc.stage * kBlockN;
+        const uint32_t d_tmem = tmem_base + acc.stage * kBlockN + half * kIssueN;
         // a 64-wide tile uses half of a 128-row slab of B scale factors: its row groups start at column 0 or 2
+        // (the movers of a SwiGLU tile with 64-row pieces have already picked the right halves)
         const uint32_t sfb_shift = kBlockN >= 128 ? 0u : static_cast<uint32_t>(((tile / num_m_blocks) * kBlockN & 127) >> 5);
+        const uint32_t sf_t0 = tmem_base + kSfaCol + 16 + half * (kIssueN / 32) + sfb_shift;
         for (int kt = 0; kt < p.num_k_tiles; ++kt) {
-          if (!wait_bounded(full_bar(st.stage), st.phase, abort_flag)) {
+          // the slab movers have put this stage's scale factors into its set of TMEM columns (usually long
+          // before the operands land), and the operand tiles are in shared memory
+          if (!wait_bounded(sf_full_bar(st.stage), st.phase, abort_flag) ||
+              !wait_bounded(full_bar(st.stage), st.phase, abort_flag)) {
             atomicOr(p.status, kStatusTimeoutMma);
             ok = false;
             break;
           }
           ptx::tc_fence_after_sync();
-          const uint32_t sa = smem_base + st.stage * L.stage_bytes;
-          const uint32_t sb = sa + L.a_bytes;
-          const int kblocks = min(4, (p.k - kt * kBlockK + 63) >> 6);   // 64-wide MMA steps with data
-          // the slab movers have put this stage's scale factors into its set of TMEM columns
-          if (!wait_bounded(sf_full_bar(st.stage), st.phase, abort_flag)) {
-            atomicOr(p.status, kStatusTimeoutMma);
-            ok = false;
-            break;
-          }
-          ptx::tc_fence_after_sync();
+          const uint64_t stage_off = static_cast<uint64_t>(st.stage * (L.stage_bytes >> 4));
+          const uint64_t da = a_desc0 + stage_off, db = b_desc0 + stage_off;      // + 2 per 32 bytes of K
+          const uint32_t sfb_t = sf_t0 + st.stage * kSfSetCols;
           const uint32_t sfa_t = tmem_base + kSfaCol + st.stage * kSfSetCols;
-          const uint32_t sfb_t = sfa_t + 16;
+          const int kblocks = kt + 1 == p.num_k_tiles ? last_kblocks : 4;
+          ptx::mma_mxf4nvf4(d_tmem, da, db, kIdesc, sfa_t, sfb_t, kt != 0 ? 1u : 0u);
 #pragma unroll
-          for (int kb = 0; kb < 4; ++kb) {
-            if (kb < kblocks) {
-              ptx::mma_mxf4nvf4(d_tmem, ptx::smem_desc_sw128(sa + 32 * kb), ptx::smem_desc_sw128(sb + 32 * kb), kIdesc,
-                                sfa_t + 4 * kb, sfb_t + kSfbColsPerKb * kb + sfb_shift, (kt | kb) != 0 ? 1u : 0u);
-            }
+          for (int kb = 1; kb < 4; ++kb) {
+            if (kb < kblocks)
+              ptx::mma_mxf4nvf4(d_tmem, da + 2 * kb, db + 2 * kb, kIdesc, sfa_t + 4 * kb, sfb_t + kSfbColsPerKb * kb, 1u);
           }
           ptx::tc_commit(empty_bar(st.stage));        // stage reusable once these MMAs have read it
           st.advance(kStages);
@@ -388,7 +421,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         acc.advance(kAccStages);
       }
     }
-  } else if (warp >= kFirstSfWarp) {
+  } else if (warp >= kFirstSfWarp && warp < kFirstSfWarp + 4) {
     // =============================== scale-slab movers ===============================
     // Lane l of every quarter needs the 16 bytes of slab row l per 64-wide K block: 4 columns of SFA
     // (row groups 0-3 of the 128-row tile) and 4 per 128 rows of B.  All four warps write the same
@@ -397,8 +430,10 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     PipeState st;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      // 64-row pieces: rows (n_blk * 64) % 128 .. +63 of their slab = its row groups 0-1 or 2-3
+      const bool upper_half = kHalfSlabPieces && ((tile / num_m_blocks) & 1) != 0;
       for (int kt = 0; kt < p.num_k_tiles; ++kt) {
-        if (!wait_bounded(full_bar(st.stage), st.phase, abort_flag)) {
+        if (!wait_bounded(sf_loaded_bar(st.stage), st.phase, abort_flag)) {
           if (lane == 0) atomicOr(p.status, kStatusTimeoutMma);
           ok = false;
           break;
@@ -413,7 +448,18 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
         ptx::tmem_st_32x16(t_sf, ra);
         const uint8_t* slab_b = slab + L.sfa_bytes;
-        if constexpr (kBPieces == 2) {
+        if constexpr (kHalfSlabPieces) {
+          // columns per K block: [up rows 0-31, up rows 32-63, gate rows 0-31, gate rows 32-63] of the tile
+          uint32_t rb[16];
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+            const uint4 u = *reinterpret_cast<const uint4*>(slab_b + 512 * kb);
+            const uint4 g = *reinterpret_cast<const uint4*>(slab_b + 2048 + 512 * kb);
+            rb[4 * kb] = upper_half ? u.z : u.x, rb[4 * kb + 1] = upper_half ? u.w : u.y;
+            rb[4 * kb + 2] = upper_half ? g.z : g.x, rb[4 * kb + 3] = upper_half ? g.w : g.y;
+          }
+          ptx::tmem_st_32x16(t_sf + 16, rb);
+        } else if constexpr (kBPieces == 2) {
           uint32_t rb[32];
 #pragma unroll
           for (int kb = 0; kb < 4; ++kb) {
@@ -441,9 +487,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         st.advance(kStages);
       }
     }
-  } else {
+  } else if (warp >= 2 && warp < kFirstSfWarp) {
     // =============================== epilogue ===============================
-    constexpr int kParts = epilogue_warps(kBlockN) / 4;
+    constexpr int kParts = kEpiWarps / 4;
     const int quarter = warp & 3;                      // TMEM lanes this warp may touch
     const int part = (warp - 2) >> 2;                  // which share of the columns (two warps per quarter)
     const int row = quarter * 32 + lane;
@@ -452,7 +498,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const int m_blk = tile % num_m_blocks;
       const int n_blk = tile / num_m_blocks;
       const int group = p.m_block_group != nullptr ? __ldg(p.m_block_group + m_blk) : 0;
-      if (!wait_bounded(acc_full_bar(acc.stage), acc.phase, abort_flag)) {
+      if (!wait_bounded<64>(acc_full_bar(acc.stage), acc.phase, abort_flag)) {
         if (lane == 0) atomicOr(p.status, kStatusTimeoutEpilogue);
         break;
       }

@@ -24,7 +24,8 @@ int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* 
                  const float* w1_alpha, const float* fc2_input_scale, const int* num_m_blocks_dev,
                  const int* m_block_expert, const int* m_block_rows, int max_m_blocks, int hidden, int inter,
                  int experts, int* status, cudaStream_t stream);
-int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, float* partial,
+int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, void* partial,
+                 int rows_bf16,
                  const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
                  const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int* status,
                  cudaStream_t stream);
@@ -196,9 +197,21 @@ moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, const int* __restr
   }
 }
 
+// four consecutive elements of a per-slot output row (f32 or bf16 storage) as f32
+template <typename RowT>
+__device__ __forceinline__ float4 load_row4(const RowT* p) {
+  if constexpr (sizeof(RowT) == 4) {
+    return *reinterpret_cast<const float4*>(p);
+  } else {
+    const uint2 u = *reinterpret_cast<const uint2*>(p);
+    return make_float4(Pair16<__nv_bfloat16>::lo(u.x), Pair16<__nv_bfloat16>::hi(u.x), Pair16<__nv_bfloat16>::lo(u.y),
+                       Pair16<__nv_bfloat16>::hi(u.y));
+  }
+}
+
 // one CTA per token; every thread owns 4 output columns at a time
-template <typename OutT>
-__global__ void moe_combine_kernel(const float* __restrict__ partial, const int* __restrict__ slot_row,
+template <typename OutT, typename RowT>
+__global__ void moe_combine_kernel(const RowT* __restrict__ partial, const int* __restrict__ slot_row,
                                    const float* __restrict__ weights, OutT* __restrict__ out, int hidden,
                                    int top_k, int accumulate) {
   __shared__ int s_rows[64];
@@ -214,7 +227,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ partial, const int*
     for (int j = 0; j < top_k; ++j) {
       const int row = s_rows[j];
       if (row < 0) continue;
-      const float4 pv = *reinterpret_cast<const float4*>(partial + static_cast<int64_t>(row) * hidden + c);
+      const float4 pv = load_row4(partial + static_cast<int64_t>(row) * hidden + c);
       const float w = s_w[j];
       acc.x = __fadd_rn(acc.x, __fmul_rn(w, pv.x));
       acc.y = __fadd_rn(acc.y, __fmul_rn(w, pv.y));
@@ -319,7 +332,9 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
               void* out, int64_t tokens, int hidden, int inter, int experts, int top_k, int expert_lo,
               int accumulate, int out_dtype, void* workspace, size_t workspace_bytes, int* status,
               cudaStream_t stream) {
-  if (out_dtype != 1 && out_dtype != 2) return fail(kUnsupported, "out_dtype code %d (1 bf16, 2 f32)", out_dtype);
+  if (out_dtype < 1 || out_dtype > 3)
+    return fail(kUnsupported, "out_dtype code %d (1 bf16, 2 f32, 3 bf16 with bf16 per-slot rows)", out_dtype);
+  const int rows_bf16 = out_dtype == 3;
   if (x == nullptr || w1 == nullptr || w1_sf == nullptr || w2 == nullptr || w2_sf == nullptr || ids == nullptr ||
       route_w == nullptr || out == nullptr || workspace == nullptr || status == nullptr)
     return fail(kInvalidArgument, "null pointer argument");
@@ -349,15 +364,19 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
   int rc = gemm_moe_fc1(ws.xq, ws.xq_sf, w1, w1_sf, ws.act, ws.act_sf, w1_alpha, fc2_input_scale, ws.h.num_m_blocks,
                         ws.h.m_block_expert, ws.h.m_block_rows, ws.max_m_blocks, hidden, inter, experts, status, stream);
   if (rc) return rc;
-  rc = gemm_moe_fc2(ws.act, ws.act_sf, w2, w2_sf, ws.partial, w2_alpha, ws.h.num_m_blocks, ws.h.m_block_expert,
+  rc = gemm_moe_fc2(ws.act, ws.act_sf, w2, w2_sf, ws.partial, rows_bf16, w2_alpha, ws.h.num_m_blocks, ws.h.m_block_expert,
                     ws.h.m_block_rows, ws.max_m_blocks, hidden, inter, experts, status, stream);
   if (rc) return rc;
   const int threads = hidden / 4 >= 256 ? 256 : 128;
   if (out_dtype == 2) {
-    moe_combine_kernel<float><<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
+    moe_combine_kernel<float, float><<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
         ws.partial, ws.h.slot_row, route_w, static_cast<float*>(out), hidden, top_k, accumulate);
+  } else if (rows_bf16) {
+    moe_combine_kernel<__nv_bfloat16, __nv_bfloat16><<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(ws.partial), ws.h.slot_row, route_w, static_cast<__nv_bfloat16*>(out),
+        hidden, top_k, accumulate);
   } else {
-    moe_combine_kernel<__nv_bfloat16><<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
+    moe_combine_kernel<__nv_bfloat16, float><<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
         ws.partial, ws.h.slot_row, route_w, static_cast<__nv_bfloat16*>(out), hidden, top_k, accumulate);
   }
   return check_cuda(cudaGetLastError(), "moe_combine_kernel launch");
@@ -419,9 +438,10 @@ EpLayout ep_layout(int64_t tokens_local, int hidden, int inter, int experts_loca
   L.tok_codes = take(static_cast<size_t>(tokens_local) * (hidden / 2));
   L.tok_sf = take(static_cast<size_t>(tokens_local) * (hidden / 16));
   L.tok_ids = take(sizeof(int) * tokens_local * top_k);
-  L.recv = take(static_cast<size_t>(tokens_local) * top_k * hidden * sizeof(float));
-  L.partial = take(static_cast<size_t>(rows) * hidden * sizeof(float));
-  L.row_dst = take(sizeof(float*) * rows);
+  // per-slot output rows cross NVLink and are summed as bf16 rows (f32 accumulation in the combine)
+  L.recv = take(static_cast<size_t>(tokens_local) * top_k * hidden * sizeof(__nv_bfloat16));
+  L.partial = take(static_cast<size_t>(rows) * hidden * sizeof(__nv_bfloat16));
+  L.row_dst = take(sizeof(void*) * rows);
   L.counts = take(sizeof(int) * experts_local);
   L.cursor = take(sizeof(int) * experts_local);
   L.offsets = take(sizeof(int) * (experts_local + 1));
@@ -471,7 +491,7 @@ __global__ void ep_count_kernel(PeerPtrs peers, size_t tok_ids_off, int slots_pe
 // one CTA per token of ANY rank: rows for its local slots, then the quantised row is pulled from its owner
 template <int kThreads>
 __global__ void __launch_bounds__(kThreads)
-ep_gather_kernel(PeerPtrs peers, EpLayout L, MoeHeader h, float** row_dst, uint8_t* xq, uint8_t* xq_sf,
+ep_gather_kernel(PeerPtrs peers, EpLayout L, MoeHeader h, __nv_bfloat16** row_dst, uint8_t* xq, uint8_t* xq_sf,
                  int tokens_local, int hidden, int top_k, int expert_lo, int experts, int max_rows) {
   __shared__ int s_rows[64];
   __shared__ int s_any;
@@ -492,7 +512,7 @@ ep_gather_kernel(PeerPtrs peers, EpLayout L, MoeHeader h, float** row_dst, uint8
     if (row >= 0) {
       s_any = 1;
       // the output row of this slot goes home: slot (t, j) of rank src
-      row_dst[row] = reinterpret_cast<float*>(peers.p[src] + L.recv) +
+      row_dst[row] = reinterpret_cast<__nv_bfloat16*>(peers.p[src] + L.recv) +
                      (static_cast<int64_t>(t) * top_k + threadIdx.x) * hidden;
     }
   }
@@ -514,31 +534,32 @@ ep_gather_kernel(PeerPtrs peers, EpLayout L, MoeHeader h, float** row_dst, uint8
   }
 }
 
-// one CTA per row of the expert-major output: copy it to the landing zone of the token's rank
-__global__ void ep_return_rows_kernel(const float* __restrict__ partial, float* const* __restrict__ row_dst,
+// one CTA per row of the expert-major output (bf16): copy it to the landing zone of the token's rank
+__global__ void ep_return_rows_kernel(const __nv_bfloat16* __restrict__ partial,
+                                      __nv_bfloat16* const* __restrict__ row_dst,
                                       const int* __restrict__ num_m_blocks, const int* __restrict__ m_block_rows,
                                       int hidden) {
   const int blk = blockIdx.x >> 7;
   const int r = blockIdx.x & 127;
   if (blk >= __ldg(num_m_blocks) || r >= __ldg(m_block_rows + blk)) return;
   const int64_t row = blockIdx.x;
-  const float4* src = reinterpret_cast<const float4*>(partial + row * hidden);
-  float4* dst = reinterpret_cast<float4*>(row_dst[row]);
-  for (int i = threadIdx.x; i < hidden / 4; i += blockDim.x) dst[i] = src[i];
+  const uint4* src = reinterpret_cast<const uint4*>(partial + row * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(row_dst[row]);
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = src[i];
 }
 
 // one CTA per local token: its k output rows have been delivered into this rank's own buffer
-__global__ void ep_combine_kernel(const float* __restrict__ recv, const float* __restrict__ weights,
+__global__ void ep_combine_kernel(const __nv_bfloat16* __restrict__ recv, const float* __restrict__ weights,
                                   __nv_bfloat16* __restrict__ out, int hidden, int top_k) {
   __shared__ float s_w[64];
   const int t = blockIdx.x;
   if (threadIdx.x < top_k) s_w[threadIdx.x] = weights[static_cast<int64_t>(t) * top_k + threadIdx.x];
   __syncthreads();
-  const float* rows = recv + static_cast<int64_t>(t) * top_k * hidden;
+  const __nv_bfloat16* rows = recv + static_cast<int64_t>(t) * top_k * hidden;
   for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int j = 0; j < top_k; ++j) {
-      const float4 pv = *reinterpret_cast<const float4*>(rows + static_cast<int64_t>(j) * hidden + c);
+      const float4 pv = load_row4(rows + static_cast<int64_t>(j) * hidden + c);
       const float w = s_w[j];
       acc.x = __fadd_rn(acc.x, __fmul_rn(w, pv.x));
       acc.y = __fadd_rn(acc.y, __fmul_rn(w, pv.y));
@@ -619,7 +640,7 @@ int moe_ep_compute(const void* const* peer_buffers, int rank, int world, const v
   h.m_block_expert = reinterpret_cast<int*>(b + L.m_block_expert);
   h.m_block_rows = reinterpret_cast<int*>(b + L.m_block_rows);
   h.slot_row = nullptr;
-  float** row_dst = reinterpret_cast<float**>(b + L.row_dst);
+  __nv_bfloat16** row_dst = reinterpret_cast<__nv_bfloat16**>(b + L.row_dst);
   const int expert_lo = rank * experts_local;
   const int slots_per_rank = static_cast<int>(tokens_local * top_k);
   const int total_slots = slots_per_rank * world;
@@ -637,12 +658,12 @@ int moe_ep_compute(const void* const* peer_buffers, int rank, int world, const v
                     h.num_m_blocks, h.m_block_expert, h.m_block_rows, L.max_m_blocks, hidden, inter, experts_local,
                     status, stream);
   if (rc) return rc;
-  rc = gemm_moe_fc2(b + L.act, b + L.act_sf, w2, w2_sf, reinterpret_cast<float*>(b + L.partial), w2_alpha,
+  rc = gemm_moe_fc2(b + L.act, b + L.act_sf, w2, w2_sf, b + L.partial, /*rows_bf16=*/1, w2_alpha,
                     h.num_m_blocks, h.m_block_expert, h.m_block_rows, L.max_m_blocks, hidden, inter, experts_local,
                     status, stream);
   if (rc) return rc;
   ep_return_rows_kernel<<<static_cast<unsigned>(max_rows), 256, 0, stream>>>(
-      reinterpret_cast<const float*>(b + L.partial), row_dst, h.num_m_blocks, h.m_block_rows, hidden);
+      reinterpret_cast<const __nv_bfloat16*>(b + L.partial), row_dst, h.num_m_blocks, h.m_block_rows, hidden);
   return check_cuda(cudaGetLastError(), "ep_return_rows_kernel launch");
 }
 
@@ -660,7 +681,8 @@ int moe_ep_combine(const void* const* peer_buffers, int rank, int world, const i
   const int threads = hidden / 4 >= 256 ? 256 : 128;
   (void)ids;
   ep_combine_kernel<<<static_cast<unsigned>(tokens_local), threads, 0, stream>>>(
-      reinterpret_cast<const float*>(peers.p[rank] + L.recv), weights, static_cast<__nv_bfloat16*>(out), hidden, top_k);
+      reinterpret_cast<const __nv_bfloat16*>(peers.p[rank] + L.recv), weights, static_cast<__nv_bfloat16*>(out), hidden,
+      top_k);
   return check_cuda(cudaGetLastError(), "ep_combine_kernel launch");
 }
 

@@ -201,6 +201,10 @@ __device__ __forceinline__ void cluster_sync() {
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// the same without memory ordering: for signals that follow completed tensor-memory accesses only
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t bar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 // tiled loads whose completion bytes are credited to a barrier of the even CTA
 __device__ __forceinline__ void tma2_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(

@@ -90,8 +90,10 @@ size_t b200fp4_moe_workspace_bytes(int64_t tokens, int hidden, int intermediate,
  * x bf16 [tokens, hidden]; w1 u8 [local_experts, 2I, hidden/2] (rows 0..I-1 = up, I..2I-1 = gate);
  * w2 u8 [local_experts, hidden, I/2]; w1_sf / w2_sf e4m3 bytes in 128x4 tiles
  * [local_experts][rows/128][K/64][32][4][4]; ids i32 and scales f32 [tokens, top_k]; alphas f32
- * [local_experts] or NULL; fc2_input_scale one f32 or NULL; out [tokens, hidden], bf16 (out_dtype 1) or
- * f32 (out_dtype 2, what expert-parallel ranks reduce across GPUs).
+ * [local_experts] or NULL; fc2_input_scale one f32 or NULL; out [tokens, hidden], bf16 (out_dtype 1 or 3) or
+ * f32 (out_dtype 2, what expert-parallel ranks reduce across GPUs).  The k per-expert rows of a token are
+ * always summed in f32 in slot order and rounded once; out_dtype 3 stores them as bf16 between FC2 and the
+ * sum (half the bytes of the step's largest stream), 1 and 2 as f32.
  * Expert ids are global: those in [local_expert_offset, local_expert_offset + local_experts) are
  * computed, the others contribute nothing (expert parallelism).  accumulate != 0 adds into out.
  * workspace: 256-byte aligned device scratch of b200fp4_moe_workspace_bytes(...) bytes. */
