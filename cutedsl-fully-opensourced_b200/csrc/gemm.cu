@@ -269,6 +269,7 @@ int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* 
   p.m_block_group = m_block_expert;
   p.m_block_rows = m_block_rows;
   p.status = status;
+  p.row_block_major = 1;
   EpilogueSwiglu epi{static_cast<uint8_t*>(act_codes), static_cast<uint8_t*>(act_sf), w1_alpha, fc2_input_scale, inter};
   if (narrow) {
     p.num_n_blocks = inter / 64;
@@ -304,6 +305,7 @@ int gemm_moe_fc2_typed(const void* act_codes, const void* act_sf, const void* w2
   p.m_block_group = m_block_expert;
   p.m_block_rows = m_block_rows;
   p.status = status;
+  p.row_block_major = 1;
   EpilogueStore<RowT> epi{partial, hidden, w2_alpha, 1};
   // Short reductions (few K tiles) spend more time draining the accumulator than filling it; the
   // 128-wide tile has two accumulators, so its epilogue overlaps the next tile's MMAs.

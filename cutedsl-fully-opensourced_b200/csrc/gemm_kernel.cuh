@@ -76,6 +76,11 @@ struct GemmParams {
   const int* m_block_group;    // null -> group 0
   const int* m_block_rows;     // null -> all 128 rows of a block hold data; else rows of the block that do
   int* status;                 // device status word (bits of GemmStatusBits)
+  // Order of the tile list.  0: column block outermost (CTAs running together share a few column blocks of B
+  // and sweep the rows of A).  1: row block outermost: the CTAs running together hold a few row blocks of A
+  // and the column blocks of their groups -- for the grouped GEMMs that keeps an expert's weights and its
+  // rows in L2 for exactly as long as they are needed.
+  int row_block_major;
 };
 
 struct SmemLayout {
@@ -320,6 +325,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 
   const int num_m_blocks = p.num_m_blocks_dev != nullptr ? __ldg(p.num_m_blocks_dev) : p.num_m_blocks;
   const int num_tiles = num_m_blocks * p.num_n_blocks;
+  auto tile_m = [&](int tile) { return p.row_block_major ? tile / p.num_n_blocks : tile % num_m_blocks; };
+  auto tile_n = [&](int tile) { return p.row_block_major ? tile % p.num_n_blocks : tile / num_m_blocks; };
 
   if (warp == 0) {
     // =============================== TMA producer ===============================
@@ -327,8 +334,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       PipeState st;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m_blk = tile % num_m_blocks;
-        const int n_blk = tile / num_m_blocks;
+        const int m_blk = tile_m(tile);
+        const int n_blk = tile_n(tile);
         const int group = p.m_block_group != nullptr ? __ldg(p.m_block_group + m_blk) : 0;
         int b_row[kBPieces];
         if constexpr (kSwigluB) {
@@ -391,7 +398,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const uint32_t d_tmem = tmem_base + acc.stage * kBlockN + half * kIssueN;
         // a 64-wide tile uses half of a 128-row slab of B scale factors: its row groups start at column 0 or 2
         // (the movers of a SwiGLU tile with 64-row pieces have already picked the right halves)
-        const uint32_t sfb_shift = kBlockN >= 128 ? 0u : static_cast<uint32_t>(((tile / num_m_blocks) * kBlockN & 127) >> 5);
+        const uint32_t sfb_shift = kBlockN >= 128 ? 0u : static_cast<uint32_t>((tile_n(tile) * kBlockN & 127) >> 5);
         const uint32_t sf_t0 = tmem_base + kSfaCol + 16 + half * (kIssueN / 32) + sfb_shift;
         for (int kt = 0; kt < p.num_k_tiles; ++kt) {
           // the slab movers have put this stage's scale factors into its set of TMEM columns (usually long
@@ -431,7 +438,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       // 64-row pieces: rows (n_blk * 64) % 128 .. +63 of their slab = its row groups 0-1 or 2-3
-      const bool upper_half = kHalfSlabPieces && ((tile / num_m_blocks) & 1) != 0;
+      const bool upper_half = kHalfSlabPieces && (tile_n(tile) & 1) != 0;
       for (int kt = 0; kt < p.num_k_tiles; ++kt) {
         if (!wait_bounded(sf_loaded_bar(st.stage), st.phase, abort_flag)) {
           if (lane == 0) atomicOr(p.status, kStatusTimeoutMma);
@@ -495,8 +502,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     const int row = quarter * 32 + lane;
     PipeState acc;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int m_blk = tile % num_m_blocks;
-      const int n_blk = tile / num_m_blocks;
+      const int m_blk = tile_m(tile);
+      const int n_blk = tile_n(tile);
       const int group = p.m_block_group != nullptr ? __ldg(p.m_block_group + m_blk) : 0;
       if (!wait_bounded<64>(acc_full_bar(acc.stage), acc.phase, abort_flag)) {
         if (lane == 0) atomicOr(p.status, kStatusTimeoutEpilogue);
