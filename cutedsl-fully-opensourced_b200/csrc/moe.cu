@@ -35,19 +35,20 @@ namespace {
 constexpr int kRouteMaxPerLane = 32;       // experts <= 1024
 
 // ---------------------------------------------------------------------------
-// route: one warp per token
+// route: one warp per token; kPerLane = experts a lane holds (experts <= 32 * kPerLane)
 // ---------------------------------------------------------------------------
+template <int kPerLane>
 __global__ void route_topk_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ weights,
                                   int tokens, int experts, int top_k, int renormalize) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= tokens) return;
   const float* row = logits + static_cast<int64_t>(warp) * experts;
-  float v[kRouteMaxPerLane];
+  float v[kPerLane];
   const int per_lane = (experts + 31) >> 5;
   float mx = -INFINITY;
 #pragma unroll
-  for (int i = 0; i < kRouteMaxPerLane; ++i) {
+  for (int i = 0; i < kPerLane; ++i) {
     const int e = lane + 32 * i;
     v[i] = (i < per_lane && e < experts) ? row[e] : -INFINITY;
     mx = fmaxf(mx, v[i]);
@@ -56,7 +57,7 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int* __restr
   for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
   float sum = 0.0f;
 #pragma unroll
-  for (int i = 0; i < kRouteMaxPerLane; ++i) {
+  for (int i = 0; i < kPerLane; ++i) {
     v[i] = (i < per_lane && lane + 32 * i < experts) ? expf(v[i] - mx) : -1.0f;   // -1 = absent / already taken
     if (v[i] > 0.0f) sum += v[i];
   }
@@ -71,7 +72,7 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int* __restr
     float best = -1.0f;
     int best_e = 0x7fffffff;
 #pragma unroll
-    for (int i = 0; i < kRouteMaxPerLane; ++i) {
+    for (int i = 0; i < kPerLane; ++i) {
       if (i < per_lane && v[i] > best) {
         best = v[i];
         best_e = lane + 32 * i;
@@ -88,7 +89,7 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int* __restr
     }
     if ((best_e & 31) == lane) {
 #pragma unroll
-      for (int i = 0; i < kRouteMaxPerLane; ++i)
+      for (int i = 0; i < kPerLane; ++i)
         if (i == (best_e >> 5)) v[i] = -1.0f;
     }
     const float prob = best * inv;
@@ -117,11 +118,22 @@ struct MoeHeader {           // all int32, contiguous
   int* slot_row;             // [tokens * top_k] row of every (token, slot), -1 if the expert is not local
 };
 
+// rows per local expert: a histogram per CTA in shared memory (experts <= 1024), then one global add per
+// expert that the CTA saw
+constexpr int kCountSlotsPerCta = 4096;
 __global__ void moe_count_kernel(const int* __restrict__ ids, int n_slots, int expert_lo, int experts, int* counts) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n_slots) return;
-  const int e = ids[i] - expert_lo;
-  if (e >= 0 && e < experts) atomicAdd(counts + e, 1);
+  __shared__ int s_hist[1024];
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) s_hist[e] = 0;
+  __syncthreads();
+  const int first = blockIdx.x * kCountSlotsPerCta;
+  const int last = min(n_slots, first + kCountSlotsPerCta);
+  for (int i = first + threadIdx.x; i < last; i += blockDim.x) {
+    const int e = ids[i] - expert_lo;
+    if (e >= 0 && e < experts) atomicAdd(s_hist + e, 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x)
+    if (s_hist[e] != 0) atomicAdd(counts + e, s_hist[e]);
 }
 
 // single CTA: padded exclusive scan over experts and the block -> expert table
@@ -315,8 +327,16 @@ int route_topk(const float* logits, int* ids, float* weights, int tokens, int ex
   if (experts > 32 * kRouteMaxPerLane) return fail(kUnsupported, "experts=%d exceeds %d", experts, 32 * kRouteMaxPerLane);
   if (tokens == 0) return kOk;
   const int warps_per_cta = 4;
-  route_topk_kernel<<<(tokens + warps_per_cta - 1) / warps_per_cta, 32 * warps_per_cta, 0, stream>>>(
-      logits, ids, weights, tokens, experts, top_k, renormalize);
+  const dim3 grid((tokens + warps_per_cta - 1) / warps_per_cta), block(32 * warps_per_cta);
+  if (experts <= 64)
+    route_topk_kernel<2><<<grid, block, 0, stream>>>(logits, ids, weights, tokens, experts, top_k, renormalize);
+  else if (experts <= 128)
+    route_topk_kernel<4><<<grid, block, 0, stream>>>(logits, ids, weights, tokens, experts, top_k, renormalize);
+  else if (experts <= 256)
+    route_topk_kernel<8><<<grid, block, 0, stream>>>(logits, ids, weights, tokens, experts, top_k, renormalize);
+  else
+    route_topk_kernel<kRouteMaxPerLane><<<grid, block, 0, stream>>>(logits, ids, weights, tokens, experts, top_k,
+                                                                     renormalize);
   return check_cuda(cudaGetLastError(), "route_topk_kernel launch");
 }
 
@@ -356,7 +376,8 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
 
   B200_CUDA(cudaMemsetAsync(ws.h.counts, 0, sizeof(int) * experts, stream));
   B200_CUDA(cudaMemsetAsync(ws.xq_sf, 0, ws.xq_sf_bytes, stream));      // rows that only pad a block read as zero
-  moe_count_kernel<<<(slots + 255) / 256, 256, 0, stream>>>(ids, slots, expert_lo, experts, ws.h.counts);
+  moe_count_kernel<<<(slots + kCountSlotsPerCta - 1) / kCountSlotsPerCta, 256, 0, stream>>>(ids, slots, expert_lo,
+                                                                                              experts, ws.h.counts);
   moe_scan_kernel<<<1, 1024, 0, stream>>>(ws.h, experts, ws.max_m_blocks);
   moe_scatter_quant_kernel<128><<<static_cast<unsigned>(tokens), 128, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), ids, ws.h, ws.xq, ws.xq_sf, hidden, top_k, expert_lo, experts, max_rows);
@@ -480,12 +501,21 @@ ep_stage_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids
 
 __global__ void ep_count_kernel(PeerPtrs peers, size_t tok_ids_off, int slots_per_rank, int world, int expert_lo,
                                 int experts, int* counts) {
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= slots_per_rank * world) return;
-  const int src = i / slots_per_rank;
-  const int* ids = reinterpret_cast<const int*>(peers.p[src] + tok_ids_off);
-  const int e = ids[i - src * slots_per_rank] - expert_lo;
-  if (e >= 0 && e < experts) atomicAdd(counts + e, 1);
+  __shared__ int s_hist[1024];
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) s_hist[e] = 0;
+  __syncthreads();
+  const int total = slots_per_rank * world;
+  const int first = blockIdx.x * kCountSlotsPerCta;
+  const int last = min(total, first + kCountSlotsPerCta);
+  for (int i = first + threadIdx.x; i < last; i += blockDim.x) {
+    const int src = i / slots_per_rank;
+    const int* ids = reinterpret_cast<const int*>(peers.p[src] + tok_ids_off);
+    const int e = ids[i - src * slots_per_rank] - expert_lo;
+    if (e >= 0 && e < experts) atomicAdd(s_hist + e, 1);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts; e += blockDim.x)
+    if (s_hist[e] != 0) atomicAdd(counts + e, s_hist[e]);
 }
 
 // one CTA per token of ANY rank: rows for its local slots, then the quantised row is pulled from its owner
@@ -647,8 +677,8 @@ int moe_ep_compute(const void* const* peer_buffers, int rank, int world, const v
   const int max_rows = L.max_m_blocks * 128;
   B200_CUDA(cudaMemsetAsync(h.counts, 0, sizeof(int) * experts_local, stream));
   B200_CUDA(cudaMemsetAsync(b + L.xq_sf, 0, L.xq_sf_bytes, stream));
-  ep_count_kernel<<<(total_slots + 255) / 256, 256, 0, stream>>>(peers, L.tok_ids, slots_per_rank, world, expert_lo,
-                                                                experts_local, h.counts);
+  ep_count_kernel<<<(total_slots + kCountSlotsPerCta - 1) / kCountSlotsPerCta, 256, 0, stream>>>(
+      peers, L.tok_ids, slots_per_rank, world, expert_lo, experts_local, h.counts);
   moe_scan_kernel<<<1, 1024, 0, stream>>>(h, experts_local, L.max_m_blocks);
   ep_gather_kernel<128><<<static_cast<unsigned>(tokens_local * world), 128, 0, stream>>>(
       peers, L, h, row_dst, b + L.xq, b + L.xq_sf, static_cast<int>(tokens_local), hidden, top_k, expert_lo,
