@@ -67,14 +67,18 @@ def test_expert_parallel_two_gpus_matches_single_gpu(b200, tmp_path):
     w = _dev_weights(w1c, w1s, w2c, w2s, slice(0, experts), "cuda")
     single = b200.b12x_fused_moe(x.cuda(), w["w1"], w["w1_sf"], w["w2"], w["w2_sf"], ids.cuda(), wts.cuda(), experts,
                                  top_k, w1_alpha=w["w1_alpha"]).cpu()
+    single_f32_rows = b200.b12x_fused_moe(x.cuda(), w["w1"], w["w1_sf"], w["w2"], w["w2_sf"], ids.cuda(), wts.cuda(),
+                                          experts, top_k, w1_alpha=w["w1_alpha"],
+                                          slot_rows_dtype=torch.float32).cpu()
     ref = O.moe_ref(x, w1c, w1s, w2c, w2s, ids, wts, np.full(experts, 0.02, np.float32))
     for kind in ("collective", "peer"):
         got = torch.cat([torch.load(os.path.join(tmp_path, f"out_{kind}{r}.pt")) for r in range(world)])
         if kind == "peer":
-            # same rows, same slot order, same single rounding as on one GPU
+            # same bf16 per-slot rows, same slot order, same single rounding as on one GPU
             assert torch.equal(got, single), "peer-memory expert parallelism differs from the single-GPU result"
         else:
-            # same per-slot rows; only the f32 summation order across ranks differs from slot order
-            err = torch.linalg.vector_norm(got.float() - single.float()) / torch.linalg.vector_norm(single.float())
+            # same f32 per-slot rows; only the f32 summation order across ranks differs from slot order
+            base = single_f32_rows.float()
+            err = torch.linalg.vector_norm(got.float() - base) / torch.linalg.vector_norm(base)
             assert err <= 2e-3, float(err)
         assert torch.linalg.vector_norm(got.float() - ref.float()) / torch.linalg.vector_norm(ref.float()) <= 1e-2
