@@ -120,7 +120,7 @@ struct MoeHeader {           // all int32, contiguous
 
 // rows per local expert: a histogram per CTA in shared memory (experts <= 1024), then one global add per
 // expert that the CTA saw
-constexpr int kCountSlotsPerCta = 4096;
+constexpr int kCountSlotsPerCta = 1024;
 __global__ void moe_count_kernel(const int* __restrict__ ids, int n_slots, int expert_lo, int experts, int* counts) {
   __shared__ int s_hist[1024];
   for (int e = threadIdx.x; e < experts; e += blockDim.x) s_hist[e] = 0;

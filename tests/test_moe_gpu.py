@@ -133,7 +133,7 @@ def test_hot_expert_and_expert_parallel_split(b200):
 
 def test_router_matches_oracle(b200):
     torch.manual_seed(0)
-    for tokens, experts, k in [(1, 8, 2), (64, 128, 8), (333, 256, 8), (50, 40, 5)]:
+    for tokens, experts, k in [(1, 8, 2), (64, 128, 8), (333, 256, 8), (50, 40, 5), (77, 300, 6), (9, 1024, 8)]:
         logits = torch.randn(tokens, experts)
         ids_ref, w_ref = O.route_topk_ref(logits, k)
         ids, w = b200.topk_route(logits.cuda(), k)
