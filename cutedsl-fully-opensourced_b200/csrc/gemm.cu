@@ -179,6 +179,8 @@ int gemm_dense_typed(const void* a, const void* b, const void* sfa, const void* 
   rc = device_status_word(&p.status);
   if (rc) return rc;
   EpilogueStore<OutT> epi{static_cast<OutT*>(c), n, alpha, 0};
+  // few waves of tiles: walk row blocks first (measured 3-4 % faster at 4096^3 and M = 1024, 2 % slower at 8192^3)
+  p.row_block_major = static_cast<int64_t>(p.num_m_blocks) * ((n + tile_n - 1) / tile_n) <= 8 * sm_count_of_current_device();
   if (tile_n == 256) {
     p.num_n_blocks = (n + 255) / 256;
     return launch_gemm<256, false>(ta, tb, p, epi, p.num_m_blocks * p.num_n_blocks, stream);
