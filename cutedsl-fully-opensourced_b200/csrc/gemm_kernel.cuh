@@ -86,9 +86,13 @@ struct GemmParams {
 struct SmemLayout {
   int stages;
   uint32_t a_bytes, b_bytes, sfa_bytes, sfb_bytes, stage_bytes, total;
+  uint32_t epi_stage_bytes;    // per epilogue warp: its 32 rows of the output tile, parked for a TMA store (0 = none)
 };
+constexpr uint32_t kBarrierBytes = 512;
 
-template <int kBlockN, bool kSwigluB = false>
+// kOutBytes: element size of an output tile that leaves through shared memory and a TMA store (128-wide plain
+// tiles only; 0 = the epilogue stores from registers)
+template <int kBlockN, bool kSwigluB = false, int kOutBytes = 0>
 __host__ __device__ constexpr SmemLayout smem_layout() {
   SmemLayout s{};
   s.a_bytes = kBlockM * 128;
@@ -97,8 +101,10 @@ __host__ __device__ constexpr SmemLayout smem_layout() {
   // whole 128-row slabs, also for 64-row pieces; the up and gate pieces of a SwiGLU tile sit in different slabs
   s.sfb_bytes = (kSwigluB ? 2 : (kBlockN >= 128 ? kBlockN / 128 : 1)) * 2048;
   s.stage_bytes = s.a_bytes + s.b_bytes + s.sfa_bytes + s.sfb_bytes;
-  s.stages = kBlockN == 256 ? 4 : (kBlockN == 128 ? (kSwigluB ? 5 : 6) : 7);
-  s.total = s.stages * s.stage_bytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
+  s.epi_stage_bytes = (kBlockN == 128 && !kSwigluB) ? 32u * 128u * kOutBytes : 0u;
+  s.stages = kBlockN == 256 ? 4 : (kBlockN == 128 ? (kSwigluB ? 5 : (kOutBytes == 0 ? 6 : (kOutBytes == 4 ? 4 : 5))) : 7);
+  s.total = s.stages * s.stage_bytes + 1024 /*alignment slack*/ + kBarrierBytes +
+            (s.epi_stage_bytes != 0 ? 1024 + 4 * s.epi_stage_bytes : 0);
   return s;
 }
 
@@ -145,11 +151,75 @@ struct EpilogueStore {
   const float* alpha;           // one scale, or one per group (alpha_per_group); null = 1
   int alpha_per_group;
 
+  static constexpr int kOutBytes = static_cast<int>(sizeof(OutT));
+
+  // The warp parks its 32 rows of the tile in shared memory (boxes of 32 rows x 128 bytes in the 128-byte
+  // swizzle of the tensor map) and one lane hands them to TMA stores: the accumulator is free as soon as it has
+  // been read, and the rows leave as whole lines while the next tile is computed.  Stores from registers put
+  // every lane on another output row, which an SM sustains at about 11 bytes per cycle only.
+  template <int kBlockN, typename Loader>
+  __device__ __forceinline__ void tma_path(const GemmParams& p, int m_blk, int n_blk, int row, float scale,
+                                           Loader&& load, uint8_t* stage, const CUtensorMap* cmap) const {
+    constexpr int kBoxCols = 128 / static_cast<int>(sizeof(OutT));     // columns in the 128 bytes of a box row
+    constexpr int kBoxes = kBlockN / kBoxCols;
+    const int lane = row & 31;
+    if (lane == 0) ptx::bulk_wait_group_read0();      // the previous tile's stores have read this memory
+    __syncwarp();
+#pragma unroll
+    for (int b = 0; b < kBoxes; ++b) {
+      uint8_t* box = stage + b * 4096 + lane * 128;
+#pragma unroll
+      for (int h = 0; h < kBoxCols / 32; ++h) {
+        uint32_t r[32];
+        load(b * kBoxCols + 32 * h, r);
+        if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            uint4 v;
+            v.x = __float_as_uint(__uint_as_float(r[4 * q]) * scale);
+            v.y = __float_as_uint(__uint_as_float(r[4 * q + 1]) * scale);
+            v.z = __float_as_uint(__uint_as_float(r[4 * q + 2]) * scale);
+            v.w = __float_as_uint(__uint_as_float(r[4 * q + 3]) * scale);
+            *reinterpret_cast<uint4*>(box + ((q ^ (lane & 7)) << 4)) = v;
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 v;
+            v.x = Pair16<OutT>::pack(__uint_as_float(r[8 * q]) * scale, __uint_as_float(r[8 * q + 1]) * scale);
+            v.y = Pair16<OutT>::pack(__uint_as_float(r[8 * q + 2]) * scale, __uint_as_float(r[8 * q + 3]) * scale);
+            v.z = Pair16<OutT>::pack(__uint_as_float(r[8 * q + 4]) * scale, __uint_as_float(r[8 * q + 5]) * scale);
+            v.w = Pair16<OutT>::pack(__uint_as_float(r[8 * q + 6]) * scale, __uint_as_float(r[8 * q + 7]) * scale);
+            *reinterpret_cast<uint4*>(box + (((4 * h + q) ^ (lane & 7)) << 4)) = v;
+          }
+        }
+      }
+    }
+    ptx::fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      const int y = m_blk * kBlockM + (row & ~31);
+#pragma unroll
+      for (int b = 0; b < kBoxes; ++b) {
+        const int col = n_blk * kBlockN + b * kBoxCols;
+        if (col < p.n_cols && y < p.m_rows)
+          ptx::tma_store_2d(cmap, col * static_cast<int>(sizeof(OutT)), y, ptx::smem_u32(stage + b * 4096));
+      }
+      ptx::bulk_commit_group();
+    }
+  }
+
   // part / parts: which share of the tile's columns this warp drains (two warps per TMEM quarter when parts == 2)
+  // stage / cmap: the warp's parking space and the tensor map of the output for the TMA-store variant, or null
   template <int kBlockN, typename Loader>
   __device__ __forceinline__ void operator()(const GemmParams& p, int m_blk, int n_blk, int group, int row,
-                                             int rows_valid, int part, int parts, Loader&& load) const {
+                                             int rows_valid, int part, int parts, Loader&& load,
+                                             uint8_t* stage = nullptr, const CUtensorMap* cmap = nullptr) const {
     const float scale = alpha == nullptr ? 1.0f : __ldg(alpha + (alpha_per_group ? group : 0));
+    if (stage != nullptr) {
+      tma_path<kBlockN>(p, m_blk, n_blk, row, scale, load, stage, cmap);
+      return;
+    }
     const int64_t grow = static_cast<int64_t>(m_blk) * kBlockM + row;
     const bool row_ok = grow < p.m_rows && row < rows_valid;
     OutT* crow = c + grow * ldc + static_cast<int64_t>(n_blk) * kBlockN;
@@ -205,6 +275,7 @@ struct EpilogueStore {
 // act = bf16(silu(gate) * up), re-quantised to NVFP4 with the MoE activation packer
 // (tests/python/test_flashinfer_b12x_verbatim.py:214-218) and written as the A operand of FC2.
 struct EpilogueSwiglu {
+  static constexpr int kOutBytes = 0;     // stores from registers
   uint8_t* act_codes;           // [m_rows, inter/2]
   uint8_t* act_sf;              // tiled [m_tiles][rk2][512], rk2 = ceil(inter/64)
   const float* w1_alpha;        // per group
@@ -213,7 +284,8 @@ struct EpilogueSwiglu {
 
   template <int kBlockN, typename Loader>
   __device__ __forceinline__ void operator()(const GemmParams& p, int m_blk, int n_blk, int group, int row,
-                                             int rows_valid, int part, int parts, Loader&& load) const {
+                                             int rows_valid, int part, int parts, Loader&& load,
+                                             uint8_t* /*stage*/ = nullptr, const CUtensorMap* /*cmap*/ = nullptr) const {
     constexpr int kHalf = kBlockN / 2;
     static_assert(kHalf % 64 == 0, "the SwiGLU epilogue pairs two halves of whole 32-column groups per warp");
     const float a1 = w1_alpha == nullptr ? 1.0f : __ldg(w1_alpha + group);
@@ -260,8 +332,8 @@ struct EpilogueSwiglu {
 template <int kBlockN, bool kSwigluB, typename Epilogue>
 __global__ void __launch_bounds__(gemm_threads(kBlockN, kSwigluB), 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                  const GemmParams p, const Epilogue epi) {
-  constexpr SmemLayout L = smem_layout<kBlockN, kSwigluB>();
+                  const __grid_constant__ CUtensorMap tmap_c, const GemmParams p, const Epilogue epi) {
+  constexpr SmemLayout L = smem_layout<kBlockN, kSwigluB, Epilogue::kOutBytes>();
   constexpr int kStages = L.stages;
   constexpr int kAccStages = kBlockN == 256 ? 1 : 2;
   constexpr int kBPieces = kSwigluB ? 2 : (kBlockN >= 128 ? kBlockN / 128 : 1);
@@ -312,6 +384,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
+    if (L.epi_stage_bytes != 0) ptx::prefetch_tensormap(&tmap_c);
   }
   if (warp == 0) {
     __syncwarp();
@@ -518,16 +591,25 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc.stage * kBlockN;
       const int rows_valid = p.m_block_rows != nullptr ? __ldg(p.m_block_rows + m_blk) : kBlockM;
       if (quarter * 32 < rows_valid) {                 // a warp whose 32 rows only pad the block has nothing to do
+        // parking space of the TMA-store variant: 1024-byte aligned, one slice per epilogue warp
+        uint8_t* stage = nullptr;
+        if constexpr (L.epi_stage_bytes != 0) {
+          const uint32_t off = ((kStages * L.stage_bytes + kBarrierBytes + 1023u) & ~1023u) + (warp - 2) * L.epi_stage_bytes;
+          stage = smem_gen + off;
+        }
         epi.template operator()<kBlockN>(p, m_blk, n_blk, group, row, rows_valid, part, kParts,
                                          [&](int c0, uint32_t (&r)[32]) {
                                            ptx::tmem_ld_32x32(t_acc + c0, r);
                                            ptx::tmem_ld_wait();
-                                         });
+                                         },
+                                         stage, &tmap_c);
       }
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(acc_empty_bar(acc.stage));
       acc.advance(kAccStages);
     }
+    // the TMA stores of this warp's last tiles must have left shared memory and reached global memory
+    if (L.epi_stage_bytes != 0 && lane == 0) ptx::bulk_wait_group0();
   }
 
   // ---- teardown: everybody meets, then the allocating warp frees tensor memory
