@@ -496,7 +496,7 @@ def main():
     ap.add_argument("--nk", type=int, default=None, help="gemm: override N = K (small profiling cases)")
     ap.add_argument("--tile-n", type=int, default=0, help="gemm: force the 128- or 256-wide tile")
     ap.add_argument("--cuda-graph", action="store_true",
-                    help="moe: capture one step in a CUDA graph after warm-up and replay it in the timed region")
+                    help="moe, gemm: capture a step in a CUDA graph after warm-up and replay it in the timed region")
     ap.add_argument("--tokens", type=int, default=None, help="moe: override the token count (decode: 1 / 8 / 64)")
     args = ap.parse_args()
 
@@ -556,6 +556,22 @@ def main():
         with torch.cuda.graph(graph):
             wl.step()
         step_fn, launch_mode = graph.replay, "cuda graph replay"
+    elif args.cuda_graph and args.workload == "gemm":
+        # one graph per rotating operand set (a graph pins its pointers)
+        torch.cuda.synchronize()
+        graphs = []
+        for i in range(wl.sets):
+            wl.i = i
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                wl.step()
+            graphs.append(g)
+        turn = [0]
+
+        def replay_next():
+            graphs[turn[0] % len(graphs)].replay()
+            turn[0] += 1
+        step_fn, launch_mode = replay_next, "cuda graph replay"
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:

@@ -104,11 +104,11 @@ int device_status_word(int** out) {
 }
 
 // tc: tensor map of the output for the variants whose tiles leave through TMA stores (others never touch it)
-template <int kBlockN, bool kSwigluB, typename Epilogue>
+template <int kBlockN, bool kSwigluB, int kARows = 128, typename Epilogue>
 int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                 const Epilogue& epi, int max_tiles, cudaStream_t stream) {
-  auto kern = nvfp4_gemm_kernel<kBlockN, kSwigluB, Epilogue>;
-  constexpr SmemLayout L = smem_layout<kBlockN, kSwigluB, Epilogue::kOutBytes>();
+  auto kern = nvfp4_gemm_kernel<kBlockN, kSwigluB, Epilogue, kARows>;
+  constexpr SmemLayout L = smem_layout<kBlockN, kSwigluB, Epilogue::kOutBytes, kARows>();
   static bool configured = false;      // per instantiation
   if (!configured) {
     B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L.total)));
@@ -261,7 +261,8 @@ int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, v
 int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* w1_sf, void* act_codes, void* act_sf,
                  const float* w1_alpha, const float* fc2_input_scale, const int* num_m_blocks_dev,
                  const int* m_block_expert, const int* m_block_rows, int max_m_blocks, int hidden, int inter,
-                 int experts, int* status, cudaStream_t stream) {
+                 int experts, int few_rows, int* status, cudaStream_t stream) {
+  // few_rows: no row block holds more than 32 rows (the caller knows: at most 32 tokens) -> stages of 32 rows of A
   // Tile width: [up 64 | gate 64] tiles have two accumulators, so the SwiGLU + re-quantisation epilogue of one
   // tile runs under the MMAs of the next; [up 128 | gate 128] tiles have one accumulator but half the MMAs per
   // flop.  The epilogue costs the same per output column either way, the MMAs scale with the reduction length:
@@ -272,7 +273,8 @@ int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* 
   }();
   const bool narrow = forced_tile == 128 || (forced_tile != 256 && hidden <= 4096);
   CUtensorMap ta, tb;
-  int rc = make_operand_map(&ta, xq, static_cast<int64_t>(max_m_blocks) * 128, hidden, 0);
+  const bool small_a = few_rows != 0 && !narrow;
+  int rc = make_operand_map(&ta, xq, static_cast<int64_t>(max_m_blocks) * 128, hidden, 0, small_a ? 32 : 128);
   if (rc) return rc;
   rc = make_operand_map(&tb, w1, 2 * inter, hidden, experts, narrow ? 64 : 128);
   if (rc) return rc;
@@ -298,6 +300,7 @@ int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* 
     p.num_n_blocks = inter / 64;
     return launch_gemm<128, true>(ta, tb, CUtensorMap{}, p, epi, max_m_blocks * p.num_n_blocks, stream);
   }
+  if (small_a) return launch_gemm<256, true, 32>(ta, tb, CUtensorMap{}, p, epi, max_m_blocks * p.num_n_blocks, stream);
   return launch_gemm<256, true>(ta, tb, CUtensorMap{}, p, epi, max_m_blocks * p.num_n_blocks, stream);
 }
 
@@ -307,10 +310,12 @@ int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* 
 template <typename RowT>
 int gemm_moe_fc2_typed(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, RowT* partial,
                        const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
-                       const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int* status,
-                       cudaStream_t stream) {
+                       const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int few_rows,
+                       int* status, cudaStream_t stream) {
   CUtensorMap ta, tb;
-  int rc = make_operand_map(&ta, act_codes, static_cast<int64_t>(max_m_blocks) * 128, inter, 0);
+  const bool wide = hidden % 256 == 0 && (inter + kBlockK - 1) / kBlockK > 4;
+  const bool small_a = few_rows != 0 && wide;
+  int rc = make_operand_map(&ta, act_codes, static_cast<int64_t>(max_m_blocks) * 128, inter, 0, small_a ? 32 : 128);
   if (rc) return rc;
   rc = make_operand_map(&tb, w2, hidden, inter, experts);
   if (rc) return rc;
@@ -336,9 +341,9 @@ int gemm_moe_fc2_typed(const void* act_codes, const void* act_sf, const void* w2
   if (rc) return rc;
   // Short reductions (few K tiles) spend more time draining the accumulator than filling it; the
   // 128-wide tile has two accumulators, so its epilogue overlaps the next tile's MMAs.
-  const bool wide = hidden % 256 == 0 && p.num_k_tiles > 4;
   if (wide) {
     p.num_n_blocks = hidden / 256;
+    if (small_a) return launch_gemm<256, false, 32>(ta, tb, tc, p, epi, max_m_blocks * p.num_n_blocks, stream);
     return launch_gemm<256, false>(ta, tb, tc, p, epi, max_m_blocks * p.num_n_blocks, stream);
   }
   p.num_n_blocks = (hidden + 127) / 128;
@@ -347,14 +352,15 @@ int gemm_moe_fc2_typed(const void* act_codes, const void* act_sf, const void* w2
 
 int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, void* partial,
                  int rows_bf16, const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
-                 const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int* status,
-                 cudaStream_t stream) {
+                 const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int few_rows,
+                 int* status, cudaStream_t stream) {
   if (rows_bf16)
     return gemm_moe_fc2_typed(act_codes, act_sf, w2, w2_sf, static_cast<__nv_bfloat16*>(partial), w2_alpha,
                               num_m_blocks_dev, m_block_expert, m_block_rows, max_m_blocks, hidden, inter, experts,
-                              status, stream);
+                              few_rows, status, stream);
   return gemm_moe_fc2_typed(act_codes, act_sf, w2, w2_sf, static_cast<float*>(partial), w2_alpha, num_m_blocks_dev,
-                            m_block_expert, m_block_rows, max_m_blocks, hidden, inter, experts, status, stream);
+                            m_block_expert, m_block_rows, max_m_blocks, hidden, inter, experts, few_rows, status,
+                            stream);
 }
 
 }  // namespace b200fp4

@@ -56,6 +56,7 @@ enum GemmStatusBits : int {
   kStatusTimeoutProducer = 1,
   kStatusTimeoutMma = 2,
   kStatusTimeoutEpilogue = 4,
+  kStatusRowsExceedTile = 8,    // a few-row launch met a row block with more rows than it loads
 };
 
 struct GemmParams {
@@ -92,17 +93,20 @@ constexpr uint32_t kBarrierBytes = 512;
 
 // kOutBytes: element size of an output tile that leaves through shared memory and a TMA store (128-wide plain
 // tiles only; 0 = the epilogue stores from registers)
-template <int kBlockN, bool kSwigluB = false, int kOutBytes = 0>
+// kARows: rows of A that a stage holds.  Below 128 (256-wide tiles of launches whose row blocks all hold that few
+// rows: decode) the MMA still reads 128 rows -- the rest of its A operand is whatever follows in the stage, times
+// scale factors that are zero for rows without data -- and the shared memory saved buys another stage of B.
+template <int kBlockN, bool kSwigluB = false, int kOutBytes = 0, int kARows = 128>
 __host__ __device__ constexpr SmemLayout smem_layout() {
   SmemLayout s{};
-  s.a_bytes = kBlockM * 128;
+  s.a_bytes = kARows * 128;
   s.b_bytes = kBlockN * 128;
   s.sfa_bytes = 2048;
   // whole 128-row slabs, also for 64-row pieces; the up and gate pieces of a SwiGLU tile sit in different slabs
   s.sfb_bytes = (kSwigluB ? 2 : (kBlockN >= 128 ? kBlockN / 128 : 1)) * 2048;
   s.stage_bytes = s.a_bytes + s.b_bytes + s.sfa_bytes + s.sfb_bytes;
   s.epi_stage_bytes = (kBlockN == 128 && !kSwigluB) ? 32u * 128u * kOutBytes : 0u;
-  s.stages = kBlockN == 256 ? 4 : (kBlockN == 128 ? (kSwigluB ? 5 : (kOutBytes == 0 ? 6 : (kOutBytes == 4 ? 4 : 5))) : 7);
+  s.stages = kBlockN == 256 ? (kARows <= 32 ? 5 : 4) : (kBlockN == 128 ? (kSwigluB ? 5 : (kOutBytes == 0 ? 6 : (kOutBytes == 4 ? 4 : 5))) : 7);
   s.total = s.stages * s.stage_bytes + 1024 /*alignment slack*/ + kBarrierBytes +
             (s.epi_stage_bytes != 0 ? 1024 + 4 * s.epi_stage_bytes : 0);
   return s;
@@ -329,11 +333,12 @@ struct EpilogueSwiglu {
 // kSwigluB: B tile = two pieces of kBlockN/2 rows (up rows, gate rows); otherwise consecutive 128-row pieces
 // (one 64-row piece for 64-wide tiles).
 // ----------------------------------------------------------------------------
-template <int kBlockN, bool kSwigluB, typename Epilogue>
+template <int kBlockN, bool kSwigluB, typename Epilogue, int kARows = 128>
 __global__ void __launch_bounds__(gemm_threads(kBlockN, kSwigluB), 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_c, const GemmParams p, const Epilogue epi) {
-  constexpr SmemLayout L = smem_layout<kBlockN, kSwigluB, Epilogue::kOutBytes>();
+  static_assert(kARows == 128 || (kBlockN == 256 && kARows == 32), "few-row stages exist for 256-wide tiles");
+  constexpr SmemLayout L = smem_layout<kBlockN, kSwigluB, Epilogue::kOutBytes, kARows>();
   constexpr int kStages = L.stages;
   constexpr int kAccStages = kBlockN == 256 ? 1 : 2;
   constexpr int kBPieces = kSwigluB ? 2 : (kBlockN >= 128 ? kBlockN / 128 : 1);
@@ -418,6 +423,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
 #pragma unroll
           for (int i = 0; i < kBPieces; ++i) b_row[i] = n_blk * kBlockN + kBPieceRows * i;
         }
+        if (kARows < kBlockM && p.m_block_rows != nullptr && __ldg(p.m_block_rows + m_blk) > kARows)
+          atomicOr(p.status, kStatusRowsExceedTile);      // results of this block are wrong: tell the host
         for (int kt = 0; kt < p.num_k_tiles; ++kt) {
           if (!wait_bounded(empty_bar(st.stage), st.phase ^ 1u, abort_flag)) {
             atomicOr(p.status, kStatusTimeoutProducer);

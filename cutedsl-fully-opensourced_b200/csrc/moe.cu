@@ -23,12 +23,11 @@ namespace b200fp4 {
 int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* w1_sf, void* act_codes, void* act_sf,
                  const float* w1_alpha, const float* fc2_input_scale, const int* num_m_blocks_dev,
                  const int* m_block_expert, const int* m_block_rows, int max_m_blocks, int hidden, int inter,
-                 int experts, int* status, cudaStream_t stream);
+                 int experts, int few_rows, int* status, cudaStream_t stream);
 int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, void* partial,
-                 int rows_bf16,
-                 const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
-                 const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int* status,
-                 cudaStream_t stream);
+                 int rows_bf16, const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
+                 const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int few_rows,
+                 int* status, cudaStream_t stream);
 
 namespace {
 
@@ -382,11 +381,16 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
   moe_scatter_quant_kernel<128><<<static_cast<unsigned>(tokens), 128, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(x), ids, ws.h, ws.xq, ws.xq_sf, hidden, top_k, expert_lo, experts, max_rows);
   B200_CUDA(cudaGetLastError());
+  // With at most 32 tokens no expert receives more than 32 rows (a token names an expert once, as top-k selection
+  // does): the wide GEMM variants then keep 32 rows of A per stage and one more stage of weights in flight.  A
+  // row block that breaks the assumption raises bit 8 of the device status word instead of passing unnoticed.
+  const int few_rows = tokens <= 32;
   int rc = gemm_moe_fc1(ws.xq, ws.xq_sf, w1, w1_sf, ws.act, ws.act_sf, w1_alpha, fc2_input_scale, ws.h.num_m_blocks,
-                        ws.h.m_block_expert, ws.h.m_block_rows, ws.max_m_blocks, hidden, inter, experts, status, stream);
+                        ws.h.m_block_expert, ws.h.m_block_rows, ws.max_m_blocks, hidden, inter, experts, few_rows,
+                        status, stream);
   if (rc) return rc;
   rc = gemm_moe_fc2(ws.act, ws.act_sf, w2, w2_sf, ws.partial, rows_bf16, w2_alpha, ws.h.num_m_blocks, ws.h.m_block_expert,
-                    ws.h.m_block_rows, ws.max_m_blocks, hidden, inter, experts, status, stream);
+                    ws.h.m_block_rows, ws.max_m_blocks, hidden, inter, experts, few_rows, status, stream);
   if (rc) return rc;
   const int threads = hidden / 4 >= 256 ? 256 : 128;
   if (out_dtype == 2) {
@@ -684,13 +688,14 @@ int moe_ep_compute(const void* const* peer_buffers, int rank, int world, const v
       peers, L, h, row_dst, b + L.xq, b + L.xq_sf, static_cast<int>(tokens_local), hidden, top_k, expert_lo,
       experts_local, max_rows);
   B200_CUDA(cudaGetLastError());
+  const int few_rows = tokens_local * world <= 32;
   rc = gemm_moe_fc1(b + L.xq, b + L.xq_sf, w1, w1_sf, b + L.act, b + L.act_sf, w1_alpha, fc2_input_scale,
                     h.num_m_blocks, h.m_block_expert, h.m_block_rows, L.max_m_blocks, hidden, inter, experts_local,
-                    status, stream);
+                    few_rows, status, stream);
   if (rc) return rc;
   rc = gemm_moe_fc2(b + L.act, b + L.act_sf, w2, w2_sf, b + L.partial, /*rows_bf16=*/1, w2_alpha,
                     h.num_m_blocks, h.m_block_expert, h.m_block_rows, L.max_m_blocks, hidden, inter, experts_local,
-                    status, stream);
+                    few_rows, status, stream);
   if (rc) return rc;
   ep_return_rows_kernel<<<static_cast<unsigned>(max_rows), 256, 0, stream>>>(
       reinterpret_cast<const __nv_bfloat16*>(b + L.partial), row_dst, h.num_m_blocks, h.m_block_rows, hidden);

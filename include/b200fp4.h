@@ -144,7 +144,8 @@ int b200fp4_moe_ep_combine(const void* const* peer_buffers, int rank, int world,
 
 /* Kernels never trap: a device-side wait that exceeds its bound ORs a bit into a per-device
  * status word and the kernel returns.  This call synchronises the stream and copies the word
- * to *status_out (0 = healthy; 1/2/4 = GEMM producer / MMA / epilogue wait expired), clearing
+ * to *status_out (0 = healthy; 1/2/4 = GEMM producer / MMA / epilogue wait expired; 8 = a fused-MoE call with
+ * at most 32 tokens named one expert more than 32 times: those rows are wrong), clearing
  * it when clear != 0.  No counterpart in the reference, whose kernels wait without bounds. */
 int b200fp4_device_status(void* stream, int* status_out, int clear);
 

@@ -190,3 +190,19 @@ def test_prefill_config_sampled_tokens(b200):
     sample = torch.arange(0, tokens, 171)[:24]
     ref = O.moe_ref(x[sample], w1c, w1s, w2c, w2s, ids[sample], wts[sample], a1.numpy())
     assert rel_l2(out.cpu()[sample], ref) <= 1e-2
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 32, 40])
+def test_decode_shapes_wide_tiles(b200, tokens):
+    """Few tokens, long reductions (hidden 4352 > 4096, intermediate 1280): FC1 and FC2 take their 256-wide
+    tiles; with at most 32 tokens they keep 32 rows of A per stage, with 40 the full 128."""
+    experts, hidden, inter, top_k = 6, 4352, 1280, 3
+    rng = np.random.default_rng(100 + tokens)
+    torch.manual_seed(tokens)
+    w1c, w1s, w2c, w2s = random_weights(rng, experts, hidden, inter)
+    x = torch.randn(tokens, hidden).to(torch.bfloat16)
+    ids, wts = O.route_topk_ref(torch.randn(tokens, experts), top_k)
+    a1 = torch.full((experts,), 0.01)
+    ref = O.moe_ref(x, w1c, w1s, w2c, w2s, ids, wts, a1.numpy())
+    out = run_gpu(b200, x, w1c, w1s, w2c, w2s, ids, wts.contiguous(), w1_alpha=a1.cuda())
+    assert rel_l2(out, ref) <= 1e-2
