@@ -270,6 +270,66 @@ __global__ void moe_combine_kernel(const RowT* __restrict__ partial, const int* 
   }
 }
 
+// The same for few tokens: CTA (token, column chunk), every thread owns 4 output columns and reads the k rows
+// with independent loads (a decode step with one token is nothing but the latency of these reads; with thousands
+// of tokens the plain kernel above is faster).
+template <typename OutT, typename RowT>
+__global__ void moe_combine_few_kernel(const RowT* __restrict__ partial, const int* __restrict__ slot_row,
+                                   const float* __restrict__ weights, OutT* __restrict__ out, int hidden,
+                                   int top_k, int accumulate) {
+  __shared__ int s_rows[64];
+  __shared__ float s_w[64];
+  const int token = blockIdx.x;
+  if (threadIdx.x < top_k) {
+    s_rows[threadIdx.x] = slot_row[static_cast<int64_t>(token) * top_k + threadIdx.x];
+    s_w[threadIdx.x] = weights[static_cast<int64_t>(token) * top_k + threadIdx.x];
+  }
+  __syncthreads();
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (c >= hidden) return;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int j0 = 0; j0 < top_k; j0 += 8) {
+    float4 pv[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int row = j0 + u < top_k ? s_rows[j0 + u] : -1;
+      pv[u] = row >= 0 ? load_row4(partial + static_cast<int64_t>(row) * hidden + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (j0 + u < top_k && s_rows[j0 + u] >= 0) {      // slot order, one product and one sum per slot
+        const float w = s_w[j0 + u];
+        acc.x = __fadd_rn(acc.x, __fmul_rn(w, pv[u].x));
+        acc.y = __fadd_rn(acc.y, __fmul_rn(w, pv[u].y));
+        acc.z = __fadd_rn(acc.z, __fmul_rn(w, pv[u].z));
+        acc.w = __fadd_rn(acc.w, __fmul_rn(w, pv[u].w));
+      }
+    }
+  }
+  OutT* o = out + static_cast<int64_t>(token) * hidden + c;
+  if constexpr (sizeof(OutT) == 4) {
+    if (accumulate) {
+      const float4 prev = *reinterpret_cast<const float4*>(o);
+      acc.x += prev.x;
+      acc.y += prev.y;
+      acc.z += prev.z;
+      acc.w += prev.w;
+    }
+    *reinterpret_cast<float4*>(o) = acc;
+  } else {
+    if (accumulate) {
+      acc.x += __bfloat162float(o[0]);
+      acc.y += __bfloat162float(o[1]);
+      acc.z += __bfloat162float(o[2]);
+      acc.w += __bfloat162float(o[3]);
+    }
+    uint2 packed;
+    packed.x = Pair16<__nv_bfloat16>::pack(acc.x, acc.y);
+    packed.y = Pair16<__nv_bfloat16>::pack(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(o) = packed;
+  }
+}
+
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct MoeWorkspace {
@@ -393,7 +453,12 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
                     ws.h.m_block_rows, ws.max_m_blocks, hidden, inter, experts, few_rows, status, stream);
   if (rc) return rc;
   const int threads = hidden / 4 >= 256 ? 256 : 128;
-  if (out_dtype == 2) {
+  if (tokens <= 256 && out_dtype == 3) {
+    const dim3 cgrid(static_cast<unsigned>(tokens), (hidden / 4 + threads - 1) / threads);
+    moe_combine_few_kernel<__nv_bfloat16, __nv_bfloat16><<<cgrid, threads, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(ws.partial), ws.h.slot_row, route_w, static_cast<__nv_bfloat16*>(out),
+        hidden, top_k, accumulate);
+  } else if (out_dtype == 2) {
     moe_combine_kernel<float, float><<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
         ws.partial, ws.h.slot_row, route_w, static_cast<float*>(out), hidden, top_k, accumulate);
   } else if (rows_bf16) {
@@ -607,6 +672,39 @@ __global__ void ep_combine_kernel(const __nv_bfloat16* __restrict__ recv, const 
   }
 }
 
+// CTA (local token, column chunk): the token's k output rows have been delivered into this rank's own buffer
+__global__ void ep_combine_few_kernel(const __nv_bfloat16* __restrict__ recv, const float* __restrict__ weights,
+                                  __nv_bfloat16* __restrict__ out, int hidden, int top_k) {
+  __shared__ float s_w[64];
+  const int t = blockIdx.x;
+  if (threadIdx.x < top_k) s_w[threadIdx.x] = weights[static_cast<int64_t>(t) * top_k + threadIdx.x];
+  __syncthreads();
+  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (c >= hidden) return;
+  const __nv_bfloat16* rows = recv + static_cast<int64_t>(t) * top_k * hidden;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int j0 = 0; j0 < top_k; j0 += 8) {
+    float4 pv[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      pv[u] = j0 + u < top_k ? load_row4(rows + static_cast<int64_t>(j0 + u) * hidden + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (j0 + u < top_k) {
+        const float w = s_w[j0 + u];
+        acc.x = __fadd_rn(acc.x, __fmul_rn(w, pv[u].x));
+        acc.y = __fadd_rn(acc.y, __fmul_rn(w, pv[u].y));
+        acc.z = __fadd_rn(acc.z, __fmul_rn(w, pv[u].z));
+        acc.w = __fadd_rn(acc.w, __fmul_rn(w, pv[u].w));
+      }
+    }
+  }
+  uint2 packed;
+  packed.x = Pair16<__nv_bfloat16>::pack(acc.x, acc.y);
+  packed.y = Pair16<__nv_bfloat16>::pack(acc.z, acc.w);
+  *reinterpret_cast<uint2*>(out + static_cast<int64_t>(t) * hidden + c) = packed;
+}
+
 int ep_check(int64_t tokens_local, int hidden, int inter, int experts_local, int top_k, int world, int rank) {
   if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
     return fail(kInvalidArgument, "world=%d rank=%d (at most %d ranks)", world, rank, kMaxPeers);
@@ -715,9 +813,15 @@ int moe_ep_combine(const void* const* peer_buffers, int rank, int world, const i
   const EpLayout L = ep_layout(tokens_local, hidden, inter, experts_local, top_k, world);
   const int threads = hidden / 4 >= 256 ? 256 : 128;
   (void)ids;
-  ep_combine_kernel<<<static_cast<unsigned>(tokens_local), threads, 0, stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(peers.p[rank] + L.recv), weights, static_cast<__nv_bfloat16*>(out), hidden,
-      top_k);
+  if (tokens_local <= 256) {
+    ep_combine_few_kernel<<<dim3(static_cast<unsigned>(tokens_local), (hidden / 4 + threads - 1) / threads), threads, 0,
+                            stream>>>(reinterpret_cast<const __nv_bfloat16*>(peers.p[rank] + L.recv), weights,
+                                      static_cast<__nv_bfloat16*>(out), hidden, top_k);
+  } else {
+    ep_combine_kernel<<<static_cast<unsigned>(tokens_local), threads, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(peers.p[rank] + L.recv), weights, static_cast<__nv_bfloat16*>(out),
+        hidden, top_k);
+  }
   return check_cuda(cudaGetLastError(), "ep_combine_kernel launch");
 }
 
