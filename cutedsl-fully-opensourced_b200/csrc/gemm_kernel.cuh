@@ -13,11 +13,9 @@
 //           128 bytes, 128-byte swizzle), one per 128-row piece of B, and plain
 //           bulk copies of the scale-factor slabs (2 KB per 128 rows: four
 //           512-byte 128x4 tiles are contiguous in the tiled layout)
-//   warp 1 and the last warp  MMA issuers: per stage each issues four tcgen05.mma kind::mxf4nvf4
-//           (K = 64 each) for its half of the tile's columns into its half of a TMEM accumulator;
-//           tcgen05.commit releases the stage.  One thread cannot keep the tensor pipe busy with
-//           block-scaled MMAs (about 160 cycles between its instructions whatever their width, against
-//           128 cycles of pipe time for 128 x 256 x 64); two threads with half-width instructions do
+//   warp 1  MMA issuer: per stage four tcgen05.mma kind::mxf4nvf4 (K = 64 each) accumulate into a TMEM
+//           accumulator; tcgen05.commit releases the stage.  The whole warp walks the loop and an elected lane
+//           issues, so that the operands stay in warp-wide registers (see the role below)
 //   last 4 warps  scale-slab movers: shared memory -> registers -> tensor memory (tcgen05.st),
 //           one set of slab columns per stage.  tcgen05.cp would do the same copy, but it runs
 //           in the MMA pipe: twelve copies per stage cost a third of the kernel's time there
@@ -44,10 +42,8 @@ __host__ __device__ constexpr int epilogue_warps(int block_n, bool swiglu = fals
 }
 // ... + four warps (one per 32-lane quarter of tensor memory) that move the scale slabs of every K
 // tile from shared memory into tensor memory
-// ... + the second MMA issuer (tiles of 128 columns and more)
-__host__ __device__ constexpr int mma_issuers(int block_n) { return 1; }
 __host__ __device__ constexpr int gemm_threads(int block_n, bool swiglu = false) {
-  return 64 + 32 * epilogue_warps(block_n, swiglu) + 128 + (mma_issuers(block_n) == 2 ? 32 : 0);
+  return 64 + 32 * epilogue_warps(block_n, swiglu) + 128;
 }
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitLimitCycles = 4000000000LL;   // ~2 s at 2 GHz
@@ -349,11 +345,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   constexpr uint32_t kSfbColsPerKb = kBlockN >= 128 ? kBlockN / 32 : 4;
   constexpr uint32_t kSfaCol = kAccStages * kBlockN;            // TMEM columns: accumulators first
   constexpr uint32_t kSfSetCols = 16 + 4 * kSfbColsPerKb;       // columns of one set of scale slabs (SFA + SFB)
-  constexpr int kIssuers = mma_issuers(kBlockN);
-  constexpr int kIssueN = kBlockN / kIssuers;                   // columns per MMA instruction
-  constexpr uint32_t kIdesc = ptx::idesc_mxf4nvf4(kIssueN);
+  constexpr uint32_t kIdesc = ptx::idesc_mxf4nvf4(kBlockN);
   constexpr int kFirstSfWarp = 2 + kEpiWarps;
-  constexpr int kSecondMmaWarp = kFirstSfWarp + 4;
   static_assert(kSfaCol + kStages * kSfSetCols <= kTmemCols, "TMEM budget: one set of slab columns per stage");
 
   extern __shared__ uint8_t smem_raw[];
@@ -377,12 +370,12 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(full_bar(s), 1);
-      ptx::mbar_init(empty_bar(s), kIssuers);              // one commit per MMA issuer
+      ptx::mbar_init(empty_bar(s), 1);
       ptx::mbar_init(sf_full_bar(s), 4);                 // one arrival per slab-mover warp
       ptx::mbar_init(sf_loaded_bar(s), 1);
     }
     for (int s = 0; s < 2; ++s) {
-      ptx::mbar_init(acc_full_bar(s), kIssuers);
+      ptx::mbar_init(acc_full_bar(s), 1);
       ptx::mbar_init(acc_empty_bar(s), 32 * kEpiWarps);
     }
     *abort_flag = 0;
@@ -456,19 +449,18 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
       }
     }
-  } else if (warp == 1 || (kIssuers == 2 && warp == kSecondMmaWarp)) {
-    // =============================== MMA issuers ===============================
+  } else if (warp == 1) {
+    // =============================== MMA issuer ===============================
     // The whole warp walks the loop and one elected lane issues: every operand of the MMAs (descriptors,
     // tensor-memory addresses) is then the same in all lanes, which lets the compiler keep them in the
     // warp-wide registers the instructions read.  Computed in one lane only they must be moved there before
     // every MMA, and a lone thread spends about 110 cycles per MMA on that instead of 55 to 65.
     {
-      const uint32_t half = warp == 1 ? 0u : 1u;        // which half of the tile's columns (rows of B)
       PipeState st;
       PipeState acc;
       bool ok = true;
       const uint64_t a_desc0 = ptx::smem_desc_sw128(smem_base);
-      const uint64_t b_desc0 = ptx::smem_desc_sw128(smem_base + L.a_bytes + half * (kIssueN * 128));
+      const uint64_t b_desc0 = ptx::smem_desc_sw128(smem_base + L.a_bytes);
       const int last_kblocks = ((p.k - (p.num_k_tiles - 1) * kBlockK) + 63) >> 6;   // 64-wide steps of the last K tile
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         if (!wait_bounded(acc_empty_bar(acc.stage), acc.phase ^ 1u, abort_flag)) {
@@ -476,11 +468,11 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           break;
         }
         ptx::tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc.stage * kBlockN + half * kIssueN;
+        const uint32_t d_tmem = tmem_base + acc.stage * kBlockN;
         // a 64-wide tile uses half of a 128-row slab of B scale factors: its row groups start at column 0 or 2
         // (the movers of a SwiGLU tile with 64-row pieces have already picked the right halves)
         const uint32_t sfb_shift = kBlockN >= 128 ? 0u : static_cast<uint32_t>((tile_n(tile) * kBlockN & 127) >> 5);
-        const uint32_t sf_t0 = tmem_base + kSfaCol + 16 + half * (kIssueN / 32) + sfb_shift;
+        const uint32_t sf_t0 = tmem_base + kSfaCol + 16 + sfb_shift;
         for (int kt = 0; kt < p.num_k_tiles; ++kt) {
           // the slab movers have put this stage's scale factors into its set of TMEM columns (usually long
           // before the operands land), and the operand tiles are in shared memory

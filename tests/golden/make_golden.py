@@ -251,7 +251,9 @@ def gemm_cases():
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path to a checkout of the reference repository>")
+    ref_root = sys.argv[1]
     N = _load("ref_normtest", os.path.join(ref_root, "tests/python/test_flashinfer_norm_verbatim.py"))
     M = _load("ref_moetest", os.path.join(ref_root, "tests/python/test_flashinfer_b12x_verbatim.py"))
     torch.set_num_threads(max(1, os.cpu_count() or 1))

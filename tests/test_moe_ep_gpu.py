@@ -59,7 +59,7 @@ def _worker(rank, world, port, result_dir):
 
 def test_expert_parallel_two_gpus_matches_single_gpu(b200, tmp_path):
     if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs (run under `gpurun --gpus 2`)")
+        pytest.skip("needs two GPUs")
     import torch.multiprocessing as mp
     world, port = 2, 29600 + os.getpid() % 2000
     mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
