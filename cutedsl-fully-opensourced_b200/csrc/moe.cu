@@ -169,6 +169,99 @@ __global__ void moe_scan_kernel(MoeHeader h, int experts, int max_m_blocks) {
   }
 }
 
+// Few slots (<= 1024): count, scan and row assignment in one CTA -- one launch instead of a memset and three
+// kernels, which is most of a decode step's bookkeeping time.  Rows of an expert go to its slots in slot order.
+__global__ void __launch_bounds__(1024) moe_prepare_small_kernel(const int* __restrict__ ids, int n_slots, int expert_lo,
+                                                                 MoeHeader h, int experts, int max_m_blocks,
+                                                                 int max_rows) {
+  __shared__ int s_count[1024];
+  __shared__ int s_blocks[1024];
+  __shared__ int s_offset[1024];
+  __shared__ int s_expert[1024];
+  const int t = threadIdx.x;
+  s_count[t] = 0;
+  int e = -1, rank_in_expert = 0;
+  if (t < n_slots) {
+    e = ids[t] - expert_lo;
+    if (e < 0 || e >= experts) e = -1;
+  }
+  s_expert[t] = e;
+  __syncthreads();
+  // position of the slot among the slots of its expert, in slot order: count earlier slots with the same expert
+  if (e >= 0) {
+    atomicAdd(s_count + e, 1);
+    for (int i = 0; i < t; ++i) rank_in_expert += s_expert[i] == e;
+  }
+  __syncthreads();
+  const int count = t < experts ? s_count[t] : 0;
+  const int blocks = (count + 127) >> 7;
+  s_blocks[t] = blocks;
+  __syncthreads();
+  for (int o = 1; o < 1024; o <<= 1) {
+    const int add = t >= o ? s_blocks[t - o] : 0;
+    __syncthreads();
+    s_blocks[t] += add;
+    __syncthreads();
+  }
+  const int incl = s_blocks[t];
+  const int excl = incl - blocks;
+  s_offset[t] = excl * 128;
+  if (t < experts) {
+    h.counts[t] = count;
+    h.offsets[t] = excl * 128;
+    h.cursor[t] = count;
+    for (int b = 0; b < blocks; ++b) {
+      if (excl + b < max_m_blocks) {
+        h.m_block_expert[excl + b] = t;
+        h.m_block_rows[excl + b] = min(128, count - 128 * b);
+      }
+    }
+  }
+  if (t == experts - 1) {
+    h.offsets[experts] = incl * 128;
+    *h.num_m_blocks = min(incl, max_m_blocks);
+  }
+  __syncthreads();
+  if (t < n_slots) {
+    int row = -1;
+    if (e >= 0) {
+      row = s_offset[e] + rank_in_expert;
+      if (row >= max_rows) row = -1;
+    }
+    h.slot_row[t] = row;
+  }
+}
+
+// CTA (token, part): quantise a share of the row's 16-element blocks and write it to the rows assigned above
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads)
+moe_scatter_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ slot_row, uint8_t* xq,
+                              uint8_t* xq_sf, int hidden, int top_k) {
+  __shared__ int s_rows[64];
+  const int token = blockIdx.x;
+  if (threadIdx.x < top_k) s_rows[threadIdx.x] = slot_row[static_cast<int64_t>(token) * top_k + threadIdx.x];
+  __syncthreads();
+  const int nchunks = hidden >> 4;
+  const int rk = (nchunks + 3) >> 2;
+  for (int chunk = blockIdx.y * kThreads + threadIdx.x; chunk < nchunks; chunk += gridDim.y * kThreads) {
+    const U32x8 raw = ld_stream_32B(x + static_cast<int64_t>(token) * hidden + chunk * 16);
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[2 * i] = Pair16<__nv_bfloat16>::lo(raw.v[i]);
+      v[2 * i + 1] = Pair16<__nv_bfloat16>::hi(raw.v[i]);
+    }
+    uint32_t lo, hi, sfb;
+    quantize_block16<true>(v, 1.0f, lo, hi, sfb);
+    for (int j = 0; j < top_k; ++j) {
+      const int row = s_rows[j];
+      if (row < 0) continue;
+      *reinterpret_cast<uint2*>(xq + static_cast<int64_t>(row) * (hidden >> 1) + chunk * 8) = make_uint2(lo, hi);
+      xq_sf[sf_swizzled_offset(row, chunk, rk)] = static_cast<uint8_t>(sfb);
+    }
+  }
+}
+
 // one CTA per token: quantise the row once, then write it to the row of every local slot
 template <int kThreads>
 __global__ void __launch_bounds__(kThreads)
@@ -433,13 +526,20 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
   const int slots = static_cast<int>(tokens * top_k);
   const int max_rows = ws.max_m_blocks * 128;
 
-  B200_CUDA(cudaMemsetAsync(ws.h.counts, 0, sizeof(int) * experts, stream));
   B200_CUDA(cudaMemsetAsync(ws.xq_sf, 0, ws.xq_sf_bytes, stream));      // rows that only pad a block read as zero
-  moe_count_kernel<<<(slots + kCountSlotsPerCta - 1) / kCountSlotsPerCta, 256, 0, stream>>>(ids, slots, expert_lo,
-                                                                                              experts, ws.h.counts);
-  moe_scan_kernel<<<1, 1024, 0, stream>>>(ws.h, experts, ws.max_m_blocks);
-  moe_scatter_quant_kernel<128><<<static_cast<unsigned>(tokens), 128, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(x), ids, ws.h, ws.xq, ws.xq_sf, hidden, top_k, expert_lo, experts, max_rows);
+  if (slots <= 1024) {
+    moe_prepare_small_kernel<<<1, 1024, 0, stream>>>(ids, slots, expert_lo, ws.h, experts, ws.max_m_blocks, max_rows);
+    const int parts = std::max(1, std::min(8, (hidden / 16) / 128));
+    moe_scatter_quant_rows_kernel<128><<<dim3(static_cast<unsigned>(tokens), parts), 128, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), ws.h.slot_row, ws.xq, ws.xq_sf, hidden, top_k);
+  } else {
+    B200_CUDA(cudaMemsetAsync(ws.h.counts, 0, sizeof(int) * experts, stream));
+    moe_count_kernel<<<(slots + kCountSlotsPerCta - 1) / kCountSlotsPerCta, 256, 0, stream>>>(ids, slots, expert_lo,
+                                                                                                experts, ws.h.counts);
+    moe_scan_kernel<<<1, 1024, 0, stream>>>(ws.h, experts, ws.max_m_blocks);
+    moe_scatter_quant_kernel<128><<<static_cast<unsigned>(tokens), 128, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), ids, ws.h, ws.xq, ws.xq_sf, hidden, top_k, expert_lo, experts, max_rows);
+  }
   B200_CUDA(cudaGetLastError());
   // With at most 32 tokens no expert receives more than 32 rows (a token names an expert once, as top-k selection
   // does): the wide GEMM variants then keep 32 rows of A per stage and one more stage of weights in flight.  A
