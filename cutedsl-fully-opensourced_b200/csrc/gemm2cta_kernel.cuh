@@ -232,13 +232,15 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
                                        [&](int c0, uint32_t (&r)[32]) {
                                          ptx::tmem_ld_32x32(t_acc + c0, r);
                                          ptx::tmem_ld_wait();
+                                       },
+                                       [&]() {      // called once the warp has read its share of the accumulator
+                                         ptx::tc_fence_before_sync();
+                                         __syncwarp();
+                                         if (lane == 0) {
+                                           if (rank == 0) ptx::mbar_arrive(acc_empty_bar);
+                                           else ptx::mbar_arrive_cluster_relaxed(acc_empty_bar & ptx::kPeerBitMask);   // tcgen05.wait::ld has returned
+                                         }
                                        });
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        if (rank == 0) ptx::mbar_arrive(acc_empty_bar);
-        else ptx::mbar_arrive_cluster_relaxed(acc_empty_bar & ptx::kPeerBitMask);   // tcgen05.wait::ld has returned
-      }
       acc_phase ^= 1u;
     }
   }

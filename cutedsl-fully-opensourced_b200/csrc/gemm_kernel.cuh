@@ -211,13 +211,54 @@ struct EpilogueStore {
 
   // part / parts: which share of the tile's columns this warp drains (two warps per TMEM quarter when parts == 2)
   // stage / cmap: the warp's parking space and the tensor map of the output for the TMA-store variant, or null
-  template <int kBlockN, typename Loader>
+  template <int kBlockN, typename Loader, typename Release>
   __device__ __forceinline__ void operator()(const GemmParams& p, int m_blk, int n_blk, int group, int row,
-                                             int rows_valid, int part, int parts, Loader&& load,
+                                             int rows_valid, int part, int parts, Loader&& load, Release&& release,
                                              uint8_t* stage = nullptr, const CUtensorMap* cmap = nullptr) const {
     const float scale = alpha == nullptr ? 1.0f : __ldg(alpha + (alpha_per_group ? group : 0));
     if (stage != nullptr) {
       tma_path<kBlockN>(p, m_blk, n_blk, row, scale, load, stage, cmap);
+      release();
+      return;
+    }
+    if constexpr (sizeof(OutT) == 2 && kBlockN == 256) {
+      // One accumulator per CTA: its drain is what the next tile waits for.  A warp's 128 columns fit in 64
+      // registers once packed to 16 bits, so read and pack everything first, hand the accumulator back, and
+      // store afterwards (the stores of a tile take ten times longer than reading it).
+      const int64_t grow = static_cast<int64_t>(m_blk) * kBlockM + row;
+      const bool row_ok = grow < p.m_rows && row < rows_valid;
+      OutT* crow = c + grow * ldc + static_cast<int64_t>(n_blk) * kBlockN;
+      const int cols_left = p.n_cols - n_blk * kBlockN;
+      const int span = kBlockN / parts;          // 128 with two warps per TMEM quarter
+      uint32_t packed[64];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (32 * i < span) {
+          uint32_t r[32];
+          load(part * span + 32 * i, r);
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            packed[16 * i + j] =
+                Pair16<OutT>::pack(__uint_as_float(r[2 * j]) * scale, __uint_as_float(r[2 * j + 1]) * scale);
+        }
+      }
+      release();
+      if (!row_ok) return;
+      const bool wide = (reinterpret_cast<uintptr_t>(crow) & 31) == 0 && (ldc & 15) == 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {              // 16 columns = 32 bytes per store
+        const int c0 = part * span + 16 * i;
+        if (16 * i >= span) break;
+        U32x8 v;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v.v[j] = packed[8 * i + j];
+        if (wide && c0 + 8 < cols_left) {
+          st_32B(crow + c0, v);
+        } else {
+          if (c0 < cols_left) *reinterpret_cast<uint4*>(crow + c0) = make_uint4(v.v[0], v.v[1], v.v[2], v.v[3]);
+          if (c0 + 8 < cols_left) *reinterpret_cast<uint4*>(crow + c0 + 8) = make_uint4(v.v[4], v.v[5], v.v[6], v.v[7]);
+        }
+      }
       return;
     }
     const int64_t grow = static_cast<int64_t>(m_blk) * kBlockM + row;
@@ -268,6 +309,7 @@ struct EpilogueStore {
         }
       }
     }
+    release();
   }
 };
 
@@ -282,9 +324,9 @@ struct EpilogueSwiglu {
   const float* fc2_input_scale; // one f32 (global scale of the activation quantiser)
   int inter;                    // activation columns per row
 
-  template <int kBlockN, typename Loader>
+  template <int kBlockN, typename Loader, typename Release>
   __device__ __forceinline__ void operator()(const GemmParams& p, int m_blk, int n_blk, int group, int row,
-                                             int rows_valid, int part, int parts, Loader&& load,
+                                             int rows_valid, int part, int parts, Loader&& load, Release&& release,
                                              uint8_t* /*stage*/ = nullptr, const CUtensorMap* /*cmap*/ = nullptr) const {
     constexpr int kHalf = kBlockN / 2;
     static_assert(kHalf % 64 == 0, "the SwiGLU epilogue pairs two halves of whole 32-column groups per warp");
@@ -300,6 +342,7 @@ struct EpilogueSwiglu {
       uint32_t up[32], gate[32];
       load(c0, up);
       load(kHalf + c0, gate);
+      if (c0 + 32 >= (part + 1) * span) release();      // last read of the accumulator: the arithmetic follows
       if (j0 + c0 >= inter) continue;
       uint32_t sfpair = 0;
       uint32_t codes[4];
@@ -596,15 +639,22 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const uint32_t off = ((kStages * L.stage_bytes + kBarrierBytes + 1023u) & ~1023u) + (warp - 2) * L.epi_stage_bytes;
           stage = smem_gen + off;
         }
+        // the functor calls `release` once, as soon as it has read the accumulator for the last time: the MMAs
+        // of the next tile may start while it is still converting and storing
         epi.template operator()<kBlockN>(p, m_blk, n_blk, group, row, rows_valid, part, kParts,
                                          [&](int c0, uint32_t (&r)[32]) {
                                            ptx::tmem_ld_32x32(t_acc + c0, r);
                                            ptx::tmem_ld_wait();
                                          },
+                                         [&]() {
+                                           ptx::tc_fence_before_sync();
+                                           ptx::mbar_arrive(acc_empty_bar(acc.stage));
+                                         },
                                          stage, &tmap_c);
+      } else {
+        ptx::tc_fence_before_sync();
+        ptx::mbar_arrive(acc_empty_bar(acc.stage));
       }
-      ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(acc_empty_bar(acc.stage));
       acc.advance(kAccStages);
     }
     // the TMA stores of this warp's last tiles must have left shared memory and reached global memory
