@@ -233,7 +233,10 @@ int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, v
     // wide tiles halve the operand traffic per flop; keep narrow ones while they are needed to fill the SMs
     const int sms = sm_count_of_current_device();
     const int64_t m_blocks = (m + 127) / 128;
-    if (m_blocks * ((n + 255) / 256) >= sms) tile_n = 256;
+    static const bool no_pairs = getenv("B200FP4_NO_PAIRS") != nullptr;
+    // a full wave of 256 x 256 tiles on CTA pairs: each CTA fills 38 KB per K step instead of 54 KB
+    if (!no_pairs && ((m + 255) / 256) * static_cast<int64_t>((n + 255) / 256) >= sms / 2 && k >= 1024) tile_n = 512;
+    else if (m_blocks * ((n + 255) / 256) >= sms) tile_n = 256;
     else if (m_blocks * ((n + 127) / 128) >= sms) tile_n = 128;
     else tile_n = 64;            // few rows (weight streaming): narrow tiles put more SMs on the stream of B
   }

@@ -126,45 +126,47 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     }
   } else if (warp == 1) {
     // =============================== MMA issuer (even CTA only) ===============================
-    if (lane == 0 && rank == 0) {
+    // the whole warp walks the loop, an elected lane issues (see the single-CTA kernel)
+    if (rank == 0) {
       PipeState st;
       uint32_t acc_phase = 0;
       bool ok = true;
+      const uint64_t a_desc0 = ptx::smem_desc_sw128(smem_base);
+      const uint64_t b_desc0 = ptx::smem_desc_sw128(smem_base + kABytes);
+      const int last_kblocks = ((p.k - (p.num_k_tiles - 1) * kBlockK) + 63) >> 6;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         if (!wait_bounded(acc_empty_bar, acc_phase ^ 1u, abort_flag)) {
-          atomicOr(p.status, kStatusTimeoutMma);
+          if (lane == 0) atomicOr(p.status, kStatusTimeoutMma);
           break;
         }
         ptx::tc_fence_after_sync();
         for (int kt = 0; kt < p.num_k_tiles; ++kt) {
-          if (!wait_bounded(full_bar(st.stage), st.phase, abort_flag)) {
-            atomicOr(p.status, kStatusTimeoutMma);
+          if (!wait_bounded(sf_full_bar(st.stage), st.phase, abort_flag) ||
+              !wait_bounded(full_bar(st.stage), st.phase, abort_flag)) {
+            if (lane == 0) atomicOr(p.status, kStatusTimeoutMma);
             ok = false;
             break;
           }
           ptx::tc_fence_after_sync();
-          const uint32_t sa = smem_base + st.stage * kPairStageBytes;
-          const uint32_t sb = sa + kABytes;
-          const int kblocks = min(4, (p.k - kt * kBlockK + 63) >> 6);
-          if (!wait_bounded(sf_full_bar(st.stage), st.phase, abort_flag)) {
-            atomicOr(p.status, kStatusTimeoutMma);
-            ok = false;
-            break;
-          }
-          ptx::tc_fence_after_sync();
+          const uint64_t stage_off = static_cast<uint64_t>(st.stage * (kPairStageBytes >> 4));
+          const uint64_t da = a_desc0 + stage_off, db = b_desc0 + stage_off;
           const uint32_t sfa_t = tmem_base + kSfaCol + st.stage * kSfSetCols;
           const uint32_t sfb_t = sfa_t + 16;
+          const int kblocks = kt + 1 == p.num_k_tiles ? last_kblocks : 4;
+          if (ptx::elect_one()) {
+            ptx::mma2_mxf4nvf4(tmem_base, da, db, kIdesc, sfa_t, sfb_t, kt != 0 ? 1u : 0u);
 #pragma unroll
-          for (int kb = 0; kb < 4; ++kb) {
-            if (kb < kblocks) {
-              ptx::mma2_mxf4nvf4(tmem_base, ptx::smem_desc_sw128(sa + 32 * kb), ptx::smem_desc_sw128(sb + 32 * kb),
-                                 kIdesc, sfa_t + 4 * kb, sfb_t + 8 * kb, (kt | kb) != 0 ? 1u : 0u);
+            for (int kb = 1; kb < 4; ++kb) {
+              if (kb < kblocks)
+                ptx::mma2_mxf4nvf4(tmem_base, da + 2 * kb, db + 2 * kb, kIdesc, sfa_t + 4 * kb, sfb_t + 8 * kb, 1u);
             }
+            ptx::tc2_commit_mcast(empty_bar(st.stage), 3);      // frees the stage in both CTAs
           }
-          ptx::tc2_commit_mcast(empty_bar(st.stage), 3);      // frees the stage in both CTAs
+          __syncwarp();
           st.advance(kStages);
         }
-        if (ok) ptx::tc2_commit_mcast(acc_full_bar, 3);       // accumulators of both CTAs are complete
+        if (ok && ptx::elect_one()) ptx::tc2_commit_mcast(acc_full_bar, 3);   // accumulators of both CTAs are complete
+        __syncwarp();
         acc_phase ^= 1u;
       }
     }
@@ -222,7 +224,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
     for (int tile = pair; tile < num_tiles; tile += num_pairs) {
       const int m2 = tile % p.num_m_blocks;
       const int n_blk = tile / p.num_m_blocks;
-      if (!wait_bounded(acc_full_bar, acc_phase, abort_flag)) {
+      if (!wait_bounded<64>(acc_full_bar, acc_phase, abort_flag)) {
         if (lane == 0) atomicOr(p.status, kStatusTimeoutEpilogue);
         break;
       }
