@@ -507,6 +507,10 @@ def main():
         nk = args.nk or 8192
         wl = GemmWorkload(rank, args.m or 8192, nk, nk)
         wl.tile_n = args.tile_n
+        wl.kernel = {0: "nvfp4_gemm_pair_kernel (256x256 tiles on CTA pairs) for a full wave of such tiles, "
+                        "else nvfp4_gemm_kernel<256|128|64>",
+                     512: "nvfp4_gemm_pair_kernel (256x256 tiles on CTA pairs)"}.get(
+                         args.tile_n, f"nvfp4_gemm_kernel<{args.tile_n}>")
     elif args.workload.startswith("moe_"):
         wl = MoeWorkload(rank, args.workload[4:], args.tokens, world)
     else:
