@@ -78,7 +78,12 @@ def device_status(clear: bool = True, device=None) -> int:
 def raise_on_device_status(device=None) -> None:
     st = device_status(True, device)
     if st:
-        raise B200Fp4Error(f"a device-side wait expired (status bits {st:#x}); results are invalid")
+        what = []
+        if st & 7:
+            what.append("a device-side wait expired")
+        if st & 8:
+            what.append("a fused-MoE call with at most 32 tokens named one expert more than 32 times")
+        raise B200Fp4Error(f"{'; '.join(what) or 'device error'} (status bits {st:#x}); results are invalid")
 
 
 def ptr(t) -> int:

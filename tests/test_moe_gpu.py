@@ -206,3 +206,20 @@ def test_decode_shapes_wide_tiles(b200, tokens):
     ref = O.moe_ref(x, w1c, w1s, w2c, w2s, ids, wts, a1.numpy())
     out = run_gpu(b200, x, w1c, w1s, w2c, w2s, ids, wts.contiguous(), w1_alpha=a1.cuda())
     assert rel_l2(out, ref) <= 1e-2
+
+
+def test_few_token_launch_flags_an_expert_named_too_often(b200):
+    """With at most 32 tokens the wide GEMM variants load 32 rows of A per block.  Expert ids that repeat inside a
+    token can give one expert more rows than that; the kernels then raise bit 8 of the device status word."""
+    experts, hidden, inter, top_k, tokens = 2, 4352, 1280, 8, 8
+    rng = np.random.default_rng(3)
+    w1c, w1s, w2c, w2s = random_weights(rng, experts, hidden, inter)
+    x = torch.randn(tokens, hidden).to(torch.bfloat16)
+    ids = torch.zeros(tokens, top_k, dtype=torch.int32)           # 64 rows for expert 0
+    wts = torch.full((tokens, top_k), 1.0 / top_k)
+    b200._lib.device_status()                                      # clear
+    b200.b12x_fused_moe(x.cuda(), torch.from_numpy(O.pack_e2m1(w1c)).cuda(), six_mode(w1s),
+                        torch.from_numpy(O.pack_e2m1(w2c)).cuda(), six_mode(w2s), ids.cuda(), wts.cuda(), experts, top_k)
+    torch.cuda.synchronize()
+    assert b200._lib.device_status() == 8
+    assert b200._lib.device_status() == 0                          # reading clears it
