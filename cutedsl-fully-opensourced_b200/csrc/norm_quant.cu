@@ -56,8 +56,11 @@ __device__ __forceinline__ float warp_sum(float v) {
 // works on one row per warp (hidden <= 512); otherwise the team is the CTA.
 // kCap: upper bound of the block size of this instantiation; small blocks ask the compiler for a
 // register budget that lets five of them share an SM.
-template <typename T, bool kAdd, int kVec, int kUnits, bool kWarpRow, int kCap>
-__global__ void __launch_bounds__(kCap, kCap <= 256 ? 5 : 2) norm_quant_kernel(const NormParams p) {
+// kPipe: the loads of the team's next row are issued as soon as the current row's registers have been consumed
+// (before the row reduction), so DRAM requests stay in flight through the reduction, the quantisation and the
+// stores; costs the 32 load registers per thread for the whole loop, hence fewer resident CTAs.
+template <typename T, bool kAdd, int kVec, int kUnits, bool kWarpRow, int kCap, bool kPipe = false>
+__global__ void __launch_bounds__(kCap, kPipe ? 3 : (kCap <= 256 ? 5 : 2)) norm_quant_kernel(const NormParams p) {
   extern __shared__ float4 wsm[];          // per-thread weight slices, f32
   __shared__ float red[2][kMaxThreads / 32];
 
@@ -100,11 +103,30 @@ __global__ void __launch_bounds__(kCap, kCap <= 256 ? 5 : 2) norm_quant_kernel(c
   const int64_t row_step = kWarpRow ? static_cast<int64_t>(gridDim.x) * nwarps : gridDim.x;
   int parity = 0;
   const uint32_t row_bytes = static_cast<uint32_t>(p.hidden) * 2u;
+  // kPipe: raw rows travel in these registers from one iteration to the next
+  U32x8 xnext[kPipe ? kUnits * kVec : 1], rnext[kPipe && kAdd ? kUnits * kVec : 1];
+  auto load_row = [&](int64_t r) {
+#pragma unroll
+    for (int u = 0; u < kUnits; ++u) {
+#pragma unroll
+      for (int v = 0; v < kVec; ++v) {
+        const int chunk = (tid + u * team) * kVec + v;
+        if (chunk < nchunks) {
+          xnext[u * kVec + v] = ld_stream_32B(xg + r * p.x_row_stride + chunk * 16);
+          if constexpr (kAdd) rnext[u * kVec + v] = ld_32B(rg + r * p.res_row_stride + chunk * 16);
+        }
+      }
+    }
+  };
+  if constexpr (kPipe) {
+    if (row0 < p.rows) load_row(row0);
+  }
   for (int64_t row = row0; row < p.rows; row += row_step, parity ^= 1) {
-    // pull the row this team will work on next into L2 while the current one is processed
-    if (tid == 0 && row + row_step < p.rows) {
-      prefetch_l2_bulk(xg + (row + row_step) * p.x_row_stride, row_bytes);
-      if constexpr (kAdd) prefetch_l2_bulk(rg + (row + row_step) * p.res_row_stride, row_bytes);
+    // pull the row this team will work on next (kPipe: the one after it) into L2 while the current one is processed
+    const int64_t ahead = row + (kPipe ? 2 : 1) * row_step;
+    if (tid == 0 && ahead < p.rows) {
+      prefetch_l2_bulk(xg + ahead * p.x_row_stride, row_bytes);
+      if constexpr (kAdd) prefetch_l2_bulk(rg + ahead * p.res_row_stride, row_bytes);
     }
     // ---- phase 1: load, (add, round, write residual), sum of squares; all f32 math on register pairs
     // what phase 2 normalises, kept as packed 16-bit pairs so that few registers live across the row reduction
@@ -117,10 +139,10 @@ __global__ void __launch_bounds__(kCap, kCap <= 256 ? 5 : 2) norm_quant_kernel(c
         const int c = u * kVec + v;
         const int chunk = (tid + u * team) * kVec + v;
         if (chunk < nchunks) {
-          const U32x8 xv = ld_stream_32B(xg + row * p.x_row_stride + chunk * 16);
+          const U32x8 xv = kPipe ? xnext[c] : ld_stream_32B(xg + row * p.x_row_stride + chunk * 16);
           if constexpr (kAdd) {
             T* rptr = rg + row * p.res_row_stride + chunk * 16;
-            const U32x8 rv = ld_32B(rptr);
+            const U32x8 rv = kPipe ? rnext[c] : ld_32B(rptr);
             U32x8 outv;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
@@ -150,6 +172,9 @@ __global__ void __launch_bounds__(kCap, kCap <= 256 ? 5 : 2) norm_quant_kernel(c
       }
     }
     float ssq = __fadd_rn(f32x2_lo(ssq2), f32x2_hi(ssq2));
+    if constexpr (kPipe) {
+      if (row + row_step < p.rows) load_row(row + row_step);      // in flight until the next iteration's phase 1
+    }
 
     // ---- row reduction: lanes, then (CTA teams) warps through shared memory
     ssq = warp_sum(ssq);
@@ -246,9 +271,9 @@ int sm_count() {
   return cached;
 }
 
-template <typename T, bool kAdd, int kVec, int kUnits, bool kWarpRow, int kCap>
+template <typename T, bool kAdd, int kVec, int kUnits, bool kWarpRow, int kCap, bool kPipe = false>
 int launch_one(const NormParams& p, int threads, cudaStream_t stream) {
-  auto kern = norm_quant_kernel<T, kAdd, kVec, kUnits, kWarpRow, kCap>;
+  auto kern = norm_quant_kernel<T, kAdd, kVec, kUnits, kWarpRow, kCap, kPipe>;
   const size_t smem = static_cast<size_t>(kUnits) * kVec * 4 * sizeof(float4) * threads;
   if (smem > 48 * 1024) {
     B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
@@ -276,6 +301,10 @@ int dispatch(const NormParams& p, cudaStream_t stream) {
   const int threads = (((nunits + units - 1) / units) + 31) / 32 * 32;
   switch (units) {
     case 1:
+      // the residual-add variant keeps its next row's loads in flight in registers (three resident CTAs instead
+      // of four: 71.2 -> 70.0 us at [8192, 7168]; with four pipelined CTAs 77 us); the plain variant, with half
+      // the bytes per row, does better with more resident CTAs and the L2 prefetch alone
+      if (kAdd && threads <= 256) return launch_one<T, kAdd, 2, 1, false, 256, kAdd>(p, threads, stream);
       return threads <= 256 ? launch_one<T, kAdd, 2, 1, false, 256>(p, threads, stream)
                             : launch_one<T, kAdd, 2, 1, false, kMaxThreads>(p, threads, stream);
     case 2: return launch_one<T, kAdd, 2, 2, false, kMaxThreads>(p, threads, stream);
