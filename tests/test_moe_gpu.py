@@ -206,6 +206,10 @@ def test_decode_shapes_wide_tiles(b200, tokens):
     ref = O.moe_ref(x, w1c, w1s, w2c, w2s, ids, wts, a1.numpy())
     out = run_gpu(b200, x, w1c, w1s, w2c, w2s, ids, wts.contiguous(), w1_alpha=a1.cuda())
     assert rel_l2(out, ref) <= 1e-2
+    if tokens in (8, 40):           # the same through f32 per-slot rows and an f32 output
+        out32 = run_gpu(b200, x, w1c, w1s, w2c, w2s, ids, wts.contiguous(), w1_alpha=a1.cuda(),
+                        output_dtype=torch.float32)
+        assert out32.dtype == torch.float32 and rel_l2(out32, ref) <= 1e-2
 
 
 def test_few_token_launch_flags_an_expert_named_too_often(b200):
