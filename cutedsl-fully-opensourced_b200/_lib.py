@@ -14,7 +14,7 @@ LIB_PATH = os.path.join(_PKG, "lib", "libb200fp4.so")
 
 OK, INVALID_ARGUMENT, UNSUPPORTED, CUDA_ERROR, DEVICE_TIMEOUT, NOT_INITIALISED = range(6)
 
-_vp, _i32, _i64, _f32, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
+_vp, _i32, _i64, _f32, _f64, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_double, C.c_size_t
 
 # name -> (restype, argtypes); kept in the order of include/b200fp4.h
 SIGNATURES = {
@@ -27,11 +27,19 @@ SIGNATURES = {
     "b200fp4_topk_route": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "b200fp4_moe_workspace_bytes": (_sz, [_i64, _i32, _i32, _i32, _i32]),
     "b200fp4_moe_fused": (_i32, [_vp] * 11 + [_i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
+    "b200fp4_moe_fused_routed": (_i32, [_vp, _vp, _i32, _i32] + [_vp] * 10 + [_i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32,
+                                               _vp, _sz, _vp]),
     "b200fp4_moe_fused_noalloc": (_i32, [_vp] * 11 + [_i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
     "b200fp4_moe_ep_buffer_bytes": (_sz, [_i64, _i32, _i32, _i32, _i32, _i32]),
-    "b200fp4_moe_ep_stage": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp]),
-    "b200fp4_moe_ep_compute": (_i32, [_vp, _i32, _i32] + [_vp] * 7 + [_i64, _i32, _i32, _i32, _i32, _vp]),
-    "b200fp4_moe_ep_combine": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _vp]),
+    "b200fp4_moe_ep_reset": (_i32, [_vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "b200fp4_moe_ep_dispatch": (_i32, [_vp, _vp, _vp, _i32, _vp, _i32, _i32, _i64, _i32, _i32, _i32, _i32, _f64, _vp]),
+    "b200fp4_moe_ep_dispatch_count": (_i32, [_vp, _vp, _vp, _i32, _vp, _i32, _i32, _i64, _i32, _i32, _i32, _i32, _f64, _vp]),
+    "b200fp4_moe_ep_dispatch_place": (_i32, [_vp, _vp, _vp, _i32, _vp, _i32, _i32, _i64, _i32, _i32, _i32, _i32, _f64, _vp]),
+    "b200fp4_moe_ep_compute": (_i32, [_vp, _i32, _i32] + [_vp] * 7 + [_i64, _i32, _i32, _i32, _i32, _f64, _vp]),
+    "b200fp4_moe_ep_combine": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f64, _vp]),
+    "b200fp4_moe_ep_routing": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "b200fp4_selftest_peer_wait": (_i32, [_vp, _i32, _f64, _i64, _i32, _i32, _i32, _i32, _vp]),
+    "b200fp4_selftest_bounded_wait": (_i32, [C.c_longlong, _vp, _vp]),
     "b200fp4_device_status": (_i32, [_vp, C.POINTER(C.c_int), _i32]),
 }
 
@@ -75,15 +83,35 @@ def device_status(clear: bool = True, device=None) -> int:
     return out.value
 
 
+STATUS_GEMM_WAIT = 7          # bits 1 | 2 | 4: producer / MMA / epilogue wait of a GEMM kernel expired
+STATUS_ROWS_EXCEED_TILE = 8
+STATUS_PEER_WAIT = 16         # a wait for another rank of an expert-parallel group expired
+
+
+def describe_status(st: int) -> str:
+    what = []
+    if st & STATUS_GEMM_WAIT:
+        what.append("a wait inside a GEMM kernel expired")
+    if st & STATUS_ROWS_EXCEED_TILE:
+        what.append("a few-row GEMM launch met a row block with more rows than it loads")
+    if st & STATUS_PEER_WAIT:
+        what.append("a wait for another rank of the expert-parallel group expired (a peer is late or gone)")
+    return "; ".join(what) or "unknown device error"
+
+
 def raise_on_device_status(device=None) -> None:
+    """The sync point of the error contract: synchronise the current stream, read and clear the device status
+    word, and raise if a kernel reported trouble since the last check (kernels never trap; they record and
+    return)."""
     st = device_status(True, device)
     if st:
-        what = []
-        if st & 7:
-            what.append("a device-side wait expired")
-        if st & 8:
-            what.append("a fused-MoE call with at most 32 tokens named one expert more than 32 times")
-        raise B200Fp4Error(f"{'; '.join(what) or 'device error'} (status bits {st:#x}); results are invalid")
+        raise B200Fp4Error(f"{describe_status(st)} (status bits {st:#x}); results since the last check are invalid")
+
+
+def synchronize(device=None) -> None:
+    """``torch.cuda.synchronize`` for users of this package: waits for the current stream and raises
+    ``B200Fp4Error`` if any kernel of the library reported an expired wait."""
+    raise_on_device_status(device)
 
 
 def ptr(t) -> int:

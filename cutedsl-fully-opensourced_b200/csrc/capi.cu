@@ -36,22 +36,30 @@ int device_status_word(int** out);
 int route_topk(const float* logits, int* ids, float* weights, int tokens, int experts, int top_k, int renormalize,
                cudaStream_t stream);
 size_t moe_workspace_bytes(int64_t tokens, int hidden, int inter, int experts, int top_k);
-int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, const void* w2_sf, const int* ids,
-              const float* route_w, const float* w1_alpha, const float* w2_alpha, const float* fc2_input_scale,
-              void* out, int64_t tokens, int hidden, int inter, int experts, int top_k, int expert_lo,
-              int accumulate, int out_dtype, void* workspace, size_t workspace_bytes, int* status,
-              cudaStream_t stream);
+int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, const void* w2_sf, int* ids,
+              float* route_w, const float* logits, int route_experts, int renormalize, const float* w1_alpha,
+              const float* w2_alpha, const float* fc2_input_scale, void* out, int64_t tokens, int hidden, int inter,
+              int experts, int top_k, int expert_lo, int accumulate, int out_dtype, void* workspace,
+              size_t workspace_bytes, int* status, cudaStream_t stream);
+int bounded_wait_selftest(long long limit_cycles, int* gave_up_dev, cudaStream_t stream);
 
 size_t moe_ep_buffer_bytes(int64_t tokens_local, int hidden, int inter, int experts_local, int top_k, int world);
-int moe_ep_stage(const void* x, const int* ids, void* own_buffer, int64_t tokens_local, int hidden, int inter,
-                 int experts_local, int top_k, int world, cudaStream_t stream);
+int moe_ep_reset(void* own_buffer, int64_t tokens_local, int hidden, int inter, int experts_local, int top_k,
+                 int world, cudaStream_t stream);
+int moe_ep_dispatch(const void* x, const int* ids, const float* logits, int route_experts, int renormalize,
+                    const void* const* peer_buffers, int rank, int world, int64_t tokens_local, int hidden, int inter,
+                    int experts_local, int top_k, double wait_ms, int phases, int* status, cudaStream_t stream);
 int moe_ep_compute(const void* const* peer_buffers, int rank, int world, const void* w1, const void* w1_sf,
                    const void* w2, const void* w2_sf, const float* w1_alpha, const float* w2_alpha,
                    const float* fc2_input_scale, int64_t tokens_local, int hidden, int inter, int experts_local,
-                   int top_k, int* status, cudaStream_t stream);
+                   int top_k, double wait_ms, int* status, cudaStream_t stream);
 int moe_ep_combine(const void* const* peer_buffers, int rank, int world, const int* ids, const float* weights,
                    void* out, int64_t tokens_local, int hidden, int inter, int experts_local, int top_k,
-                   cudaStream_t stream);
+                   double wait_ms, int* status, cudaStream_t stream);
+int moe_ep_routing(const void* own_buffer, int* ids_out, float* weights_out, int64_t tokens_local, int hidden,
+                   int inter, int experts_local, int top_k, int world, cudaStream_t stream);
+int moe_ep_wait_selftest(void* own_buffer, int world, double wait_ms, int64_t tokens_local, int hidden, int inter,
+                         int experts_local, int top_k, int* status, cudaStream_t stream);
 
 }  // namespace b200fp4
 
@@ -104,9 +112,27 @@ int b200fp4_moe_fused(const void* x, const void* w1, const void* w1_sf, const vo
   int* status = nullptr;
   int rc = device_status_word(&status);
   if (rc) return rc;
-  return moe_fused(x, w1, w1_sf, w2, w2_sf, token_selected_experts, token_final_scales, w1_alpha, w2_alpha,
-                   fc2_input_scale, out, tokens, hidden, intermediate, local_experts, top_k, local_expert_offset,
-                   accumulate, out_dtype, workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream));
+  // ids and scales are inputs here: the routed variant below is the one that writes them
+  return moe_fused(x, w1, w1_sf, w2, w2_sf, const_cast<int*>(token_selected_experts),
+                   const_cast<float*>(token_final_scales), nullptr, 0, 0, w1_alpha, w2_alpha, fc2_input_scale, out,
+                   tokens, hidden, intermediate, local_experts, top_k, local_expert_offset, accumulate, out_dtype,
+                   workspace, workspace_bytes, status, static_cast<cudaStream_t>(stream));
+}
+
+int b200fp4_moe_fused_routed(const void* x, const float* router_logits, int num_experts, int renormalize,
+                             const void* w1, const void* w1_sf, const void* w2, const void* w2_sf,
+                             int* token_selected_experts_out, float* token_final_scales_out, const float* w1_alpha,
+                             const float* w2_alpha, const float* fc2_input_scale, void* out, int64_t tokens,
+                             int hidden, int intermediate, int local_experts, int top_k, int local_expert_offset,
+                             int accumulate, int out_dtype, void* workspace, size_t workspace_bytes, void* stream) {
+  if (router_logits == nullptr) return fail(kInvalidArgument, "router_logits is null");
+  int* status = nullptr;
+  int rc = device_status_word(&status);
+  if (rc) return rc;
+  return moe_fused(x, w1, w1_sf, w2, w2_sf, token_selected_experts_out, token_final_scales_out, router_logits,
+                   num_experts, renormalize, w1_alpha, w2_alpha, fc2_input_scale, out, tokens, hidden, intermediate,
+                   local_experts, top_k, local_expert_offset, accumulate, out_dtype, workspace, workspace_bytes, status,
+                   static_cast<cudaStream_t>(stream));
 }
 
 size_t b200fp4_moe_ep_buffer_bytes(int64_t tokens_local, int hidden, int intermediate, int local_experts, int top_k,
@@ -115,29 +141,86 @@ size_t b200fp4_moe_ep_buffer_bytes(int64_t tokens_local, int hidden, int interme
   return moe_ep_buffer_bytes(tokens_local, hidden, intermediate, local_experts, top_k, world);
 }
 
-int b200fp4_moe_ep_stage(const void* x, const int* token_selected_experts, void* own_buffer, int64_t tokens_local,
-                         int hidden, int intermediate, int local_experts, int top_k, int world, void* stream) {
-  return moe_ep_stage(x, token_selected_experts, own_buffer, tokens_local, hidden, intermediate, local_experts, top_k,
-                      world, static_cast<cudaStream_t>(stream));
+int b200fp4_moe_ep_reset(void* own_buffer, int64_t tokens_local, int hidden, int intermediate, int local_experts,
+                         int top_k, int world, void* stream) {
+  return moe_ep_reset(own_buffer, tokens_local, hidden, intermediate, local_experts, top_k, world,
+                      static_cast<cudaStream_t>(stream));
+}
+
+static int ep_dispatch_phases(const void* x, const int* ids, const float* logits, int renormalize,
+                              const void* const* peer_buffers, int rank, int world, int64_t tokens_local, int hidden,
+                              int intermediate, int local_experts, int top_k, double wait_ms, int phases, void* stream) {
+  int* status = nullptr;
+  int rc = device_status_word(&status);
+  if (rc) return rc;
+  return moe_ep_dispatch(x, ids, logits, local_experts * world, renormalize, peer_buffers, rank, world, tokens_local,
+                         hidden, intermediate, local_experts, top_k, wait_ms, phases, status,
+                         static_cast<cudaStream_t>(stream));
+}
+
+int b200fp4_moe_ep_dispatch(const void* x, const int* token_selected_experts, const float* router_logits,
+                            int renormalize, const void* const* peer_buffers, int rank, int world,
+                            int64_t tokens_local, int hidden, int intermediate, int local_experts, int top_k,
+                            double wait_ms, void* stream) {
+  return ep_dispatch_phases(x, token_selected_experts, router_logits, renormalize, peer_buffers, rank, world,
+                            tokens_local, hidden, intermediate, local_experts, top_k, wait_ms, 3, stream);
+}
+
+int b200fp4_moe_ep_dispatch_count(const void* x, const int* token_selected_experts, const float* router_logits,
+                                  int renormalize, const void* const* peer_buffers, int rank, int world,
+                                  int64_t tokens_local, int hidden, int intermediate, int local_experts, int top_k,
+                                  double wait_ms, void* stream) {
+  return ep_dispatch_phases(x, token_selected_experts, router_logits, renormalize, peer_buffers, rank, world,
+                            tokens_local, hidden, intermediate, local_experts, top_k, wait_ms, 1, stream);
+}
+
+int b200fp4_moe_ep_dispatch_place(const void* x, const int* token_selected_experts, const float* router_logits,
+                                  int renormalize, const void* const* peer_buffers, int rank, int world,
+                                  int64_t tokens_local, int hidden, int intermediate, int local_experts, int top_k,
+                                  double wait_ms, void* stream) {
+  return ep_dispatch_phases(x, token_selected_experts, router_logits, renormalize, peer_buffers, rank, world,
+                            tokens_local, hidden, intermediate, local_experts, top_k, wait_ms, 2, stream);
 }
 
 int b200fp4_moe_ep_compute(const void* const* peer_buffers, int rank, int world, const void* w1, const void* w1_sf,
                            const void* w2, const void* w2_sf, const float* w1_alpha, const float* w2_alpha,
                            const float* fc2_input_scale, int64_t tokens_local, int hidden, int intermediate,
-                           int local_experts, int top_k, void* stream) {
+                           int local_experts, int top_k, double wait_ms, void* stream) {
   int* status = nullptr;
   int rc = device_status_word(&status);
   if (rc) return rc;
   return moe_ep_compute(peer_buffers, rank, world, w1, w1_sf, w2, w2_sf, w1_alpha, w2_alpha, fc2_input_scale,
-                        tokens_local, hidden, intermediate, local_experts, top_k, status,
+                        tokens_local, hidden, intermediate, local_experts, top_k, wait_ms, status,
                         static_cast<cudaStream_t>(stream));
 }
 
 int b200fp4_moe_ep_combine(const void* const* peer_buffers, int rank, int world, const int* token_selected_experts,
                            const float* token_final_scales, void* out, int64_t tokens_local, int hidden,
-                           int intermediate, int local_experts, int top_k, void* stream) {
+                           int intermediate, int local_experts, int top_k, double wait_ms, void* stream) {
+  int* status = nullptr;
+  int rc = device_status_word(&status);
+  if (rc) return rc;
   return moe_ep_combine(peer_buffers, rank, world, token_selected_experts, token_final_scales, out, tokens_local,
-                        hidden, intermediate, local_experts, top_k, static_cast<cudaStream_t>(stream));
+                        hidden, intermediate, local_experts, top_k, wait_ms, status, static_cast<cudaStream_t>(stream));
+}
+
+int b200fp4_moe_ep_routing(const void* own_buffer, int* ids_out, float* weights_out, int64_t tokens_local, int hidden,
+                           int intermediate, int local_experts, int top_k, int world, void* stream) {
+  return moe_ep_routing(own_buffer, ids_out, weights_out, tokens_local, hidden, intermediate, local_experts, top_k,
+                        world, static_cast<cudaStream_t>(stream));
+}
+
+int b200fp4_selftest_peer_wait(void* own_buffer, int world, double wait_ms, int64_t tokens_local, int hidden,
+                               int intermediate, int local_experts, int top_k, void* stream) {
+  int* status = nullptr;
+  int rc = device_status_word(&status);
+  if (rc) return rc;
+  return moe_ep_wait_selftest(own_buffer, world, wait_ms, tokens_local, hidden, intermediate, local_experts, top_k,
+                              status, static_cast<cudaStream_t>(stream));
+}
+
+int b200fp4_selftest_bounded_wait(long long limit_cycles, int* gave_up, void* stream) {
+  return bounded_wait_selftest(limit_cycles, gave_up, static_cast<cudaStream_t>(stream));
 }
 
 int b200fp4_device_status(void* stream, int* status_out, int clear) {

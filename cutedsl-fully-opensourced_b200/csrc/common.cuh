@@ -290,6 +290,12 @@ __device__ __forceinline__ void quantize_block16(const float (&v)[16], float gs,
   quantize_block16<kImplicitOne>(v2, gs, codes_lo, codes_hi, sf_bits);
 }
 
+// exchange buffers of the ranks of an expert-parallel group, as mapped into this process
+constexpr int kMaxPeers = 16;
+struct PeerPtrs {
+  uint8_t* p[kMaxPeers];
+};
+
 // offset of scale factor (row m, K-block kb) in the 128x4 tiled layout with rk
 // K-tiles per row tile (python/cutlass_compat/cutlass/utils/blockscaled_layout.py:37-42)
 __device__ __host__ __forceinline__ int64_t sf_swizzled_offset(int64_t m, int kb, int rk) {

@@ -1,8 +1,11 @@
 // Host side of the NVFP4 GEMM family: tensor-map construction, launch
 // configuration and argument checks for the dense block-scaled GEMM and the
 // two grouped GEMMs of the fused MoE.  The device code is in gemm_kernel.cuh.
+#include <atomic>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
+#include <unordered_map>
 
 #include "gemm2cta_kernel.cuh"
 #include "gemm_kernel.cuh"
@@ -29,8 +32,44 @@ EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// Tensor maps are pure functions of (base pointer, shape, box): encoding one costs a driver call of a few
+// microseconds, which is most of the host time of a small GEMM.  They are memoised here and re-encoded only
+// when a key has not been seen (the reference re-encodes when an operand's base pointer changes,
+// python/self_cutedsl/frontend/jit.py:412-435).
+struct MapKey {
+  uint64_t kind, base, d0, d1, d2, box;
+  bool operator==(const MapKey& o) const { return memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    uint64_t h = 0x9e3779b97f4a7c15ull;
+    const uint64_t v[6] = {k.kind, k.base, k.d0, k.d1, k.d2, k.box};
+    for (uint64_t x : v) h = (h ^ x) * 0x100000001b3ull + (h >> 29);
+    return static_cast<size_t>(h);
+  }
+};
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+constexpr size_t kMapCacheLimit = 8192;      // entries; the cache is dropped when it grows beyond this
+
+bool cached_map(const MapKey& key, CUtensorMap* out) {
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  auto it = g_map_cache.find(key);
+  if (it == g_map_cache.end()) return false;
+  *out = it->second;
+  return true;
+}
+void remember_map(const MapKey& key, const CUtensorMap& map) {
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  if (g_map_cache.size() >= kMapCacheLimit) g_map_cache.clear();
+  g_map_cache.emplace(key, map);
+}
+
 // K-major e2m1 operand viewed as bytes: [groups][rows][k/2], boxes of 128 rows x 128 bytes, 128-byte swizzle.
 int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int k, int64_t groups, int box_rows = 128) {
+  const MapKey key{1, reinterpret_cast<uint64_t>(base), static_cast<uint64_t>(rows), static_cast<uint64_t>(k),
+                   static_cast<uint64_t>(groups), static_cast<uint64_t>(box_rows)};
+  if (cached_map(key, map)) return kOk;
   EncodeTiledFn enc = encode_tiled_fn();
   if (enc == nullptr) return fail(kCudaError, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t row_bytes = static_cast<cuuint64_t>(k) / 2;
@@ -43,12 +82,16 @@ int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int k, in
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(kCudaError, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  remember_map(key, *map);
   return kOk;
 }
 
 // Output matrix viewed as bytes: [rows][row_bytes] with `pitch_bytes` between rows; boxes of 32 rows x 128 bytes
 // in the 128-byte swizzle (the layout the epilogue warps park their rows in).
 int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t row_bytes, int64_t pitch_bytes) {
+  const MapKey key{2, reinterpret_cast<uint64_t>(base), static_cast<uint64_t>(rows), static_cast<uint64_t>(row_bytes),
+                   static_cast<uint64_t>(pitch_bytes), 0};
+  if (cached_map(key, map)) return kOk;
   EncodeTiledFn enc = encode_tiled_fn();
   if (enc == nullptr) return fail(kCudaError, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(rows)};
@@ -58,12 +101,15 @@ int make_output_map(CUtensorMap* map, void* base, int64_t rows, int64_t row_byte
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, base, dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(kCudaError, "cuTensorMapEncodeTiled (output) failed with CUresult %d", static_cast<int>(r));
+  remember_map(key, *map);
   return kOk;
 }
 
 // Tiled scale-factor storage viewed as rows of 256 bytes; a box of 8 rows is the 2 KB slab of one
 // 128-row tile and four 64-wide K tiles.  Rows past the end read as zero.
 int make_sf_map(CUtensorMap* map, const void* base, int64_t total_bytes) {
+  const MapKey key{3, reinterpret_cast<uint64_t>(base), static_cast<uint64_t>(total_bytes), 0, 0, 0};
+  if (cached_map(key, map)) return kOk;
   EncodeTiledFn enc = encode_tiled_fn();
   if (enc == nullptr) return fail(kCudaError, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[2] = {256, static_cast<cuuint64_t>(total_bytes / 256)};
@@ -74,6 +120,7 @@ int make_sf_map(CUtensorMap* map, const void* base, int64_t total_bytes) {
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(kCudaError, "cuTensorMapEncodeTiled (scale factors) failed with CUresult %d", static_cast<int>(r));
+  remember_map(key, *map);
   return kOk;
 }
 
@@ -82,11 +129,37 @@ int* g_status_word[64] = {};
 
 }  // namespace
 
-int sm_count_of_current_device() {
-  int dev = 0, n = 0;
+constexpr int kMaxDevices = 64;
+
+int current_device_ordinal() {
+  int dev = 0;
   cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-  return n > 0 ? n : 148;
+  return dev >= 0 && dev < kMaxDevices ? dev : 0;
+}
+
+// cached per device ordinal (attribute queries cost a driver call each)
+int sm_count_of_current_device() {
+  static std::atomic<int> cached[kMaxDevices];
+  const int dev = current_device_ordinal();
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+    cached[dev].store(n, std::memory_order_relaxed);
+  }
+  return n;
+}
+
+// The opt-in to more than 48 KB of dynamic shared memory is a per-device attribute of a kernel: remember per
+// device ordinal (and per kernel instantiation: one flag array per call site) that it has been set.
+template <typename Kernel>
+int configure_smem_once(std::atomic<bool>* done, Kernel kern, int bytes) {
+  const int dev = current_device_ordinal();
+  if (!done[dev].load(std::memory_order_acquire)) {
+    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    done[dev].store(true, std::memory_order_release);
+  }
+  return kOk;
 }
 
 // One int per device that kernels OR failure bits into (bounded waits that expired).
@@ -103,17 +176,46 @@ int device_status_word(int** out) {
   return kOk;
 }
 
+// Self-test of the bounded wait: a CTA initialises an mbarrier on which nothing ever arrives and waits for it with
+// the GEMM kernels' own wait routine and a short cycle limit.  The wait gives up, the abort flag goes up, the
+// kernel ORs kStatusTimeoutMma into the status word and returns; no operand, no copy and no tensor memory is
+// involved, so nothing is left in flight.
+__global__ void bounded_wait_selftest_kernel(int* status, long long limit_cycles, int* gave_up) {
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(ptx::smem_u32(&bar), 1);
+    abort_flag = 0;
+    ptx::fence_mbar_init();
+  }
+  __syncthreads();
+  const bool ok = wait_bounded(ptx::smem_u32(&bar), 0u, &abort_flag, limit_cycles);
+  if (!ok && threadIdx.x == 0) {
+    atomicOr(status, kStatusTimeoutMma);
+    *gave_up = abort_flag;
+  }
+}
+
+int bounded_wait_selftest(long long limit_cycles, int* gave_up_dev, cudaStream_t stream) {
+  if (gave_up_dev == nullptr) return fail(kInvalidArgument, "gave_up is null");
+  if (limit_cycles < 1 || limit_cycles > 2000000000LL)
+    return fail(kInvalidArgument, "limit_cycles must be in [1, 2e9]");
+  int* status = nullptr;
+  int rc = device_status_word(&status);
+  if (rc) return rc;
+  bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(status, limit_cycles, gave_up_dev);
+  return check_cuda(cudaGetLastError(), "bounded_wait_selftest_kernel launch");
+}
+
 // tc: tensor map of the output for the variants whose tiles leave through TMA stores (others never touch it)
 template <int kBlockN, bool kSwigluB, int kARows = 128, typename Epilogue>
 int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                 const Epilogue& epi, int max_tiles, cudaStream_t stream) {
   auto kern = nvfp4_gemm_kernel<kBlockN, kSwigluB, Epilogue, kARows>;
   constexpr SmemLayout L = smem_layout<kBlockN, kSwigluB, Epilogue::kOutBytes, kARows>();
-  static bool configured = false;      // per instantiation
-  if (!configured) {
-    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L.total)));
-    configured = true;
-  }
+  static std::atomic<bool> configured[kMaxDevices];      // per instantiation and device
+  int rc_cfg = configure_smem_once(configured, kern, static_cast<int>(L.total));
+  if (rc_cfg) return rc_cfg;
   int grid = sm_count_of_current_device();
   if (grid > max_tiles) grid = max_tiles;
   if (grid < 1) return kOk;
@@ -147,11 +249,9 @@ int gemm_dense_pair(const void* a, const void* b, const void* sfa, const void* s
   if (rc) return rc;
   EpilogueStore<OutT> epi{static_cast<OutT*>(c), n, alpha, 0};
   auto kern = nvfp4_gemm_pair_kernel<EpilogueStore<OutT>>;
-  static bool configured = false;
-  if (!configured) {
-    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kPairSmemBytes)));
-    configured = true;
-  }
+  static std::atomic<bool> configured[kMaxDevices];
+  rc = configure_smem_once(configured, kern, static_cast<int>(kPairSmemBytes));
+  if (rc) return rc;
   int pairs = sm_count_of_current_device() / 2;
   const int tiles = p.num_m_blocks * p.num_n_blocks;
   if (pairs > tiles) pairs = tiles;
@@ -295,6 +395,7 @@ int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* 
   p.num_m_blocks_dev = num_m_blocks_dev;
   p.num_m_blocks = max_m_blocks;
   p.m_block_group = m_block_expert;
+  p.num_groups = experts;
   p.m_block_rows = m_block_rows;
   p.status = status;
   p.row_block_major = 1;
@@ -334,6 +435,7 @@ int gemm_moe_fc2_typed(const void* act_codes, const void* act_sf, const void* w2
   p.num_m_blocks_dev = num_m_blocks_dev;
   p.num_m_blocks = max_m_blocks;
   p.m_block_group = m_block_expert;
+  p.num_groups = experts;
   p.m_block_rows = m_block_rows;
   p.status = status;
   p.row_block_major = 1;
@@ -351,6 +453,46 @@ int gemm_moe_fc2_typed(const void* act_codes, const void* act_sf, const void* w2
   }
   p.num_n_blocks = (hidden + 127) / 128;
   return launch_gemm<128, false>(ta, tb, tc, p, epi, max_m_blocks * p.num_n_blocks, stream);
+}
+
+// FC2 of the expert-parallel MoE: as gemm_moe_fc2 with bf16 rows, but every row is stored into the landing zone
+// of the rank that owns its token (EpiloguePushRows) instead of a local buffer.
+int gemm_moe_fc2_push(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf,
+                      const int* row_tag, const PeerPtrs& peers, size_t recv_off, const int* abort_flag,
+                      const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
+                      const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int few_rows,
+                      int* status, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  const bool wide = hidden % 256 == 0 && (inter + kBlockK - 1) / kBlockK > 4;
+  const bool small_a = few_rows != 0 && wide;
+  int rc = make_operand_map(&ta, act_codes, static_cast<int64_t>(max_m_blocks) * 128, inter, 0, small_a ? 32 : 128);
+  if (rc) return rc;
+  rc = make_operand_map(&tb, w2, hidden, inter, experts);
+  if (rc) return rc;
+  GemmParams p{};
+  p.sfa = static_cast<const uint8_t*>(act_sf);
+  p.sfb = static_cast<const uint8_t*>(w2_sf);
+  p.m_rows = max_m_blocks * 128;
+  p.n_cols = hidden;
+  p.k = inter;
+  p.rk = (inter + 63) / 64;
+  p.num_k_tiles = (inter + kBlockK - 1) / kBlockK;
+  p.b_row_tiles = (hidden + 127) / 128;
+  p.num_m_blocks_dev = num_m_blocks_dev;
+  p.num_m_blocks = max_m_blocks;
+  p.m_block_group = m_block_expert;
+  p.num_groups = experts;
+  p.m_block_rows = m_block_rows;
+  p.status = status;
+  p.row_block_major = 1;
+  EpiloguePushRows epi{row_tag, peers, recv_off, hidden, w2_alpha, abort_flag};
+  if (wide) {
+    p.num_n_blocks = hidden / 256;
+    if (small_a) return launch_gemm<256, false, 32>(ta, tb, CUtensorMap{}, p, epi, max_m_blocks * p.num_n_blocks, stream);
+    return launch_gemm<256, false>(ta, tb, CUtensorMap{}, p, epi, max_m_blocks * p.num_n_blocks, stream);
+  }
+  p.num_n_blocks = (hidden + 127) / 128;
+  return launch_gemm<128, false>(ta, tb, CUtensorMap{}, p, epi, max_m_blocks * p.num_n_blocks, stream);
 }
 
 int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, void* partial,

@@ -71,6 +71,7 @@ struct GemmParams {
   const int* num_m_blocks_dev; // null -> num_m_blocks
   int num_m_blocks;
   const int* m_block_group;    // null -> group 0
+  int num_groups;              // groups of B (experts); group indices read from device memory are clamped to it
   const int* m_block_rows;     // null -> all 128 rows of a block hold data; else rows of the block that do
   int* status;                 // device status word (bits of GemmStatusBits)
   // Order of the tile list.  0: column block outermost (CTAs running together share a few column blocks of B
@@ -123,7 +124,8 @@ struct PipeState {
 // kBackoffNs > 0: sleep between polls.  Warps that spin take issue slots from the warps on the critical
 // path (MMA issuer, slab movers); roles that can afford some wake-up latency back off.
 template <int kBackoffNs = 0>
-__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                             long long limit_cycles = kWaitLimitCycles) {
   if (ptx::mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   for (uint32_t it = 1;; ++it) {
@@ -131,7 +133,7 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
     if constexpr (kBackoffNs > 0) __nanosleep(kBackoffNs);
     if ((it & 255u) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit_cycles) {
         *abort_flag = 1;
         return false;
       }
@@ -152,6 +154,7 @@ struct EpilogueStore {
   int alpha_per_group;
 
   static constexpr int kOutBytes = static_cast<int>(sizeof(OutT));
+  static constexpr bool kUsesOutputMap = true;      // 128-wide tiles leave through TMA stores
 
   // The warp parks its 32 rows of the tile in shared memory (boxes of 32 rows x 128 bytes in the 128-byte
   // swizzle of the tensor map) and one lane hands them to TMA stores: the accumulator is free as soon as it has
@@ -313,11 +316,105 @@ struct EpilogueStore {
   }
 };
 
+// FC2 of the expert-parallel MoE: every output row goes straight to the GPU that owns its token.  `row_tag[r]`
+// names the destination of expert-major row r as (rank << 24 | slot), slot = token * top_k + j at that rank; the
+// row lands at recv[slot][0..hidden) (bf16) in that rank's exchange buffer.  All remote accesses are plain
+// stores of this kernel over NVLink (no TMA, no bulk copy to peer memory).  128-wide tiles park the warp's 32
+// rows in shared memory first so that every row leaves as 256 contiguous bytes (16 lanes x 16 bytes, two rows
+// per store instruction); 256-wide tiles store 32 bytes per lane from registers.
+struct EpiloguePushRows {
+  static constexpr int kOutBytes = 2;
+  static constexpr bool kUsesOutputMap = false;
+  const int* row_tag;           // [rows] destination of every expert-major row
+  PeerPtrs peers;               // exchange buffer of every rank as mapped into this process
+  size_t recv_off;              // offset of the landing zone inside an exchange buffer
+  int hidden;                   // row length
+  const float* alpha;           // per group, or null
+  const int* abort_flag;        // non-zero: a cross-rank wait expired earlier in this step -> touch no peer memory
+
+  __device__ __forceinline__ __nv_bfloat16* row_dst(int tag) const {
+    return reinterpret_cast<__nv_bfloat16*>(peers.p[(tag >> 24) & (kMaxPeers - 1)] + recv_off) +
+           static_cast<int64_t>(tag & 0xffffff) * hidden;
+  }
+
+  template <int kBlockN, typename Loader, typename Release>
+  __device__ __forceinline__ void operator()(const GemmParams& p, int m_blk, int n_blk, int group, int row,
+                                             int rows_valid, int part, int parts, Loader&& load, Release&& release,
+                                             uint8_t* stage = nullptr, const CUtensorMap* /*cmap*/ = nullptr) const {
+    const float scale = alpha == nullptr ? 1.0f : __ldg(alpha + group);
+    const int lane = row & 31;
+    const int64_t grow = static_cast<int64_t>(m_blk) * kBlockM + row;
+    const bool live = __ldg(abort_flag) == 0;
+    const int tag = (row < rows_valid && live) ? __ldg(row_tag + grow) : -1;
+    if constexpr (kBlockN == 128) {
+      // park: 2 boxes of 32 rows x 128 bytes, 16-byte chunks XOR-swizzled by the row (no bank conflicts either way)
+#pragma unroll
+      for (int b = 0; b < 2; ++b) {
+        uint8_t* box = stage + b * 4096 + lane * 128;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t r[32];
+          load(b * 64 + 32 * h, r);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 v;
+            v.x = Pair16<__nv_bfloat16>::pack(__uint_as_float(r[8 * q]) * scale, __uint_as_float(r[8 * q + 1]) * scale);
+            v.y = Pair16<__nv_bfloat16>::pack(__uint_as_float(r[8 * q + 2]) * scale, __uint_as_float(r[8 * q + 3]) * scale);
+            v.z = Pair16<__nv_bfloat16>::pack(__uint_as_float(r[8 * q + 4]) * scale, __uint_as_float(r[8 * q + 5]) * scale);
+            v.w = Pair16<__nv_bfloat16>::pack(__uint_as_float(r[8 * q + 6]) * scale, __uint_as_float(r[8 * q + 7]) * scale);
+            *reinterpret_cast<uint4*>(box + (((4 * h + q) ^ (lane & 7)) << 4)) = v;
+          }
+        }
+      }
+      release();                                   // the accumulator has been read
+      __syncwarp();
+      const int col0 = n_blk * kBlockN;
+      const int c16 = lane & 15;                   // 16-byte chunk of the 256-byte row piece
+      const bool col_ok = col0 + c16 * 8 < p.n_cols;
+#pragma unroll 4
+      for (int pr = 0; pr < 16; ++pr) {
+        const int r = 2 * pr + (lane >> 4);
+        const int t = __shfl_sync(0xffffffffu, tag, r);
+        const uint4 v = *reinterpret_cast<const uint4*>(stage + (c16 >> 3) * 4096 + r * 128 + (((c16 & 7) ^ (r & 7)) << 4));
+        if (t >= 0 && col_ok) *reinterpret_cast<uint4*>(row_dst(t) + col0 + c16 * 8) = v;
+      }
+      __syncwarp();                                // the parking space is free for the next tile
+    } else {
+      static_assert(kBlockN == 256, "rows are pushed from 128- or 256-wide tiles");
+      const int span = kBlockN / parts;
+      uint32_t packed[64];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (32 * i < span) {
+          uint32_t r[32];
+          load(part * span + 32 * i, r);
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            packed[16 * i + j] =
+                Pair16<__nv_bfloat16>::pack(__uint_as_float(r[2 * j]) * scale, __uint_as_float(r[2 * j + 1]) * scale);
+        }
+      }
+      release();
+      if (tag < 0) return;
+      __nv_bfloat16* crow = row_dst(tag) + static_cast<int64_t>(n_blk) * kBlockN;
+      const int cols_left = p.n_cols - n_blk * kBlockN;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int c0 = part * span + 16 * i;
+        if (16 * i >= span) break;
+        if (c0 < cols_left) *reinterpret_cast<uint4*>(crow + c0) = make_uint4(packed[8 * i], packed[8 * i + 1], packed[8 * i + 2], packed[8 * i + 3]);
+        if (c0 + 8 < cols_left) *reinterpret_cast<uint4*>(crow + c0 + 8) = make_uint4(packed[8 * i + 4], packed[8 * i + 5], packed[8 * i + 6], packed[8 * i + 7]);
+      }
+    }
+  }
+};
+
 // FC1 of the MoE: the accumulator columns are [up j0..j0+h-1 | gate j0..j0+h-1], h = half the tile width;
 // act = bf16(silu(gate) * up), re-quantised to NVFP4 with the MoE activation packer
 // (tests/python/test_flashinfer_b12x_verbatim.py:214-218) and written as the A operand of FC2.
 struct EpilogueSwiglu {
   static constexpr int kOutBytes = 0;     // stores from registers
+  static constexpr bool kUsesOutputMap = false;
   uint8_t* act_codes;           // [m_rows, inter/2]
   uint8_t* act_sf;              // tiled [m_tiles][rk2][512], rk2 = ceil(inter/64)
   const float* w1_alpha;        // per group
@@ -425,7 +522,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
-    if (L.epi_stage_bytes != 0) ptx::prefetch_tensormap(&tmap_c);
+    if (L.epi_stage_bytes != 0 && Epilogue::kUsesOutputMap) ptx::prefetch_tensormap(&tmap_c);
   }
   if (warp == 0) {
     __syncwarp();
@@ -437,7 +534,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_ptr_smem;
 
-  const int num_m_blocks = p.num_m_blocks_dev != nullptr ? __ldg(p.num_m_blocks_dev) : p.num_m_blocks;
+  // grouped launches read the number of row blocks from device memory; never trust it beyond the table size
+  const int num_m_blocks =
+      p.num_m_blocks_dev != nullptr ? max(0, min(__ldg(p.num_m_blocks_dev), p.num_m_blocks)) : p.num_m_blocks;
   const int num_tiles = num_m_blocks * p.num_n_blocks;
   auto tile_m = [&](int tile) { return p.row_block_major ? tile / p.num_n_blocks : tile % num_m_blocks; };
   auto tile_n = [&](int tile) { return p.row_block_major ? tile % p.num_n_blocks : tile / num_m_blocks; };
@@ -450,7 +549,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m_blk = tile_m(tile);
         const int n_blk = tile_n(tile);
-        const int group = p.m_block_group != nullptr ? __ldg(p.m_block_group + m_blk) : 0;
+        const int group =
+            p.m_block_group != nullptr ? max(0, min(__ldg(p.m_block_group + m_blk), p.num_groups - 1)) : 0;
         int b_row[kBPieces];
         if constexpr (kSwigluB) {
           b_row[0] = n_blk * kBPieceRows;
@@ -624,7 +724,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       const int m_blk = tile_m(tile);
       const int n_blk = tile_n(tile);
-      const int group = p.m_block_group != nullptr ? __ldg(p.m_block_group + m_blk) : 0;
+      const int group =
+          p.m_block_group != nullptr ? max(0, min(__ldg(p.m_block_group + m_blk), p.num_groups - 1)) : 0;
       if (!wait_bounded<64>(acc_full_bar(acc.stage), acc.phase, abort_flag)) {
         if (lane == 0) atomicOr(p.status, kStatusTimeoutEpilogue);
         break;

@@ -5,10 +5,12 @@
 // the reference's routed golden (same file, lines 28-65 and 209-219):
 //
 //   route (optional)   softmax over expert logits -> top-k -> renormalise
-//   count / scan       rows per local expert; every expert's segment is padded to whole 128-row
-//                      blocks so that a GEMM tile never straddles two experts
-//   scatter + quant    each token is quantised ONCE to NVFP4 with the activation packer and its
-//                      codes / scale bytes are written to the row of every (token, slot) pair
+//   count              (fused with the router when logits are given) rows per expert, and the position of
+//                      every (token, slot) pair among the rows of its expert
+//   quantise + place   every CTA rebuilds the padded row offsets from the counts (every expert's segment is
+//                      padded to whole 128-row blocks so that a GEMM tile never straddles two experts);
+//                      each token is quantised ONCE to NVFP4 with the activation packer and its codes /
+//                      scale bytes are written to the row of every (token, slot) pair
 //   FC1 grouped GEMM   [up | gate] = Xq . W1[e]^T, epilogue silu(gate)*up -> bf16 -> NVFP4   (gemm.cu)
 //   FC2 grouped GEMM   partial = Actq . W2[e]^T * w2_alpha[e]                               (gemm.cu)
 //   combine            out[t] = bf16( sum_j weight[t,j] * partial[row(t,j)] ), f32, slot order
@@ -29,6 +31,8 @@ int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, cons
                  const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int few_rows,
                  int* status, cudaStream_t stream);
 
+int sm_count_of_current_device();
+
 namespace {
 
 constexpr int kRouteMaxPerLane = 32;       // experts <= 1024
@@ -36,13 +40,10 @@ constexpr int kRouteMaxPerLane = 32;       // experts <= 1024
 // ---------------------------------------------------------------------------
 // route: one warp per token; kPerLane = experts a lane holds (experts <= 32 * kPerLane)
 // ---------------------------------------------------------------------------
+// Lane j (< top_k) of the warp returns the j-th choice of the token whose logits start at `row`.
 template <int kPerLane>
-__global__ void route_topk_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ weights,
-                                  int tokens, int experts, int top_k, int renormalize) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  if (warp >= tokens) return;
-  const float* row = logits + static_cast<int64_t>(warp) * experts;
+__device__ __forceinline__ void route_one_token(const float* __restrict__ row, int lane, int experts, int top_k,
+                                                int renormalize, int& my_id, float& my_w) {
   float v[kPerLane];
   const int per_lane = (experts + 31) >> 5;
   float mx = -INFINITY;
@@ -64,8 +65,8 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int* __restr
   for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
   const float inv = 1.0f / sum;
   float picked = 0.0f;
-  float my_w = 0.0f;
-  int my_id = 0;
+  my_w = 0.0f;
+  my_id = 0;
   for (int j = 0; j < top_k; ++j) {
     // lane-local best (lowest index among equals), then the warp's best
     float best = -1.0f;
@@ -98,9 +99,21 @@ __global__ void route_topk_kernel(const float* __restrict__ logits, int* __restr
       my_id = best_e;
     }
   }
+  if (renormalize) my_w = my_w / picked;
+}
+
+template <int kPerLane>
+__global__ void route_topk_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ weights,
+                                  int tokens, int experts, int top_k, int renormalize) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp >= tokens) return;
+  int my_id;
+  float my_w;
+  route_one_token<kPerLane>(logits + static_cast<int64_t>(warp) * experts, lane, experts, top_k, renormalize, my_id, my_w);
   if (lane < top_k) {
     ids[static_cast<int64_t>(warp) * top_k + lane] = my_id;
-    weights[static_cast<int64_t>(warp) * top_k + lane] = renormalize ? my_w / picked : my_w;
+    weights[static_cast<int64_t>(warp) * top_k + lane] = my_w;
   }
 }
 
@@ -117,63 +130,303 @@ struct MoeHeader {           // all int32, contiguous
   int* slot_row;             // [tokens * top_k] row of every (token, slot), -1 if the expert is not local
 };
 
-// rows per local expert: a histogram per CTA in shared memory (experts <= 1024), then one global add per
-// expert that the CTA saw
-constexpr int kCountSlotsPerCta = 1024;
-__global__ void moe_count_kernel(const int* __restrict__ ids, int n_slots, int expert_lo, int experts, int* counts) {
-  __shared__ int s_hist[1024];
-  for (int e = threadIdx.x; e < experts; e += blockDim.x) s_hist[e] = 0;
+// ---------------------------------------------------------------------------
+// Front end shared by the single-GPU operator and the expert-parallel one.
+//
+// Experts are numbered 0 .. experts_total-1 and expert e lives on rank e / experts_local (single GPU: one
+// rank).  Every rank owns a buffer of identical layout; peers.p[d] is rank d's buffer as mapped into this
+// process (single GPU: the workspace).  Two kernels:
+//
+//   count   one warp per token: (route from logits, or take the given ids) and claim, per (token, slot), a
+//           position among THIS rank's slots of the same expert; the last CTA publishes the rank's counts
+//           to every rank and raises signal 0
+//   place   wait for signal 0 of every rank; every CTA derives from the counts of all ranks where each
+//           expert's rows start at its owner (segments padded to 128-row blocks) and where this rank's rows
+//           start inside the segment; then quantises its tokens once and writes codes + scale bytes into the
+//           row of every slot AT THE OWNER OF THE SLOT'S EXPERT (plain stores; over NVLink when the owner is
+//           a peer: 4.5 bits per element cross the wire), plus the row's return address; the last CTA raises
+//           signal 1.  CTA 0 also writes this rank's block tables for the grouped GEMMs.
+//
+// Signals are per (phase, source rank) words in the destination's buffer carrying a step counter; waits on
+// them are bounded in time: on expiry the kernel sets kStatusPeerWaitExpired in the device status word and the
+// abort word of the buffer, after which no kernel touches peer memory until the host resets the exchange.
+// ---------------------------------------------------------------------------
+enum CtrlWord : int {
+  kCtrlEpoch = 0,            // completed steps; every kernel of a step signals / waits for epoch + 1
+  kCtrlTicketCount = 1,      // CTAs of the count kernel that have finished
+  kCtrlTicketPlace = 2,
+  kCtrlTicketCombine = 3,
+  kCtrlAbort = 4,            // a cross-rank wait expired
+  kCtrlWords = 16,
+};
+constexpr int kStatusPeerWaitExpired = 16;
+constexpr int kSignalPhases = 3;       // 0: counts published, 1: rows placed, 2: output rows delivered
+
+struct Exchange {
+  PeerPtrs peers;
+  size_t flags, counts_all, xq, xq_sf, row_tag;      // offsets inside a rank's buffer (written by peers)
+  int rank, world, experts_local;
+  unsigned long long wait_ns;
+};
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// wait until *flag has reached `epoch`; gives up after limit_ns
+__device__ __forceinline__ bool wait_flag(const int* flag, int epoch, unsigned long long limit_ns) {
+  if (ld_acquire_sys(flag) - epoch >= 0) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+    if (ld_acquire_sys(flag) - epoch >= 0) return true;
+    if (globaltimer_ns() - t0 > limit_ns) return false;
+    __nanosleep(64);
+  }
+}
+// Threads 0..world-1 of the CTA wait for `phase` of their rank; returns false (to all threads) when a wait
+// expired now or earlier in the step.  The first failure is recorded in the status word.
+__device__ __forceinline__ bool wait_all_ranks(const Exchange& ex, int phase, int* ctrl, int* status, int* s_ok) {
+  if (ex.world <= 1) return true;
+  if (threadIdx.x == 0) *s_ok = 1;
   __syncthreads();
-  const int first = blockIdx.x * kCountSlotsPerCta;
-  const int last = min(n_slots, first + kCountSlotsPerCta);
-  for (int i = first + threadIdx.x; i < last; i += blockDim.x) {
-    const int e = ids[i] - expert_lo;
-    if (e >= 0 && e < experts) atomicAdd(s_hist + e, 1);
+  if (threadIdx.x < ex.world && threadIdx.x != ex.rank) {
+    const int epoch = *reinterpret_cast<volatile int*>(ctrl + kCtrlEpoch) + 1;
+    const int* flags = reinterpret_cast<const int*>(ex.peers.p[ex.rank] + ex.flags) + phase * kMaxPeers;
+    if (*reinterpret_cast<volatile int*>(ctrl + kCtrlAbort) != 0) {
+      *s_ok = 0;
+    } else if (!wait_flag(flags + threadIdx.x, epoch, ex.wait_ns)) {
+      *s_ok = 0;
+      atomicOr(status, kStatusPeerWaitExpired);
+      atomicExch(ctrl + kCtrlAbort, 1);
+    }
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < experts; e += blockDim.x)
-    if (s_hist[e] != 0) atomicAdd(counts + e, s_hist[e]);
+  return *s_ok != 0;
+}
+// Called by all threads at the end of a kernel whose CTAs wrote to peer memory: the last CTA to arrive raises
+// `phase` at every peer.  `ticket` counts finished CTAs and is left at zero.
+__device__ __forceinline__ void signal_when_all_ctas_done(const Exchange& ex, int phase, int* ctrl, int ticket, int* s_last) {
+  if (ex.world <= 1) return;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    *s_last = atomicAdd(ctrl + ticket, 1) == static_cast<int>(gridDim.x * gridDim.y) - 1;
+  }
+  __syncthreads();
+  if (!*s_last) return;
+  if (threadIdx.x < ex.world && threadIdx.x != ex.rank &&
+      *reinterpret_cast<volatile int*>(ctrl + kCtrlAbort) == 0) {
+    __threadfence_system();
+    const int epoch = *reinterpret_cast<volatile int*>(ctrl + kCtrlEpoch) + 1;
+    st_release_sys(reinterpret_cast<int*>(ex.peers.p[threadIdx.x] + ex.flags) + phase * kMaxPeers + ex.rank, epoch);
+  }
+  if (threadIdx.x == 0) ctrl[ticket] = 0;
 }
 
-// single CTA: padded exclusive scan over experts and the block -> expert table
-__global__ void moe_scan_kernel(MoeHeader h, int experts, int max_m_blocks) {
-  __shared__ int s_blocks[1024];
-  const int t = threadIdx.x;
-  int blocks = 0;
-  if (t < experts) blocks = (h.counts[t] + 127) >> 7;
-  s_blocks[t] = blocks;
-  __syncthreads();
-  // Hillis-Steele inclusive scan over up to 1024 experts
-  for (int o = 1; o < 1024; o <<= 1) {
-    const int add = t >= o ? s_blocks[t - o] : 0;
-    __syncthreads();
-    s_blocks[t] += add;
-    __syncthreads();
-  }
-  const int incl = s_blocks[t];
-  const int excl = incl - blocks;
-  if (t < experts) {
-    h.offsets[t] = excl * 128;
-    h.cursor[t] = 0;
-    const int count = h.counts[t];
-    for (int b = 0; b < blocks; ++b) {
-      if (excl + b < max_m_blocks) {
-        h.m_block_expert[excl + b] = t;
-        h.m_block_rows[excl + b] = min(128, count - 128 * b);
+// count: one warp per token, four tokens per CTA.  kPerLane > 0: route from logits (experts <= 32 * kPerLane)
+// and write ids / weights; kPerLane == 0: ids are given.
+template <int kPerLane>
+__global__ void __launch_bounds__(128)
+moe_count_kernel(const float* __restrict__ logits, int route_experts, int renormalize, const int* __restrict__ ids_in,
+                 int* __restrict__ ids_out, float* __restrict__ weights_out, int tokens, int top_k, int expert_lo,
+                 int experts_total, int* my_counts, int* __restrict__ slot_pos, int* ctrl, Exchange ex) {
+  __shared__ int s_last;
+  const int token = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (token < tokens) {
+    if constexpr (kPerLane > 0) {
+      int my_id;
+      float my_w;
+      route_one_token<kPerLane>(logits + static_cast<int64_t>(token) * route_experts, lane, route_experts, top_k,
+                                renormalize, my_id, my_w);
+      if (lane < top_k) {
+        const int64_t slot = static_cast<int64_t>(token) * top_k + lane;
+        ids_out[slot] = my_id;
+        weights_out[slot] = my_w;
+        const int e = my_id - expert_lo;
+        slot_pos[slot] = (e >= 0 && e < experts_total) ? atomicAdd(my_counts + e, 1) : -1;
+      }
+    } else {
+      for (int j = lane; j < top_k; j += 32) {
+        const int64_t slot = static_cast<int64_t>(token) * top_k + j;
+        const int e = ids_in[slot] - expert_lo;
+        slot_pos[slot] = (e >= 0 && e < experts_total) ? atomicAdd(my_counts + e, 1) : -1;
       }
     }
   }
-  if (t == experts - 1) {
-    h.offsets[experts] = incl * 128;
-    *h.num_m_blocks = min(incl, max_m_blocks);
+  // the last CTA hands the counts to every rank (and clears them for the next step)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = atomicAdd(ctrl + kCtrlTicketCount, 1) == static_cast<int>(gridDim.x) - 1;
   }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const bool live = *reinterpret_cast<volatile int*>(ctrl + kCtrlAbort) == 0;
+  for (int e = threadIdx.x; e < experts_total; e += blockDim.x) {
+    const int c = atomicExch(my_counts + e, 0);
+    for (int d = 0; d < ex.world; ++d)
+      if (d == ex.rank || live)
+        reinterpret_cast<int*>(ex.peers.p[d] + ex.counts_all)[ex.rank * experts_total + e] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x < ex.world && threadIdx.x != ex.rank && live) {
+    __threadfence_system();
+    const int epoch = *reinterpret_cast<volatile int*>(ctrl + kCtrlEpoch) + 1;
+    st_release_sys(reinterpret_cast<int*>(ex.peers.p[threadIdx.x] + ex.flags) + 0 * kMaxPeers + ex.rank, epoch);
+  }
+  if (threadIdx.x == 0) ctrl[kCtrlTicketCount] = 0;
+}
+
+// place: see the section comment.  rows_per_block: valid rows that a 128-row block may hold (128, or 32 for the
+// few-row GEMM variants).  Dynamic shared memory: 3 * experts_total ints.
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads)
+moe_quant_place_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids,
+                       const int* __restrict__ slot_pos, Exchange ex, int tokens, int hidden, int top_k,
+                       int expert_lo, int experts_total, int max_m_blocks, int rows_per_block, int* slot_row,
+                       int* num_m_blocks, int* m_block_expert, int* m_block_rows, int* ctrl, int* status) {
+  extern __shared__ int s_dyn[];
+  int* s_base = s_dyn;                       // blocks before expert e (over all experts, in expert order)
+  int* s_myoff = s_dyn + experts_total;      // rows of lower ranks inside expert e's segment
+  int* s_tot = s_dyn + 2 * experts_total;    // rows of expert e over all ranks
+  __shared__ int s_warp[kThreads / 32];
+  __shared__ int s_flag;
+  __shared__ int s_rows[64];
+  __shared__ int s_dst[64];
+  if (!wait_all_ranks(ex, 0, ctrl, status, &s_flag)) return;
+
+  const int rpb = rows_per_block;
+  const int el = ex.experts_local;
+  const int* counts = reinterpret_cast<const int*>(ex.peers.p[ex.rank] + ex.counts_all);
+  const int per_thread = (experts_total + kThreads - 1) / kThreads;
+  const int e0 = threadIdx.x * per_thread;
+  int my_blocks = 0;
+  for (int i = 0; i < per_thread; ++i) {
+    const int e = e0 + i;
+    if (e < experts_total) {
+      int tot = 0, off = 0;
+      for (int r = 0; r < ex.world; ++r) {
+        const int c = __ldcg(counts + r * experts_total + e);
+        if (r < ex.rank) off += c;
+        tot += c;
+      }
+      s_tot[e] = tot;
+      s_myoff[e] = off;
+      my_blocks += (tot + rpb - 1) / rpb;
+    }
+  }
+  // exclusive scan of my_blocks over the CTA's threads
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int incl = my_blocks;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == 31) s_warp[warp] = incl;
+  __syncthreads();
+  int before = 0;
+  for (int w = 0; w < warp; ++w) before += s_warp[w];
+  int run = before + incl - my_blocks;
+  for (int i = 0; i < per_thread; ++i) {
+    const int e = e0 + i;
+    if (e < experts_total) {
+      s_base[e] = run;
+      run += (s_tot[e] + rpb - 1) / rpb;
+    }
+  }
+  __syncthreads();
+
+  if (blockIdx.x == 0) {               // block tables of this rank's experts for the grouped GEMMs
+    const int first = ex.rank * el;
+    const int seg0 = s_base[first];
+    for (int le = threadIdx.x; le < el; le += kThreads) {
+      const int tot = s_tot[first + le];
+      const int nb = (tot + rpb - 1) / rpb;
+      const int b0 = s_base[first + le] - seg0;
+      for (int b = 0; b < nb; ++b) {
+        if (b0 + b < max_m_blocks) {
+          m_block_expert[b0 + b] = le;
+          m_block_rows[b0 + b] = min(rpb, tot - rpb * b);
+        }
+      }
+    }
+    if (threadIdx.x == 0) {
+      const int last = first + el - 1;
+      *num_m_blocks = min(s_base[last] - seg0 + (s_tot[last] + rpb - 1) / rpb, max_m_blocks);
+    }
+  }
+
+  const int nchunks = hidden >> 4;
+  const int rk = (nchunks + 3) >> 2;
+  const int trips = (nchunks + kThreads - 1) / kThreads;
+  for (int token = blockIdx.x; token < tokens; token += gridDim.x) {
+    __syncthreads();
+    if (threadIdx.x < top_k) {
+      const int64_t slot = static_cast<int64_t>(token) * top_k + threadIdx.x;
+      const int e = ids[slot] - expert_lo;
+      const int pos = slot_pos[slot];
+      int row = -1, d = 0;
+      if (e >= 0 && e < experts_total && pos >= 0) {
+        d = e / el;
+        const int r = s_myoff[e] + pos;
+        row = (s_base[e] - s_base[d * el] + r / rpb) * 128 + r % rpb;
+        if (row >= max_m_blocks * 128) row = -1;
+        else reinterpret_cast<int*>(ex.peers.p[d] + ex.row_tag)[row] = (ex.rank << 24) | static_cast<int>(slot);
+      }
+      s_rows[threadIdx.x] = row;
+      s_dst[threadIdx.x] = d;
+      if (slot_row != nullptr) slot_row[slot] = row;
+    }
+    __syncthreads();
+    for (int it = 0; it < trips; ++it) {
+      const int chunk = it * kThreads + threadIdx.x;
+      const bool valid = chunk < nchunks;
+      uint32_t lo = 0, hi = 0, sfb = 0;
+      if (valid) {
+        const U32x8 raw = ld_stream_32B(x + static_cast<int64_t>(token) * hidden + chunk * 16);
+        uint64_t v2[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v2[i] = pair16_to_f32x2<__nv_bfloat16>(raw.v[i]);
+        quantize_block16<true>(v2, 1.0f, lo, hi, sfb);
+      }
+      // the scale bytes of four consecutive blocks of a row are adjacent in the 128x4 tiles: one 32-bit store
+      uint32_t quad = sfb & 0xffu;
+      quad |= (__shfl_down_sync(0xffffffffu, sfb, 1) & 0xffu) << 8;
+      quad |= (__shfl_down_sync(0xffffffffu, sfb, 2) & 0xffu) << 16;
+      quad |= (__shfl_down_sync(0xffffffffu, sfb, 3) & 0xffu) << 24;
+      if (!valid) continue;
+      for (int j = 0; j < top_k; ++j) {
+        const int row = s_rows[j];
+        if (row < 0) continue;
+        uint8_t* base = ex.peers.p[s_dst[j]];
+        *reinterpret_cast<uint2*>(base + ex.xq + static_cast<int64_t>(row) * (hidden >> 1) + chunk * 8) = make_uint2(lo, hi);
+        if ((chunk & 3) == 0)
+          *reinterpret_cast<uint32_t*>(base + ex.xq_sf + sf_swizzled_offset(row, chunk, rk)) = quad;
+      }
+    }
+  }
+  signal_when_all_ctas_done(ex, 1, ctrl, kCtrlTicketPlace, &s_flag);
 }
 
 // Few slots (<= 1024): count, scan and row assignment in one CTA -- one launch instead of a memset and three
 // kernels, which is most of a decode step's bookkeeping time.  Rows of an expert go to its slots in slot order.
+// rows_per_block: valid rows that a 128-row block may hold.  128 normally; 32 for the few-row GEMM variants, which
+// load only the first 32 rows of every block (an expert with more rows than that simply gets more blocks).
 __global__ void __launch_bounds__(1024) moe_prepare_small_kernel(const int* __restrict__ ids, int n_slots, int expert_lo,
                                                                  MoeHeader h, int experts, int max_m_blocks,
-                                                                 int max_rows) {
+                                                                 int max_rows, int rows_per_block) {
   __shared__ int s_count[1024];
   __shared__ int s_blocks[1024];
   __shared__ int s_offset[1024];
@@ -194,7 +447,7 @@ __global__ void __launch_bounds__(1024) moe_prepare_small_kernel(const int* __re
   }
   __syncthreads();
   const int count = t < experts ? s_count[t] : 0;
-  const int blocks = (count + 127) >> 7;
+  const int blocks = (count + rows_per_block - 1) / rows_per_block;
   s_blocks[t] = blocks;
   __syncthreads();
   for (int o = 1; o < 1024; o <<= 1) {
@@ -213,7 +466,7 @@ __global__ void __launch_bounds__(1024) moe_prepare_small_kernel(const int* __re
     for (int b = 0; b < blocks; ++b) {
       if (excl + b < max_m_blocks) {
         h.m_block_expert[excl + b] = t;
-        h.m_block_rows[excl + b] = min(128, count - 128 * b);
+        h.m_block_rows[excl + b] = min(rows_per_block, count - rows_per_block * b);
       }
     }
   }
@@ -225,7 +478,7 @@ __global__ void __launch_bounds__(1024) moe_prepare_small_kernel(const int* __re
   if (t < n_slots) {
     int row = -1;
     if (e >= 0) {
-      row = s_offset[e] + rank_in_expert;
+      row = s_offset[e] + (rank_in_expert / rows_per_block) * 128 + rank_in_expert % rows_per_block;
       if (row >= max_rows) row = -1;
     }
     h.slot_row[t] = row;
@@ -244,45 +497,6 @@ moe_scatter_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, const int* __
   const int nchunks = hidden >> 4;
   const int rk = (nchunks + 3) >> 2;
   for (int chunk = blockIdx.y * kThreads + threadIdx.x; chunk < nchunks; chunk += gridDim.y * kThreads) {
-    const U32x8 raw = ld_stream_32B(x + static_cast<int64_t>(token) * hidden + chunk * 16);
-    float v[16];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      v[2 * i] = Pair16<__nv_bfloat16>::lo(raw.v[i]);
-      v[2 * i + 1] = Pair16<__nv_bfloat16>::hi(raw.v[i]);
-    }
-    uint32_t lo, hi, sfb;
-    quantize_block16<true>(v, 1.0f, lo, hi, sfb);
-    for (int j = 0; j < top_k; ++j) {
-      const int row = s_rows[j];
-      if (row < 0) continue;
-      *reinterpret_cast<uint2*>(xq + static_cast<int64_t>(row) * (hidden >> 1) + chunk * 8) = make_uint2(lo, hi);
-      xq_sf[sf_swizzled_offset(row, chunk, rk)] = static_cast<uint8_t>(sfb);
-    }
-  }
-}
-
-// one CTA per token: quantise the row once, then write it to the row of every local slot
-template <int kThreads>
-__global__ void __launch_bounds__(kThreads)
-moe_scatter_quant_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids, MoeHeader h, uint8_t* xq,
-                         uint8_t* xq_sf, int hidden, int top_k, int expert_lo, int experts, int max_rows) {
-  __shared__ int s_rows[64];
-  const int token = blockIdx.x;
-  if (threadIdx.x < top_k) {
-    const int e = ids[static_cast<int64_t>(token) * top_k + threadIdx.x] - expert_lo;
-    int row = -1;
-    if (e >= 0 && e < experts) {
-      row = h.offsets[e] + atomicAdd(h.cursor + e, 1);
-      if (row >= max_rows) row = -1;
-    }
-    s_rows[threadIdx.x] = row;
-    h.slot_row[static_cast<int64_t>(token) * top_k + threadIdx.x] = row;
-  }
-  __syncthreads();
-  const int nchunks = hidden >> 4;
-  const int rk = (nchunks + 3) >> 2;
-  for (int chunk = threadIdx.x; chunk < nchunks; chunk += kThreads) {
     const U32x8 raw = ld_stream_32B(x + static_cast<int64_t>(token) * hidden + chunk * 16);
     float v[16];
 #pragma unroll
@@ -425,14 +639,26 @@ __global__ void moe_combine_few_kernel(const RowT* __restrict__ partial, const i
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// With at most 32 tokens (and few enough slots for the single-CTA bookkeeping kernel) the wide GEMM variants keep
+// only 32 rows of A per stage, which buys another stage of weights in flight.  The bookkeeping then fills every
+// 128-row block with at most 32 rows, so an expert that is named more than 32 times (ids may repeat inside a
+// token: the reference's own bench draws them with replacement, tools/perf/bench_flashinfer_b12x.py:70-71)
+// gets several blocks instead of wrong results.
+inline bool moe_few_rows(int64_t tokens, int top_k) { return tokens <= 32 && tokens * top_k <= 1024; }
+
 struct MoeWorkspace {
   MoeHeader h;
+  int* ctrl;               // [kCtrlWords] + my_counts [experts] right behind it: cleared together at every call
+  int* my_counts;
+  int* counts_all;         // [experts]
+  int* slot_pos;           // [slots]
+  int* row_tag;            // [rows]
   uint8_t* xq;
   uint8_t* xq_sf;
   uint8_t* act;
   uint8_t* act_sf;
   float* partial;
-  size_t header_bytes;     // counts .. slot_row
+  size_t clear_bytes;      // ctrl + my_counts
   size_t xq_sf_bytes;
   size_t total;
   int max_m_blocks;
@@ -441,7 +667,8 @@ struct MoeWorkspace {
 MoeWorkspace carve(void* base, int64_t tokens, int hidden, int inter, int experts, int top_k) {
   MoeWorkspace w{};
   const int64_t slots = tokens * top_k;
-  const int64_t blocks = std::min<int64_t>(experts, slots) + slots / 128;
+  // few-row launches (see moe_fused) fill a block with at most 32 rows
+  const int64_t blocks = std::min<int64_t>(experts, slots) + slots / (moe_few_rows(tokens, top_k) ? 32 : 128);
   w.max_m_blocks = static_cast<int>(blocks);
   const int64_t rows = blocks * 128;
   uint8_t* p = static_cast<uint8_t*>(base);
@@ -458,7 +685,12 @@ MoeWorkspace carve(void* base, int64_t tokens, int hidden, int inter, int expert
   w.h.m_block_expert = reinterpret_cast<int*>(take(sizeof(int) * blocks));
   w.h.m_block_rows = reinterpret_cast<int*>(take(sizeof(int) * blocks));
   w.h.slot_row = reinterpret_cast<int*>(take(sizeof(int) * slots));
-  w.header_bytes = off;
+  w.ctrl = reinterpret_cast<int*>(take(sizeof(int) * (kCtrlWords + experts)));
+  w.my_counts = w.ctrl == nullptr ? nullptr : w.ctrl + kCtrlWords;
+  w.clear_bytes = sizeof(int) * (kCtrlWords + experts);
+  w.counts_all = reinterpret_cast<int*>(take(sizeof(int) * experts));
+  w.slot_pos = reinterpret_cast<int*>(take(sizeof(int) * slots));
+  w.row_tag = reinterpret_cast<int*>(take(sizeof(int) * rows));
   w.xq_sf_bytes = static_cast<size_t>(blocks) * ((hidden + 63) / 64) * 512;
   w.xq_sf = take(w.xq_sf_bytes);
   w.xq = take(static_cast<size_t>(rows) * (hidden / 2));
@@ -469,14 +701,64 @@ MoeWorkspace carve(void* base, int64_t tokens, int hidden, int inter, int expert
   return w;
 }
 
+// launch of the count kernel: routing from logits when `logits` is given (ids_out / weights_out receive the
+// result), else the caller's ids
+int launch_count(const float* logits, int route_experts, int renormalize, const int* ids_in, int* ids_out,
+                 float* weights_out, int tokens, int top_k, int expert_lo, int experts_total, int* my_counts,
+                 int* slot_pos, int* ctrl, const Exchange& ex, cudaStream_t stream) {
+  const dim3 grid((tokens + 3) / 4), block(128);
+  if (logits == nullptr) {
+    moe_count_kernel<0><<<grid, block, 0, stream>>>(nullptr, 0, 0, ids_in, nullptr, nullptr, tokens, top_k, expert_lo,
+                                                    experts_total, my_counts, slot_pos, ctrl, ex);
+  } else if (route_experts <= 64) {
+    moe_count_kernel<2><<<grid, block, 0, stream>>>(logits, route_experts, renormalize, nullptr, ids_out, weights_out,
+                                                    tokens, top_k, expert_lo, experts_total, my_counts, slot_pos, ctrl, ex);
+  } else if (route_experts <= 128) {
+    moe_count_kernel<4><<<grid, block, 0, stream>>>(logits, route_experts, renormalize, nullptr, ids_out, weights_out,
+                                                    tokens, top_k, expert_lo, experts_total, my_counts, slot_pos, ctrl, ex);
+  } else if (route_experts <= 256) {
+    moe_count_kernel<8><<<grid, block, 0, stream>>>(logits, route_experts, renormalize, nullptr, ids_out, weights_out,
+                                                    tokens, top_k, expert_lo, experts_total, my_counts, slot_pos, ctrl, ex);
+  } else {
+    moe_count_kernel<kRouteMaxPerLane><<<grid, block, 0, stream>>>(logits, route_experts, renormalize, nullptr, ids_out,
+                                                                   weights_out, tokens, top_k, expert_lo, experts_total,
+                                                                   my_counts, slot_pos, ctrl, ex);
+  }
+  return check_cuda(cudaGetLastError(), "moe_count_kernel launch");
+}
+
+int launch_place(const void* x, const int* ids, const int* slot_pos, const Exchange& ex, int tokens, int hidden,
+                 int top_k, int expert_lo, int experts_total, int max_m_blocks, int rows_per_block, int* slot_row,
+                 int* num_m_blocks, int* m_block_expert, int* m_block_rows, int* ctrl, int* status,
+                 cudaStream_t stream) {
+  const int grid = std::max(1, std::min(tokens, 8 * sm_count_of_current_device()));
+  const size_t smem = sizeof(int) * 3 * experts_total;
+  if (hidden >= 4096) {
+    moe_quant_place_kernel<256><<<grid, 256, smem, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), ids, slot_pos, ex, tokens, hidden, top_k, expert_lo, experts_total,
+        max_m_blocks, rows_per_block, slot_row, num_m_blocks, m_block_expert, m_block_rows, ctrl, status);
+  } else {
+    moe_quant_place_kernel<128><<<grid, 128, smem, stream>>>(
+        static_cast<const __nv_bfloat16*>(x), ids, slot_pos, ex, tokens, hidden, top_k, expert_lo, experts_total,
+        max_m_blocks, rows_per_block, slot_row, num_m_blocks, m_block_expert, m_block_rows, ctrl, status);
+  }
+  return check_cuda(cudaGetLastError(), "moe_quant_place_kernel launch");
+}
+
+int route_check(int tokens, int experts, int top_k) {
+  if (tokens < 0 || experts < 1 || top_k < 1 || top_k > 32 || top_k > experts)
+    return fail(kInvalidArgument, "tokens=%d experts=%d top_k=%d", tokens, experts, top_k);
+  if (experts > 32 * kRouteMaxPerLane) return fail(kUnsupported, "experts=%d exceeds %d", experts, 32 * kRouteMaxPerLane);
+  return kOk;
+}
+
 }  // namespace
 
 int route_topk(const float* logits, int* ids, float* weights, int tokens, int experts, int top_k, int renormalize,
                cudaStream_t stream) {
   if (logits == nullptr || ids == nullptr || weights == nullptr) return fail(kInvalidArgument, "null pointer argument");
-  if (tokens < 0 || experts < 1 || top_k < 1 || top_k > 32 || top_k > experts)
-    return fail(kInvalidArgument, "tokens=%d experts=%d top_k=%d", tokens, experts, top_k);
-  if (experts > 32 * kRouteMaxPerLane) return fail(kUnsupported, "experts=%d exceeds %d", experts, 32 * kRouteMaxPerLane);
+  int rc = route_check(tokens, experts, top_k);
+  if (rc) return rc;
   if (tokens == 0) return kOk;
   const int warps_per_cta = 4;
   const dim3 grid((tokens + warps_per_cta - 1) / warps_per_cta), block(32 * warps_per_cta);
@@ -497,13 +779,15 @@ size_t moe_workspace_bytes(int64_t tokens, int hidden, int inter, int experts, i
 }
 
 // status: device word that the GEMM kernels OR failure bits into.
-// experts = number of LOCAL experts (w1/w2/alphas hold exactly those); token_selected_experts holds global
-// ids, of which [expert_lo, expert_lo + experts) are served here.  accumulate != 0 adds into `out`.
-int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, const void* w2_sf, const int* ids,
-              const float* route_w, const float* w1_alpha, const float* w2_alpha, const float* fc2_input_scale,
-              void* out, int64_t tokens, int hidden, int inter, int experts, int top_k, int expert_lo,
-              int accumulate, int out_dtype, void* workspace, size_t workspace_bytes, int* status,
-              cudaStream_t stream) {
+// experts = number of LOCAL experts (w1/w2/alphas hold exactly those); the expert ids are global, of which
+// [expert_lo, expert_lo + experts) are served here.  accumulate != 0 adds into `out`.
+// Routing: either `ids` and `route_w` are inputs (logits == nullptr), or `logits` f32 [tokens, route_experts] is
+// given and the router runs inside the front end, writing its choice to `ids` / `route_w` (then outputs).
+int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, const void* w2_sf, int* ids,
+              float* route_w, const float* logits, int route_experts, int renormalize, const float* w1_alpha,
+              const float* w2_alpha, const float* fc2_input_scale, void* out, int64_t tokens, int hidden, int inter,
+              int experts, int top_k, int expert_lo, int accumulate, int out_dtype, void* workspace,
+              size_t workspace_bytes, int* status, cudaStream_t stream) {
   if (out_dtype < 1 || out_dtype > 3)
     return fail(kUnsupported, "out_dtype code %d (1 bf16, 2 f32, 3 bf16 with bf16 per-slot rows)", out_dtype);
   const int rows_bf16 = out_dtype == 3;
@@ -518,33 +802,54 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
       ((reinterpret_cast<uintptr_t>(w1) | reinterpret_cast<uintptr_t>(w2) | reinterpret_cast<uintptr_t>(w1_sf) |
         reinterpret_cast<uintptr_t>(w2_sf)) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
     return fail(kInvalidArgument, "misaligned pointer (x 32 B, weights 16 B, workspace 256 B, out 16 B)");
-  if (tokens * top_k > (1ll << 30)) return fail(kUnsupported, "too many routed rows");
+  if (tokens * top_k > (1ll << 24)) return fail(kUnsupported, "too many routed rows (at most 2^24 slots)");
+  if (logits != nullptr) {
+    int rc = route_check(static_cast<int>(tokens), route_experts, top_k);
+    if (rc) return rc;
+  }
   if (tokens == 0) return kOk;
   MoeWorkspace ws = carve(workspace, tokens, hidden, inter, experts, top_k);
   if (workspace_bytes < ws.total)
     return fail(kInvalidArgument, "workspace holds %zu bytes, %zu needed", workspace_bytes, ws.total);
   const int slots = static_cast<int>(tokens * top_k);
   const int max_rows = ws.max_m_blocks * 128;
+  const int few_rows = moe_few_rows(tokens, top_k);
 
   B200_CUDA(cudaMemsetAsync(ws.xq_sf, 0, ws.xq_sf_bytes, stream));      // rows that only pad a block read as zero
   if (slots <= 1024) {
-    moe_prepare_small_kernel<<<1, 1024, 0, stream>>>(ids, slots, expert_lo, ws.h, experts, ws.max_m_blocks, max_rows);
+    // few slots: one CTA counts, scans and assigns rows in slot order; quantisation splits a token's columns
+    // over several CTAs (a decode step is mostly the latency of these small kernels)
+    if (logits != nullptr) {
+      int rc = route_topk(logits, ids, route_w, static_cast<int>(tokens), route_experts, top_k, renormalize, stream);
+      if (rc) return rc;
+    }
+    moe_prepare_small_kernel<<<1, 1024, 0, stream>>>(ids, slots, expert_lo, ws.h, experts, ws.max_m_blocks, max_rows,
+                                                     few_rows ? 32 : 128);
     const int parts = std::max(1, std::min(8, (hidden / 16) / 128));
     moe_scatter_quant_rows_kernel<128><<<dim3(static_cast<unsigned>(tokens), parts), 128, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(x), ws.h.slot_row, ws.xq, ws.xq_sf, hidden, top_k);
   } else {
-    B200_CUDA(cudaMemsetAsync(ws.h.counts, 0, sizeof(int) * experts, stream));
-    moe_count_kernel<<<(slots + kCountSlotsPerCta - 1) / kCountSlotsPerCta, 256, 0, stream>>>(ids, slots, expert_lo,
-                                                                                                experts, ws.h.counts);
-    moe_scan_kernel<<<1, 1024, 0, stream>>>(ws.h, experts, ws.max_m_blocks);
-    moe_scatter_quant_kernel<128><<<static_cast<unsigned>(tokens), 128, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(x), ids, ws.h, ws.xq, ws.xq_sf, hidden, top_k, expert_lo, experts, max_rows);
+    // two launches for any number of tokens: (route +) count, then scan + quantise + place
+    B200_CUDA(cudaMemsetAsync(ws.ctrl, 0, ws.clear_bytes, stream));
+    Exchange ex{};
+    uint8_t* base = static_cast<uint8_t*>(workspace);
+    ex.peers.p[0] = base;
+    ex.counts_all = reinterpret_cast<uint8_t*>(ws.counts_all) - base;
+    ex.xq = ws.xq - base;
+    ex.xq_sf = ws.xq_sf - base;
+    ex.row_tag = reinterpret_cast<uint8_t*>(ws.row_tag) - base;
+    ex.rank = 0;
+    ex.world = 1;
+    ex.experts_local = experts;
+    int rc = launch_count(logits, route_experts, renormalize, ids, ids, route_w, static_cast<int>(tokens), top_k,
+                          expert_lo, experts, ws.my_counts, ws.slot_pos, ws.ctrl, ex, stream);
+    if (rc) return rc;
+    rc = launch_place(x, ids, ws.slot_pos, ex, static_cast<int>(tokens), hidden, top_k, expert_lo, experts,
+                      ws.max_m_blocks, 128, ws.h.slot_row, ws.h.num_m_blocks, ws.h.m_block_expert, ws.h.m_block_rows,
+                      ws.ctrl, status, stream);
+    if (rc) return rc;
   }
   B200_CUDA(cudaGetLastError());
-  // With at most 32 tokens no expert receives more than 32 rows (a token names an expert once, as top-k selection
-  // does): the wide GEMM variants then keep 32 rows of A per stage and one more stage of weights in flight.  A
-  // row block that breaks the assumption raises bit 8 of the device status word instead of passing unnoticed.
-  const int few_rows = tokens <= 32;
   int rc = gemm_moe_fc1(ws.xq, ws.xq_sf, w1, w1_sf, ws.act, ws.act_sf, w1_alpha, fc2_input_scale, ws.h.num_m_blocks,
                         ws.h.m_block_expert, ws.h.m_block_rows, ws.max_m_blocks, hidden, inter, experts, few_rows,
                         status, stream);
@@ -578,253 +883,207 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
 // Expert parallelism over peer memory.
 //
 // Every rank owns a slice of the token batch and a contiguous range of experts.  All ranks hold a
-// buffer of identical layout that the others can address (peer pointers: NVLink loads, no
-// multimem, no TMA from peer memory).  One step is three launches per rank, separated by two
-// cross-rank barriers that the caller provides:
+// buffer of identical layout that the others can address (peer pointers over NVLink: plain loads
+// and stores of these kernels, no multimem, no TMA or bulk copy on peer memory).  One step per rank:
 //
-//   stage      quantise the local tokens ONCE to NVFP4 and publish codes, scale bytes and expert
-//              ids in the own buffer                                                   -- barrier --
-//   compute    count the slots of ALL ranks' tokens that hit local experts, lay the rows out,
-//              pull the quantised rows over NVLink straight into the expert-major GEMM operand
-//              (4.5 bits per element cross the wire instead of 16), FC1, FC2, then send every
-//              output row home: whole 8 KB rows written into the buffer of the rank that owns the
-//              token (coalesced peer stores; row-strided 32-byte stores from inside the GEMM
-//              epilogue were measured 2x slower end to end)                            -- barrier --
-//   combine    every rank sums the k rows that arrived for each of its tokens (local memory),
-//              one bf16 rounding
+//   dispatch   count kernel (routing optional) -> signal 0 -> place kernel: waits for every rank's
+//              counts, then quantises the rank's tokens ONCE to NVFP4 and writes every (token, slot)
+//              row straight into the expert-major FC1 operand of the rank that owns the slot's
+//              expert (4.5 bits per element cross the wire instead of 16) -> signal 1
+//   compute    wait for signal 1 of every rank; FC1; FC2, whose epilogue stores every output row
+//              (bf16) into the landing zone of the rank that owns the token while the remaining
+//              tiles are still being computed; -> signal 2
+//   combine    wait for signal 2 of every rank; sum the k rows of each local token in f32 in slot
+//              order, one bf16 rounding
 //
-// The reference has no multi-GPU path; this is the dispatch / combine all-to-all of an
-// expert-parallel MoE written as kernels over peer memory.
+// The signals carry a step counter, so the three of them also separate consecutive steps (a rank can
+// only run ahead of a peer by less than one phase of the same kind); there is no other barrier.
+// Every wait is bounded (Exchange::wait_ns).  The reference has no multi-GPU path; this is the
+// dispatch / combine all-to-all of an expert-parallel MoE written as kernels over peer memory.
 // =============================================================================================
 namespace b200fp4 {
+
+int gemm_moe_fc2_push(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf,
+                      const int* row_tag, const PeerPtrs& peers, size_t recv_off, const int* abort_flag,
+                      const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
+                      const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int few_rows,
+                      int* status, cudaStream_t stream);
+
 namespace {
 
-constexpr int kMaxPeers = 16;
-struct PeerPtrs {
-  uint8_t* p[kMaxPeers];
-};
-
 struct EpLayout {
-  // published for peers: the rank's quantised tokens, and the landing zone of its tokens' output rows
-  size_t tok_codes, tok_sf, tok_ids, recv;
+  // written by peers
+  size_t flags, counts_all, xq_sf, xq, row_tag, recv;
   // private to the rank
-  size_t partial, row_dst, counts, cursor, offsets, num_m_blocks, m_block_expert, m_block_rows, xq_sf, xq, act_sf, act;
+  size_t ctrl, my_counts, slot_pos, ids, weights, num_m_blocks, m_block_expert, m_block_rows, act_sf, act;
   size_t xq_sf_bytes, total;
-  int max_m_blocks;
+  int max_m_blocks, rows_per_block;
 };
 
 EpLayout ep_layout(int64_t tokens_local, int hidden, int inter, int experts_local, int top_k, int world) {
   EpLayout L{};
-  const int64_t slots = tokens_local * world * top_k;
-  const int64_t blocks = std::min<int64_t>(experts_local, slots) + slots / 128;
+  const int64_t slots_local = tokens_local * top_k;
+  const int64_t slots = slots_local * world;
+  // the few-row GEMM variants when the whole batch has at most 32 tokens (decode): 32 rows per block
+  L.rows_per_block = moe_few_rows(tokens_local * world, top_k) ? 32 : 128;
+  const int64_t blocks = std::min<int64_t>(experts_local, slots) + slots / L.rows_per_block;
   L.max_m_blocks = static_cast<int>(blocks);
   const int64_t rows = blocks * 128;
+  const int64_t experts_total = static_cast<int64_t>(experts_local) * world;
   size_t off = 0;
   auto take = [&](size_t bytes) {
     const size_t r = off;
     off = align_up(off + bytes, 256);
     return r;
   };
-  L.tok_codes = take(static_cast<size_t>(tokens_local) * (hidden / 2));
-  L.tok_sf = take(static_cast<size_t>(tokens_local) * (hidden / 16));
-  L.tok_ids = take(sizeof(int) * tokens_local * top_k);
-  // per-slot output rows cross NVLink and are summed as bf16 rows (f32 accumulation in the combine)
-  L.recv = take(static_cast<size_t>(tokens_local) * top_k * hidden * sizeof(__nv_bfloat16));
-  L.partial = take(static_cast<size_t>(rows) * hidden * sizeof(__nv_bfloat16));
-  L.row_dst = take(sizeof(void*) * rows);
-  L.counts = take(sizeof(int) * experts_local);
-  L.cursor = take(sizeof(int) * experts_local);
-  L.offsets = take(sizeof(int) * (experts_local + 1));
-  L.num_m_blocks = take(sizeof(int));
-  L.m_block_expert = take(sizeof(int) * blocks);
-  L.m_block_rows = take(sizeof(int) * blocks);
+  L.flags = take(sizeof(int) * kSignalPhases * kMaxPeers);
+  L.counts_all = take(sizeof(int) * world * experts_total);
   L.xq_sf_bytes = static_cast<size_t>(blocks) * ((hidden + 63) / 64) * 512;
   L.xq_sf = take(L.xq_sf_bytes);
   L.xq = take(static_cast<size_t>(rows) * (hidden / 2));
+  L.row_tag = take(sizeof(int) * rows);
+  // per-slot output rows cross NVLink and are summed as bf16 rows (f32 accumulation in the combine)
+  L.recv = take(static_cast<size_t>(slots_local) * hidden * sizeof(__nv_bfloat16));
+  L.ctrl = take(sizeof(int) * kCtrlWords);
+  L.my_counts = take(sizeof(int) * experts_total);
+  L.slot_pos = take(sizeof(int) * slots_local);
+  L.ids = take(sizeof(int) * slots_local);
+  L.weights = take(sizeof(float) * slots_local);
+  L.num_m_blocks = take(sizeof(int));
+  L.m_block_expert = take(sizeof(int) * blocks);
+  L.m_block_rows = take(sizeof(int) * blocks);
   L.act_sf = take(static_cast<size_t>(blocks) * ((inter + 63) / 64) * 512);
   L.act = take(static_cast<size_t>(rows) * (inter / 2));
   L.total = off;
   return L;
 }
 
-// one CTA per local token: NVFP4 codes + row-major scale bytes + the token's expert ids
-template <int kThreads>
-__global__ void __launch_bounds__(kThreads)
-ep_stage_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids, uint8_t* tok_codes, uint8_t* tok_sf,
-                int* tok_ids, int hidden, int top_k) {
-  const int token = blockIdx.x;
-  if (threadIdx.x < top_k)
-    tok_ids[static_cast<int64_t>(token) * top_k + threadIdx.x] = ids[static_cast<int64_t>(token) * top_k + threadIdx.x];
-  const int nchunks = hidden >> 4;
-  for (int chunk = threadIdx.x; chunk < nchunks; chunk += kThreads) {
-    const U32x8 raw = ld_stream_32B(x + static_cast<int64_t>(token) * hidden + chunk * 16);
-    uint64_t v2[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v2[i] = pair16_to_f32x2<__nv_bfloat16>(raw.v[i]);
-    uint32_t lo, hi, sfb;
-    quantize_block16<true>(v2, 1.0f, lo, hi, sfb);
-    *reinterpret_cast<uint2*>(tok_codes + static_cast<int64_t>(token) * (hidden >> 1) + chunk * 8) = make_uint2(lo, hi);
-    tok_sf[static_cast<int64_t>(token) * nchunks + chunk] = static_cast<uint8_t>(sfb);
+// one warp: wait for `phase` of every rank (bounded).  When the wait fails (now or earlier in the step) the
+// block count of the grouped GEMMs that follow is set to zero: their tables may not have been written.
+__global__ void ep_wait_kernel(Exchange ex, int phase, int* ctrl, int* status, int* num_m_blocks) {
+  __shared__ int s_ok;
+  const bool ok = wait_all_ranks(ex, phase, ctrl, status, &s_ok);
+  if (!ok && threadIdx.x == 0 && num_m_blocks != nullptr) *num_m_blocks = 0;
+}
+
+// one warp, launched behind kernels that wrote to peer memory: raise `phase` at every peer
+__global__ void ep_signal_kernel(Exchange ex, int phase, int* ctrl) {
+  if (threadIdx.x < ex.world && threadIdx.x != ex.rank && *reinterpret_cast<volatile int*>(ctrl + kCtrlAbort) == 0) {
+    __threadfence_system();
+    const int epoch = *reinterpret_cast<volatile int*>(ctrl + kCtrlEpoch) + 1;
+    st_release_sys(reinterpret_cast<int*>(ex.peers.p[threadIdx.x] + ex.flags) + phase * kMaxPeers + ex.rank, epoch);
   }
 }
 
-__global__ void ep_count_kernel(PeerPtrs peers, size_t tok_ids_off, int slots_per_rank, int world, int expert_lo,
-                                int experts, int* counts) {
-  __shared__ int s_hist[1024];
-  for (int e = threadIdx.x; e < experts; e += blockDim.x) s_hist[e] = 0;
-  __syncthreads();
-  const int total = slots_per_rank * world;
-  const int first = blockIdx.x * kCountSlotsPerCta;
-  const int last = min(total, first + kCountSlotsPerCta);
-  for (int i = first + threadIdx.x; i < last; i += blockDim.x) {
-    const int src = i / slots_per_rank;
-    const int* ids = reinterpret_cast<const int*>(peers.p[src] + tok_ids_off);
-    const int e = ids[i - src * slots_per_rank] - expert_lo;
-    if (e >= 0 && e < experts) atomicAdd(s_hist + e, 1);
-  }
-  __syncthreads();
-  for (int e = threadIdx.x; e < experts; e += blockDim.x)
-    if (s_hist[e] != 0) atomicAdd(counts + e, s_hist[e]);
-}
-
-// one CTA per token of ANY rank: rows for its local slots, then the quantised row is pulled from its owner
-template <int kThreads>
-__global__ void __launch_bounds__(kThreads)
-ep_gather_kernel(PeerPtrs peers, EpLayout L, MoeHeader h, __nv_bfloat16** row_dst, uint8_t* xq, uint8_t* xq_sf,
-                 int tokens_local, int hidden, int top_k, int expert_lo, int experts, int max_rows) {
-  __shared__ int s_rows[64];
-  __shared__ int s_any;
-  const int g = blockIdx.x;                        // global token index
-  const int src = g / tokens_local;
-  const int t = g - src * tokens_local;
-  const uint8_t* peer = peers.p[src];
-  if (threadIdx.x == 0) s_any = 0;
-  __syncthreads();
-  if (threadIdx.x < top_k) {
-    const int e = reinterpret_cast<const int*>(peer + L.tok_ids)[static_cast<int64_t>(t) * top_k + threadIdx.x] - expert_lo;
-    int row = -1;
-    if (e >= 0 && e < experts) {
-      row = h.offsets[e] + atomicAdd(h.cursor + e, 1);
-      if (row >= max_rows) row = -1;
-    }
-    s_rows[threadIdx.x] = row;
-    if (row >= 0) {
-      s_any = 1;
-      // the output row of this slot goes home: slot (t, j) of rank src
-      row_dst[row] = reinterpret_cast<__nv_bfloat16*>(peers.p[src] + L.recv) +
-                     (static_cast<int64_t>(t) * top_k + threadIdx.x) * hidden;
-    }
-  }
-  __syncthreads();
-  if (!s_any) return;
-  const int nchunks = hidden >> 4;
-  const int rk = (nchunks + 3) >> 2;
-  const uint8_t* codes = peer + L.tok_codes + static_cast<int64_t>(t) * (hidden >> 1);
-  const uint8_t* sf = peer + L.tok_sf + static_cast<int64_t>(t) * nchunks;
-  for (int chunk = threadIdx.x; chunk < nchunks; chunk += kThreads) {
-    const uint2 c = *reinterpret_cast<const uint2*>(codes + chunk * 8);
-    const uint8_t s = sf[chunk];
-    for (int j = 0; j < top_k; ++j) {
-      const int row = s_rows[j];
-      if (row < 0) continue;
-      *reinterpret_cast<uint2*>(xq + static_cast<int64_t>(row) * (hidden >> 1) + chunk * 8) = c;
-      xq_sf[sf_swizzled_offset(row, chunk, rk)] = s;
-    }
-  }
-}
-
-// one CTA per row of the expert-major output (bf16): copy it to the landing zone of the token's rank
-__global__ void ep_return_rows_kernel(const __nv_bfloat16* __restrict__ partial,
-                                      __nv_bfloat16* const* __restrict__ row_dst,
-                                      const int* __restrict__ num_m_blocks, const int* __restrict__ m_block_rows,
-                                      int hidden) {
-  const int blk = blockIdx.x >> 7;
-  const int r = blockIdx.x & 127;
-  if (blk >= __ldg(num_m_blocks) || r >= __ldg(m_block_rows + blk)) return;
-  const int64_t row = blockIdx.x;
-  const uint4* src = reinterpret_cast<const uint4*>(partial + row * hidden);
-  uint4* dst = reinterpret_cast<uint4*>(row_dst[row]);
-  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = src[i];
-}
-
-// one CTA per local token: its k output rows have been delivered into this rank's own buffer
-__global__ void ep_combine_kernel(const __nv_bfloat16* __restrict__ recv, const float* __restrict__ weights,
-                                  __nv_bfloat16* __restrict__ out, int hidden, int top_k) {
+// Weighted sum of the k rows that arrived for each local token (this rank's own memory).  kFew: CTA (token,
+// column chunk) with independent loads of the k rows; otherwise one CTA per token.  Slots whose expert id is
+// outside [0, experts_total) were never computed and are skipped.  The last CTA closes the step.
+template <bool kFew>
+__global__ void ep_combine_kernel(const __nv_bfloat16* __restrict__ recv, const int* __restrict__ ids,
+                                  const float* __restrict__ weights, __nv_bfloat16* __restrict__ out, int hidden,
+                                  int top_k, int experts_total, Exchange ex, int* ctrl, int* status) {
   __shared__ float s_w[64];
+  __shared__ int s_valid[64];
+  __shared__ int s_flag;
+  const bool ok = wait_all_ranks(ex, 2, ctrl, status, &s_flag);
   const int t = blockIdx.x;
-  if (threadIdx.x < top_k) s_w[threadIdx.x] = weights[static_cast<int64_t>(t) * top_k + threadIdx.x];
-  __syncthreads();
-  const __nv_bfloat16* rows = recv + static_cast<int64_t>(t) * top_k * hidden;
-  for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int j = 0; j < top_k; ++j) {
-      const float4 pv = load_row4(rows + static_cast<int64_t>(j) * hidden + c);
-      const float w = s_w[j];
-      acc.x = __fadd_rn(acc.x, __fmul_rn(w, pv.x));
-      acc.y = __fadd_rn(acc.y, __fmul_rn(w, pv.y));
-      acc.z = __fadd_rn(acc.z, __fmul_rn(w, pv.z));
-      acc.w = __fadd_rn(acc.w, __fmul_rn(w, pv.w));
+  if (ok) {
+    if (threadIdx.x < top_k) {
+      const int id = ids[static_cast<int64_t>(t) * top_k + threadIdx.x];
+      s_valid[threadIdx.x] = id >= 0 && id < experts_total;
+      s_w[threadIdx.x] = weights[static_cast<int64_t>(t) * top_k + threadIdx.x];
     }
-    uint2 packed;
-    packed.x = Pair16<__nv_bfloat16>::pack(acc.x, acc.y);
-    packed.y = Pair16<__nv_bfloat16>::pack(acc.z, acc.w);
-    *reinterpret_cast<uint2*>(out + static_cast<int64_t>(t) * hidden + c) = packed;
-  }
-}
-
-// CTA (local token, column chunk): the token's k output rows have been delivered into this rank's own buffer
-__global__ void ep_combine_few_kernel(const __nv_bfloat16* __restrict__ recv, const float* __restrict__ weights,
-                                  __nv_bfloat16* __restrict__ out, int hidden, int top_k) {
-  __shared__ float s_w[64];
-  const int t = blockIdx.x;
-  if (threadIdx.x < top_k) s_w[threadIdx.x] = weights[static_cast<int64_t>(t) * top_k + threadIdx.x];
-  __syncthreads();
-  const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
-  if (c >= hidden) return;
-  const __nv_bfloat16* rows = recv + static_cast<int64_t>(t) * top_k * hidden;
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int j0 = 0; j0 < top_k; j0 += 8) {
-    float4 pv[8];
+    __syncthreads();
+    const __nv_bfloat16* rows = recv + static_cast<int64_t>(t) * top_k * hidden;
+    if constexpr (kFew) {
+      const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+      if (c < hidden) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j0 = 0; j0 < top_k; j0 += 8) {
+          float4 pv[8];
 #pragma unroll
-    for (int u = 0; u < 8; ++u)
-      pv[u] = j0 + u < top_k ? load_row4(rows + static_cast<int64_t>(j0 + u) * hidden + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int u = 0; u < 8; ++u)
+            pv[u] = (j0 + u < top_k && s_valid[j0 + u]) ? load_row4(rows + static_cast<int64_t>(j0 + u) * hidden + c)
+                                                        : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      if (j0 + u < top_k) {
-        const float w = s_w[j0 + u];
-        acc.x = __fadd_rn(acc.x, __fmul_rn(w, pv[u].x));
-        acc.y = __fadd_rn(acc.y, __fmul_rn(w, pv[u].y));
-        acc.z = __fadd_rn(acc.z, __fmul_rn(w, pv[u].z));
-        acc.w = __fadd_rn(acc.w, __fmul_rn(w, pv[u].w));
+          for (int u = 0; u < 8; ++u) {
+            if (j0 + u < top_k && s_valid[j0 + u]) {
+              const float w = s_w[j0 + u];
+              acc.x = __fadd_rn(acc.x, __fmul_rn(w, pv[u].x));
+              acc.y = __fadd_rn(acc.y, __fmul_rn(w, pv[u].y));
+              acc.z = __fadd_rn(acc.z, __fmul_rn(w, pv[u].z));
+              acc.w = __fadd_rn(acc.w, __fmul_rn(w, pv[u].w));
+            }
+          }
+        }
+        uint2 packed;
+        packed.x = Pair16<__nv_bfloat16>::pack(acc.x, acc.y);
+        packed.y = Pair16<__nv_bfloat16>::pack(acc.z, acc.w);
+        *reinterpret_cast<uint2*>(out + static_cast<int64_t>(t) * hidden + c) = packed;
+      }
+    } else {
+      for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int j = 0; j < top_k; ++j) {
+          if (!s_valid[j]) continue;
+          const float4 pv = load_row4(rows + static_cast<int64_t>(j) * hidden + c);
+          const float w = s_w[j];
+          acc.x = __fadd_rn(acc.x, __fmul_rn(w, pv.x));
+          acc.y = __fadd_rn(acc.y, __fmul_rn(w, pv.y));
+          acc.z = __fadd_rn(acc.z, __fmul_rn(w, pv.z));
+          acc.w = __fadd_rn(acc.w, __fmul_rn(w, pv.w));
+        }
+        uint2 packed;
+        packed.x = Pair16<__nv_bfloat16>::pack(acc.x, acc.y);
+        packed.y = Pair16<__nv_bfloat16>::pack(acc.z, acc.w);
+        *reinterpret_cast<uint2*>(out + static_cast<int64_t>(t) * hidden + c) = packed;
       }
     }
   }
-  uint2 packed;
-  packed.x = Pair16<__nv_bfloat16>::pack(acc.x, acc.y);
-  packed.y = Pair16<__nv_bfloat16>::pack(acc.z, acc.w);
-  *reinterpret_cast<uint2*>(out + static_cast<int64_t>(t) * hidden + c) = packed;
+  // the last CTA closes the step: the next step's kernels signal and wait for epoch + 1
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(ctrl + kCtrlTicketCombine, 1) == static_cast<int>(gridDim.x * gridDim.y) - 1) {
+      ctrl[kCtrlTicketCombine] = 0;
+      if (ok) atomicAdd(ctrl + kCtrlEpoch, 1);
+    }
+  }
 }
 
 int ep_check(int64_t tokens_local, int hidden, int inter, int experts_local, int top_k, int world, int rank) {
   if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
     return fail(kInvalidArgument, "world=%d rank=%d (at most %d ranks)", world, rank, kMaxPeers);
-  if (tokens_local < 0 || top_k < 1 || top_k > 64 || experts_local < 1 || experts_local > 1024)
-    return fail(kInvalidArgument, "tokens=%lld top_k=%d experts=%d", static_cast<long long>(tokens_local), top_k,
-                experts_local);
+  if (tokens_local < 0 || top_k < 1 || top_k > 64 || experts_local < 1 ||
+      static_cast<int64_t>(experts_local) * world > 1024)
+    return fail(kInvalidArgument, "tokens=%lld top_k=%d experts=%d x %d ranks (at most 1024 experts in total)",
+                static_cast<long long>(tokens_local), top_k, experts_local, world);
   if (hidden % 64 != 0 || hidden < 64) return fail(kUnsupported, "hidden=%d must be a multiple of 64", hidden);
   if (inter % 128 != 0 || inter < 128) return fail(kUnsupported, "intermediate=%d must be a multiple of 128", inter);
-  if (tokens_local * world * top_k > (1ll << 30)) return fail(kUnsupported, "too many routed rows");
+  if (tokens_local * top_k > (1ll << 24) || tokens_local * world * top_k > (1ll << 30))
+    return fail(kUnsupported, "too many routed rows");
   return kOk;
 }
 
-int ep_peers(const void* const* peer_buffers, int world, PeerPtrs* out) {
+int ep_exchange(const void* const* peer_buffers, int rank, int world, int experts_local, const EpLayout& L,
+                double wait_ms, Exchange* ex) {
   if (peer_buffers == nullptr) return fail(kInvalidArgument, "peer_buffers is null");
-  for (int i = 0; i < kMaxPeers; ++i) out->p[i] = nullptr;
+  *ex = Exchange{};
   for (int i = 0; i < world; ++i) {
     if (peer_buffers[i] == nullptr || (reinterpret_cast<uintptr_t>(peer_buffers[i]) & 255))
       return fail(kInvalidArgument, "peer buffer %d is null or not 256-byte aligned", i);
-    out->p[i] = static_cast<uint8_t*>(const_cast<void*>(peer_buffers[i]));
+    ex->peers.p[i] = static_cast<uint8_t*>(const_cast<void*>(peer_buffers[i]));
   }
+  ex->flags = L.flags;
+  ex->counts_all = L.counts_all;
+  ex->xq = L.xq;
+  ex->xq_sf = L.xq_sf;
+  ex->row_tag = L.row_tag;
+  ex->rank = rank;
+  ex->world = world;
+  ex->experts_local = experts_local;
+  if (!(wait_ms > 0.0) || wait_ms > 60000.0) return fail(kInvalidArgument, "wait_ms must be in (0, 60000]");
+  ex->wait_ns = static_cast<unsigned long long>(wait_ms * 1e6);
   return kOk;
 }
 
@@ -834,95 +1093,171 @@ size_t moe_ep_buffer_bytes(int64_t tokens_local, int hidden, int inter, int expe
   return ep_layout(tokens_local, hidden, inter, experts_local, top_k, world).total;
 }
 
-int moe_ep_stage(const void* x, const int* ids, void* own_buffer, int64_t tokens_local, int hidden, int inter,
-                 int experts_local, int top_k, int world, cudaStream_t stream) {
+// Clears the signal words, counters and the abort word of the rank's own buffer.  Call it on every rank with a
+// host-side barrier before and after (no step may be in flight anywhere), once after allocating the buffers and
+// again to recover after a wait expired.
+int moe_ep_reset(void* own_buffer, int64_t tokens_local, int hidden, int inter, int experts_local, int top_k,
+                 int world, cudaStream_t stream) {
   int rc = ep_check(tokens_local, hidden, inter, experts_local, top_k, world, 0);
   if (rc) return rc;
-  if (x == nullptr || ids == nullptr || own_buffer == nullptr) return fail(kInvalidArgument, "null pointer argument");
-  if ((reinterpret_cast<uintptr_t>(x) & 31) || (reinterpret_cast<uintptr_t>(own_buffer) & 255))
-    return fail(kInvalidArgument, "x must be 32-byte and the buffer 256-byte aligned");
-  if (tokens_local == 0) return kOk;
+  if (own_buffer == nullptr || (reinterpret_cast<uintptr_t>(own_buffer) & 255))
+    return fail(kInvalidArgument, "own_buffer is null or not 256-byte aligned");
   const EpLayout L = ep_layout(tokens_local, hidden, inter, experts_local, top_k, world);
   uint8_t* b = static_cast<uint8_t*>(own_buffer);
-  ep_stage_kernel<128><<<static_cast<unsigned>(tokens_local), 128, 0, stream>>>(
-      static_cast<const __nv_bfloat16*>(x), ids, b + L.tok_codes, b + L.tok_sf, reinterpret_cast<int*>(b + L.tok_ids),
-      hidden, top_k);
-  return check_cuda(cudaGetLastError(), "ep_stage_kernel launch");
+  B200_CUDA(cudaMemsetAsync(b + L.flags, 0, sizeof(int) * kSignalPhases * kMaxPeers, stream));
+  // control words, counters, routing and the block tables of the grouped GEMMs (zero blocks = nothing to do)
+  B200_CUDA(cudaMemsetAsync(b + L.ctrl, 0, L.act_sf - L.ctrl, stream));
+  return kOk;
+}
+
+// dispatch: (route +) count, publish counts, quantise and place the rows at the expert owners.
+// logits == nullptr: ids (and weights, used by the combine) are the caller's; else they are computed here into
+// the rank's buffer.  phases: bit 0 = the count kernel, bit 1 = the place kernel (the two are separate entry
+// points as well so that a test can interleave the ranks of a group on one stream).
+int moe_ep_dispatch(const void* x, const int* ids, const float* logits, int route_experts, int renormalize,
+                    const void* const* peer_buffers, int rank, int world, int64_t tokens_local, int hidden, int inter,
+                    int experts_local, int top_k, double wait_ms, int phases, int* status, cudaStream_t stream) {
+  int rc = ep_check(tokens_local, hidden, inter, experts_local, top_k, world, rank);
+  if (rc) return rc;
+  if (x == nullptr || (ids == nullptr && logits == nullptr) || status == nullptr)
+    return fail(kInvalidArgument, "null pointer argument");
+  if (reinterpret_cast<uintptr_t>(x) & 31) return fail(kInvalidArgument, "x must be 32-byte aligned");
+  const int experts_total = experts_local * world;
+  if (logits != nullptr) {
+    rc = route_check(static_cast<int>(tokens_local), route_experts, top_k);
+    if (rc) return rc;
+    if (route_experts != experts_total)
+      return fail(kInvalidArgument, "logits have %d columns but the group serves %d experts", route_experts, experts_total);
+  }
+  const EpLayout L = ep_layout(tokens_local, hidden, inter, experts_local, top_k, world);
+  Exchange ex;
+  rc = ep_exchange(peer_buffers, rank, world, experts_local, L, wait_ms, &ex);
+  if (rc) return rc;
+  if (tokens_local == 0) return fail(kUnsupported, "every rank must hold at least one token");
+  uint8_t* b = ex.peers.p[rank];
+  int* ctrl = reinterpret_cast<int*>(b + L.ctrl);
+  int* ids_buf = reinterpret_cast<int*>(b + L.ids);
+  float* w_buf = reinterpret_cast<float*>(b + L.weights);
+  if (phases & 1) {
+    // rows that only pad a block must read as zero; peers write into this memory only after this rank's signal 0
+    B200_CUDA(cudaMemsetAsync(b + L.xq_sf, 0, L.xq_sf_bytes, stream));
+    rc = launch_count(logits, route_experts, renormalize, ids, ids_buf, w_buf, static_cast<int>(tokens_local), top_k, 0,
+                      experts_total, reinterpret_cast<int*>(b + L.my_counts), reinterpret_cast<int*>(b + L.slot_pos),
+                      ctrl, ex, stream);
+    if (rc) return rc;
+  }
+  if (phases & 2) {
+    rc = launch_place(x, logits != nullptr ? ids_buf : ids, reinterpret_cast<int*>(b + L.slot_pos), ex,
+                      static_cast<int>(tokens_local), hidden, top_k, 0, experts_total, L.max_m_blocks,
+                      L.rows_per_block, nullptr, reinterpret_cast<int*>(b + L.num_m_blocks),
+                      reinterpret_cast<int*>(b + L.m_block_expert), reinterpret_cast<int*>(b + L.m_block_rows), ctrl,
+                      status, stream);
+    if (rc) return rc;
+  }
+  return kOk;
 }
 
 int moe_ep_compute(const void* const* peer_buffers, int rank, int world, const void* w1, const void* w1_sf,
                    const void* w2, const void* w2_sf, const float* w1_alpha, const float* w2_alpha,
                    const float* fc2_input_scale, int64_t tokens_local, int hidden, int inter, int experts_local,
-                   int top_k, int* status, cudaStream_t stream) {
+                   int top_k, double wait_ms, int* status, cudaStream_t stream) {
   int rc = ep_check(tokens_local, hidden, inter, experts_local, top_k, world, rank);
   if (rc) return rc;
   if (w1 == nullptr || w1_sf == nullptr || w2 == nullptr || w2_sf == nullptr || status == nullptr)
     return fail(kInvalidArgument, "null pointer argument");
-  PeerPtrs peers;
-  rc = ep_peers(peer_buffers, world, &peers);
-  if (rc) return rc;
-  if (tokens_local == 0) return kOk;
   const EpLayout L = ep_layout(tokens_local, hidden, inter, experts_local, top_k, world);
-  uint8_t* b = peers.p[rank];
-  MoeHeader h{};
-  h.counts = reinterpret_cast<int*>(b + L.counts);
-  h.cursor = reinterpret_cast<int*>(b + L.cursor);
-  h.offsets = reinterpret_cast<int*>(b + L.offsets);
-  h.num_m_blocks = reinterpret_cast<int*>(b + L.num_m_blocks);
-  h.m_block_expert = reinterpret_cast<int*>(b + L.m_block_expert);
-  h.m_block_rows = reinterpret_cast<int*>(b + L.m_block_rows);
-  h.slot_row = nullptr;
-  __nv_bfloat16** row_dst = reinterpret_cast<__nv_bfloat16**>(b + L.row_dst);
-  const int expert_lo = rank * experts_local;
-  const int slots_per_rank = static_cast<int>(tokens_local * top_k);
-  const int total_slots = slots_per_rank * world;
-  const int max_rows = L.max_m_blocks * 128;
-  B200_CUDA(cudaMemsetAsync(h.counts, 0, sizeof(int) * experts_local, stream));
-  B200_CUDA(cudaMemsetAsync(b + L.xq_sf, 0, L.xq_sf_bytes, stream));
-  ep_count_kernel<<<(total_slots + kCountSlotsPerCta - 1) / kCountSlotsPerCta, 256, 0, stream>>>(
-      peers, L.tok_ids, slots_per_rank, world, expert_lo, experts_local, h.counts);
-  moe_scan_kernel<<<1, 1024, 0, stream>>>(h, experts_local, L.max_m_blocks);
-  ep_gather_kernel<128><<<static_cast<unsigned>(tokens_local * world), 128, 0, stream>>>(
-      peers, L, h, row_dst, b + L.xq, b + L.xq_sf, static_cast<int>(tokens_local), hidden, top_k, expert_lo,
-      experts_local, max_rows);
-  B200_CUDA(cudaGetLastError());
-  const int few_rows = tokens_local * world <= 32;
-  rc = gemm_moe_fc1(b + L.xq, b + L.xq_sf, w1, w1_sf, b + L.act, b + L.act_sf, w1_alpha, fc2_input_scale,
-                    h.num_m_blocks, h.m_block_expert, h.m_block_rows, L.max_m_blocks, hidden, inter, experts_local,
-                    few_rows, status, stream);
+  Exchange ex;
+  rc = ep_exchange(peer_buffers, rank, world, experts_local, L, wait_ms, &ex);
   if (rc) return rc;
-  rc = gemm_moe_fc2(b + L.act, b + L.act_sf, w2, w2_sf, b + L.partial, /*rows_bf16=*/1, w2_alpha,
-                    h.num_m_blocks, h.m_block_expert, h.m_block_rows, L.max_m_blocks, hidden, inter, experts_local,
-                    few_rows, status, stream);
+  uint8_t* b = ex.peers.p[rank];
+  int* ctrl = reinterpret_cast<int*>(b + L.ctrl);
+  int* num_m_blocks = reinterpret_cast<int*>(b + L.num_m_blocks);
+  const int* m_block_expert = reinterpret_cast<const int*>(b + L.m_block_expert);
+  const int* m_block_rows = reinterpret_cast<const int*>(b + L.m_block_rows);
+  if (world > 1) {
+    ep_wait_kernel<<<1, 32, 0, stream>>>(ex, 1, ctrl, status, num_m_blocks);
+    B200_CUDA(cudaGetLastError());
+  }
+  const int few_rows = L.rows_per_block == 32;
+  rc = gemm_moe_fc1(b + L.xq, b + L.xq_sf, w1, w1_sf, b + L.act, b + L.act_sf, w1_alpha, fc2_input_scale, num_m_blocks,
+                    m_block_expert, m_block_rows, L.max_m_blocks, hidden, inter, experts_local, few_rows, status, stream);
   if (rc) return rc;
-  ep_return_rows_kernel<<<static_cast<unsigned>(max_rows), 256, 0, stream>>>(
-      reinterpret_cast<const __nv_bfloat16*>(b + L.partial), row_dst, h.num_m_blocks, h.m_block_rows, hidden);
-  return check_cuda(cudaGetLastError(), "ep_return_rows_kernel launch");
+  rc = gemm_moe_fc2_push(b + L.act, b + L.act_sf, w2, w2_sf, reinterpret_cast<const int*>(b + L.row_tag), ex.peers,
+                         L.recv, ctrl + kCtrlAbort, w2_alpha, num_m_blocks, m_block_expert, m_block_rows,
+                         L.max_m_blocks, hidden, inter, experts_local, few_rows, status, stream);
+  if (rc) return rc;
+  if (world > 1) {
+    ep_signal_kernel<<<1, 32, 0, stream>>>(ex, 2, ctrl);
+    B200_CUDA(cudaGetLastError());
+  }
+  return kOk;
 }
 
+// ids / weights: the routing of the local tokens; null = what the dispatch computed from logits
 int moe_ep_combine(const void* const* peer_buffers, int rank, int world, const int* ids, const float* weights,
                    void* out, int64_t tokens_local, int hidden, int inter, int experts_local, int top_k,
-                   cudaStream_t stream) {
+                   double wait_ms, int* status, cudaStream_t stream) {
   int rc = ep_check(tokens_local, hidden, inter, experts_local, top_k, world, rank);
   if (rc) return rc;
-  if (ids == nullptr || weights == nullptr || out == nullptr) return fail(kInvalidArgument, "null pointer argument");
-  PeerPtrs peers;
-  rc = ep_peers(peer_buffers, world, &peers);
+  if (out == nullptr || status == nullptr || (ids == nullptr) != (weights == nullptr))
+    return fail(kInvalidArgument, "null pointer argument (ids and weights are given together or not at all)");
+  const EpLayout L = ep_layout(tokens_local, hidden, inter, experts_local, top_k, world);
+  Exchange ex;
+  rc = ep_exchange(peer_buffers, rank, world, experts_local, L, wait_ms, &ex);
   if (rc) return rc;
   if (tokens_local == 0) return kOk;
-  const EpLayout L = ep_layout(tokens_local, hidden, inter, experts_local, top_k, world);
+  uint8_t* b = ex.peers.p[rank];
+  int* ctrl = reinterpret_cast<int*>(b + L.ctrl);
+  if (ids == nullptr) {
+    ids = reinterpret_cast<const int*>(b + L.ids);
+    weights = reinterpret_cast<const float*>(b + L.weights);
+  }
+  const __nv_bfloat16* recv = reinterpret_cast<const __nv_bfloat16*>(b + L.recv);
   const int threads = hidden / 4 >= 256 ? 256 : 128;
-  (void)ids;
+  const int experts_total = experts_local * world;
   if (tokens_local <= 256) {
-    ep_combine_few_kernel<<<dim3(static_cast<unsigned>(tokens_local), (hidden / 4 + threads - 1) / threads), threads, 0,
-                            stream>>>(reinterpret_cast<const __nv_bfloat16*>(peers.p[rank] + L.recv), weights,
-                                      static_cast<__nv_bfloat16*>(out), hidden, top_k);
+    ep_combine_kernel<true><<<dim3(static_cast<unsigned>(tokens_local), (hidden / 4 + threads - 1) / threads), threads, 0,
+                              stream>>>(recv, ids, weights, static_cast<__nv_bfloat16*>(out), hidden, top_k,
+                                        experts_total, ex, ctrl, status);
   } else {
-    ep_combine_kernel<<<static_cast<unsigned>(tokens_local), threads, 0, stream>>>(
-        reinterpret_cast<const __nv_bfloat16*>(peers.p[rank] + L.recv), weights, static_cast<__nv_bfloat16*>(out),
-        hidden, top_k);
+    ep_combine_kernel<false><<<static_cast<unsigned>(tokens_local), threads, 0, stream>>>(
+        recv, ids, weights, static_cast<__nv_bfloat16*>(out), hidden, top_k, experts_total, ex, ctrl, status);
   }
   return check_cuda(cudaGetLastError(), "ep_combine_kernel launch");
+}
+
+// Copies the routing that the dispatch computed from logits (ids i32, weights f32, [tokens_local, top_k]).
+int moe_ep_routing(const void* own_buffer, int* ids_out, float* weights_out, int64_t tokens_local, int hidden,
+                   int inter, int experts_local, int top_k, int world, cudaStream_t stream) {
+  int rc = ep_check(tokens_local, hidden, inter, experts_local, top_k, world, 0);
+  if (rc) return rc;
+  if (own_buffer == nullptr || ids_out == nullptr || weights_out == nullptr)
+    return fail(kInvalidArgument, "null pointer argument");
+  const EpLayout L = ep_layout(tokens_local, hidden, inter, experts_local, top_k, world);
+  const uint8_t* b = static_cast<const uint8_t*>(own_buffer);
+  const size_t n = static_cast<size_t>(tokens_local) * top_k;
+  B200_CUDA(cudaMemcpyAsync(ids_out, b + L.ids, n * sizeof(int), cudaMemcpyDeviceToDevice, stream));
+  B200_CUDA(cudaMemcpyAsync(weights_out, b + L.weights, n * sizeof(float), cudaMemcpyDeviceToDevice, stream));
+  return kOk;
+}
+
+// Self-test of the bounded cross-rank wait on ONE GPU: a wait for `world` ranks on a buffer whose signal words
+// nobody writes.  The kernel gives up after wait_ms, sets kStatusPeerWaitExpired in the device status word and
+// the abort word of the buffer, and returns; no peer memory is involved.
+int moe_ep_wait_selftest(void* own_buffer, int world, double wait_ms, int64_t tokens_local, int hidden, int inter,
+                         int experts_local, int top_k, int* status, cudaStream_t stream) {
+  int rc = ep_check(tokens_local, hidden, inter, experts_local, top_k, world, 0);
+  if (rc) return rc;
+  if (own_buffer == nullptr || status == nullptr) return fail(kInvalidArgument, "null pointer argument");
+  const EpLayout L = ep_layout(tokens_local, hidden, inter, experts_local, top_k, world);
+  const void* bufs[kMaxPeers];
+  for (int i = 0; i < world; ++i) bufs[i] = own_buffer;      // only this rank's words are ever read
+  Exchange ex;
+  rc = ep_exchange(bufs, 0, world, experts_local, L, wait_ms, &ex);
+  if (rc) return rc;
+  ep_wait_kernel<<<1, 32, 0, stream>>>(ex, 1, reinterpret_cast<int*>(static_cast<uint8_t*>(own_buffer) + L.ctrl), status,
+                                       nullptr);
+  return check_cuda(cudaGetLastError(), "ep_wait_kernel launch");
 }
 
 }  // namespace b200fp4

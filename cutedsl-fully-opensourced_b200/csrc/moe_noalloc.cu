@@ -24,11 +24,11 @@
 namespace b200fp4 {
 
 size_t moe_workspace_bytes(int64_t tokens, int hidden, int inter, int experts, int top_k);
-int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, const void* w2_sf, const int* ids,
-              const float* route_w, const float* w1_alpha, const float* w2_alpha, const float* fc2_input_scale,
-              void* out, int64_t tokens, int hidden, int inter, int experts, int top_k, int expert_lo,
-              int accumulate, int out_dtype, void* workspace, size_t workspace_bytes, int* status,
-              cudaStream_t stream);
+int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, const void* w2_sf, int* ids,
+              float* route_w, const float* logits, int route_experts, int renormalize, const float* w1_alpha,
+              const float* w2_alpha, const float* fc2_input_scale, void* out, int64_t tokens, int hidden, int inter,
+              int experts, int top_k, int expert_lo, int accumulate, int out_dtype, void* workspace,
+              size_t workspace_bytes, int* status, cudaStream_t stream);
 
 namespace {
 
@@ -67,7 +67,8 @@ extern "C" int b200fp4_moe_fused_noalloc(const void* x, const void* w1, const vo
                                          int local_expert_offset, int accumulate, int* status_word, void* stream) {
   if (status_word == nullptr) return fail(kInvalidArgument, "status_word is null");
   if (tokens < 0 || hidden <= 0 || intermediate <= 0 || local_experts <= 0 || top_k <= 0)
-    return fail(kInvalidArgument, "tokens, hidden, intermediate, local_experts, top_k must be positive");
+    return fail(kInvalidArgument,
+                "tokens must not be negative; hidden, intermediate, local_experts and top_k must be positive");
   const size_t need = moe_workspace_bytes(tokens, hidden, intermediate, local_experts, top_k);
   if (need > kBuiltinScratchBytes)
     return fail(kUnsupported,
@@ -76,8 +77,8 @@ extern "C" int b200fp4_moe_fused_noalloc(const void* x, const void* w1, const vo
   void* scratch = nullptr;
   int rc = builtin_scratch(&scratch);
   if (rc) return rc;
-  return moe_fused(x, w1, w1_sf, w2, w2_sf, token_selected_experts, token_final_scales, w1_alpha, w2_alpha,
-                   fc2_input_scale, out, tokens, hidden, intermediate, local_experts, top_k, local_expert_offset,
+  return moe_fused(x, w1, w1_sf, w2, w2_sf, const_cast<int*>(token_selected_experts),
+                   const_cast<float*>(token_final_scales), nullptr, 0, 0, w1_alpha, w2_alpha, fc2_input_scale, out, tokens, hidden, intermediate, local_experts, top_k, local_expert_offset,
                    accumulate, /*out_dtype=bf16*/ 1, scratch, kBuiltinScratchBytes, status_word,
                    static_cast<cudaStream_t>(stream));
 }

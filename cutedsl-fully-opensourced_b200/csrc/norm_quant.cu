@@ -13,6 +13,8 @@
 // and in the 128x4 tiled scale-factor layout.  The grid is persistent (a
 // multiple of the SM count); every thread parks the f32 copy of its own slice
 // of the weight vector in shared memory once and re-reads it per row.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace b200fp4 {
@@ -260,33 +262,54 @@ __global__ void __launch_bounds__(kCap, kPipe ? 3 : (kCap <= 256 ? 5 : 2)) norm_
   }
 }
 
-int sm_count() {
-  static int cached = 0;
-  if (cached == 0) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
-    if (cached <= 0) cached = 148;
+constexpr int kMaxDevices = 64;
+
+int current_device_ordinal() {
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return dev >= 0 && dev < kMaxDevices ? dev : 0;
+}
+
+// SM count, cached per device ordinal
+int sm_count(int dev) {
+  static std::atomic<int> cached[kMaxDevices];
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+    cached[dev].store(n, std::memory_order_relaxed);
   }
-  return cached;
+  return n;
 }
 
 template <typename T, bool kAdd, int kVec, int kUnits, bool kWarpRow, int kCap, bool kPipe = false>
 int launch_one(const NormParams& p, int threads, cudaStream_t stream) {
   auto kern = norm_quant_kernel<T, kAdd, kVec, kUnits, kWarpRow, kCap, kPipe>;
   const size_t smem = static_cast<size_t>(kUnits) * kVec * 4 * sizeof(float4) * threads;
-  if (smem > 48 * 1024) {
-    B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-  }
+  // Shared-memory opt-in and occupancy are per device and per block size: queried once for each (this
+  // instantiation, device, block size) and remembered -- the two driver calls cost more host time than the
+  // launch of a small problem.  per_sm_cache holds (threads << 8 | resident CTAs), 0 = not yet known.
+  static std::atomic<int> per_sm_cache[kMaxDevices];
+  const int dev = current_device_ordinal();
   int per_sm = 0;
-  B200_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, smem));
-  if (per_sm < 1) return fail(kUnsupported, "norm_quant_kernel does not fit on an SM (%zu bytes of shared memory)", smem);
+  const int cached = per_sm_cache[dev].load(std::memory_order_acquire);
+  if (cached != 0 && (cached >> 8) == threads) {
+    per_sm = cached & 0xff;
+  } else {
+    if (smem > 48 * 1024) {
+      B200_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    }
+    B200_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, threads, smem));
+    if (per_sm < 1) return fail(kUnsupported, "norm_quant_kernel does not fit on an SM (%zu bytes of shared memory)", smem);
+    if (per_sm > 255) per_sm = 255;
+    per_sm_cache[dev].store((threads << 8) | per_sm, std::memory_order_release);
+  }
   // the residual-add variant is DRAM-bound with four resident CTAs per SM already; more of them only
   // lengthen the last wave (measured on B200: 70 us with 4, 74 us with 6 at [8192, 7168])
   if (kAdd && !kWarpRow && per_sm > 4) per_sm = 4;
   const int64_t rows_per_cta = kWarpRow ? threads / 32 : 1;
   const int64_t want = (p.rows + rows_per_cta - 1) / rows_per_cta;
-  int64_t grid = static_cast<int64_t>(sm_count()) * per_sm;
+  int64_t grid = static_cast<int64_t>(sm_count(dev)) * per_sm;
   if (grid > want) grid = want;
   kern<<<static_cast<unsigned>(grid), threads, smem, stream>>>(p);
   return check_cuda(cudaGetLastError(), "norm_quant_kernel launch");

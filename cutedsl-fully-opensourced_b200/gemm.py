@@ -222,18 +222,69 @@ def run(mnkl, a_dtype, b_dtype, sf_dtype, sf_vec_size, c_dtype, a_major="k", b_m
                   tile_shape_mnk, epi_tile, tolerance, warmup_iterations, iterations, skip_ref_check, use_cold_l2)
 
 
-def quantize_operand(x: torch.Tensor, global_scale: Optional[float] = None):
-    """Host-side convenience used by examples and benchmarks: quantise an f32 [rows, K] matrix to
-    NVFP4 with torch ops (amax-based e4m3 scale per 16 elements, nearest e2m1 code).  Returns
-    (packed uint8 [rows, K/2], tiled scale bytes, global_scale).  Not on the hot path."""
-    rows, k = x.shape
-    xf = x.float()
-    gs = float(448.0 * 6.0 / xf.abs().max()) if global_scale is None else float(global_scale)
+_E2M1_MIDPOINTS = (0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0)
+
+
+def _quantize_rows(xf: torch.Tensor, gs: float):
+    """[rows, K] f32 -> (codes uint8 [rows, K], scale bytes uint8 [rows, K/16]) with global scale gs."""
+    rows, k = xf.shape
     blocks = xf.reshape(rows, k // 16, 16)
     sf = (blocks.abs().amax(-1) * gs / 6.0).clamp(max=448.0).to(torch.float8_e4m3fn)
     sfq = sf.float()
     scaled = torch.where(sfq[..., None] > 0, blocks * gs / sfq[..., None], torch.zeros_like(blocks))
-    mids = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0], device=x.device)
-    idx = (scaled.abs()[..., None] > mids).sum(-1).to(torch.uint8)
+    mids = torch.tensor(_E2M1_MIDPOINTS, device=xf.device)
+    idx = torch.bucketize(scaled.abs(), mids).to(torch.uint8)          # number of midpoints strictly below |v|
     codes = (idx | (((scaled < 0) & (idx > 0)).to(torch.uint8) << 3)).reshape(rows, k)
-    return pack_e2m1(codes), swizzle_sf(sf.view(torch.uint8)), gs
+    return codes, sf.view(torch.uint8)
+
+
+def quantize_operand(x: torch.Tensor, global_scale: Optional[float] = None):
+    """Host-side convenience used by examples and benchmarks: quantise an f32 [rows, K] matrix to
+    NVFP4 with torch ops (amax-based e4m3 scale per 16 elements, nearest e2m1 code, ties to the smaller
+    magnitude: the recipe of tests/python/test_flashinfer_norm_verbatim.py:58-68).  Returns
+    (packed uint8 [rows, K/2], tiled scale bytes, global_scale).  Not on the hot path."""
+    xf = x.float()
+    gs = float(448.0 * 6.0 / xf.abs().max()) if global_scale is None else float(global_scale)
+    codes, sf_bits = _quantize_rows(xf, gs)
+    return pack_e2m1(codes), swizzle_sf(sf_bits), gs
+
+
+def quantize_operand_batched(w: torch.Tensor):
+    """[E, rows, K] -> (codes uint8 [E, rows, K], scale bytes uint8 [E, rows, K/16], global scales f32 [E]),
+    every expert with its own global scale 448 * 6 / amax.  One expert at a time to bound the temporaries."""
+    e, rows, k = w.shape
+    codes = torch.empty(e, rows, k, dtype=torch.uint8, device=w.device)
+    sf = torch.empty(e, rows, k // 16, dtype=torch.uint8, device=w.device)
+    gs = torch.empty(e, dtype=torch.float32, device=w.device)
+    for i in range(e):
+        wf = w[i].float()
+        g = float(448.0 * 6.0 / wf.abs().max().clamp_min(1e-30))
+        codes[i], sf[i] = _quantize_rows(wf, g)
+        gs[i] = g
+    return codes, sf, gs
+
+
+def mm_fp4(a: torch.Tensor, b: torch.Tensor, a_descale: torch.Tensor, b_descale: torch.Tensor,
+           alpha: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
+           out: Optional[torch.Tensor] = None, block_size: int = 16, use_8x4_sf_layout: bool = False,
+           backend: str = "b200fp4") -> torch.Tensor:
+    """flashinfer-style front door of the same kernel: ``out = alpha * (a * a_descale) @ (b * b_descale)``.
+
+    ``a`` [m, k/2] packed e2m1 with its 128x4-tiled e4m3 block scales ``a_descale`` is exactly what
+    ``rmsnorm_fp4quant`` / ``add_rmsnorm_fp4quant(..., is_sf_swizzled_layout=True)`` produce
+    (tests/python/test_flashinfer_norm_verbatim.py:155-164), so the norm output feeds the GEMM
+    (.../dense_blockscaled_gemm_persistent_cooperative.py:281-439) without a layout step.  ``b`` is the weight,
+    either [n, k/2] row-major or, as flashinfer passes it, the [k/2, n] transposed view of that storage;
+    ``b_descale`` likewise (tiled over [n, k/16]).  ``alpha`` = 1 / (global_scale_a * global_scale_b)."""
+    if block_size != 16 or use_8x4_sf_layout:
+        raise NotImplementedError("only NVFP4 (block_size=16) with the 128x4 scale layout is implemented")
+    if out_dtype not in (torch.bfloat16, torch.float16, torch.float32):
+        raise NotImplementedError(f"out_dtype {out_dtype}")
+    bu = b.view(torch.uint8)
+    if bu.dim() == 2 and not bu.is_contiguous() and bu.t().is_contiguous():
+        bu = bu.t()
+    sfb = b_descale
+    if sfb.dim() == 2 and not sfb.is_contiguous() and sfb.t().is_contiguous():
+        sfb = sfb.t()
+    return nvfp4_gemm(a.view(torch.uint8), bu, a_descale.contiguous().view(torch.uint8), sfb.contiguous().view(torch.uint8),
+                      alpha=alpha, out=out, out_dtype=out_dtype)

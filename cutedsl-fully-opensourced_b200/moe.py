@@ -1,21 +1,22 @@
-"""Drop-in ``b12x_fused_moe`` (NVFP4 weights, bf16 tokens) and the router.
+"""Drop-in ``b12x_fused_moe`` (NVFP4 weights, bf16 tokens), the router, the wrapper object and the weight packer.
 
 Call signature of flashinfer's ``fused_moe.cute_dsl.b12x_moe.b12x_fused_moe`` as
 the reference calls it (tests/python/test_flashinfer_b12x_verbatim.py:99-116,
 tools/perf/bench_flashinfer_b12x.py:77-81).  One call = a fixed sequence of CUDA
-kernels on the current stream inside ``b200fp4_moe_fused``: count / scan,
-quantise + scatter, grouped FC1 with SwiGLU and re-quantisation, grouped FC2,
-weighted combine.  Scratch memory comes from a per-device buffer that only
-grows; pass ``workspace=`` to control it.
+kernels on the current stream inside ``b200fp4_moe_fused``: (route +) count,
+quantise + place, grouped FC1 with SwiGLU and re-quantisation, grouped FC2,
+weighted combine.  Scratch memory comes from ``workspace=`` or from a
+``B12xMoEWrapper`` (allocated once); without either, a per-device buffer that
+only grows is used.
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
 from . import _lib
-from .layout import six_mode_to_storage
+from .layout import pack_e2m1, six_mode_to_storage, swizzle_sf
 
 _WORKSPACES = {}
 
@@ -31,6 +32,17 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
         ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
         _WORKSPACES[key] = ws
     return ws
+
+
+def _on_device(device, **tensors) -> None:
+    """Every tensor argument must live on the GPU that runs the kernels: a CPU tensor or one on another GPU would
+    hand the kernels an address they cannot read."""
+    for name, t in tensors.items():
+        if t is None:
+            continue
+        if not isinstance(t, torch.Tensor) or not t.is_cuda or t.device != device:
+            where = getattr(t, "device", type(t).__name__)
+            raise ValueError(f"{name} must be a CUDA tensor on {device} (got {where})")
 
 
 def _sf_storage(sf: torch.Tensor, experts: int, rows: int, k: int, name: str) -> torch.Tensor:
@@ -65,8 +77,8 @@ def b12x_fused_moe(
     w1_weight_sf: torch.Tensor,
     w2_weight: torch.Tensor,
     w2_weight_sf: torch.Tensor,
-    token_selected_experts: torch.Tensor,
-    token_final_scales: torch.Tensor,
+    token_selected_experts: Optional[torch.Tensor],
+    token_final_scales: Optional[torch.Tensor],
     num_experts: int,
     top_k: int,
     *,
@@ -83,12 +95,18 @@ def b12x_fused_moe(
     accumulate: bool = False,
     workspace: Optional[torch.Tensor] = None,
     slot_rows_dtype: Optional[torch.dtype] = None,
+    router_logits: Optional[torch.Tensor] = None,
+    renormalize: bool = True,
 ) -> torch.Tensor:
     """out[t] = sum_j scale[t,j] * FC2_e(quant(silu(gate) * up)),  [up|gate] = FC1_e(quant(x[t])), e = expert[t,j].
 
     ``w1_weight`` [E_local, 2I, H/2] uint8 holds the up rows first, then the gate rows; scale tensors are the
     six-mode e4m3 views the reference builds.  With ``num_local_experts`` / ``local_expert_offset`` only the experts
     of this rank are computed and other slots contribute zero.
+
+    ``router_logits`` (float32 [tokens, num_experts]): route on the GPU inside the operator's first kernel instead
+    of taking ids and scales.  ``token_selected_experts`` / ``token_final_scales`` may then be ``None`` or
+    pre-allocated tensors that receive the routing.
 
     ``slot_rows_dtype``: storage of the k per-expert output rows of a token between FC2 and the weighted sum.
     The sum itself always runs in float32 in slot order and is rounded once.  ``torch.bfloat16`` (default for a
@@ -106,7 +124,12 @@ def b12x_fused_moe(
     if x.dim() != 2 or not x.is_contiguous():
         raise ValueError("x must be contiguous [tokens, hidden]")
     tokens, hidden = x.shape
+    dev = x.device
     local = num_experts if num_local_experts is None else num_local_experts
+    ids, scales = token_selected_experts, token_final_scales
+    _on_device(dev, w1_weight=w1_weight, w1_weight_sf=w1_weight_sf, w2_weight=w2_weight, w2_weight_sf=w2_weight_sf,
+               token_selected_experts=ids, token_final_scales=scales, w1_alpha=w1_alpha, w2_alpha=w2_alpha,
+               fc2_input_scale=fc2_input_scale, output=output, workspace=workspace, router_logits=router_logits)
     w1 = w1_weight.view(torch.uint8)
     w2 = w2_weight.view(torch.uint8)
     if w1.dim() != 3 or w1.shape[0] != local or w1.shape[2] * 2 != hidden or not w1.is_contiguous():
@@ -114,7 +137,16 @@ def b12x_fused_moe(
     inter = w1.shape[1] // 2
     if tuple(w2.shape) != (local, hidden, inter // 2) or not w2.is_contiguous():
         raise ValueError(f"w2_weight must be contiguous [{local}, {hidden}, {inter // 2}]")
-    ids, scales = token_selected_experts, token_final_scales
+    if router_logits is not None:
+        if (router_logits.dtype != torch.float32 or tuple(router_logits.shape) != (tokens, num_experts)
+                or not router_logits.is_contiguous()):
+            raise ValueError(f"router_logits must be contiguous float32 [{tokens}, {num_experts}]")
+        if ids is None:
+            ids = torch.empty(tokens, top_k, dtype=torch.int32, device=dev)
+        if scales is None:
+            scales = torch.empty(tokens, top_k, dtype=torch.float32, device=dev)
+    elif ids is None or scales is None:
+        raise ValueError("token_selected_experts and token_final_scales are required without router_logits")
     if ids.dtype != torch.int32 or tuple(ids.shape) != (tokens, top_k) or not ids.is_contiguous():
         raise ValueError("token_selected_experts must be contiguous int32 [tokens, top_k]")
     if scales.dtype != torch.float32 or tuple(scales.shape) != (tokens, top_k) or not scales.is_contiguous():
@@ -127,7 +159,7 @@ def b12x_fused_moe(
     if fc2_input_scale is not None and (fc2_input_scale.dtype != torch.float32 or fc2_input_scale.numel() != 1):
         raise ValueError("fc2_input_scale must be one float32")
     if output is None:
-        output = torch.empty(tokens, hidden, dtype=output_dtype, device=x.device)
+        output = torch.empty(tokens, hidden, dtype=output_dtype, device=dev)
         if accumulate:
             output.zero_()
     elif (tuple(output.shape) != (tokens, hidden) or output.dtype not in (torch.bfloat16, torch.float32)
@@ -142,14 +174,100 @@ def b12x_fused_moe(
     if tokens == 0:
         return output
     need = moe_workspace_bytes(tokens, hidden, inter, local, top_k)
-    ws = _workspace(x.device, need) if workspace is None else workspace
+    ws = _workspace(dev, need) if workspace is None else workspace
     if ws.numel() * ws.element_size() < need:
         raise ValueError(f"workspace too small: {need} bytes needed")
-    with torch.cuda.device(x.device):
-        _lib.check(_lib.lib.b200fp4_moe_fused(
-            x.data_ptr(), w1.data_ptr(), s1.data_ptr(), w2.data_ptr(), s2.data_ptr(), ids.data_ptr(),
-            scales.data_ptr(), _lib.ptr(w1_alpha), _lib.ptr(w2_alpha), _lib.ptr(fc2_input_scale), output.data_ptr(),
-            tokens, hidden, inter, local, top_k, int(local_expert_offset), 1 if accumulate else 0,
-            2 if output.dtype == torch.float32 else (3 if slot_rows_dtype == torch.bfloat16 else 1), ws.data_ptr(),
-            ws.numel() * ws.element_size(), _lib.current_stream_ptr(x.device)))
+    out_code = 2 if output.dtype == torch.float32 else (3 if slot_rows_dtype == torch.bfloat16 else 1)
+    tail = (_lib.ptr(w1_alpha), _lib.ptr(w2_alpha), _lib.ptr(fc2_input_scale), output.data_ptr(), tokens, hidden,
+            inter, local, top_k, int(local_expert_offset), 1 if accumulate else 0, out_code, ws.data_ptr(),
+            ws.numel() * ws.element_size(), _lib.current_stream_ptr(dev))
+    with torch.cuda.device(dev):
+        if router_logits is None:
+            _lib.check(_lib.lib.b200fp4_moe_fused(x.data_ptr(), w1.data_ptr(), s1.data_ptr(), w2.data_ptr(),
+                                                  s2.data_ptr(), ids.data_ptr(), scales.data_ptr(), *tail))
+        else:
+            _lib.check(_lib.lib.b200fp4_moe_fused_routed(
+                x.data_ptr(), router_logits.data_ptr(), num_experts, 1 if renormalize else 0, w1.data_ptr(),
+                s1.data_ptr(), w2.data_ptr(), s2.data_ptr(), ids.data_ptr(), scales.data_ptr(), *tail))
     return output
+
+
+class B12xMoEWrapper:
+    """The wrapper object upstream callers build once and call every step (flashinfer's ``B12xMoEWrapper``; the
+    reference's bench calls the functional form, tools/perf/bench_flashinfer_b12x.py:70-81).
+
+    Construction fixes the problem shape and allocates the workspace and the routing buffers for ``max_num_tokens``
+    once, so ``run`` allocates nothing (and can be captured in a CUDA graph by the caller).  ``run`` accepts either
+    the routing (ids + scales) or ``router_logits``.
+    """
+
+    def __init__(self, num_experts: int, top_k: int, hidden_size: int, intermediate_size: int, *,
+                 max_num_tokens: int, num_local_experts: Optional[int] = None, local_expert_offset: int = 0,
+                 output_dtype: torch.dtype = torch.bfloat16, slot_rows_dtype: Optional[torch.dtype] = None,
+                 device: Optional[torch.device] = None, quant_mode: str = "nvfp4", activation: str = "silu"):
+        if quant_mode != "nvfp4" or activation not in ("silu", "swiglu"):
+            raise NotImplementedError("only NVFP4 with SwiGLU is implemented")
+        self.num_experts, self.top_k = num_experts, top_k
+        self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
+        self.num_local_experts = num_experts if num_local_experts is None else num_local_experts
+        self.local_expert_offset = local_expert_offset
+        self.max_num_tokens = max_num_tokens
+        self.output_dtype, self.slot_rows_dtype = output_dtype, slot_rows_dtype
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        need = max(moe_workspace_bytes(t, hidden_size, intermediate_size, self.num_local_experts, top_k)
+                   for t in {1, min(32, max_num_tokens), min(33, max_num_tokens), max_num_tokens})
+        if need == 0:
+            raise ValueError("bad MoE shape")
+        self.workspace = torch.empty(need, dtype=torch.uint8, device=self.device)
+        self._ids = torch.empty(max_num_tokens, top_k, dtype=torch.int32, device=self.device)
+        self._scales = torch.empty(max_num_tokens, top_k, dtype=torch.float32, device=self.device)
+
+    def run(self, x, w1_weight, w1_weight_sf, w2_weight, w2_weight_sf, token_selected_experts=None,
+            token_final_scales=None, *, router_logits=None, w1_alpha=None, w2_alpha=None, fc2_input_scale=None,
+            output=None, renormalize: bool = True):
+        tokens = x.shape[0]
+        if tokens > self.max_num_tokens:
+            raise ValueError(f"{tokens} tokens exceed max_num_tokens={self.max_num_tokens}")
+        if router_logits is not None and token_selected_experts is None:
+            token_selected_experts, token_final_scales = self._ids[:tokens], self._scales[:tokens]
+        if output is None:
+            output = torch.empty(tokens, self.hidden_size, dtype=self.output_dtype, device=x.device)
+        return b12x_fused_moe(
+            x, w1_weight, w1_weight_sf, w2_weight, w2_weight_sf, token_selected_experts, token_final_scales,
+            self.num_experts, self.top_k, w1_alpha=w1_alpha, w2_alpha=w2_alpha, fc2_input_scale=fc2_input_scale,
+            num_local_experts=self.num_local_experts, local_expert_offset=self.local_expert_offset, output=output,
+            output_dtype=self.output_dtype, workspace=self.workspace, slot_rows_dtype=self.slot_rows_dtype,
+            router_logits=router_logits, renormalize=renormalize)
+
+    def last_routing(self, tokens: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """(ids, scales) written by the last ``run(..., router_logits=...)`` that did not pass its own buffers."""
+        return self._ids[:tokens], self._scales[:tokens]
+
+
+def pack_moe_weights(w1: torch.Tensor, w2: torch.Tensor, *, fc2_input_scale: float = 1.0) -> dict:
+    """Checkpoint-side packer: bf16 / f32 expert weights -> what ``b12x_fused_moe`` consumes.
+
+    ``w1`` [E, 2I, H] (up rows, then gate rows) and ``w2`` [E, H, I] are quantised per expert to NVFP4 with a
+    per-expert global scale ``gs_e = 448 * 6 / amax(|W_e|)`` (the recipe of
+    tests/python/test_flashinfer_norm_verbatim.py:58-68 applied per expert), packed two codes per byte (lower K
+    index in the low nibble), and their e4m3 block scales are laid out in the six-mode MMA view
+    ``(32, 4, m_tiles, 4, k_tiles, E)`` (tests/python/test_flashinfer_b12x_verbatim.py:68-89).  The reciprocal
+    global scales are returned as ``w1_alpha`` / ``w2_alpha`` (``w2_alpha`` also carries 1 / fc2_input_scale, the
+    operator's convention for undoing the activation quantiser's global scale).  Runs on whatever device the
+    weights are on; not a hot path."""
+    from .gemm import quantize_operand_batched
+    if w1.dim() != 3 or w2.dim() != 3 or w1.shape[0] != w2.shape[0]:
+        raise ValueError("w1 must be [E, 2I, H] and w2 [E, H, I]")
+    e, two_i, h = w1.shape
+    if tuple(w2.shape) != (e, h, two_i // 2) or two_i % 256 or h % 64:
+        raise ValueError("shapes must be w1 [E, 2I, H], w2 [E, H, I] with I a multiple of 128 and H of 64")
+    out = {}
+    for name, w, extra in (("w1", w1, 1.0), ("w2", w2, float(fc2_input_scale))):
+        codes, sf_bits, gs = quantize_operand_batched(w)
+        rows, k = w.shape[1], w.shape[2]
+        storage = swizzle_sf(sf_bits).view(e, -(-rows // 128), -(-(k // 16) // 4), 32, 4, 4)
+        out[f"{name}_weight"] = pack_e2m1(codes)
+        out[f"{name}_weight_sf"] = storage.view(torch.float8_e4m3fn).permute(3, 4, 1, 5, 2, 0)
+        out[f"{name}_alpha"] = (1.0 / (gs * extra)).to(torch.float32).contiguous()
+    out["fc2_input_scale"] = torch.tensor([float(fc2_input_scale)], dtype=torch.float32, device=w1.device)
+    return out

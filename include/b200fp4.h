@@ -62,7 +62,8 @@ int b200fp4_add_rmsnorm_fp4quant(const void* x, void* residual, const void* weig
  * A [l][m][k/2] and B [l][n][k/2]: e2m1 codes, two per byte (lower k in the low nibble), K contiguous.
  * SFA / SFB: e4m3 bytes, one per 16 K-elements, in 128x4 tiles [l][ceil(rows/128)][ceil(k/64)][32][4][4]
  * (padding bytes zero).  C row-major, c_dtype 0 = fp16, 1 = bf16, 2 = f32; f32 accumulation.
- * alpha: one f32 in device memory, or NULL for 1.  tile_n: 0 = choose, 128 or 256.
+ * alpha: one f32 in device memory, or NULL for 1.  tile_n: 0 = choose (by problem size), or force one of
+ * 64 / 128 / 256 (output columns per single-CTA tile) or 512 (256 x 256 tiles on CTA pairs).
  * Stands in for Sm120BlockScaledGemmKernel.__call__ and its kernel:
  *   third_party/cutlass/examples/python/CuTeDSL/cute/blackwell_geforce/kernel/blockscaled_gemm/
  *   dense_blockscaled_gemm_persistent_cooperative.py:281-439 (host), :443-1185 (device),
@@ -103,9 +104,24 @@ int b200fp4_moe_fused(const void* x, const void* w1, const void* w1_sf, const vo
                       int intermediate, int local_experts, int top_k, int local_expert_offset, int accumulate,
                       int out_dtype, void* workspace, size_t workspace_bytes, void* stream);
 
+/* b200fp4_moe_fused with the router inside: router_logits f32 [tokens, num_experts] -> softmax -> top_k ->
+ * (renormalised) weights as b200fp4_topk_route computes them, fused into the first kernel of the front end
+ * (one launch fewer, and the ids never leave the GPU).  The routing is written to
+ * token_selected_experts_out / token_final_scales_out ([tokens, top_k]) for the caller.  Other arguments as
+ * b200fp4_moe_fused.  The reference op takes ids and weights as inputs and its harness draws them
+ * (tools/perf/bench_flashinfer_b12x.py:70-74); this entry is the same operator with that step on the GPU. */
+int b200fp4_moe_fused_routed(const void* x, const float* router_logits, int num_experts, int renormalize,
+                             const void* w1, const void* w1_sf, const void* w2, const void* w2_sf,
+                             int* token_selected_experts_out, float* token_final_scales_out, const float* w1_alpha,
+                             const float* w2_alpha, const float* fc2_input_scale, void* out, int64_t tokens,
+                             int hidden, int intermediate, int local_experts, int top_k, int local_expert_offset,
+                             int accumulate, int out_dtype, void* workspace, size_t workspace_bytes, void* stream);
+
 /* The same fused MoE for callers that cannot allocate device memory (engines that forbid cudaMalloc after
  * start-up, plugins that only receive raw pointers, latency-critical loops).  It has no counterpart in the
- * reference; it exists only in this library.  Arguments as b200fp4_moe_fused, without the workspace: the
+ * reference; it exists only in this library.  Arguments as b200fp4_moe_fused, without the workspace and without
+ * out_dtype: `out` is always bf16 [tokens, hidden] and the k per-expert rows of a token are kept in f32 between
+ * FC2 and the weighted sum (what out_dtype 1 selects in b200fp4_moe_fused).  The
  * scratch is a fixed 32 MiB array inside the library's device image (held by every GPU that loads the
  * library until the process ends).  Problems whose b200fp4_moe_workspace_bytes(...) exceeds 32 MiB are
  * refused with B200FP4_UNSUPPORTED.  status_word: a caller-owned int in device memory, zeroed by the
@@ -122,31 +138,72 @@ int b200fp4_moe_fused_noalloc(const void* x, const void* w1, const void* w1_sf, 
  * local_experts consecutive experts (rank r: experts r*local_experts ...), and every rank holds a
  * buffer of b200fp4_moe_ep_buffer_bytes(...) bytes that all ranks can address (peer_buffers[i] is
  * rank i's buffer as seen from the calling process, e.g. CUDA IPC or symmetric memory; 256-byte
- * aligned).  One step = stage, <cross-rank barrier>, compute, <cross-rank barrier>, combine, all
- * stream-ordered; the barriers are the caller's (any stream-ordered barrier across the ranks).
- *   stage    quantise the rank's tokens once to NVFP4 and publish them with their expert ids;
- *   compute  pull the rows routed to local experts from their owners, FC1 / SwiGLU / FC2;
- *   combine  out[t] = bf16(sum_j scale[t,j] * row_j), rows read from the ranks that computed them.
- * Arguments as b200fp4_moe_fused (ids are global).  The reference is single-GPU and has no
- * counterpart; these entry points are the dispatch / combine of an expert-parallel deployment of
- * the same operator (tests/python/test_flashinfer_b12x_verbatim.py:99-116). */
+ * aligned; cleared once with b200fp4_moe_ep_reset).  One step = dispatch, compute, combine on every rank,
+ * all stream-ordered; the kernels synchronise the ranks themselves with three signals per step (words in
+ * the buffers that carry a step counter), so the caller provides no barrier:
+ *   dispatch (route +) count the slots per expert and publish the counts [signal 0]; wait for the counts of
+ *            all ranks; quantise the rank's tokens once to NVFP4 and store every (token, slot) row straight
+ *            into the expert-major FC1 operand of the rank that owns the slot's expert [signal 1];
+ *   compute  wait for the rows of all ranks; FC1 / SwiGLU / FC2, whose epilogue stores every output row
+ *            (bf16) into the buffer of the rank that owns the token [signal 2];
+ *   combine  wait for the rows of all ranks; out[t] = bf16(sum_j scale[t,j] * row_j) in f32, slot order.
+ * All peer accesses are plain loads / stores of these kernels over NVLink.  Every wait is bounded by wait_ms
+ * (0 < wait_ms <= 60000): on expiry the kernel ORs bit 16 into the device status word, marks the buffer as
+ * aborted and returns; later kernels of the group then touch no peer memory until b200fp4_moe_ep_reset.
+ * Routing: either token_selected_experts (global ids) is given, or router_logits f32
+ * [tokens_local, world*local_experts] and the dispatch routes on the GPU (then pass NULL ids / scales to the
+ * combine, and fetch the routing with b200fp4_moe_ep_routing if it is wanted).
+ * Arguments otherwise as b200fp4_moe_fused.  The reference is single-GPU and has no counterpart; these entry
+ * points are the dispatch / combine all-to-all of an expert-parallel deployment of the same operator
+ * (tests/python/test_flashinfer_b12x_verbatim.py:99-116). */
 size_t b200fp4_moe_ep_buffer_bytes(int64_t tokens_local, int hidden, int intermediate, int local_experts, int top_k,
                                    int world);
-int b200fp4_moe_ep_stage(const void* x, const int* token_selected_experts, void* own_buffer, int64_t tokens_local,
-                         int hidden, int intermediate, int local_experts, int top_k, int world, void* stream);
+/* Clears the signal words, counters and abort word of the rank's own buffer.  No step may be in flight on any
+ * rank (host-side barrier before and after). */
+int b200fp4_moe_ep_reset(void* own_buffer, int64_t tokens_local, int hidden, int intermediate, int local_experts,
+                         int top_k, int world, void* stream);
+int b200fp4_moe_ep_dispatch(const void* x, const int* token_selected_experts, const float* router_logits,
+                            int renormalize, const void* const* peer_buffers, int rank, int world,
+                            int64_t tokens_local, int hidden, int intermediate, int local_experts, int top_k,
+                            double wait_ms, void* stream);
+/* The two halves of the dispatch as separate calls (count + signal 0, then wait + place + signal 1; same
+ * arguments).  A harness that emulates several ranks of a group on ONE GPU must issue all ranks' counts before
+ * any rank's place, all places before any compute and all computes before any combine, on one stream: then
+ * every wait is already satisfied when its kernel starts and no kernel ever waits for a later launch. */
+int b200fp4_moe_ep_dispatch_count(const void* x, const int* token_selected_experts, const float* router_logits,
+                                  int renormalize, const void* const* peer_buffers, int rank, int world,
+                                  int64_t tokens_local, int hidden, int intermediate, int local_experts, int top_k,
+                                  double wait_ms, void* stream);
+int b200fp4_moe_ep_dispatch_place(const void* x, const int* token_selected_experts, const float* router_logits,
+                                  int renormalize, const void* const* peer_buffers, int rank, int world,
+                                  int64_t tokens_local, int hidden, int intermediate, int local_experts, int top_k,
+                                  double wait_ms, void* stream);
 int b200fp4_moe_ep_compute(const void* const* peer_buffers, int rank, int world, const void* w1, const void* w1_sf,
                            const void* w2, const void* w2_sf, const float* w1_alpha, const float* w2_alpha,
                            const float* fc2_input_scale, int64_t tokens_local, int hidden, int intermediate,
-                           int local_experts, int top_k, void* stream);
+                           int local_experts, int top_k, double wait_ms, void* stream);
 int b200fp4_moe_ep_combine(const void* const* peer_buffers, int rank, int world, const int* token_selected_experts,
                            const float* token_final_scales, void* out, int64_t tokens_local, int hidden,
-                           int intermediate, int local_experts, int top_k, void* stream);
+                           int intermediate, int local_experts, int top_k, double wait_ms, void* stream);
+int b200fp4_moe_ep_routing(const void* own_buffer, int* ids_out, float* weights_out, int64_t tokens_local, int hidden,
+                           int intermediate, int local_experts, int top_k, int world, void* stream);
+
+/* Self-tests of the bounded waits; they fault nothing and leave nothing in flight.
+ * b200fp4_selftest_peer_wait: on ONE GPU, waits for the signal of `world` ranks on a cleared buffer that nobody
+ * signals; after wait_ms the kernel gives up, ORs bit 16 into the device status word and returns.
+ * b200fp4_selftest_bounded_wait: one CTA waits, with the GEMM kernels' own wait routine and a limit of
+ * limit_cycles, on an mbarrier on which nothing arrives; it gives up, ORs bit 2 into the device status word and
+ * writes 1 to *gave_up (device memory).  Neither has a counterpart in the reference, whose kernels wait without
+ * bounds (python/self_cutedsl/frontend/jit.py:237-242). */
+int b200fp4_selftest_peer_wait(void* own_buffer, int world, double wait_ms, int64_t tokens_local, int hidden,
+                               int intermediate, int local_experts, int top_k, void* stream);
+int b200fp4_selftest_bounded_wait(long long limit_cycles, int* gave_up, void* stream);
 
 /* Kernels never trap: a device-side wait that exceeds its bound ORs a bit into a per-device
  * status word and the kernel returns.  This call synchronises the stream and copies the word
- * to *status_out (0 = healthy; 1/2/4 = GEMM producer / MMA / epilogue wait expired; 8 = a fused-MoE call with
- * at most 32 tokens named one expert more than 32 times: those rows are wrong), clearing
- * it when clear != 0.  No counterpart in the reference, whose kernels wait without bounds. */
+ * to *status_out (0 = healthy; 1/2/4 = GEMM producer / MMA / epilogue wait expired; 8 = a few-row GEMM launch
+ * met a row block with more rows than it loads (the MoE front end never builds such a block); 16 = a wait for
+ * another rank of an expert-parallel group expired), clearing it when clear != 0.  No counterpart in the reference, whose kernels wait without bounds. */
 int b200fp4_device_status(void* stream, int* status_out, int clear);
 
 #ifdef __cplusplus

@@ -303,7 +303,7 @@ def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 
 def moe_ref(x: torch.Tensor, w1_codes, w1_sf, w2_codes, w2_sf, ids: torch.Tensor, weights: torch.Tensor,
-            w1_alpha=None, w2_alpha=None, fc2_input_scale: float = 1.0) -> torch.Tensor:
+            w1_alpha=None, w2_alpha=None, fc2_input_scale: float = 1.0, weight_key=None) -> torch.Tensor:
     """Routed NVFP4 MoE on the CPU.
 
     x bf16 [T,H]; w1_codes [E,2I,H] (rows 0..I-1 = up, I..2I-1 = gate) with
@@ -311,6 +311,10 @@ def moe_ref(x: torch.Tensor, w1_codes, w1_sf, w2_codes, w2_sf, ids: torch.Tensor
     weights f32 [T,k].  Per (token, slot): quantise the token with the MoE
     packer, FC1, silu(gate)*up in f32, round to bf16, quantise again, FC2;
     slots are summed in f32 in slot order and rounded once to bf16.
+
+    weight_key: optional function expert -> key; experts with equal keys share their (de-quantised) weight
+    matrices, which are then de-quantised once per key (the weight containers only need ``.shape`` and
+    ``[expert]``).  Large test shapes build a few distinct experts and tell them apart by their alphas.
     """
     t, h = x.shape
     e, two_i, _ = w1_codes.shape
@@ -322,12 +326,23 @@ def moe_ref(x: torch.Tensor, w1_codes, w1_sf, w2_codes, w2_sf, ids: torch.Tensor
     xq = torch.from_numpy(dequantize_nvfp4(xc, xs, 1.0))
     acc = torch.zeros(t, h, dtype=torch.float32)
     ids_np = ids.numpy()
+    cache = {}
+
+    def dequantised(ex):
+        key = ex if weight_key is None else weight_key(ex)
+        if key not in cache:
+            pair = (torch.from_numpy(dequantize_nvfp4(w1_codes[ex], w1_sf[ex])),
+                    torch.from_numpy(dequantize_nvfp4(w2_codes[ex], w2_sf[ex])))
+            if weight_key is None:
+                return pair
+            cache[key] = pair
+        return cache[key]
+
     for slot in range(k):
         part = torch.zeros(t, h, dtype=torch.float32)
         for ex in np.unique(ids_np[:, slot]):
             rows = torch.from_numpy(np.nonzero(ids_np[:, slot] == ex)[0])
-            w1 = torch.from_numpy(dequantize_nvfp4(w1_codes[ex], w1_sf[ex]))
-            w2 = torch.from_numpy(dequantize_nvfp4(w2_codes[ex], w2_sf[ex]))
+            w1, w2 = dequantised(int(ex))
             fc1 = (xq[rows] @ w1.t()) * float(a1[ex])
             act = silu_mul(fc1[:, inter:], fc1[:, :inter]).to(torch.bfloat16).float()
             ac, asf = quantize_nvfp4(act.numpy(), fc2_input_scale, implicit_one_packing=True)

@@ -146,3 +146,99 @@ def test_large_square_integer_exact(b200):
         ref = ((a_ref[0] * sa_ref[0]) @ (b_ref[0] * sb_ref[0]).t()).to(torch.bfloat16)
         assert torch.equal(c, ref), f"{size}: {(c != ref).float().mean().item():.3e} of outputs differ"
         del a, b, sa, sb, a_ref, b_ref, sa_ref, sb_ref, c, ref
+
+
+def test_benchmark_config_data_small_m_sweep(b200):
+    """The benchmark's GEMM configuration with its stated data at the small ends of the M sweep: A, B ~ N(0,1)
+    quantised by the golden quantiser with per-tensor global scales, alpha = 1 / (gs_A * gs_B), bf16 output,
+    N = K = 8192, M in {1024, 128}, through every tile variant that the automatic choice can take there.
+    Golden: dequantise-then-f32-product (.../dense_blockscaled_gemm_persistent_cooperative.py:1791-1806)."""
+    torch.manual_seed(0)
+    n = k = 8192
+    A, B = torch.randn(1024, k), torch.randn(n, k)
+    gsa, gsb = O.nvfp4_global_scale(A), O.nvfp4_global_scale(B)
+    ac, sfa = O.quantize_nvfp4(A.numpy(), gsa)
+    bc, sfb = O.quantize_nvfp4(B.numpy(), gsb)
+    alpha = 1.0 / (gsa * gsb)
+    ref = O.gemm_nvfp4_ref(ac, sfa, bc, sfb, alpha=alpha)
+    alpha_d = torch.tensor([alpha], device="cuda")
+    for m, tiles in ((1024, (0, 512, 256, 128)), (128, (0, 64, 128, 256))):
+        a, b, sa, sb = _dev_operands(ac[:m], sfa[:m], bc, sfb)
+        for tile_n in tiles:
+            c = b200.nvfp4_gemm(a, b, sa, sb, alpha=alpha_d, out_dtype=torch.bfloat16, tile_n=tile_n)
+            torch.cuda.synchronize()
+            _check_status(b200)
+            err = torch.linalg.vector_norm(c.cpu().float() - ref[:m]) / torch.linalg.vector_norm(ref[:m])
+            assert err <= 1e-2 and err <= 4e-3, (m, tile_n, float(err))
+
+
+def test_norm_quant_output_feeds_the_gemm(b200):
+    """add_rmsnorm_fp4quant(..., is_sf_swizzled_layout=True) -> its y_fp4 / block_scale are the GEMM's A / SFA
+    with no layout step in between (K = 7168, ragged row count), through nvfp4_gemm and the mm_fp4 front door;
+    compared with the same chain on the CPU oracle (tests/python/test_flashinfer_norm_verbatim.py:155-164 feeding
+    .../dense_blockscaled_gemm_persistent_cooperative.py:281-439)."""
+    torch.manual_seed(1)
+    rows, hidden, n = 200, 7168, 384
+    x = torch.randn(rows, hidden).to(torch.bfloat16)
+    r = torch.randn(rows, hidden).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(hidden)).to(torch.bfloat16)
+    W = 0.05 * torch.randn(n, hidden)
+    gs_x = O.nvfp4_global_scale(O.rmsnorm_true((x.float() + r.float()).to(torch.bfloat16), w, 1e-6))
+    gs_w = O.nvfp4_global_scale(W)
+    _, ac, sfa = O.add_rmsnorm_fp4quant_ref(x, r, w, 1e-6, gs_x)
+    bc, sfb = O.quantize_nvfp4(W.numpy(), gs_w)
+    alpha = 1.0 / (gs_x * gs_w)
+    ref = O.gemm_nvfp4_ref(ac, sfa, bc, sfb, alpha=alpha)
+    y, sf = b200.add_rmsnorm_fp4quant(x.cuda(), r.cuda(), w.cuda(), global_scale=torch.tensor([gs_x], device="cuda"),
+                                      eps=1e-6, is_sf_swizzled_layout=True)
+    b = torch.from_numpy(O.pack_e2m1(bc)).cuda()
+    sb = torch.from_numpy(O.swizzle_sf(sfb)).cuda()
+    alpha_d = torch.tensor([alpha], device="cuda")
+    c = b200.nvfp4_gemm(y, b, sf, sb, alpha=alpha_d, out_dtype=torch.bfloat16)
+    # flashinfer's calling convention: the weight and its scales as transposed views
+    c2 = b200.mm_fp4(y, b.t(), sf, sb.view(torch.float8_e4m3fn), alpha_d, torch.bfloat16)
+    torch.cuda.synchronize()
+    _check_status(b200)
+    assert torch.equal(c, c2)
+    err = torch.linalg.vector_norm(c.cpu().float() - ref) / torch.linalg.vector_norm(ref)
+    assert err <= 1e-2, float(err)
+    # the plain variant's tiled scale output is an operand of the same kind
+    y3, sf3 = b200.rmsnorm_fp4quant(x.cuda(), w.cuda(), global_scale=torch.tensor([gs_x], device="cuda"),
+                                    is_sf_swizzled_layout=True)
+    c3 = b200.mm_fp4(y3, b.t(), sf3, sb, alpha_d, torch.float32)
+    ac3, sfa3 = O.rmsnorm_fp4quant_ref(x, w, 1e-6, gs_x)
+    ref3 = O.gemm_nvfp4_ref(ac3, sfa3, bc, sfb, alpha=alpha)
+    torch.cuda.synchronize()
+    assert torch.linalg.vector_norm(c3.cpu() - ref3) / torch.linalg.vector_norm(ref3) <= 1e-2
+
+
+def test_bounded_wait_gives_up_and_the_next_launch_is_healthy(b200):
+    """The GEMM kernels' bounded wait, exercised on an mbarrier on which nothing ever arrives, with a limit of
+    about a millisecond: the kernel returns, the status bit is set, and the next GEMM runs normally."""
+    lib, check = b200._lib.lib, b200._lib.check
+    b200._lib.device_status()
+    gave_up = torch.zeros(1, dtype=torch.int32, device="cuda")
+    check(lib.b200fp4_selftest_bounded_wait(1_000_000, gave_up.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert int(gave_up.item()) == 1
+    with pytest.raises(b200.B200Fp4Error, match="wait inside a GEMM kernel expired"):
+        b200.synchronize()
+    ac, sfa, bc, sfb = O.integer_gemm_operands(256, 256, 512, seed=1)
+    a, b, sa, sb = _dev_operands(ac, sfa, bc, sfb)
+    c = b200.nvfp4_gemm(a, b, sa, sb, out_dtype=torch.float32)
+    b200.synchronize()
+    assert torch.equal(c.cpu(), O.gemm_nvfp4_ref(ac, sfa, bc, sfb))
+
+
+def test_two_devices_in_one_process(b200):
+    """Launch configuration (shared-memory opt-in, SM count) is kept per device."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ac, sfa, bc, sfb = O.integer_gemm_operands(256, 512, 1024, seed=2)
+    ref = O.gemm_nvfp4_ref(ac, sfa, bc, sfb)
+    for dev in ("cuda:0", "cuda:1"):
+        ops = [torch.from_numpy(t).to(dev) for t in (O.pack_e2m1(ac), O.pack_e2m1(bc), O.swizzle_sf(sfa), O.swizzle_sf(sfb))]
+        for tile_n in (128, 256, 512):
+            c = b200.nvfp4_gemm(*ops, out_dtype=torch.float32, tile_n=tile_n)
+            torch.cuda.synchronize(dev)
+            assert torch.equal(c.cpu(), ref)

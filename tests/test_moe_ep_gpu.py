@@ -1,5 +1,7 @@
-"""Expert-parallel MoE on two GPUs (one process per GPU, NCCL) against the single-GPU operator.
-Needs two devices; on a one-GPU box it reports a skip with that reason."""
+"""Expert-parallel MoE on two GPUs (one process per GPU, NCCL + symmetric memory) against the single-GPU operator:
+the peer-memory path (bit-equal, with ids and with the router inside the dispatch, a masked slot included) and the
+all-to-all-v fallback.  Needs two devices; on a one-GPU box it reports a skip with that reason (the same kernels
+are covered there by tests/test_moe_ep_emulated_gpu.py, which emulates the ranks on one GPU)."""
 import os
 
 import numpy as np
@@ -20,8 +22,14 @@ def _problem():
     w1s = rng.integers(0x18, 0x30, size=(experts, 2 * inter, hidden // 16), dtype=np.uint8)
     w2s = rng.integers(0x18, 0x30, size=(experts, hidden, inter // 16), dtype=np.uint8)
     x = torch.randn(tokens, hidden).to(torch.bfloat16)
-    ids, wts = O.route_topk_ref(torch.randn(tokens, experts), top_k)
+    ids, wts = O.route_topk_ref(_logits(), top_k)
+    ids = ids.clone()
+    ids[5, 1] = -1                      # a masked slot: contributes nothing on either path
     return (w1c, w1s, w2c, w2s), x, ids, wts.contiguous(), experts, top_k
+
+
+def _logits():
+    return torch.randn(96, 8, generator=torch.Generator().manual_seed(12))
 
 
 def _dev_weights(w1c, w1s, w2c, w2s, sl, dev):
@@ -50,9 +58,13 @@ def _worker(rank, world, port, result_dir):
             w = _dev_weights(w1c, w1s, w2c, w2s, sl, dev)
             for _ in range(3):          # several steps: buffers are reused
                 out = ep.forward(x[mine].to(dev), ids[mine].to(dev), wts[mine].to(dev), w)
-            torch.cuda.synchronize()
-            assert b200._lib.device_status() == 0
+            b200.synchronize()          # raises if a wait expired
             torch.save(out.cpu(), os.path.join(result_dir, f"out_{kind}{rank}.pt"))
+            if kind == "peer":
+                logits = _logits()[mine].to(dev)
+                out = ep.forward(x[mine].to(dev), None, None, w, router_logits=logits, check=True)
+                ids_r, w_r = ep.last_routing()
+                torch.save((out.cpu(), ids_r.cpu(), w_r.cpu()), os.path.join(result_dir, f"routed{rank}.pt"))
     finally:
         dist.destroy_process_group()
 
@@ -67,18 +79,24 @@ def test_expert_parallel_two_gpus_matches_single_gpu(b200, tmp_path):
     w = _dev_weights(w1c, w1s, w2c, w2s, slice(0, experts), "cuda")
     single = b200.b12x_fused_moe(x.cuda(), w["w1"], w["w1_sf"], w["w2"], w["w2_sf"], ids.cuda(), wts.cuda(), experts,
                                  top_k, w1_alpha=w["w1_alpha"]).cpu()
-    single_f32_rows = b200.b12x_fused_moe(x.cuda(), w["w1"], w["w1_sf"], w["w2"], w["w2_sf"], ids.cuda(), wts.cuda(),
-                                          experts, top_k, w1_alpha=w["w1_alpha"],
-                                          slot_rows_dtype=torch.float32).cpu()
-    ref = O.moe_ref(x, w1c, w1s, w2c, w2s, ids, wts, np.full(experts, 0.02, np.float32))
+    valid = ids >= 0
+    ref = O.moe_ref(x, w1c, w1s, w2c, w2s, torch.where(valid, ids, torch.zeros_like(ids)),
+                    torch.where(valid, wts, torch.zeros_like(wts)), np.full(experts, 0.02, np.float32))
+    # routed inside the dispatch: same bits as routing with topk_route and the single-GPU operator
+    ids_g, w_g = b200.topk_route(_logits().cuda(), top_k)
+    single_routed = b200.b12x_fused_moe(x.cuda(), w["w1"], w["w1_sf"], w["w2"], w["w2_sf"], ids_g, w_g, experts, top_k,
+                                        w1_alpha=w["w1_alpha"]).cpu()
+    parts = [torch.load(os.path.join(tmp_path, f"routed{r}.pt")) for r in range(world)]
+    assert torch.equal(torch.cat([p[1] for p in parts]), ids_g.cpu())
+    assert torch.equal(torch.cat([p[0] for p in parts]), single_routed)
     for kind in ("collective", "peer"):
         got = torch.cat([torch.load(os.path.join(tmp_path, f"out_{kind}{r}.pt")) for r in range(world)])
         if kind == "peer":
             # same bf16 per-slot rows, same slot order, same single rounding as on one GPU
             assert torch.equal(got, single), "peer-memory expert parallelism differs from the single-GPU result"
         else:
-            # same f32 per-slot rows; only the f32 summation order across ranks differs from slot order
-            base = single_f32_rows.float()
+            # bf16 rows both ways, f32 weighted sum by torch: only the summation order may differ
+            base = single.float()
             err = torch.linalg.vector_norm(got.float() - base) / torch.linalg.vector_norm(base)
             assert err <= 2e-3, float(err)
         assert torch.linalg.vector_norm(got.float() - ref.float()) / torch.linalg.vector_norm(ref.float()) <= 1e-2

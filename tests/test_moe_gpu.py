@@ -212,18 +212,122 @@ def test_decode_shapes_wide_tiles(b200, tokens):
         assert out32.dtype == torch.float32 and rel_l2(out32, ref) <= 1e-2
 
 
-def test_few_token_launch_flags_an_expert_named_too_often(b200):
-    """With at most 32 tokens the wide GEMM variants load 32 rows of A per block.  Expert ids that repeat inside a
-    token can give one expert more rows than that; the kernels then raise bit 8 of the device status word."""
+def test_few_tokens_with_repeated_expert_ids(b200):
+    """With at most 32 tokens the wide GEMM variants load 32 rows of A per block.  Expert ids may repeat inside a
+    token (the reference's bench draws them with replacement, tools/perf/bench_flashinfer_b12x.py:70-71), so one
+    expert can receive more than 32 rows: the front end then gives it several blocks and the result is exact."""
     experts, hidden, inter, top_k, tokens = 2, 4352, 1280, 8, 8
     rng = np.random.default_rng(3)
+    torch.manual_seed(3)
     w1c, w1s, w2c, w2s = random_weights(rng, experts, hidden, inter)
     x = torch.randn(tokens, hidden).to(torch.bfloat16)
     ids = torch.zeros(tokens, top_k, dtype=torch.int32)           # 64 rows for expert 0
+    ids[:, 5] = 1
     wts = torch.full((tokens, top_k), 1.0 / top_k)
-    b200._lib.device_status()                                      # clear
-    b200.b12x_fused_moe(x.cuda(), torch.from_numpy(O.pack_e2m1(w1c)).cuda(), six_mode(w1s),
-                        torch.from_numpy(O.pack_e2m1(w2c)).cuda(), six_mode(w2s), ids.cuda(), wts.cuda(), experts, top_k)
+    a1 = torch.full((experts,), 0.01)
+    ref = O.moe_ref(x, w1c, w1s, w2c, w2s, ids, wts, a1.numpy())
+    out = run_gpu(b200, x, w1c, w1s, w2c, w2s, ids, wts, w1_alpha=a1.cuda())     # run_gpu asserts status == 0
+    assert rel_l2(out, ref) <= 1e-2
+
+
+class _SharedExperts:
+    """[experts, ...] container that stores `distinct` matrices and serves expert e as matrix e % distinct."""
+
+    def __init__(self, base, experts):
+        self.base, self.shape = base, (experts,) + base.shape[1:]
+
+    def __getitem__(self, e):
+        return self.base[e % self.base.shape[0]]
+
+
+@pytest.mark.parametrize("tokens", [1, 8, 64])
+@pytest.mark.parametrize("slot_rows", [None, torch.float32], ids=["rows_bf16", "rows_f32"])
+def test_decode_config_at_its_own_shape(b200, tokens, slot_rows):
+    """The decode configuration of the benchmark at its real shape: hidden 7168, 256 experts, intermediate 2048,
+    top-8, router logits ~ N(0,1) with max(1, ceil(1 % of rows)) rows forced onto expert 0, routed on the GPU.
+    To bound host memory and oracle time the 256 experts share 4 distinct weight matrices (expert e uses matrix
+    e % 4) and are told apart by per-expert alphas, so a wrong expert still gives a wrong answer."""
+    experts, hidden, inter, top_k, distinct = 256, 7168, 2048, 8, 4
+    rng = np.random.default_rng(tokens)
+    torch.manual_seed(tokens)
+    w1c, w1s, w2c, w2s = random_weights(rng, distinct, hidden, inter)
+    x = torch.randn(tokens, hidden).to(torch.bfloat16)
+    logits = torch.randn(tokens, experts)
+    n_hot = max(1, -(-tokens // 100))
+    logits[:n_hot, 0] += 1e4
+    a1 = torch.tensor(rng.uniform(0.005, 0.015, experts), dtype=torch.float32)
+    a2 = torch.tensor(rng.uniform(0.5, 2.0, experts), dtype=torch.float32)
+    idx = torch.arange(experts, device="cuda") % distinct
+    w1d = torch.from_numpy(O.pack_e2m1(w1c)).cuda()[idx].contiguous()
+    w2d = torch.from_numpy(O.pack_e2m1(w2c)).cuda()[idx].contiguous()
+    s1d = torch.from_numpy(O.swizzle_sf(w1s)).cuda()[idx].contiguous()
+    s2d = torch.from_numpy(O.swizzle_sf(w2s)).cuda()[idx].contiguous()
+    # routing on the GPU, fused into the operator's front end (router bucket of 256 experts)
+    ids_d = torch.empty(tokens, top_k, dtype=torch.int32, device="cuda")
+    w_d = torch.empty(tokens, top_k, dtype=torch.float32, device="cuda")
+    out = b200.b12x_fused_moe(x.cuda(), w1d, s1d, w2d, s2d, ids_d, w_d, experts, top_k, w1_alpha=a1.cuda(),
+                              w2_alpha=a2.cuda(), router_logits=logits.cuda(), slot_rows_dtype=slot_rows)
     torch.cuda.synchronize()
-    assert b200._lib.device_status() == 8
-    assert b200._lib.device_status() == 0                          # reading clears it
+    assert b200._lib.device_status() == 0
+    ids_ref, w_ref = O.route_topk_ref(logits, top_k)
+    assert torch.equal(ids_d.cpu(), ids_ref) and bool((ids_ref[:n_hot, 0] == 0).all())
+    assert torch.allclose(w_d.cpu(), w_ref, rtol=1e-5, atol=1e-7)
+    ref = O.moe_ref(x, _SharedExperts(w1c, experts), _SharedExperts(w1s, experts), _SharedExperts(w2c, experts),
+                    _SharedExperts(w2s, experts), ids_ref, w_ref, a1.numpy(), a2.numpy(),
+                    weight_key=lambda e: e % distinct)
+    assert rel_l2(out.cpu(), ref) <= 1e-2
+
+
+@pytest.mark.parametrize("tokens", [5, 300])
+def test_router_inside_the_operator_and_wrapper_object(b200, tokens):
+    """router_logits= routes inside the front end (both the few-slot and the general path) and gives the bits of
+    topk_route + b12x_fused_moe; B12xMoEWrapper.run does the same from its pre-allocated workspace."""
+    experts, hidden, inter, top_k = 16, 512, 256, 4
+    rng = np.random.default_rng(tokens)
+    torch.manual_seed(tokens)
+    w1c, w1s, w2c, w2s = random_weights(rng, experts, hidden, inter)
+    dev = (torch.from_numpy(O.pack_e2m1(w1c)).cuda(), six_mode(w1s), torch.from_numpy(O.pack_e2m1(w2c)).cuda(),
+           six_mode(w2s))
+    x = torch.randn(tokens, hidden).to(torch.bfloat16).cuda()
+    logits = torch.randn(tokens, experts).cuda()
+    a1 = torch.full((experts,), 0.02, device="cuda")
+    ids, wts = b200.topk_route(logits, top_k)
+    base = b200.b12x_fused_moe(x, *dev, ids, wts, experts, top_k, w1_alpha=a1)
+    fused = b200.b12x_fused_moe(x, *dev, None, None, experts, top_k, w1_alpha=a1, router_logits=logits)
+    wrapper = b200.B12xMoEWrapper(experts, top_k, hidden, inter, max_num_tokens=512)
+    before = torch.cuda.memory_allocated()
+    out_w = torch.empty(tokens, hidden, dtype=torch.bfloat16, device="cuda")
+    wrapper.run(x, *dev, router_logits=logits, w1_alpha=a1, output=out_w)
+    assert torch.cuda.memory_allocated() == before           # run() allocates nothing
+    out_ids = wrapper.run(x, *dev, ids, wts, w1_alpha=a1)
+    torch.cuda.synchronize()
+    assert b200._lib.device_status() == 0
+    assert torch.equal(fused, base) and torch.equal(out_w, base) and torch.equal(out_ids, base)
+    ids_w, wts_w = wrapper.last_routing(tokens)
+    assert torch.equal(ids_w, ids) and torch.equal(wts_w, wts)
+    with pytest.raises(ValueError):
+        wrapper.run(torch.zeros(513, hidden, dtype=torch.bfloat16, device="cuda"), *dev, router_logits=logits)
+
+
+def test_packed_checkpoint_weights_run_through_the_operator(b200):
+    """pack_moe_weights (bf16 experts -> NVFP4 codes, six-mode scales, per-expert alphas) feeds the operator and
+    the result tracks the un-quantised f32 MoE within the accuracy NVFP4 allows."""
+    experts, hidden, inter, top_k, tokens = 4, 256, 128, 2, 64
+    torch.manual_seed(0)
+    w1 = (0.05 * torch.randn(experts, 2 * inter, hidden)).cuda()
+    w2 = (0.05 * torch.randn(experts, hidden, inter)).cuda()
+    x = torch.randn(tokens, hidden).to(torch.bfloat16).cuda()
+    ids, wts = b200.topk_route(torch.randn(tokens, experts).cuda(), top_k)
+    packed = b200.pack_moe_weights(w1, w2)
+    out = b200.b12x_fused_moe(x, packed["w1_weight"], packed["w1_weight_sf"], packed["w2_weight"],
+                              packed["w2_weight_sf"], ids, wts, experts, top_k, w1_alpha=packed["w1_alpha"],
+                              w2_alpha=packed["w2_alpha"], fc2_input_scale=packed["fc2_input_scale"])
+    torch.cuda.synchronize()
+    ref = torch.zeros(tokens, hidden, device="cuda")
+    for j in range(top_k):
+        for e in range(experts):
+            m = ids[:, j] == e
+            fc1 = x[m].float() @ w1[e].t()
+            act = torch.nn.functional.silu(fc1[:, inter:]) * fc1[:, :inter]
+            ref[m] += wts[m, j:j + 1] * (act @ w2[e].t())
+    assert rel_l2(out, ref) <= 0.2       # two 4-bit quantisations per GEMM: ~10 % is the format's own noise

@@ -205,3 +205,22 @@ def test_full_size_add_rmsnorm_properties(b200):
     rel = diff / (normed.abs() + 1e-8)
     assert float(((diff <= 0.5) | (rel <= 0.3)).float().mean()) >= 0.99
     assert bool(((diff <= 2.0) | (rel <= 0.5)).all())
+
+
+def test_rmsnorm_swizzled_scale_layout_on_the_config_fixture(b200):
+    """rmsnorm_fp4quant(..., is_sf_swizzled_layout=True) on the bf16 [128, 4096] configuration: codes equal the
+    fixture's, and the tiled scale bytes equal the oracle's swizzle of the fixture's row-major scale bytes."""
+    g = golden("norm_bf16_128x4096.npz")
+    x = torch.from_numpy(g["x"].copy()).view(torch.bfloat16).cuda()
+    w = torch.from_numpy(g["w"].copy()).view(torch.bfloat16).cuda()
+    gs = torch.tensor([float(g["gs_rms"])], device="cuda")
+    eps = float(g["eps"])
+    y, s = b200.rmsnorm_fp4quant(x, w, global_scale=gs, eps=eps, block_size=16, is_sf_swizzled_layout=True)
+    y_row, s_row = b200.rmsnorm_fp4quant(x, w, global_scale=gs, eps=eps, block_size=16)
+    torch.cuda.synchronize()
+    # the large fixtures allow rare one-step differences from the f32 summation order (none observed)
+    assert_nvfp4_close(y_row.cpu().numpy(), s_row.cpu().numpy(), g["rms_packed"], g["rms_sf"], exact=False)
+    assert torch.equal(y, y_row)
+    assert np.array_equal(s.cpu().numpy().reshape(-1), O.swizzle_sf(s_row.cpu().numpy().reshape(128, 256)))
+    assert np.array_equal(s.cpu().numpy().reshape(-1), O.swizzle_sf(g["rms_sf"]))
+    assert s.numel() == 32768

@@ -1,5 +1,5 @@
-"""Host-side partitioning logic and the expert-parallel gather / reduce-scatter bookkeeping, run as two CPU
-ranks over the gloo backend (the local expert compute is the CPU oracle, injected in place of the CUDA op)."""
+"""Host-side partitioning logic, the all-to-all-v dispatch / combine bookkeeping and the peer health check, run as
+two CPU ranks over the gloo backend (the local expert compute is the CPU oracle, injected in place of the CUDA op)."""
 import os
 
 import numpy as np
@@ -49,20 +49,13 @@ def _problem():
 
 
 def _local_oracle(weights):
+    """One expert per row, as the all-to-all-v path asks for: rows [n, H], local expert ids [n] -> rows [n, H]."""
     w1c, w1s, w2c, w2s = weights
 
-    def fn(x_all, ids_all, w_all, lo, n):
-        # slots of foreign experts contribute nothing: give them weight 0 and a valid local id
-        local = (ids_all >= lo) & (ids_all < lo + n)
-        ids_l = torch.where(local, ids_all - lo, torch.zeros_like(ids_all))
-        w_l = torch.where(local, w_all, torch.zeros_like(w_all))
+    def fn(rows, ids_local, lo, n):
         sl = slice(lo, lo + n)
-        out = torch.zeros(x_all.shape, dtype=torch.float32)
-        for slot in range(ids_all.shape[1]):
-            part = O.moe_ref(x_all, w1c[sl], w1s[sl], w2c[sl], w2s[sl], ids_l[:, slot:slot + 1],
-                             torch.ones(x_all.shape[0], 1), np.full(n, 0.02, np.float32))
-            out += w_l[:, slot:slot + 1] * part.float()
-        return out
+        return O.moe_ref(rows, w1c[sl], w1s[sl], w2c[sl], w2s[sl], ids_local.reshape(-1, 1).to(torch.int32),
+                         torch.ones(rows.shape[0], 1), np.full(n, 0.02, np.float32))
     return fn
 
 
@@ -74,6 +67,8 @@ def _worker(rank, world, port, result_dir):
         import cutedsl_fully_opensourced_b200  # noqa: F401  (loads the library; no GPU needed for that)
         from cutedsl_fully_opensourced_b200.parallel import ExpertParallelMoE
         weights, x, ids, wts, experts, top_k = _problem()
+        ids = ids.clone()
+        ids[1, 0] = -1                       # a masked slot contributes nothing
         ep = ExpertParallelMoE(experts, top_k, local_moe=_local_oracle(weights))
         assert (ep.expert_lo, ep.local_experts) == (rank * 2, 2)
         t = x.shape[0] // world
@@ -84,13 +79,51 @@ def _worker(rank, world, port, result_dir):
         dist.destroy_process_group()
 
 
-def test_expert_parallel_bookkeeping_two_gloo_ranks(tmp_path, lib_built):
+def test_expert_parallel_all_to_all_two_gloo_ranks(tmp_path, lib_built):
     world = 2
     port = 29500 + os.getpid() % 2000
     mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
     weights, x, ids, wts, experts, top_k = _problem()
-    single = _local_oracle(weights)(x, ids, wts, 0, experts).to(torch.bfloat16)
+    wts = wts.clone()
+    wts[1, 0] = 0.0                          # the reference result of the masked slot
+    single = O.moe_ref(x, *[weights[i] for i in (0, 1, 2, 3)], ids, wts, np.full(experts, 0.02, np.float32))
     got = torch.cat([torch.load(os.path.join(tmp_path, f"out{r}.pt")) for r in range(world)])
     assert got.shape == single.shape
     err = torch.linalg.vector_norm(got.float() - single.float()) / torch.linalg.vector_norm(single.float())
     assert err <= 1e-2
+
+
+def _leaver(rank, world, port, result_dir):
+    """Two ranks run a healthy step; then rank 1 leaves (between steps, nothing in flight) and rank 0's health
+    check before its next step must raise instead of hanging."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import cutedsl_fully_opensourced_b200  # noqa: F401
+    from cutedsl_fully_opensourced_b200.parallel import PeerHealth
+    health = PeerHealth(timeout_s=3.0)
+    health.check()                           # step 1: both ranks are there
+    if rank == 1:
+        os._exit(0)                          # leaves without a word
+    try:
+        health.check()                       # step 2
+        outcome = "no error"
+    except RuntimeError as e:
+        outcome = f"raised: {e}"
+    with open(os.path.join(result_dir, "outcome.txt"), "w") as f:
+        f.write(outcome)
+    os._exit(0)                              # the group cannot be torn down cleanly any more
+
+
+def test_survivor_raises_when_a_rank_leaves_between_steps(tmp_path, lib_built):
+    world = 2
+    port = 31500 + os.getpid() % 2000
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_leaver, args=(r, world, port, str(tmp_path))) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+        assert not p.is_alive(), "a rank hung"
+    outcome = open(os.path.join(tmp_path, "outcome.txt")).read()
+    assert outcome.startswith("raised: expert-parallel group is incomplete"), outcome

@@ -68,11 +68,17 @@ def test_noalloc_entry_matches_regular_entry_on_two_calls_in_a_row(b200):
         ref_out = torch.zeros(tokens, hidden, dtype=torch.bfloat16, device="cuda")
         rc, ws = _call_regular(lib, d, ref_out, tokens, hidden, inter, experts, top_k, stream)
         assert rc == 0, lib.b200fp4_last_error()
-        for _ in range(2):
-            out = torch.full((tokens, hidden), float("nan"), dtype=torch.bfloat16, device="cuda")
+        outs = [torch.full((tokens, hidden), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(2)]
+        free_before = None
+        for out in outs:
             rc = _call_noalloc(lib, d, out, status, tokens, hidden, inter, experts, top_k, stream)
             assert rc == 0, lib.b200fp4_last_error()
             torch.cuda.synchronize()
+            # the entry point allocates nothing: once its first call on this GPU has been made, the device's free
+            # memory does not move across further calls (outputs were allocated beforehand)
+            free_now = torch.cuda.mem_get_info()[0]
+            assert free_before is None or free_now == free_before, "the no-alloc entry point changed free memory"
+            free_before = free_now
             assert int(status.item()) == 0, "a device-side wait expired"
             assert torch.equal(out, ref_out), "no-alloc entry point disagrees with b200fp4_moe_fused"
         # and both agree with the CPU oracle within the MoE tolerance of the other tests
