@@ -1,27 +1,34 @@
 #!/usr/bin/env python3
 """Benchmark of the NVFP4 hot path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--parts a,b,...]
 
-One "step" is one pass of the selected workload over one batch of seeded
-synthetic input that is already resident in HBM.  The default workload is the
-configuration the headline metric is quoted on: add_rmsnorm_fp4quant over bf16
-[8192, 7168] (385 MB of algorithmic traffic per step, larger than L2).  With
-N > 1 (launched by torch.distributed.run, one process per GPU) every rank owns
-its own row block of the same size -- rows are independent, so there is no
-data-path collective -- and the value is the aggregate over ranks divided by
-the slowest rank's device time.
+One invocation times every part of the metric "NVFP4 GEMM TFLOP/s; norm-quant HBM GB/s; MoE tokens/s" on
+seeded synthetic inputs that are already resident in HBM, and prints ONE JSON line:
 
-The JSON line printed by rank 0 carries the device-timed throughput
-(``value``), the same metric through the public Python API with host buffers
-(``e2e``), the roofline of the dominant kernel and a CPU baseline (the oracle
-port timed on the host cores over a bounded sample).  ``--impl reference``
-prints only that CPU arm.
+* headline (``metric`` / ``value``): fused NVFP4 MoE, prefill configuration (4096 tokens in total, hidden 2048,
+  128 experts, top-8, intermediate 768), tokens/s.  With N > 1 (one process per GPU under torch.distributed.run)
+  the same 4096 tokens and 128 experts are split over the ranks (``"scaling": "strong"``) and dispatch / combine
+  cross NVLink inside the kernels.
+* ``parts``: ``norm_quant`` (add_rmsnorm_fp4quant bf16 [8192, 7168]; rows split over the ranks), ``gemm_8192``
+  (M = N = K = 8192; rows of A / C split), ``gemm_m1024`` / ``gemm_m128`` (the M sweep, one GPU), ``moe_decode_t64`` /
+  ``_t8`` / ``_t1`` (hidden 7168, 256 experts, top-8, intermediate 2048, 1 % of rows forced onto one hot expert;
+  expert-parallel with N > 1 where the batch divides).  Each part carries its own value, roofline, end-to-end
+  number, step statistics and (N = 1) CPU baseline.
+
+A "step" is one pass of a part over its batch.  Steps are timed one by one with CUDA events on the launching
+stream (median / p10 / p90 / min are reported; the value uses the mean), after >= 3 warm-up steps, as the
+maximum over ranks.  ``e2e`` is the same step through the public Python API with host buffers: the host->device
+copy of the inputs and the device->host copy of the result are inside the timed region.  ``roofline`` compares
+algorithmic bytes (or flops) per step with the measured peaks of MEASURED_PEAKS.json.  ``cpu_baseline`` is the
+oracle port of the reference's CPU golden path timed on the host cores over a bounded sample.
+``--impl reference`` prints that CPU arm alone, for the same parts.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -33,6 +40,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 HBM_FALLBACK_GBS = 6650.0      # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+FP4_NOMINAL_TFLOPS = 9000.0    # dense FP4 peak of a B200 (nominal; MEASURED_PEAKS.json has no FP4 figure)
+L2_BYTES = 126 << 20
 
 
 def load_peaks():
@@ -45,6 +54,26 @@ def load_peaks():
     except Exception:
         return {"hbm_gbs": HBM_FALLBACK_GBS, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
                 "source": "fallback"}
+
+
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def pct(xs, q):
+    s = sorted(xs)
+    if not s:
+        return float("nan")
+    i = min(len(s) - 1, max(0, int(round(q * (len(s) - 1)))))
+    return s[i]
+
+
+def stats_us(ms):
+    return {"median": round(1e3 * statistics.median(ms), 2), "p10": round(1e3 * pct(ms, 0.1), 2),
+            "p90": round(1e3 * pct(ms, 0.9), 2), "min": round(1e3 * min(ms), 2), "mean": round(1e3 * statistics.mean(ms), 2)}
 
 
 # ---------------------------------------------------------------------------
@@ -60,7 +89,6 @@ class ClockSampler:
         self.gpu = gpu_index
         self.proc = None
         self.lines = []
-        self.thread = None
 
     def start(self):
         try:
@@ -70,24 +98,16 @@ class ClockSampler:
         except OSError:
             self.proc = None
             return
-        self.thread = threading.Thread(target=self._pump, daemon=True)
-        self.thread.start()
+        threading.Thread(target=self._pump, daemon=True).start()
 
     def _pump(self):
         for line in self.proc.stdout:
             self.lines.append((time.time(), line.strip()))
 
-    def stop(self, t0: float, t1: float):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
+    def window(self, t0: float, t1: float):
+        """Summary of the samples taken between two wall-clock times (the sampler keeps running)."""
         sm, mx, reasons, power = [], [], set(), []
-        for ts, line in self.lines:
+        for ts, line in list(self.lines):
             if ts < t0 - 0.05 or ts > t1 + 0.15:
                 continue
             parts = [p.strip() for p in line.split(",")]
@@ -105,50 +125,81 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "power_w_max": max(power) if power else None, "reasons": sorted(reasons), "samples": len(sm)}
 
+    def stop(self):
+        if self.proc is None:
+            return
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+
 
 # ---------------------------------------------------------------------------
-# workloads
+# parts
 # ---------------------------------------------------------------------------
-class AddRmsNormWorkload:
-    """add_rmsnorm_fp4quant, bf16 [8192, 7168], weight 1 + 0.1 N(0,1), eps 1e-6,
-    per-tensor global scale 448*6/amax, scale factors in the 128x4 tiled layout."""
+class Part:
+    """One workload of the metric.  `units_per_step` is what ALL ranks together process in a step (bytes, flops or
+    tokens); `alg_bytes` / `alg_flops` are the algorithmic traffic / work of THIS rank's launch."""
+    name = ""
+    metric = ""
+    unit = ""
+    dtype = ""
+    bound = "hbm"
+    kernel = ""
+    scaling = "strong"
+    use_graph = False
+    launches_per_step = 1
+    flush = None
+
+    def supported(self, world):
+        return True
+
+    def restore(self):
+        if self.flush is not None:
+            self.flush.zero_()
+
+    def checks(self, pkg, world, rank):
+        return None
+
+    def free(self):
+        for k in list(self.__dict__):
+            if k not in ("rank", "world"):
+                self.__dict__[k] = None
+
+
+def _flush_buffer():
+    import torch
+    return torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+
+class NormPart(Part):
+    """add_rmsnorm_fp4quant, bf16 [8192, 7168] in total, weight 1 + 0.1 N(0,1), eps 1e-6, per-tensor global scale
+    448*6/amax, scale factors in the 128x4 tiled layout.  Rows are split over the ranks (128-row multiples)."""
     name = "add_rmsnorm_fp4quant_bf16_8192x7168"
     metric = "norm-quant HBM GB/s"
     unit = "GB/s"
     dtype = "bf16"
-    rows, hidden = 8192, 7168
-    bytes_per_element = 2 + 2 + 2 + 0.5 + 0.0625      # x in, residual in+out, codes, scale bytes
     kernel = "norm_quant_kernel<bf16, add>"
-    bound = "hbm"
-    # DRAM bytes inside the kernel window per element, from the ncu capture summarised in
-    # profiles/norm_quant_add_bf16.md (reads equal the algorithmic reads; most writes drain from L2 later)
+    total_rows, hidden = 8192, 7168
+    bytes_per_element = 2 + 2 + 2 + 0.5 + 0.0625      # x in, residual in+out, codes, scale bytes
+    # DRAM bytes inside the kernel window per element, from an ncu capture of a 4096-row launch (reads equal the
+    # algorithmic reads; most of the writes are still dirty in L2 when the kernel ends and drain later)
     traffic_per_element = (117496064 + 26109440) / (4096 * 7168)
 
-    def __init__(self, rank: int):
-        self.rank = rank
+    def __init__(self, rank, world):
+        from cutedsl_fully_opensourced_b200_shard import shard_rows
+        self.rank, self.world = rank, world
+        self.row0, self.rows = shard_rows(self.total_rows, world, rank)
         self.alg_bytes = int(self.rows * self.hidden * self.bytes_per_element)
-
-    @property
-    def work(self):                 # units of the metric per step: bytes
-        return float(self.alg_bytes)
+        self.units_per_step = float(self.total_rows * self.hidden * self.bytes_per_element)
+        per_set = max(1, self.alg_bytes)
+        self.sets = max(4, math.ceil(3 * L2_BYTES / per_set) + 1)
 
     def config(self, world):
-        return {"workload": self.name, "rows_per_gpu": self.rows, "hidden": self.hidden,
-                "sf_layout": "swizzled_128x4", "parallelism": f"rows x{world}",
-                "l2": f"{self.sets} rotating sets of inputs and outputs (385 MB of traffic each, 126 MB L2): a "
-                      "step never finds its inputs in L2; the residual streams are updated in place and keep "
-                      "absorbing x from step to step"}
-
-    def host_inputs(self, rows=None):
-        import torch
-        rows = rows or self.rows
-        g = torch.Generator().manual_seed(1000 + self.rank)
-        x = torch.randn(rows, self.hidden, generator=g).to(torch.bfloat16)
-        r = torch.randn(rows, self.hidden, generator=g).to(torch.bfloat16)
-        w = (1 + 0.1 * torch.randn(self.hidden, generator=torch.Generator().manual_seed(7))).to(torch.bfloat16)
-        return x, r, w
-
-    sets = 4      # rotating (x, residual, outputs) sets: a step never finds its inputs in L2
+        return {"workload": self.name, "rows": self.total_rows, "rows_per_gpu": self.total_rows // world,
+                "hidden": self.hidden, "sf_layout": "swizzled_128x4", "parallelism": f"rows split x{world}, no collective",
+                "l2": "rotating sets of inputs and outputs whose bytes between two uses of a set exceed the 126 MB L2"}
 
     def setup(self, pkg):
         import torch
@@ -163,18 +214,14 @@ class AddRmsNormWorkload:
             self.ys.append(torch.empty(self.rows, self.hidden // 2, dtype=torch.uint8, device="cuda"))
             self.sfs.append(torch.empty(swizzled_sf_numel(self.rows, self.hidden // 16), dtype=torch.uint8,
                                         device="cuda"))
-        self.x, self.r, self.y, self.sf = self.xs[0], self.rs[0], self.ys[0], self.sfs[0]
-        self.r0 = self.r.clone()
-        h = self.x.float() + self.r.float()
+        self.r0 = self.rs[0].clone()
+        h = self.xs[0].float() + self.rs[0].float()
         normed = h.to(torch.bfloat16).float() * torch.rsqrt(h.square().mean(-1, keepdim=True) + 1e-6) * self.w.float()
-        # RMSNorm output is scale-free, so this global scale stays valid while the residual streams
-        # keep absorbing x over the steps
+        # RMSNorm output is scale-free, so this global scale stays valid while the residual streams keep
+        # absorbing x over the steps
         self.gs = (448.0 * 6.0 / normed.abs().max()).reshape(1).float()
         del h, normed
         self.i = 0
-
-    def restore(self):
-        pass
 
     def step(self):
         j = self.i % self.sets
@@ -182,78 +229,96 @@ class AddRmsNormWorkload:
         self.pkg.add_rmsnorm_fp4quant(self.xs[j], self.rs[j], self.w, self.ys[j], self.sfs[j], global_scale=self.gs,
                                       eps=1e-6, block_size=16, is_sf_swizzled_layout=True)
 
-    launches_per_step = 1
-
-    # ---- end to end through the public API with host buffers
     def setup_e2e(self):
         import torch
-        self.hx = self.x.cpu().pin_memory()
+        self.hx = self.xs[0].cpu().pin_memory()
         self.hr = self.r0.cpu().pin_memory()
-        self.hy = torch.empty(self.y.shape, dtype=torch.uint8).pin_memory()
-        self.hsf = torch.empty(self.sf.shape, dtype=torch.uint8).pin_memory()
-        self.hres = torch.empty(self.r.shape, dtype=torch.bfloat16).pin_memory()
+        self.hy = torch.empty(self.ys[0].shape, dtype=torch.uint8).pin_memory()
+        self.hsf = torch.empty(self.sfs[0].shape, dtype=torch.uint8).pin_memory()
+        self.hres = torch.empty(self.rs[0].shape, dtype=torch.bfloat16).pin_memory()
         self.h2d = self.hx.numel() * 2 + self.hr.numel() * 2
         self.d2h = self.hy.numel() + self.hsf.numel() + self.hres.numel() * 2
 
     def step_e2e(self):
-        self.x.copy_(self.hx, non_blocking=True)
-        self.r.copy_(self.hr, non_blocking=True)
-        self.pkg.add_rmsnorm_fp4quant(self.x, self.r, self.w, self.y, self.sf, global_scale=self.gs, eps=1e-6,
-                                      block_size=16, is_sf_swizzled_layout=True)
-        self.hy.copy_(self.y, non_blocking=True)
-        self.hsf.copy_(self.sf, non_blocking=True)
-        self.hres.copy_(self.r, non_blocking=True)
+        x, r, y, sf = self.xs[0], self.rs[0], self.ys[0], self.sfs[0]
+        x.copy_(self.hx, non_blocking=True)
+        r.copy_(self.hr, non_blocking=True)
+        self.pkg.add_rmsnorm_fp4quant(x, r, self.w, y, sf, global_scale=self.gs, eps=1e-6, block_size=16,
+                                      is_sf_swizzled_layout=True)
+        self.hy.copy_(y, non_blocking=True)
+        self.hsf.copy_(sf, non_blocking=True)
+        self.hres.copy_(r, non_blocking=True)
 
-    # ---- CPU arm: the oracle port on a bounded sample of the same workload
-    cpu_sample_rows = 8192
+    def roofline_extra(self):
+        return {"traffic": int(self.traffic_per_element * self.rows * self.hidden)}
+
+    # CPU arm: the oracle port on all 8192 rows (a step costs ~0.1-0.2 s on 16 cores)
+    def cpu_setup(self):
+        import torch
+        g = torch.Generator().manual_seed(1000)
+        self.cx = torch.randn(self.total_rows, self.hidden, generator=g).to(torch.bfloat16)
+        self.cr = torch.randn(self.total_rows, self.hidden, generator=g).to(torch.bfloat16)
+        self.cw = (1 + 0.1 * torch.randn(self.hidden, generator=torch.Generator().manual_seed(7))).to(torch.bfloat16)
 
     def cpu_run(self, threads: int):
         import torch
         from concurrent.futures import ThreadPoolExecutor
         from oracle import nvfp4_oracle as O
-        rows = self.cpu_sample_rows
-        x, r, w = self.host_inputs(rows)
-        gs = 500.0
+        rows = self.total_rows
         chunk = max(16, rows // max(1, threads * 2))
         spans = [(i, min(rows, i + chunk)) for i in range(0, rows, chunk)]
         torch.set_num_threads(1)
         t0 = time.perf_counter()
         with ThreadPoolExecutor(max_workers=threads) as pool:
-            list(pool.map(lambda s: O.add_rmsnorm_fp4quant_ref(x[s[0]:s[1]], r[s[0]:s[1]], w, 1e-6, gs), spans))
+            list(pool.map(lambda s: O.add_rmsnorm_fp4quant_ref(self.cx[s[0]:s[1]], self.cr[s[0]:s[1]], self.cw, 1e-6,
+                                                               500.0), spans))
         dt = time.perf_counter() - t0
         return rows * self.hidden * self.bytes_per_element / dt / 1e9, dt, \
-            f"{rows} of {self.rows} rows x {self.hidden}, oracle port (numpy+torch), {threads} threads"
+            f"all {rows} rows x {self.hidden} (global scale fixed at 500), oracle port (numpy+torch), {threads} threads"
 
 
-class GemmWorkload:
-    """NVFP4 block-scaled GEMM M=N=K=8192: A, B ~ N(0,1) quantised to e2m1 with e4m3 scale factors per
+class GemmPart(Part):
+    """NVFP4 block-scaled GEMM, N = K = 8192: A, B ~ N(0,1) quantised to e2m1 with e4m3 scale factors per
     16 K-elements and a per-tensor global scale, f32 accumulate, bf16 output, alpha = 1/(gs_A*gs_B)."""
     metric = "NVFP4 GEMM TFLOP/s"
     unit = "TFLOP/s"
     dtype = "nvfp4 (e2m1 x e2m1, ue4m3 scales, f32 accumulate)"
-    kernel = "nvfp4_gemm_kernel<256>"
-    bound = "tensor"
-    launches_per_step = 1
-    sets = 3                      # rotating operand sets so no step finds its operands in L2
-    FP4_NOMINAL_TFLOPS = 9000.0   # dense FP4 peak of a B200 (nominal; no measured FP4 peak exists)
+    tile_n = 0
 
-    def __init__(self, rank: int, m: int = 8192, n: int = 8192, k: int = 8192):
-        self.rank, self.m, self.n, self.k = rank, m, n, k
-        self.rows, self.hidden = m, k
+    def __init__(self, rank, world, m=8192, n=8192, k=8192):
+        from cutedsl_fully_opensourced_b200_shard import shard_rows
+        self.rank, self.world = rank, world
+        self.m_total, self.n, self.k = m, n, k
+        _, self.m = shard_rows(m, world, rank)
         self.name = f"nvfp4_gemm_{m}x{n}x{k}_bf16out"
-        self.work = 2.0 * m * n * k
-        self.alg_bytes = m * k // 2 + n * k // 2 + (m + n) * k // 16 + 2 * m * n
+        self.units_per_step = 2.0 * m * n * k
+        self.alg_flops = 2.0 * self.m * n * k
+        self.alg_bytes = self.m * k // 2 + n * k // 2 + (self.m + n) * k // 16 + 2 * self.m * n
+        # M = 128 streams the weights once: HBM-bound; the larger problems are bound by the tensor pipe
+        self.bound = "hbm" if m <= 256 else "tensor"
+        self.kernel = ("nvfp4_gemm_pair_kernel (256x256 tiles on CTA pairs) for a full wave of such tiles, else "
+                       "nvfp4_gemm_kernel<256|128|64>")
+        self.sets = max(3, math.ceil(2 * L2_BYTES / max(1, self.alg_bytes)) + 1)
+
+    def supported(self, world):
+        return self.m_total % (128 * world) == 0
+
+    def config(self, world):
+        return {"workload": self.name, "m": self.m_total, "m_per_gpu": self.m_total // world, "n": self.n, "k": self.k,
+                "parallelism": f"rows of A / C split x{world}, B replicated, no collective",
+                "l2": "rotating operand sets whose bytes between two uses of a set exceed the 126 MB L2"}
 
     def setup(self, pkg):
         import torch
         self.pkg = pkg
         self.ops = []
+        gb = torch.Generator(device="cuda").manual_seed(77)
         for i in range(self.sets):
             g = torch.Generator(device="cuda").manual_seed(100 * self.rank + i)
             a = torch.randn(self.m, self.k, generator=g, device="cuda")
-            b = torch.randn(self.n, self.k, generator=g, device="cuda")
             aq, sfa, gsa = pkg.gemm.quantize_operand(a)
             del a
+            b = torch.randn(self.n, self.k, generator=gb, device="cuda")
             bq, sfb, gsb = pkg.gemm.quantize_operand(b)
             del b
             alpha = torch.tensor([1.0 / (gsa * gsb)], device="cuda")
@@ -261,21 +326,10 @@ class GemmWorkload:
             self.ops.append((aq, bq, sfa, sfb, alpha, c))
         self.i = 0
 
-    def restore(self):
-        pass
-
     def step(self):
         aq, bq, sfa, sfb, alpha, c = self.ops[self.i % self.sets]
         self.i += 1
         self.pkg.nvfp4_gemm(aq, bq, sfa, sfb, alpha=alpha, out=c, tile_n=self.tile_n)
-
-    tile_n = 0
-
-    def config(self, world):
-        return {"workload": self.name, "m_per_gpu": self.m, "n": self.n, "k": self.k,
-                "parallelism": f"rows of A/C x{world}, B replicated",
-                "l2": f"{self.sets} rotating operand sets of 72 MB + 134 MB output each, so a step never "
-                      "finds its operands in the 126 MB L2"}
 
     def setup_e2e(self):
         import torch
@@ -292,124 +346,139 @@ class GemmWorkload:
         self.pkg.nvfp4_gemm(aq, bq, sfa, sfb, alpha=alpha, out=c, tile_n=self.tile_n)
         self.hc.copy_(c, non_blocking=True)
 
-    def cpu_run(self, threads: int):
-        import numpy as np
+    def roofline_extra(self):
+        return {"traffic": None}
+
+    def cpu_setup(self):
         import torch
         from oracle import nvfp4_oracle as O
-        m, n, k = min(self.m, 1024), min(self.n, 1024), self.k
-        torch.set_num_threads(threads)
+        m, n, k = min(self.m_total, 512), min(self.n, 1024), self.k
         g = torch.Generator().manual_seed(0)
-        ac, sfa = O.quantize_nvfp4(torch.randn(m, k, generator=g).numpy(), 500.0)
-        bc, sfb = O.quantize_nvfp4(torch.randn(n, k, generator=g).numpy(), 500.0)
+        self.c_ac, self.c_sfa = O.quantize_nvfp4(torch.randn(m, k, generator=g).numpy(), 500.0)
+        self.c_bc, self.c_sfb = O.quantize_nvfp4(torch.randn(n, k, generator=g).numpy(), 500.0)
+        self.c_mnk = (m, n, k)
+
+    def cpu_run(self, threads: int):
+        import torch
+        from oracle import nvfp4_oracle as O
+        torch.set_num_threads(threads)
+        m, n, k = self.c_mnk
         t0 = time.perf_counter()
-        O.gemm_nvfp4_ref(ac, sfa, bc, sfb, alpha=1.0 / 250000.0)
+        O.gemm_nvfp4_ref(self.c_ac, self.c_sfa, self.c_bc, self.c_sfb, alpha=1.0 / 250000.0)
         dt = time.perf_counter() - t0
         return 2.0 * m * n * k / dt / 1e12, dt, \
-            f"{m}x{n}x{k} block of the {self.m}x{self.n}x{self.k} problem: de-quantise + f32 matmul, {threads} threads"
+            (f"{m}x{n}x{k} block of the {self.m_total}x{self.n}x{self.k} problem: de-quantise + f32 matmul "
+             f"(the demo's golden), {threads} threads")
 
 
-class MoeWorkload:
+class MoePart(Part):
     """Fused NVFP4 MoE.  prefill: 4096 tokens, hidden 2048, 128 experts, top-8, intermediate 768.
-    decode: T tokens, hidden 7168, 256 experts, top-8, intermediate 2048, 1% of rows forced onto expert 0.
-    Tokens bf16 ~ N(0,1); expert weights N(0, 0.02) quantised to NVFP4 per expert (global scale
+    decode: T tokens, hidden 7168, 256 experts, top-8, intermediate 2048, max(1, ceil(1 % of T)) rows forced onto
+    expert 0.  Tokens bf16 ~ N(0,1); expert weights N(0, 0.02) quantised to NVFP4 per expert (global scale
     448*6/amax folded into w1_alpha / w2_alpha); router logits ~ N(0,1), softmax top-k renormalised.
-    A step = router kernel + the fused MoE call."""
+    A step = router + fused MoE (the router runs inside the operator's first kernel)."""
     metric = "MoE tokens/s"
     unit = "tokens/s"
     dtype = "nvfp4 weights and activations, bf16 tokens, f32 accumulate"
-    kernel = "nvfp4_gemm_kernel<swiglu> + nvfp4_gemm_kernel (grouped FC1 / FC2)"
-    bound = "hbm"
-    launches_per_step = 8      # route, count, scan, scatter-quant, FC1, FC2, combine (+ 2 memsets not counted) 
+    kernel = "whole step: count(+route), quantise+place, grouped FC1 (SwiGLU, re-quantise), grouped FC2, weighted sum"
+    use_graph = True
 
-    scaling = "strong"         # the token batch is fixed; more GPUs split it (and the experts)
-
-    def __init__(self, rank, kind="prefill", tokens=None, world=1):
-        self.rank, self.kind, self.world = rank, kind, world
+    def __init__(self, rank, world, kind="prefill", tokens=None):
+        self.rank, self.world, self.kind = rank, world, kind
         if kind == "prefill":
             self.tokens, self.hidden, self.experts, self.top_k, self.inter = tokens or 4096, 2048, 128, 8, 768
         else:
             self.tokens, self.hidden, self.experts, self.top_k, self.inter = tokens or 64, 7168, 256, 8, 2048
-        self.rows = self.tokens
         self.name = f"moe_{kind}_T{self.tokens}_H{self.hidden}_E{self.experts}_k{self.top_k}_I{self.inter}"
-        if self.tokens % world or self.experts % world:
-            raise SystemExit(f"{self.tokens} tokens / {self.experts} experts do not divide over {world} ranks")
-        self.local_tokens = self.tokens // world
-        self.local_experts = self.experts // world
+        self.local_tokens = self.tokens // max(1, world)
+        self.local_experts = self.experts // max(1, world)
         self.expert_lo = rank * self.local_experts
-        self.work = float(self.local_tokens)      # per rank; the bench multiplies by the world size
+        self.units_per_step = float(self.tokens)
         self.expert_bytes = 3 * self.hidden * self.inter // 2 + 3 * self.hidden * self.inter // 16
+        # kernels of this library per step: count(+route), place, FC1, FC2, sum; few slots: route, prepare, quantise,
+        # FC1, FC2, sum; expert-parallel: count(+route), place, wait, FC1, FC2, signal, sum
+        self.launches_per_step = 7 if world > 1 else (5 if self.tokens * self.top_k > 1024 else 6)
 
-    def _quant_experts(self, pkg, rows, k, seed):
+    def supported(self, world):
+        return self.tokens % world == 0 and self.experts % world == 0 and self.tokens >= world
+
+    def config(self, world):
+        return {"workload": self.name, "tokens": self.tokens, "tokens_per_gpu": self.tokens // world,
+                "hidden": self.hidden, "experts": self.experts, "experts_per_gpu": self.experts // world,
+                "top_k": self.top_k, "intermediate": self.inter, "slot_rows": "bf16",
+                "parallelism": ("single GPU" if world == 1 else
+                                f"experts x{world}, tokens x{world}; dispatch / combine as NVLink peer stores inside "
+                                "the kernels, three bounded in-kernel signals per step (no NCCL call in a step)"),
+                "l2": "a 256 MB buffer is rewritten (untimed) between steps to flush the 126 MB L2"}
+
+    def _expert_weights(self, pkg, lo, n):
+        """NVFP4 weights of experts [lo, lo+n): every expert is generated from its own seed, so any rank can
+        rebuild any expert."""
         import torch
         from cutedsl_fully_opensourced_b200.layout import swizzled_sf_numel
-        e = self.local_experts                   # this rank's experts only; they never move
-        codes = torch.empty(e, rows, k // 2, dtype=torch.uint8, device="cuda")
-        sf = torch.empty(e, swizzled_sf_numel(rows, k // 16), dtype=torch.uint8, device="cuda")
-        inv_gs = torch.empty(e, dtype=torch.float32, device="cuda")
-        for i in range(e):
-            g = torch.Generator(device="cuda").manual_seed(seed * 100003 + self.expert_lo + i)
-            w = 0.02 * torch.randn(rows, k, generator=g, device="cuda")
-            c, s, gs = pkg.gemm.quantize_operand(w)
-            codes[i], sf[i], inv_gs[i] = c, s, 1.0 / gs
-        return codes, sf, inv_gs
+        h, i = self.hidden, self.inter
+        out = {}
+        for name, rows, k, seed in (("w1", 2 * i, h, 11), ("w2", h, i, 12)):
+            codes = torch.empty(n, rows, k // 2, dtype=torch.uint8, device="cuda")
+            sf = torch.empty(n, swizzled_sf_numel(rows, k // 16), dtype=torch.uint8, device="cuda")
+            inv_gs = torch.empty(n, dtype=torch.float32, device="cuda")
+            for j in range(n):
+                g = torch.Generator(device="cuda").manual_seed(seed * 100003 + lo + j)
+                w = 0.02 * torch.randn(rows, k, generator=g, device="cuda")
+                c, s, gs = pkg.gemm.quantize_operand(w)
+                codes[j], sf[j], inv_gs[j] = c, s, 1.0 / gs
+            out[name], out[name + "_sf"], out[name + "_alpha"] = codes, sf, inv_gs
+        out["fc2_input_scale"] = torch.ones(1, device="cuda")
+        return out
+
+    def _inputs(self, rank):
+        """Tokens and router logits of one rank's slice (seeded per rank: any rank can rebuild any slice)."""
+        import torch
+        t = self.local_tokens
+        g = torch.Generator(device="cuda").manual_seed(1000 + rank)
+        x = torch.randn(t, self.hidden, generator=g, device="cuda").to(torch.bfloat16)
+        logits = torch.randn(t, self.experts, generator=g, device="cuda")
+        if self.kind == "decode" and rank == 0:
+            n_hot = max(1, -(-self.tokens // 100))
+            logits[:n_hot, 0] += 1e4
+        return x, logits
 
     def setup(self, pkg):
         import torch
         self.pkg = pkg
         t, h, e, k, i = self.local_tokens, self.hidden, self.experts, self.top_k, self.inter
-        self.w1, self.w1_sf, self.a1 = self._quant_experts(pkg, 2 * i, h, 11)
-        self.w2, self.w2_sf, self.a2 = self._quant_experts(pkg, h, i, 12)
-        g = torch.Generator(device="cuda").manual_seed(1000 + self.rank)
-        self.x = torch.randn(t, h, generator=g, device="cuda").to(torch.bfloat16)
-        self.logits = torch.randn(t, e, generator=g, device="cuda")
-        if self.kind == "decode" and self.rank == 0:
-            n_hot = max(1, -(-self.tokens // 100))
-            self.logits[:n_hot, 0] += 1e4
+        self.weights = self._expert_weights(pkg, self.expert_lo, self.local_experts)
+        self.x, self.logits = self._inputs(self.rank)
         self.out = torch.empty(t, h, dtype=torch.bfloat16, device="cuda")
-        self.fc2_scale = torch.ones(1, device="cuda")
-        # per-expert output rows between FC2 and the weighted f32 sum: bf16 (default) or f32
-        self.slot_rows = torch.float32 if os.environ.get("B200FP4_SLOT_ROWS", "bf16") == "f32" else torch.bfloat16
         ids, _ = pkg.topk_route(self.logits, k)
-        active = int(torch.unique(ids).numel())
+        local = (ids >= self.expert_lo) & (ids < self.expert_lo + self.local_experts)
+        # experts of this rank that the WHOLE batch touches are not known to one rank; the roofline uses the
+        # rank's own view at N = 1 and the expectation over uniform routing otherwise
+        if self.world == 1:
+            active = int(torch.unique(ids[local]).numel())
+        else:
+            p_idle = (1.0 - 1.0 / e) ** (self.tokens * k)
+            active = round(self.local_experts * (1.0 - p_idle))
         self.active_experts = active
-        self.alg_bytes = min(active, self.local_experts) * self.expert_bytes + 2 * t * h * 2
+        self.alg_bytes = active * self.expert_bytes + 2 * t * h * 2
         self.ep = None
         if self.world > 1:
-            if os.environ.get("B200FP4_EP", "peer") == "collective":
-                self.ep = pkg.parallel.ExpertParallelMoE(e, k)
-            else:
-                self.ep = pkg.parallel.PeerExpertParallelMoE(e, k, t, h, i)
-            self.weights = {"w1": self.w1, "w1_sf": self.w1_sf, "w2": self.w2, "w2_sf": self.w2_sf,
-                            "w1_alpha": self.a1, "w2_alpha": self.a2, "fc2_input_scale": self.fc2_scale}
-        # L2 flush buffer: the weights of the prefill case (340 MB) exceed L2 by themselves; the decode
-        # cases touch as little as 0.2 GB, so a 256 MB buffer is rewritten between steps (untimed)
-        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if self.alg_bytes < (400 << 20) else None
-
-    def restore(self):
-        if self.flush is not None:
-            self.flush.zero_()
+            self.ep = pkg.parallel.PeerExpertParallelMoE(e, k, t, h, i)
+            self.ep_weights = {"w1": self.weights["w1"], "w1_sf": self.weights["w1_sf"], "w2": self.weights["w2"],
+                               "w2_sf": self.weights["w2_sf"], "w1_alpha": self.weights["w1_alpha"],
+                               "w2_alpha": self.weights["w2_alpha"], "fc2_input_scale": self.weights["fc2_input_scale"]}
+        else:
+            self.wrapper = pkg.B12xMoEWrapper(e, k, h, i, max_num_tokens=t)
+        self.flush = _flush_buffer()
 
     def step(self):
-        ids, wts = self.pkg.topk_route(self.logits, self.top_k)
+        w = self.weights
         if self.ep is not None:
-            self.ep.forward(self.x, ids, wts, self.weights, out=self.out)
+            self.ep.forward(self.x, None, None, self.ep_weights, out=self.out, router_logits=self.logits)
             return
-        self.pkg.b12x_fused_moe(self.x, self.w1, self.w1_sf, self.w2, self.w2_sf, ids, wts, self.experts, self.top_k,
-                                w1_alpha=self.a1, w2_alpha=self.a2, fc2_input_scale=self.fc2_scale, output=self.out,
-                                slot_rows_dtype=self.slot_rows)
-
-    def config(self, world):
-        return {"workload": self.name, "tokens": self.tokens, "hidden": self.hidden, "experts": self.experts,
-                "top_k": self.top_k, "intermediate": self.inter, "active_experts": self.active_experts,
-                "slot_rows": "bf16" if world > 1 or self.slot_rows is not None and "bfloat16" in str(self.slot_rows)
-                else "f32",
-                "parallelism": (f"experts x{world}, tokens x{world}; " + (
-                    "NCCL all-gather of tokens + routing, reduce-scatter of f32 partial outputs"
-                    if os.environ.get("B200FP4_EP", "peer") == "collective" else
-                    "dispatch / combine as NVLink peer loads inside the kernels, two barriers per step")
-                ) if world > 1 else "single GPU",
-                "l2": "weights streamed per step exceed the 126 MB L2" if self.flush is None else
-                      "a 256 MB buffer is rewritten (untimed) between steps to flush the 126 MB L2"}
+        self.wrapper.run(self.x, w["w1"], w["w1_sf"], w["w2"], w["w2_sf"], router_logits=self.logits,
+                         w1_alpha=w["w1_alpha"], w2_alpha=w["w2_alpha"], fc2_input_scale=w["fc2_input_scale"],
+                         output=self.out)
 
     def setup_e2e(self):
         import torch
@@ -425,61 +494,261 @@ class MoeWorkload:
         self.step()
         self.ho.copy_(self.out, non_blocking=True)
 
-    def cpu_run(self, threads: int):
+    def roofline_extra(self):
+        return {"traffic": None, "active_experts": self.active_experts,
+                "flops_per_step": 6.0 * self.local_tokens * self.top_k * self.hidden * self.inter}
+
+    # ---- parity of what is being timed
+    def checks(self, pkg, world, rank):
+        """One untimed step; the ranks' outputs are gathered on rank 0 and compared with the single-GPU operator
+        on the same tokens (must be EQUAL) and with the CPU oracle on a sample of tokens (rel-L2 <= 1e-2)."""
+        import numpy as np
+        import torch
+        import torch.distributed as dist
+        from cutedsl_fully_opensourced_b200.layout import unpack_e2m1, unswizzle_sf
+        from oracle import nvfp4_oracle as O
+        self.step()
+        torch.cuda.synchronize()
+        status = pkg._lib.device_status()
+        mine = self.out.clone()
+        if world > 1:
+            gathered = [torch.empty_like(mine) for _ in range(world)] if rank == 0 else None
+            dist.gather(mine, gathered, dst=0)
+            st = torch.tensor([status], device="cuda")
+            dist.all_reduce(st, op=dist.ReduceOp.MAX)
+            status = int(st.item())
+        else:
+            gathered = [mine]
+        result = None
+        if rank == 0:
+            got = torch.cat(gathered)
+            result = {"device_status": status}
+            xs, ls = zip(*[self._inputs(r) for r in range(world)])
+            x_all, logits_all = torch.cat(xs), torch.cat(ls)
+            ids_all, w_all = pkg.topk_route(logits_all, self.top_k)
+            if world > 1:
+                full = self._expert_weights(pkg, 0, self.experts)
+                single = pkg.b12x_fused_moe(x_all, full["w1"], full["w1_sf"], full["w2"], full["w2_sf"], ids_all, w_all,
+                                            self.experts, self.top_k, w1_alpha=full["w1_alpha"],
+                                            w2_alpha=full["w2_alpha"], fc2_input_scale=full["fc2_input_scale"])
+                torch.cuda.synchronize()
+                result["equals_single_gpu_operator"] = bool(torch.equal(got, single))
+            else:
+                full = self.weights
+            # oracle on a sample of tokens (only their experts are de-quantised on the host)
+            n_s = 4 if self.kind == "prefill" else 2
+            sample = torch.linspace(0, self.tokens - 1, n_s).long().unique()
+            ids_s, w_s = ids_all[sample].cpu(), w_all[sample].cpu()
+            used = sorted(set(ids_s.reshape(-1).tolist()))
+            remap = {e: j for j, e in enumerate(used)}
+            idx = torch.tensor(used, device="cuda")
+            h, i = self.hidden, self.inter
+            w1c = unpack_e2m1(full["w1"][idx]).cpu().numpy()
+            w2c = unpack_e2m1(full["w2"][idx]).cpu().numpy()
+            w1s = unswizzle_sf(full["w1_sf"][idx], 2 * i, h // 16).cpu().numpy()
+            w2s = unswizzle_sf(full["w2_sf"][idx], h, i // 16).cpu().numpy()
+            ids_m = torch.tensor([[remap[int(e)] for e in row] for row in ids_s.tolist()], dtype=torch.int32)
+            ref = O.moe_ref(x_all[sample].cpu(), w1c, w1s, w2c, w2s, ids_m, w_s,
+                            full["w1_alpha"][idx].cpu().numpy(), full["w2_alpha"][idx].cpu().numpy(), 1.0)
+            err = float(torch.linalg.vector_norm(got[sample].cpu().float() - ref.float()) /
+                        torch.linalg.vector_norm(ref.float()))
+            result["oracle_rel_l2_on_sampled_tokens"] = round(err, 6)
+            result["oracle_tokens"] = int(sample.numel())
+            result["ok"] = (status == 0 and err <= 1e-2 and result.get("equals_single_gpu_operator", True))
+            del full
+        return result
+
+    # ---- CPU arm: a bounded sample of the same shape
+    def cpu_setup(self):
         import numpy as np
         import torch
         from oracle import nvfp4_oracle as O
-        torch.set_num_threads(threads)
-        t = min(self.tokens, 64)
-        e = 8                                   # a bounded sample: 64 tokens routed over 8 experts of the same shape
+        # prefill: 64 tokens over 8 experts, top-8; decode (experts of 44 M weights each): up to 8 tokens over 2
+        # experts, top-2, so that a step stays near a second
+        t, e = (min(self.tokens, 64), 8) if self.kind == "prefill" else (min(self.tokens, 8), 2)
         rng = np.random.default_rng(0)
-        w1c = rng.integers(0, 16, size=(e, 2 * self.inter, self.hidden), dtype=np.uint8)
-        w2c = rng.integers(0, 16, size=(e, self.hidden, self.inter), dtype=np.uint8)
-        w1s = rng.integers(0x18, 0x30, size=(e, 2 * self.inter, self.hidden // 16), dtype=np.uint8)
-        w2s = rng.integers(0x18, 0x30, size=(e, self.hidden, self.inter // 16), dtype=np.uint8)
-        x = torch.randn(t, self.hidden).to(torch.bfloat16)
-        ids, wts = O.route_topk_ref(torch.randn(t, e), min(self.top_k, e))
+        self.c_w = (rng.integers(0, 16, size=(e, 2 * self.inter, self.hidden), dtype=np.uint8),
+                    rng.integers(0x18, 0x30, size=(e, 2 * self.inter, self.hidden // 16), dtype=np.uint8),
+                    rng.integers(0, 16, size=(e, self.hidden, self.inter), dtype=np.uint8),
+                    rng.integers(0x18, 0x30, size=(e, self.hidden, self.inter // 16), dtype=np.uint8))
+        self.c_x = torch.randn(t, self.hidden).to(torch.bfloat16)
+        self.c_ids, self.c_wts = O.route_topk_ref(torch.randn(t, e), min(self.top_k, e))
+        self.c_t, self.c_e = t, e
+
+    def cpu_run(self, threads: int):
+        import torch
+        from oracle import nvfp4_oracle as O
+        torch.set_num_threads(threads)
         t0 = time.perf_counter()
-        O.moe_ref(x, w1c, w1s, w2c, w2s, ids, wts)
+        O.moe_ref(self.c_x, *self.c_w, self.c_ids, self.c_wts, weight_key=lambda ex: ex)
         dt = time.perf_counter() - t0
-        return t / dt, dt, (f"{t} tokens over {e} experts of this shape, top-{min(self.top_k, e)}: oracle port "
-                            f"(numpy+torch), {threads} threads")
+        return self.c_t / dt, dt, (f"{self.c_t} tokens over {self.c_e} experts of this shape, top-{min(self.top_k, self.c_e)}: "
+                                   f"oracle port (numpy+torch), {threads} threads")
 
 
-WORKLOADS = {"add_rmsnorm": AddRmsNormWorkload, "gemm": GemmWorkload, "moe_prefill": MoeWorkload,
-             "moe_decode": MoeWorkload}
+def make_parts(rank, world, wanted):
+    table = [
+        ("moe_prefill", lambda: MoePart(rank, world, "prefill")),
+        ("norm_quant", lambda: NormPart(rank, world)),
+        ("gemm_8192", lambda: GemmPart(rank, world, 8192)),
+        ("gemm_m1024", lambda: GemmPart(rank, 1, 1024)),
+        ("gemm_m128", lambda: GemmPart(rank, 1, 128)),
+        ("moe_decode_t64", lambda: MoePart(rank, world, "decode", 64)),
+        ("moe_decode_t8", lambda: MoePart(rank, world, "decode", 8)),
+        ("moe_decode_t1", lambda: MoePart(rank, world, "decode", 1)),
+    ]
+    parts = []
+    for key, make in table:
+        if wanted and key not in wanted:
+            continue
+        if world > 1 and key in ("gemm_m1024", "gemm_m128"):
+            continue                                 # the M sweep is a one-GPU measurement
+        part = make()
+        if part.supported(world):
+            parts.append((key, part))
+    return parts
 
 
 # ---------------------------------------------------------------------------
-def host_threads() -> int:
-    try:
-        return len(os.sched_getaffinity(0))
-    except AttributeError:
-        return os.cpu_count() or 1
-
-
-def run_reference_arm(args, wl):
-    """The reference's CPU golden path for this workload (restated in oracle/), timed on the host cores."""
+# CPU arm
+# ---------------------------------------------------------------------------
+def cpu_part(part, steps, warmup, budget_s):
+    """Time the oracle port: `steps` steps when a step is cheap, otherwise as many as fit the budget (>= 1)."""
     threads = host_threads()
-    vals = []
-    for _ in range(max(0, min(args.warmup, 1))):
-        wl.cpu_run(threads)
-    t_total = 0.0
-    for _ in range(max(1, min(args.steps, 3))):
-        v, dt, sample = wl.cpu_run(threads)
+    part.cpu_setup()
+    for _ in range(min(warmup, 1)):
+        part.cpu_run(threads)
+    vals, times, spent, sample = [], [], 0.0, ""
+    while len(vals) < steps and (not vals or spent + times[-1] <= budget_s):
+        v, dt, sample = part.cpu_run(threads)
         vals.append(v)
-        t_total += dt
+        times.append(dt)
+        spent += dt
     value = statistics.median(vals)
+    return {"value": round(value, 4), "unit": part.unit, "cores": threads, "kind": "port",
+            "sample": f"{sample}; median of {len(vals)} steps", "steps": len(vals), "seconds": round(spent, 2),
+            "ms_per_step": round(1e3 * spent / len(vals), 3)}
+
+
+def run_reference_arm(args, world):
+    """The reference's CPU golden path (restated in oracle/) for every part, timed on the host cores."""
+    parts = make_parts(0, world, args.parts)
+    out, head = {}, None
+    for key, part in parts:
+        budget = 20.0 if key == "moe_prefill" else 6.0
+        res = cpu_part(part, args.steps, args.warmup, budget)
+        res["metric"] = part.metric
+        res["config"] = part.config(world)
+        if head is None:
+            head = (key, part, res)
+        else:
+            out[key] = res
+    key, part, res = head
     line = {
-        "impl": "reference", "metric": wl.metric, "value": round(value, 4), "unit": wl.unit, "n_gpus": args.gpus,
-        "steps": len(vals), "warmup": min(args.warmup, 1), "ms_per_step": round(1e3 * t_total / len(vals), 3),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-        "config": {"workload": wl.name, "device": "host cpu"},
-        "cpu_baseline": {"value": round(value, 4), "unit": wl.unit, "cores": threads, "kind": "port", "sample": sample},
-        "e2e": {"value": round(value, 4), "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "impl": "reference", "metric": part.metric, "value": res["value"], "unit": part.unit, "n_gpus": args.gpus,
+        "steps": res["steps"], "warmup": min(args.warmup, 1), "ms_per_step": res["ms_per_step"],
+        "higher_is_better": True, "scaling": part.scaling, "vs_baseline": None, "dtype": part.dtype,
+        "data": "synthetic", "config": part.config(world),
+        "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": res["value"], "unit": part.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "parts": out,
+        "note": "CPU arm: the oracle port of the reference's torch golden path on the host cores; a step is the bounded "
+                "sample named in cpu_baseline.sample (the full configurations take minutes per step on a CPU)",
     }
     print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def run_part(key, part, pkg, args, rank, world, barrier, sampler, peaks, all_reduce_max):
+    import torch
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+    part.setup(pkg)
+    check = part.checks(pkg, world, rank) if not args.no_checks else None
+    for _ in range(warmup):
+        part.restore()
+        part.step()
+    pkg.synchronize()
+    step_fn, launch = part.step, "eager"
+    graph = None
+    if part.use_graph and not args.no_graph:
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            part.step()
+        step_fn, launch = graph.replay, "cuda graph replay"
+    barrier()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    # untimed pre-roll right behind the barrier: the timed steps do not start on a GPU that idled while ranks met
+    for _ in range(3):
+        part.restore()
+        step_fn()
+    t0 = time.time()
+    for a, b in ev:
+        part.restore()
+        a.record()
+        step_fn()
+        b.record()
+    barrier()
+    t1 = time.time()
+    step_ms = [a.elapsed_time(b) for a, b in ev]
+    status = pkg._lib.device_status()
+    clocks = sampler.window(t0, t1) if sampler is not None else None
+
+    e2e_steps, e2e_ms = min(steps, 10), float("nan")
+    if not args.no_e2e:
+        part.setup_e2e()
+        for _ in range(2):
+            part.step_e2e()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            part.step_e2e()
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1)
+    # per-step maximum over ranks (a step is finished when its slowest rank is)
+    red = all_reduce_max(step_ms + [e2e_ms, float(status)])
+    step_ms_max, e2e_ms, status = red[:steps], red[steps], int(red[steps + 1])
+    total_ms = sum(step_ms_max)
+    res = None
+    if rank == 0:
+        ms_per_step = total_ms / steps
+        scale = {"GB/s": 1e9, "TFLOP/s": 1e12}.get(part.unit, 1.0)
+        value = part.units_per_step / (ms_per_step * 1e-3) / scale
+        k_ms = statistics.mean(step_ms)           # rank 0's own launches
+        if part.bound == "hbm":
+            achieved, peak, roof_unit = part.alg_bytes / (k_ms * 1e-3) / 1e9, peaks["hbm_gbs"], "GB/s"
+            peak_src = f"{peaks['source']} copy bandwidth"
+        else:
+            achieved, peak, roof_unit = part.alg_flops / (k_ms * 1e-3) / 1e12, FP4_NOMINAL_TFLOPS, "TFLOP/s"
+            peak_src = ("nominal dense FP4 (no measured FP4 peak; 4x measured bf16 burst = %.0f TFLOP/s, "
+                        "frac_of_that = %.3f)" % (4 * peaks["bf16_tflops"], achieved / max(1e-9, 4 * peaks["bf16_tflops"])))
+        roof = {"bound": part.bound, "kernel": part.kernel, "achieved": round(achieved, 1), "peak": peak,
+                "peak_source": peak_src, "unit": roof_unit, "frac": round(achieved / peak, 4),
+                "algorithmic_bytes_per_launch": int(part.alg_bytes), "kernel_us": round(k_ms * 1e3, 2),
+                "kernel_us_min": round(min(step_ms) * 1e3, 2)}
+        roof.update(part.roofline_extra())
+        res = {"metric": part.metric, "value": round(value, 2), "unit": part.unit, "ms_per_step": round(ms_per_step, 5),
+               "steps": steps, "step_us": stats_us(step_ms_max), "scaling": part.scaling if world > 1 else "n/a (one GPU)",
+               "config": part.config(world), "launch": launch, "roofline": roof, "clocks": clocks,
+               "gpu_launches": part.launches_per_step * steps * world, "device_status": status, "dtype": part.dtype}
+        if not args.no_e2e:
+            res["e2e"] = {"value": round(part.units_per_step / (e2e_ms / e2e_steps * 1e-3) / scale, 3), "unit": part.unit,
+                          "h2d_bytes_per_step": part.h2d * world, "d2h_bytes_per_step": part.d2h * world,
+                          "steps": e2e_steps}
+        if check is not None:
+            res["checks"] = check
+        if not args.no_cpu_baseline and world == 1:
+            res["cpu_baseline"] = cpu_part(part, 50, 0, 3.0 if key != "moe_prefill" else 6.0)
+    del graph
+    part.free()
+    import gc
+    gc.collect()
+    torch.cuda.empty_cache()
+    return res
 
 
 def main():
@@ -488,41 +757,31 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="add_rmsnorm", choices=sorted(WORKLOADS))
+    ap.add_argument("--parts", default="", help="comma-separated subset of: moe_prefill, norm_quant, gemm_8192, "
+                    "gemm_m1024, gemm_m128, moe_decode_t64, moe_decode_t8, moe_decode_t1 (default: all)")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU arm inside the GPU run")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
-    ap.add_argument("--rows", type=int, default=None, help="override the row count (small profiling cases)")
-    ap.add_argument("--m", type=int, default=None, help="gemm: override M (M-sweep 128 / 1024 / 8192)")
-    ap.add_argument("--nk", type=int, default=None, help="gemm: override N = K (small profiling cases)")
-    ap.add_argument("--tile-n", type=int, default=0, help="gemm: force the 128- or 256-wide tile")
-    ap.add_argument("--cuda-graph", action="store_true",
-                    help="moe, gemm: capture a step in a CUDA graph after warm-up and replay it in the timed region")
-    ap.add_argument("--tokens", type=int, default=None, help="moe: override the token count (decode: 1 / 8 / 64)")
+    ap.add_argument("--no-checks", action="store_true", help="skip the parity check of the MoE parts")
+    ap.add_argument("--no-graph", action="store_true", help="launch the MoE steps eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--tile-n", type=int, default=0, help="gemm parts: force a tile variant (64/128/256/512)")
     args = ap.parse_args()
+    args.parts = [p for p in args.parts.split(",") if p]
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if args.workload == "gemm":
-        nk = args.nk or 8192
-        wl = GemmWorkload(rank, args.m or 8192, nk, nk)
-        wl.tile_n = args.tile_n
-        wl.kernel = {0: "nvfp4_gemm_pair_kernel (256x256 tiles on CTA pairs) for a full wave of such tiles, "
-                        "else nvfp4_gemm_kernel<256|128|64>",
-                     512: "nvfp4_gemm_pair_kernel (256x256 tiles on CTA pairs)"}.get(
-                         args.tile_n, f"nvfp4_gemm_kernel<{args.tile_n}>")
-    elif args.workload.startswith("moe_"):
-        wl = MoeWorkload(rank, args.workload[4:], args.tokens, world)
-    else:
-        wl = WORKLOADS[args.workload](rank)
-    if args.rows and args.workload == "add_rmsnorm":
-        wl.rows = args.rows
-        wl.name += f"_rows{args.rows}"
-        wl.alg_bytes = int(wl.rows * wl.hidden * wl.bytes_per_element)
+
+    # shard_rows without importing the CUDA package (the CPU arm must not need the library)
+    import importlib.util
+    spec = importlib.util.spec_from_file_location(
+        "cutedsl_fully_opensourced_b200_shard", os.path.join(ROOT, "cutedsl-fully-opensourced_b200", "_shard.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    sys.modules["cutedsl_fully_opensourced_b200_shard"] = mod
 
     if args.impl == "reference":
         if rank == 0:
-            run_reference_arm(args, wl)
+            run_reference_arm(args, world)
         return 0
 
     import torch
@@ -539,136 +798,53 @@ def main():
 
     import cutedsl_fully_opensourced_b200 as pkg
     peaks = load_peaks()
-    wl.setup(pkg)
-    warmup = max(3, args.warmup)
-    steps = max(1, args.steps)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-timed steps (inputs resident in HBM)
-    for _ in range(warmup):
-        wl.restore()
-        wl.step()
-    step_fn, launch_mode = wl.step, "eager"
-    if args.cuda_graph and args.workload.startswith("moe_") and (
-            world == 1 or os.environ.get("B200FP4_EP", "peer") != "collective"):
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            wl.step()
-        step_fn, launch_mode = graph.replay, "cuda graph replay"
-    elif args.cuda_graph and args.workload == "gemm":
-        # one graph per rotating operand set (a graph pins its pointers)
-        torch.cuda.synchronize()
-        graphs = []
-        for i in range(wl.sets):
-            wl.i = i
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
-                wl.step()
-            graphs.append(g)
-        turn = [0]
+    def all_reduce_max(values):
+        t = torch.tensor(values, dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return [float(v) for v in t.cpu()]
 
-        def replay_next():
-            graphs[turn[0] % len(graphs)].replay()
-            turn[0] += 1
-        step_fn, launch_mode = replay_next, "cuda graph replay"
-    barrier()
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler is not None:
         sampler.start()
-        time.sleep(0.25)
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
-    barrier()
-    # three untimed pre-roll steps are queued right behind the barrier so that the timed steps do not
-    # start on a GPU that idled (and clocked down) while the ranks met; only the K steps below are timed
-    for _ in range(3):
-        wl.restore()
-        step_fn()
-    t_wall0 = time.time()
-    for a, b in ev:
-        wl.restore()
-        a.record()
-        step_fn()
-        b.record()
-    barrier()
-    t_wall1 = time.time()
-    step_ms = [a.elapsed_time(b) for a, b in ev]
-    total_ms = sum(step_ms)
-    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
-
-    # ---- end to end: host buffers in, host buffers out, copies inside the timed region
-    e2e_steps = min(steps, 10)
-    e2e_ms = float("nan")
-    if not args.no_e2e:
-        wl.setup_e2e()
-        for _ in range(3):
-            wl.step_e2e()
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(e2e_steps):
-            wl.step_e2e()
-        e1.record()
-        barrier()
-        e2e_ms = e0.elapsed_time(e1)
-
-    t = torch.tensor([total_ms, e2e_ms], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms = (float(v) for v in t.cpu())
-
+        time.sleep(0.2)
+    results = {}
+    failed = False
+    for key, part in make_parts(rank, world, args.parts):
+        part.tile_n = args.tile_n
+        res = run_part(key, part, pkg, args, rank, world, barrier, sampler, peaks, all_reduce_max)
+        if rank == 0:
+            results[key] = res
+            if res.get("device_status") or (res.get("checks") or {}).get("ok") is False:
+                failed = True
+    if sampler is not None:
+        sampler.stop()
     if rank == 0:
-        ms_per_step = total_ms / steps
-        scale = {"GB/s": 1e9, "TFLOP/s": 1e12}.get(wl.unit, 1.0)
-        value = wl.work * world / (ms_per_step * 1e-3) / scale
-        e2e_value = wl.work * world / (e2e_ms / e2e_steps * 1e-3) / scale
-        # roofline of the dominant kernel: rank 0's own launches, averaged over the timed region
-        k_ms = statistics.mean(step_ms)
-        achieved = wl.work / (k_ms * 1e-3) / scale
-        roof_unit = wl.unit
-        if wl.unit == "tokens/s":          # roofline of the whole step in bytes streamed from HBM
-            achieved, roof_unit = wl.alg_bytes / (k_ms * 1e-3) / 1e9, "GB/s"
-        if wl.bound == "hbm":
-            peak, peak_src = peaks["hbm_gbs"], peaks["source"]
-        else:
-            peak, peak_src = wl.FP4_NOMINAL_TFLOPS, "nominal dense FP4 (no measured FP4 peak; 4x measured bf16 burst = %.0f)" % (4 * peaks["bf16_tflops"])
+        keys = list(results)
+        head_key = keys[0]
+        head = results.pop(head_key)
         line = {
-            "metric": wl.metric, "value": round(value, 2), "unit": wl.unit, "n_gpus": world, "steps": steps,
-            "warmup": warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": True,
-            "scaling": getattr(wl, "scaling", "weak"),
-            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-            "config": dict(wl.config(world), launch=launch_mode),
-            "e2e": None if args.no_e2e else {
-                "value": round(e2e_value, 3), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d * world,
-                "d2h_bytes_per_step": wl.d2h * world, "steps": e2e_steps},
-            "gpu_launches": wl.launches_per_step * steps * world,
-            "roofline": {"bound": wl.bound, "kernel": wl.kernel, "achieved": round(achieved, 1),
-                         "peak": peak, "peak_source": peak_src, "unit": roof_unit,
-                         "frac": round(achieved / peak, 4),
-                         "traffic": (int(wl.traffic_per_element * wl.rows * wl.hidden)
-                                     if hasattr(wl, "traffic_per_element") else None),
-                         "algorithmic_bytes_per_launch": wl.alg_bytes,
-                         "kernel_us": round(k_ms * 1e3, 2), "kernel_us_min": round(min(step_ms) * 1e3, 2)},
-            "clocks": clocks,
+            "metric": head["metric"], "value": head["value"], "unit": head["unit"], "n_gpus": world,
+            "steps": head["steps"], "warmup": max(3, args.warmup), "ms_per_step": head["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": head["dtype"],
+            "data": "synthetic", "config": head["config"], "launch": head["launch"], "step_us": head["step_us"],
+            "e2e": head.get("e2e"), "gpu_launches": head["gpu_launches"], "roofline": head["roofline"],
+            "clocks": head["clocks"], "device_status": head["device_status"],
         }
-        if not args.no_cpu_baseline and world == 1:
-            threads = host_threads()
-            vals, spent = [], 0.0
-            while spent < 8.0 and len(vals) < 50:          # a bounded sample: about 8 s of wall time on all cores
-                v, dt, sample = wl.cpu_run(threads)
-                vals.append(v)
-                spent += dt
-            line["cpu_baseline"] = {"value": round(statistics.median(vals), 4), "unit": wl.unit, "cores": threads,
-                                    "kind": "port", "sample": f"{sample}; median of {len(vals)} runs",
-                                    "seconds": round(spent, 2)}
+        for opt in ("checks", "cpu_baseline"):
+            if opt in head:
+                line[opt] = head[opt]
+        line["parts"] = results
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
-    return 0
+    return 1 if failed else 0
 
 
 if __name__ == "__main__":

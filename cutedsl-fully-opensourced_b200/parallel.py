@@ -29,27 +29,7 @@ from typing import Callable, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-
-def shard_rows(rows: int, world: int, rank: int, multiple: int = 128) -> Tuple[int, int]:
-    """Contiguous row block of ``rank``: (start, count).  Blocks are multiples of ``multiple`` except that the
-    last ranks may get fewer (or zero) rows when ``rows`` runs out."""
-    if world < 1 or not 0 <= rank < world or rows < 0:
-        raise ValueError("bad rows / world / rank")
-    units = -(-rows // multiple)
-    per, extra = divmod(units, world)
-    start_u = rank * per + min(rank, extra)
-    count_u = per + (1 if rank < extra else 0)
-    start = min(rows, start_u * multiple)
-    end = min(rows, (start_u + count_u) * multiple)
-    return start, end - start
-
-
-def shard_experts(num_experts: int, world: int, rank: int) -> Tuple[int, int]:
-    """Contiguous expert range of ``rank``: (first expert, number of local experts)."""
-    if num_experts % world != 0:
-        raise ValueError(f"{num_experts} experts do not divide over {world} ranks")
-    per = num_experts // world
-    return rank * per, per
+from ._shard import shard_experts, shard_rows  # noqa: F401  (re-exported)
 
 
 class PeerHealth:

@@ -295,8 +295,8 @@ def test_router_inside_the_operator_and_wrapper_object(b200, tokens):
     base = b200.b12x_fused_moe(x, *dev, ids, wts, experts, top_k, w1_alpha=a1)
     fused = b200.b12x_fused_moe(x, *dev, None, None, experts, top_k, w1_alpha=a1, router_logits=logits)
     wrapper = b200.B12xMoEWrapper(experts, top_k, hidden, inter, max_num_tokens=512)
-    before = torch.cuda.memory_allocated()
     out_w = torch.empty(tokens, hidden, dtype=torch.bfloat16, device="cuda")
+    before = torch.cuda.memory_allocated()
     wrapper.run(x, *dev, router_logits=logits, w1_alpha=a1, output=out_w)
     assert torch.cuda.memory_allocated() == before           # run() allocates nothing
     out_ids = wrapper.run(x, *dev, ids, wts, w1_alpha=a1)
