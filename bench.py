@@ -94,7 +94,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.gpu}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
@@ -105,10 +105,13 @@ class ClockSampler:
             self.lines.append((time.time(), line.strip()))
 
     def window(self, t0: float, t1: float):
-        """Summary of the samples taken between two wall-clock times (the sampler keeps running)."""
+        """Summary of the samples taken between two wall-clock times (the sampler keeps running).  A sample reports
+        the clocks of the moment it was taken, and a short timed region falls between two samples, so the window
+        is widened by one sampling period on either side."""
+        time.sleep(0.06)                     # let the samples of the region's end arrive
         sm, mx, reasons, power = [], [], set(), []
         for ts, line in list(self.lines):
-            if ts < t0 - 0.05 or ts > t1 + 0.15:
+            if ts < t0 - 0.03 or ts > t1 + 0.05:
                 continue
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 8:
@@ -299,6 +302,10 @@ class GemmPart(Part):
         self.kernel = ("nvfp4_gemm_pair_kernel (256x256 tiles on CTA pairs) for a full wave of such tiles, else "
                        "nvfp4_gemm_kernel<256|128|64>")
         self.sets = max(3, math.ceil(2 * L2_BYTES / max(1, self.alg_bytes)) + 1)
+        # the small problems take less device time than an eager launch through Python costs on the host: they
+        # are replayed from CUDA graphs (one per operand set); the large ones are launched eagerly
+        self.use_graph = m <= 2048
+        self.graph_variants = self.sets
 
     def supported(self, world):
         return self.m_total % (128 * world) == 0
@@ -666,18 +673,30 @@ def run_part(key, part, pkg, args, rank, world, barrier, sampler, peaks, all_red
     steps, warmup = max(1, args.steps), max(3, args.warmup)
     part.setup(pkg)
     check = part.checks(pkg, world, rank) if not args.no_checks else None
+    # the ranks meet before they step together: rank 0 spent seconds on the check, and the kernels of an
+    # expert-parallel step wait for their peers with a time bound
+    barrier()
     for _ in range(warmup):
         part.restore()
         part.step()
     pkg.synchronize()
     step_fn, launch = part.step, "eager"
-    graph = None
+    graphs = []
     if part.use_graph and not args.no_graph:
+        # one graph per rotating operand set (a graph pins its pointers); the MoE parts have one set
         torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            part.step()
-        step_fn, launch = graph.replay, "cuda graph replay"
+        part.i = 0
+        for _ in range(getattr(part, "graph_variants", 1)):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                part.step()
+            graphs.append(g)
+        turn = [0]
+
+        def replay_next():
+            graphs[turn[0] % len(graphs)].replay()
+            turn[0] += 1
+        step_fn, launch = replay_next, "cuda graph replay"
     barrier()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
     # untimed pre-roll right behind the barrier: the timed steps do not start on a GPU that idled while ranks met
@@ -743,7 +762,7 @@ def run_part(key, part, pkg, args, rank, world, barrier, sampler, peaks, all_red
             res["checks"] = check
         if not args.no_cpu_baseline and world == 1:
             res["cpu_baseline"] = cpu_part(part, 50, 0, 3.0 if key != "moe_prefill" else 6.0)
-    del graph
+    del graphs
     part.free()
     import gc
     gc.collect()

@@ -114,6 +114,27 @@ def synchronize(device=None) -> None:
     raise_on_device_status(device)
 
 
+class _NoGuard:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_GUARD = _NoGuard()
+
+
+def on_device(device):
+    """Context that makes ``device`` current for the C call inside it; free when it already is (switching devices
+    through torch costs several microseconds, more than the launch of a small kernel)."""
+    import torch
+
+    if device.index is None or torch.cuda.current_device() == device.index:
+        return _NO_GUARD
+    return torch.cuda.device(device)
+
+
 def ptr(t) -> int:
     """Device pointer of a torch tensor (or of anything with data_ptr()); None -> NULL."""
     return None if t is None else t.data_ptr()

@@ -296,6 +296,44 @@ struct PeerPtrs {
   uint8_t* p[kMaxPeers];
 };
 
+// ---------------------------------------------------------------------------
+// cross-rank signalling of the expert-parallel kernels
+// ---------------------------------------------------------------------------
+enum CtrlWord : int {
+  kCtrlEpoch = 0,            // completed steps; every kernel of a step signals / waits for epoch + 1
+  kCtrlTicketCount = 1,      // CTAs of the count kernel that have finished
+  kCtrlTicketPlace = 2,
+  kCtrlTicketCombine = 3,
+  kCtrlAbort = 4,            // a cross-rank wait expired
+  kCtrlTicketGemm = 5,       // CTAs of the row-pushing FC2 that have finished
+  kCtrlWords = 16,
+};
+constexpr int kStatusPeerWaitExpired = 16;
+constexpr int kSignalPhases = 3;       // 0: counts published, 1: rows placed, 2: output rows delivered
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// wait until *flag has reached `epoch`; gives up after limit_ns
+__device__ __forceinline__ bool wait_flag(const int* flag, int epoch, unsigned long long limit_ns) {
+  if (ld_acquire_sys(flag) - epoch >= 0) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (;;) {
+    if (ld_acquire_sys(flag) - epoch >= 0) return true;
+    if (globaltimer_ns() - t0 > limit_ns) return false;
+    __nanosleep(64);
+  }
+}
 // offset of scale factor (row m, K-block kb) in the 128x4 tiled layout with rk
 // K-tiles per row tile (python/cutlass_compat/cutlass/utils/blockscaled_layout.py:37-42)
 __device__ __host__ __forceinline__ int64_t sf_swizzled_offset(int64_t m, int kb, int rk) {

@@ -208,10 +208,10 @@ int bounded_wait_selftest(long long limit_cycles, int* gave_up_dev, cudaStream_t
 }
 
 // tc: tensor map of the output for the variants whose tiles leave through TMA stores (others never touch it)
-template <int kBlockN, bool kSwigluB, int kARows = 128, typename Epilogue>
+template <int kBlockN, bool kSwigluB, int kARows = 128, int kEpi = 0, typename Epilogue>
 int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                 const Epilogue& epi, int max_tiles, cudaStream_t stream) {
-  auto kern = nvfp4_gemm_kernel<kBlockN, kSwigluB, Epilogue, kARows>;
+  auto kern = nvfp4_gemm_kernel<kBlockN, kSwigluB, Epilogue, kARows, kEpi>;
   constexpr SmemLayout L = smem_layout<kBlockN, kSwigluB, Epilogue::kOutBytes, kARows>();
   static std::atomic<bool> configured[kMaxDevices];      // per instantiation and device
   int rc_cfg = configure_smem_once(configured, kern, static_cast<int>(L.total));
@@ -219,7 +219,7 @@ int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap&
   int grid = sm_count_of_current_device();
   if (grid > max_tiles) grid = max_tiles;
   if (grid < 1) return kOk;
-  kern<<<grid, gemm_threads(kBlockN, kSwigluB), L.total, stream>>>(ta, tb, tc, p, epi);
+  kern<<<grid, gemm_threads(kBlockN, kSwigluB, kEpi), L.total, stream>>>(ta, tb, tc, p, epi);
   return check_cuda(cudaGetLastError(), "nvfp4_gemm_kernel launch");
 }
 
@@ -364,7 +364,7 @@ int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, v
 int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* w1_sf, void* act_codes, void* act_sf,
                  const float* w1_alpha, const float* fc2_input_scale, const int* num_m_blocks_dev,
                  const int* m_block_expert, const int* m_block_rows, int max_m_blocks, int hidden, int inter,
-                 int experts, int few_rows, int* status, cudaStream_t stream) {
+                 int experts, int few_rows, int* status, cudaStream_t stream, const PeerSync* peer) {
   // few_rows: no row block holds more than 32 rows (the caller knows: at most 32 tokens) -> stages of 32 rows of A
   // Tile width: [up 128 | gate 128] tiles by default.  They have one accumulator, but the epilogue hands it back
   // as soon as it has read its columns (before the SwiGLU arithmetic), and they need half the MMA instructions
@@ -399,6 +399,7 @@ int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* 
   p.m_block_rows = m_block_rows;
   p.status = status;
   p.row_block_major = 1;
+  if (peer != nullptr) p.peer = *peer;
   EpilogueSwiglu epi{static_cast<uint8_t*>(act_codes), static_cast<uint8_t*>(act_sf), w1_alpha, fc2_input_scale, inter};
   if (narrow) {
     p.num_n_blocks = inter / 64;
@@ -406,6 +407,17 @@ int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* 
   }
   if (small_a) return launch_gemm<256, true, 32>(ta, tb, CUtensorMap{}, p, epi, max_m_blocks * p.num_n_blocks, stream);
   return launch_gemm<256, true>(ta, tb, CUtensorMap{}, p, epi, max_m_blocks * p.num_n_blocks, stream);
+}
+
+// Epilogue warps of the 128-wide FC2 tiles (short reductions: three K steps per tile at the prefill shape, so the
+// tile rate is set by how fast accumulators are drained).  B200FP4_FC2_EPI=4|8 overrides the default.
+int fc2_epilogue_warps() {
+  static const int n = [] {
+    const char* e = getenv("B200FP4_FC2_EPI");
+    const int v = e != nullptr ? atoi(e) : 0;
+    return v == 4 || v == 8 ? v : 4;
+  }();
+  return n;
 }
 
 // FC2: partial[row][h] = (Actq . W2[e]^T) * w2_alpha[e], stored as f32 or (rows_bf16) rounded to bf16.
@@ -461,7 +473,7 @@ int gemm_moe_fc2_push(const void* act_codes, const void* act_sf, const void* w2,
                       const int* row_tag, const PeerPtrs& peers, size_t recv_off, const int* abort_flag,
                       const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
                       const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int few_rows,
-                      int* status, cudaStream_t stream) {
+                      int* status, cudaStream_t stream, const PeerSync* peer) {
   CUtensorMap ta, tb;
   const bool wide = hidden % 256 == 0 && (inter + kBlockK - 1) / kBlockK > 4;
   const bool small_a = few_rows != 0 && wide;
@@ -470,6 +482,7 @@ int gemm_moe_fc2_push(const void* act_codes, const void* act_sf, const void* w2,
   rc = make_operand_map(&tb, w2, hidden, inter, experts);
   if (rc) return rc;
   GemmParams p{};
+  if (peer != nullptr) p.peer = *peer;
   p.sfa = static_cast<const uint8_t*>(act_sf);
   p.sfb = static_cast<const uint8_t*>(w2_sf);
   p.m_rows = max_m_blocks * 128;
@@ -492,6 +505,8 @@ int gemm_moe_fc2_push(const void* act_codes, const void* act_sf, const void* w2,
     return launch_gemm<256, false>(ta, tb, CUtensorMap{}, p, epi, max_m_blocks * p.num_n_blocks, stream);
   }
   p.num_n_blocks = (hidden + 127) / 128;
+  if (fc2_epilogue_warps() == 8)
+    return launch_gemm<128, false, 128, 8>(ta, tb, CUtensorMap{}, p, epi, max_m_blocks * p.num_n_blocks, stream);
   return launch_gemm<128, false>(ta, tb, CUtensorMap{}, p, epi, max_m_blocks * p.num_n_blocks, stream);
 }
 

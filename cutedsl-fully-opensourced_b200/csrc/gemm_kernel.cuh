@@ -37,13 +37,13 @@ constexpr int kBlockK = 256;                 // e2m1 elements per stage = 128 by
 // two single-thread roles (TMA, MMA) + the epilogue warps: four for 128-wide tiles (the second
 // accumulator hides the epilogue), eight for 256-wide tiles (one accumulator: drain it twice as fast)
 // (the SwiGLU epilogue is arithmetic-heavy: eight warps at either width)
-__host__ __device__ constexpr int epilogue_warps(int block_n, bool swiglu = false) {
-  return (block_n == 256 || swiglu) ? 8 : 4;
+__host__ __device__ constexpr int epilogue_warps(int block_n, bool swiglu = false, int forced = 0) {
+  return forced != 0 ? forced : ((block_n == 256 || swiglu) ? 8 : 4);
 }
 // ... + four warps (one per 32-lane quarter of tensor memory) that move the scale slabs of every K
 // tile from shared memory into tensor memory
-__host__ __device__ constexpr int gemm_threads(int block_n, bool swiglu = false) {
-  return 64 + 32 * epilogue_warps(block_n, swiglu) + 128;
+__host__ __device__ constexpr int gemm_threads(int block_n, bool swiglu = false, int forced_epi_warps = 0) {
+  return 64 + 32 * epilogue_warps(block_n, swiglu, forced_epi_warps) + 128;
 }
 constexpr uint32_t kTmemCols = 512;
 constexpr long long kWaitLimitCycles = 4000000000LL;   // ~2 s at 2 GHz
@@ -53,6 +53,17 @@ enum GemmStatusBits : int {
   kStatusTimeoutMma = 2,
   kStatusTimeoutEpilogue = 4,
   kStatusRowsExceedTile = 8,    // a few-row launch met a row block with more rows than it loads
+};
+
+struct PeerSync {
+  const int* wait_flags = nullptr;     // this rank's signal words of the phase to wait for, one per source rank
+  int* ctrl = nullptr;                 // control words of the rank's exchange buffer (epoch, tickets, abort)
+  unsigned long long wait_ns = 0;
+  int rank = 0, world = 1;
+  int signal_phase = -1;
+  int ticket = 0;                      // control word that counts finished CTAs
+  size_t flags_off = 0;                // offset of the signal words inside an exchange buffer
+  PeerPtrs peers = {};
 };
 
 struct GemmParams {
@@ -79,6 +90,12 @@ struct GemmParams {
   // and the column blocks of their groups -- for the grouped GEMMs that keeps an expert's weights and its
   // rows in L2 for exactly as long as they are needed.
   int row_block_major;
+  // Expert-parallel launches synchronise with the other ranks inside the kernel instead of through extra
+  // launches.  peer.wait_flags != null: every CTA's producer thread waits (bounded) until the signal words of all
+  // ranks have reached this step before it issues its first load -- the operand rows were written by peers.
+  // peer.signal_phase >= 0: the last CTA to finish raises that signal at every peer (its epilogue stored rows
+  // into their memory).
+  PeerSync peer;
 };
 
 struct SmemLayout {
@@ -160,17 +177,21 @@ struct EpilogueStore {
   // swizzle of the tensor map) and one lane hands them to TMA stores: the accumulator is free as soon as it has
   // been read, and the rows leave as whole lines while the next tile is computed.  Stores from registers put
   // every lane on another output row, which an SM sustains at about 11 bytes per cycle only.
+  // part / parts: with two warps per TMEM quarter each parks and stores half of the tile's boxes
   template <int kBlockN, typename Loader>
   __device__ __forceinline__ void tma_path(const GemmParams& p, int m_blk, int n_blk, int row, float scale,
-                                           Loader&& load, uint8_t* stage, const CUtensorMap* cmap) const {
+                                           Loader&& load, uint8_t* stage, const CUtensorMap* cmap, int part,
+                                           int parts) const {
     constexpr int kBoxCols = 128 / static_cast<int>(sizeof(OutT));     // columns in the 128 bytes of a box row
     constexpr int kBoxes = kBlockN / kBoxCols;
     const int lane = row & 31;
+    const int b_first = part * (kBoxes / parts), b_last = b_first + kBoxes / parts;
     if (lane == 0) ptx::bulk_wait_group_read0();      // the previous tile's stores have read this memory
     __syncwarp();
 #pragma unroll
     for (int b = 0; b < kBoxes; ++b) {
-      uint8_t* box = stage + b * 4096 + lane * 128;
+      if (b < b_first || b >= b_last) continue;
+      uint8_t* box = stage + (b - b_first) * 4096 + lane * 128;
 #pragma unroll
       for (int h = 0; h < kBoxCols / 32; ++h) {
         uint32_t r[32];
@@ -204,9 +225,10 @@ struct EpilogueStore {
       const int y = m_blk * kBlockM + (row & ~31);
 #pragma unroll
       for (int b = 0; b < kBoxes; ++b) {
+        if (b < b_first || b >= b_last) continue;
         const int col = n_blk * kBlockN + b * kBoxCols;
         if (col < p.n_cols && y < p.m_rows)
-          ptx::tma_store_2d(cmap, col * static_cast<int>(sizeof(OutT)), y, ptx::smem_u32(stage + b * 4096));
+          ptx::tma_store_2d(cmap, col * static_cast<int>(sizeof(OutT)), y, ptx::smem_u32(stage + (b - b_first) * 4096));
       }
       ptx::bulk_commit_group();
     }
@@ -220,7 +242,7 @@ struct EpilogueStore {
                                              uint8_t* stage = nullptr, const CUtensorMap* cmap = nullptr) const {
     const float scale = alpha == nullptr ? 1.0f : __ldg(alpha + (alpha_per_group ? group : 0));
     if (stage != nullptr) {
-      tma_path<kBlockN>(p, m_blk, n_blk, row, scale, load, stage, cmap);
+      tma_path<kBlockN>(p, m_blk, n_blk, row, scale, load, stage, cmap, part, parts);
       release();
       return;
     }
@@ -347,10 +369,13 @@ struct EpiloguePushRows {
     const bool live = __ldg(abort_flag) == 0;
     const int tag = (row < rows_valid && live) ? __ldg(row_tag + grow) : -1;
     if constexpr (kBlockN == 128) {
-      // park: 2 boxes of 32 rows x 128 bytes, 16-byte chunks XOR-swizzled by the row (no bank conflicts either way)
+      // park: 2 boxes of 32 rows x 128 bytes, 16-byte chunks XOR-swizzled by the row (no bank conflicts either way);
+      // with two warps per TMEM quarter (parts == 2) each warp parks and sends one box: 128 bytes per row
+      const int b_first = part * (2 / parts), b_last = b_first + 2 / parts;
 #pragma unroll
       for (int b = 0; b < 2; ++b) {
-        uint8_t* box = stage + b * 4096 + lane * 128;
+        if (b < b_first || b >= b_last) continue;
+        uint8_t* box = stage + (b - b_first) * 4096 + lane * 128;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           uint32_t r[32];
@@ -368,12 +393,14 @@ struct EpiloguePushRows {
       }
       release();                                   // the accumulator has been read
       __syncwarp();
-      const int col0 = n_blk * kBlockN;
-      const int c16 = lane & 15;                   // 16-byte chunk of the 256-byte row piece
+      const int lanes_per_row = 16 / parts;        // 16-byte chunks of the warp's piece of a row (256 or 128 bytes)
+      const int rows_per_store = 32 / lanes_per_row;
+      const int col0 = n_blk * kBlockN + b_first * 64;
+      const int c16 = lane % lanes_per_row;
       const bool col_ok = col0 + c16 * 8 < p.n_cols;
 #pragma unroll 4
-      for (int pr = 0; pr < 16; ++pr) {
-        const int r = 2 * pr + (lane >> 4);
+      for (int pr = 0; pr < 32 / rows_per_store; ++pr) {
+        const int r = rows_per_store * pr + lane / lanes_per_row;
         const int t = __shfl_sync(0xffffffffu, tag, r);
         const uint4 v = *reinterpret_cast<const uint4*>(stage + (c16 >> 3) * 4096 + r * 128 + (((c16 & 7) ^ (r & 7)) << 4));
         if (t >= 0 && col_ok) *reinterpret_cast<uint4*>(row_dst(t) + col0 + c16 * 8) = v;
@@ -434,13 +461,9 @@ struct EpilogueSwiglu {
     const int rk2 = (inter + 63) >> 6;
     uint8_t* sf_tile = act_sf + static_cast<int64_t>(m_blk) * rk2 * 512 + (row & 31) * 16 + (row >> 5) * 4;
     const int span = kHalf / parts;
-#pragma unroll 1
-    for (int c0 = part * span; c0 < (part + 1) * span; c0 += 32) {
-      uint32_t up[32], gate[32];
-      load(c0, up);
-      load(kHalf + c0, gate);
-      if (c0 + 32 >= (part + 1) * span) release();      // last read of the accumulator: the arithmetic follows
-      if (j0 + c0 >= inter) continue;
+    // one 32-column group: silu(gate) * up -> bf16 -> NVFP4 (two 16-element blocks), codes and scale bytes out
+    auto finish = [&](int c0, const uint32_t (&up)[32], const uint32_t (&gate)[32]) {
+      if (j0 + c0 >= inter) return;
       uint32_t sfpair = 0;
       uint32_t codes[4];
 #pragma unroll
@@ -461,6 +484,16 @@ struct EpilogueSwiglu {
           make_uint4(codes[0], codes[1], codes[2], codes[3]);
       const int kb = (j0 + c0) >> 4;          // even
       *reinterpret_cast<uint16_t*>(sf_tile + (kb & 3) + (kb >> 2) * 512) = static_cast<uint16_t>(sfpair);
+    };
+    // (Reading the warp's whole share first -- 128 registers -- and releasing the accumulator before any of the
+    // arithmetic was measured slower: 116 against 103 us for FC1 of the prefill shape.)
+#pragma unroll 1
+    for (int c0 = part * span; c0 < (part + 1) * span; c0 += 32) {
+      uint32_t up[32], gate[32];
+      load(c0, up);
+      load(kHalf + c0, gate);
+      if (c0 + 32 >= (part + 1) * span) release();      // last read of the accumulator: the arithmetic follows
+      finish(c0, up, gate);
     }
   }
 };
@@ -469,8 +502,9 @@ struct EpilogueSwiglu {
 // kSwigluB: B tile = two pieces of kBlockN/2 rows (up rows, gate rows); otherwise consecutive 128-row pieces
 // (one 64-row piece for 64-wide tiles).
 // ----------------------------------------------------------------------------
-template <int kBlockN, bool kSwigluB, typename Epilogue, int kARows = 128>
-__global__ void __launch_bounds__(gemm_threads(kBlockN, kSwigluB), 1)
+// kEpi: number of epilogue warps (0 = the default of the tile shape)
+template <int kBlockN, bool kSwigluB, typename Epilogue, int kARows = 128, int kEpi = 0>
+__global__ void __launch_bounds__(gemm_threads(kBlockN, kSwigluB, kEpi), 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_c, const GemmParams p, const Epilogue epi) {
   static_assert(kARows == 128 || (kBlockN == 256 && kARows == 32), "few-row stages exist for 256-wide tiles");
@@ -480,7 +514,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   constexpr int kBPieces = kSwigluB ? 2 : (kBlockN >= 128 ? kBlockN / 128 : 1);
   constexpr int kBPieceRows = kBlockN / kBPieces;               // rows per TMA box of B
   constexpr bool kHalfSlabPieces = kSwigluB && kBPieceRows == 64;   // two 64-row pieces: half a slab each
-  constexpr int kEpiWarps = epilogue_warps(kBlockN, kSwigluB);
+  constexpr int kEpiWarps = epilogue_warps(kBlockN, kSwigluB, kEpi);
   // slab columns per 64-wide K block: one per 32 rows of the tile (64-wide tiles keep their whole slab)
   constexpr uint32_t kSfbColsPerKb = kBlockN >= 128 ? kBlockN / 32 : 4;
   constexpr uint32_t kSfaCol = kAccStages * kBlockN;            // TMEM columns: accumulators first
@@ -546,6 +580,21 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     if (lane == 0) {
       PipeState st;
       bool ok = true;
+      if (p.peer.wait_flags != nullptr && p.peer.world > 1) {
+        // rows of A come from the other ranks: wait for their "rows placed" signals (bounded)
+        const int epoch = *reinterpret_cast<volatile int*>(p.peer.ctrl + kCtrlEpoch) + 1;
+        ok = *reinterpret_cast<volatile int*>(p.peer.ctrl + kCtrlAbort) == 0;
+        for (int r = 0; r < p.peer.world && ok; ++r) {
+          if (r != p.peer.rank && !wait_flag(p.peer.wait_flags + r, epoch, p.peer.wait_ns)) {
+            ok = false;
+            atomicOr(p.status, kStatusPeerWaitExpired);
+            atomicExch(p.peer.ctrl + kCtrlAbort, 1);
+          }
+        }
+        if (!ok) *abort_flag = 1;          // the other roles leave at their next poll
+        // peers wrote the rows with ordinary stores; the loads below go through the async proxy
+        asm volatile("fence.proxy.async;" ::: "memory");
+      }
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int m_blk = tile_m(tile);
         const int n_blk = tile_n(tile);
@@ -737,7 +786,9 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // parking space of the TMA-store variant: 1024-byte aligned, one slice per epilogue warp
         uint8_t* stage = nullptr;
         if constexpr (L.epi_stage_bytes != 0) {
-          const uint32_t off = ((kStages * L.stage_bytes + kBarrierBytes + 1023u) & ~1023u) + (warp - 2) * L.epi_stage_bytes;
+          // four slices of epi_stage_bytes per CTA; with two warps per TMEM quarter each takes half a slice
+          const uint32_t off = ((kStages * L.stage_bytes + kBarrierBytes + 1023u) & ~1023u) +
+                               (warp - 2) * (L.epi_stage_bytes / (kEpiWarps / 4));
           stage = smem_gen + off;
         }
         // the functor calls `release` once, as soon as it has read the accumulator for the last time: the MMAs
@@ -765,6 +816,21 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   // ---- teardown: everybody meets, then the allocating warp frees tensor memory
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if (p.peer.signal_phase >= 0 && p.peer.world > 1 && threadIdx.x == 32) {
+    // this CTA's rows are on their way to the peers; the last CTA to get here tells every rank
+    __threadfence_system();
+    if (atomicAdd(p.peer.ctrl + p.peer.ticket, 1) == static_cast<int>(gridDim.x) - 1) {
+      p.peer.ctrl[p.peer.ticket] = 0;
+      if (*reinterpret_cast<volatile int*>(p.peer.ctrl + kCtrlAbort) == 0) {
+        __threadfence_system();
+        const int epoch = *reinterpret_cast<volatile int*>(p.peer.ctrl + kCtrlEpoch) + 1;
+        for (int r = 0; r < p.peer.world; ++r)
+          if (r != p.peer.rank)
+            st_release_sys(reinterpret_cast<int*>(p.peer.peers.p[r] + p.peer.flags_off) +
+                               p.peer.signal_phase * kMaxPeers + p.peer.rank, epoch);
+      }
+    }
+  }
   if (warp == 0) {
     if (*abort_flag) {
       // a role gave up: let copies that are still in flight land before the CTA's memory is reused

@@ -18,14 +18,14 @@
 // All intermediate buffers live in a caller-provided workspace.
 #include <algorithm>
 
-#include "common.cuh"
+#include "gemm_kernel.cuh"
 
 namespace b200fp4 {
 
 int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* w1_sf, void* act_codes, void* act_sf,
                  const float* w1_alpha, const float* fc2_input_scale, const int* num_m_blocks_dev,
                  const int* m_block_expert, const int* m_block_rows, int max_m_blocks, int hidden, int inter,
-                 int experts, int few_rows, int* status, cudaStream_t stream);
+                 int experts, int few_rows, int* status, cudaStream_t stream, const PeerSync* peer = nullptr);
 int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, void* partial,
                  int rows_bf16, const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
                  const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int few_rows,
@@ -151,17 +151,6 @@ struct MoeHeader {           // all int32, contiguous
 // them are bounded in time: on expiry the kernel sets kStatusPeerWaitExpired in the device status word and the
 // abort word of the buffer, after which no kernel touches peer memory until the host resets the exchange.
 // ---------------------------------------------------------------------------
-enum CtrlWord : int {
-  kCtrlEpoch = 0,            // completed steps; every kernel of a step signals / waits for epoch + 1
-  kCtrlTicketCount = 1,      // CTAs of the count kernel that have finished
-  kCtrlTicketPlace = 2,
-  kCtrlTicketCombine = 3,
-  kCtrlAbort = 4,            // a cross-rank wait expired
-  kCtrlWords = 16,
-};
-constexpr int kStatusPeerWaitExpired = 16;
-constexpr int kSignalPhases = 3;       // 0: counts published, 1: rows placed, 2: output rows delivered
-
 struct Exchange {
   PeerPtrs peers;
   size_t flags, counts_all, xq, xq_sf, row_tag;      // offsets inside a rank's buffer (written by peers)
@@ -169,29 +158,6 @@ struct Exchange {
   unsigned long long wait_ns;
 };
 
-__device__ __forceinline__ int ld_acquire_sys(const int* p) {
-  int v;
-  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release_sys(int* p, int v) {
-  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-// wait until *flag has reached `epoch`; gives up after limit_ns
-__device__ __forceinline__ bool wait_flag(const int* flag, int epoch, unsigned long long limit_ns) {
-  if (ld_acquire_sys(flag) - epoch >= 0) return true;
-  const unsigned long long t0 = globaltimer_ns();
-  for (;;) {
-    if (ld_acquire_sys(flag) - epoch >= 0) return true;
-    if (globaltimer_ns() - t0 > limit_ns) return false;
-    __nanosleep(64);
-  }
-}
 // Threads 0..world-1 of the CTA wait for `phase` of their rank; returns false (to all threads) when a wait
 // expired now or earlier in the step.  The first failure is recorded in the status word.
 __device__ __forceinline__ bool wait_all_ranks(const Exchange& ex, int phase, int* ctrl, int* status, int* s_ok) {
@@ -232,17 +198,41 @@ __device__ __forceinline__ void signal_when_all_ctas_done(const Exchange& ex, in
   if (threadIdx.x == 0) ctrl[ticket] = 0;
 }
 
-// count: one warp per token, four tokens per CTA.  kPerLane > 0: route from logits (experts <= 32 * kPerLane)
-// and write ids / weights; kPerLane == 0: ids are given.
+// count: one warp per token, up to 32 tokens per CTA (fewer when there are few tokens, so that the routing of a
+// small batch still spreads over many SMs).  kPerLane > 0: route from logits (experts <= 32 * kPerLane)
+// and write ids / weights; kPerLane == 0: ids are given.  Positions are claimed in two levels: a histogram of the
+// CTA's slots in shared memory (position inside the CTA's share), then ONE global add per (CTA, expert) that the
+// CTA saw -- thousands of same-address global atomics with a returned value are what made a flat version slow.
+// Dynamic shared memory: 2 * experts_total ints.
+constexpr int kCountTokensPerCta = 32;
+// one warp per token where the router's registers allow 1024 threads (routing four tokens one after the other in
+// a warp was measured at 19 us for 4096 tokens, twice the time of the routing itself)
+__host__ __device__ constexpr int count_threads(int per_lane) { return per_lane <= 8 ? 1024 : 256; }
 template <int kPerLane>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(count_threads(kPerLane))
 moe_count_kernel(const float* __restrict__ logits, int route_experts, int renormalize, const int* __restrict__ ids_in,
                  int* __restrict__ ids_out, float* __restrict__ weights_out, int tokens, int top_k, int expert_lo,
-                 int experts_total, int* my_counts, int* __restrict__ slot_pos, int* ctrl, Exchange ex) {
+                 int experts_total, int* my_counts, int* __restrict__ slot_pos, int* ctrl, Exchange ex,
+                 int tokens_per_cta, uint4* zero_fill, size_t zero_fill_vec16) {
+  const int kCountThreads = blockDim.x;
+  // scale bytes of rows that only pad a 128-row block must read as zero: clear the scale tiles of the FC1 operand
+  // (nobody writes them before this kernel has finished: the place kernels wait for its signal)
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < zero_fill_vec16;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    zero_fill[i] = make_uint4(0u, 0u, 0u, 0u);
+  extern __shared__ int s_dyn[];
+  int* s_hist = s_dyn;
+  int* s_base = s_dyn + experts_total;
+  __shared__ int s_e[kCountTokensPerCta * 64];       // expert of every slot of the CTA (-1: not served here)
+  __shared__ int s_p[kCountTokensPerCta * 64];       // its position among the CTA's slots of that expert
   __shared__ int s_last;
-  const int token = blockIdx.x * 4 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (token < tokens) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int token0 = blockIdx.x * tokens_per_cta;
+  const int n_tokens = min(tokens_per_cta, tokens - token0);
+  for (int e = threadIdx.x; e < experts_total; e += kCountThreads) s_hist[e] = 0;
+  __syncthreads();
+  for (int lt = warp; lt < n_tokens; lt += kCountThreads >> 5) {
+    const int token = token0 + lt;
     if constexpr (kPerLane > 0) {
       int my_id;
       float my_w;
@@ -253,15 +243,28 @@ moe_count_kernel(const float* __restrict__ logits, int route_experts, int renorm
         ids_out[slot] = my_id;
         weights_out[slot] = my_w;
         const int e = my_id - expert_lo;
-        slot_pos[slot] = (e >= 0 && e < experts_total) ? atomicAdd(my_counts + e, 1) : -1;
+        const bool ok = e >= 0 && e < experts_total;
+        s_e[lt * top_k + lane] = ok ? e : -1;
+        s_p[lt * top_k + lane] = ok ? atomicAdd(s_hist + e, 1) : 0;
       }
     } else {
       for (int j = lane; j < top_k; j += 32) {
-        const int64_t slot = static_cast<int64_t>(token) * top_k + j;
-        const int e = ids_in[slot] - expert_lo;
-        slot_pos[slot] = (e >= 0 && e < experts_total) ? atomicAdd(my_counts + e, 1) : -1;
+        const int e = ids_in[static_cast<int64_t>(token) * top_k + j] - expert_lo;
+        const bool ok = e >= 0 && e < experts_total;
+        s_e[lt * top_k + j] = ok ? e : -1;
+        s_p[lt * top_k + j] = ok ? atomicAdd(s_hist + e, 1) : 0;
       }
     }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < experts_total; e += kCountThreads) {
+    const int c = s_hist[e];
+    s_base[e] = c != 0 ? atomicAdd(my_counts + e, c) : 0;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_tokens * top_k; i += kCountThreads) {
+    const int e = s_e[i];
+    slot_pos[static_cast<int64_t>(token0) * top_k + i] = e >= 0 ? s_base[e] + s_p[i] : -1;
   }
   // the last CTA hands the counts to every rank (and clears them for the next step)
   __syncthreads();
@@ -289,7 +292,9 @@ moe_count_kernel(const float* __restrict__ logits, int route_experts, int renorm
 }
 
 // place: see the section comment.  rows_per_block: valid rows that a 128-row block may hold (128, or 32 for the
-// few-row GEMM variants).  Dynamic shared memory: 3 * experts_total ints.
+// few-row GEMM variants).  One warp per token at a time; a lane quantises groups of four adjacent 16-element
+// blocks (128 bytes of the token in flight per lane) and writes, per slot, their 32 bytes of codes and their four
+// scale bytes (adjacent in the 128x4 tiles) with one store each.  Dynamic shared memory: 3 * experts_total ints.
 template <int kThreads>
 __global__ void __launch_bounds__(kThreads)
 moe_quant_place_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids,
@@ -300,10 +305,11 @@ moe_quant_place_kernel(const __nv_bfloat16* __restrict__ x, const int* __restric
   int* s_base = s_dyn;                       // blocks before expert e (over all experts, in expert order)
   int* s_myoff = s_dyn + experts_total;      // rows of lower ranks inside expert e's segment
   int* s_tot = s_dyn + 2 * experts_total;    // rows of expert e over all ranks
-  __shared__ int s_warp[kThreads / 32];
+  constexpr int kWarps = kThreads / 32;
+  __shared__ int s_warp[kWarps];
   __shared__ int s_flag;
-  __shared__ int s_rows[64];
-  __shared__ int s_dst[64];
+  __shared__ int s_rows[kWarps][64];
+  __shared__ int s_dst[kWarps][64];
   if (!wait_all_ranks(ex, 0, ctrl, status, &s_flag)) return;
 
   const int rpb = rows_per_block;
@@ -368,13 +374,12 @@ moe_quant_place_kernel(const __nv_bfloat16* __restrict__ x, const int* __restric
     }
   }
 
-  const int nchunks = hidden >> 4;
-  const int rk = (nchunks + 3) >> 2;
-  const int trips = (nchunks + kThreads - 1) / kThreads;
-  for (int token = blockIdx.x; token < tokens; token += gridDim.x) {
-    __syncthreads();
-    if (threadIdx.x < top_k) {
-      const int64_t slot = static_cast<int64_t>(token) * top_k + threadIdx.x;
+  const int groups = hidden >> 6;            // groups of four 16-element blocks
+  const int rk = groups;                     // 64-wide K tiles of the scale layout
+  for (int token = blockIdx.x * kWarps + warp; token < tokens; token += gridDim.x * kWarps) {
+    __syncwarp();
+    for (int j = lane; j < top_k; j += 32) {
+      const int64_t slot = static_cast<int64_t>(token) * top_k + j;
       const int e = ids[slot] - expert_lo;
       const int pos = slot_pos[slot];
       int row = -1, d = 0;
@@ -385,35 +390,33 @@ moe_quant_place_kernel(const __nv_bfloat16* __restrict__ x, const int* __restric
         if (row >= max_m_blocks * 128) row = -1;
         else reinterpret_cast<int*>(ex.peers.p[d] + ex.row_tag)[row] = (ex.rank << 24) | static_cast<int>(slot);
       }
-      s_rows[threadIdx.x] = row;
-      s_dst[threadIdx.x] = d;
+      s_rows[warp][j] = row;
+      s_dst[warp][j] = d;
       if (slot_row != nullptr) slot_row[slot] = row;
     }
-    __syncthreads();
-    for (int it = 0; it < trips; ++it) {
-      const int chunk = it * kThreads + threadIdx.x;
-      const bool valid = chunk < nchunks;
-      uint32_t lo = 0, hi = 0, sfb = 0;
-      if (valid) {
-        const U32x8 raw = ld_stream_32B(x + static_cast<int64_t>(token) * hidden + chunk * 16);
+    __syncwarp();
+    const __nv_bfloat16* xrow = x + static_cast<int64_t>(token) * hidden;
+    for (int g = lane; g < groups; g += 32) {
+      U32x8 raw[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) raw[c] = ld_stream_32B(xrow + g * 64 + c * 16);
+      U32x8 codes;
+      uint32_t quad = 0;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
         uint64_t v2[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v2[i] = pair16_to_f32x2<__nv_bfloat16>(raw.v[i]);
-        quantize_block16<true>(v2, 1.0f, lo, hi, sfb);
+        for (int i = 0; i < 8; ++i) v2[i] = pair16_to_f32x2<__nv_bfloat16>(raw[c].v[i]);
+        uint32_t sfb;
+        quantize_block16<true>(v2, 1.0f, codes.v[2 * c], codes.v[2 * c + 1], sfb);
+        quad |= (sfb & 0xffu) << (8 * c);
       }
-      // the scale bytes of four consecutive blocks of a row are adjacent in the 128x4 tiles: one 32-bit store
-      uint32_t quad = sfb & 0xffu;
-      quad |= (__shfl_down_sync(0xffffffffu, sfb, 1) & 0xffu) << 8;
-      quad |= (__shfl_down_sync(0xffffffffu, sfb, 2) & 0xffu) << 16;
-      quad |= (__shfl_down_sync(0xffffffffu, sfb, 3) & 0xffu) << 24;
-      if (!valid) continue;
       for (int j = 0; j < top_k; ++j) {
-        const int row = s_rows[j];
+        const int row = s_rows[warp][j];
         if (row < 0) continue;
-        uint8_t* base = ex.peers.p[s_dst[j]];
-        *reinterpret_cast<uint2*>(base + ex.xq + static_cast<int64_t>(row) * (hidden >> 1) + chunk * 8) = make_uint2(lo, hi);
-        if ((chunk & 3) == 0)
-          *reinterpret_cast<uint32_t*>(base + ex.xq_sf + sf_swizzled_offset(row, chunk, rk)) = quad;
+        uint8_t* base = ex.peers.p[s_dst[warp][j]];
+        st_32B(base + ex.xq + static_cast<int64_t>(row) * (hidden >> 1) + g * 32, codes);
+        *reinterpret_cast<uint32_t*>(base + ex.xq_sf + sf_swizzled_offset(row, 4 * g, rk)) = quad;
       }
     }
   }
@@ -705,25 +708,23 @@ MoeWorkspace carve(void* base, int64_t tokens, int hidden, int inter, int expert
 // result), else the caller's ids
 int launch_count(const float* logits, int route_experts, int renormalize, const int* ids_in, int* ids_out,
                  float* weights_out, int tokens, int top_k, int expert_lo, int experts_total, int* my_counts,
-                 int* slot_pos, int* ctrl, const Exchange& ex, cudaStream_t stream) {
-  const dim3 grid((tokens + 3) / 4), block(128);
-  if (logits == nullptr) {
-    moe_count_kernel<0><<<grid, block, 0, stream>>>(nullptr, 0, 0, ids_in, nullptr, nullptr, tokens, top_k, expert_lo,
-                                                    experts_total, my_counts, slot_pos, ctrl, ex);
-  } else if (route_experts <= 64) {
-    moe_count_kernel<2><<<grid, block, 0, stream>>>(logits, route_experts, renormalize, nullptr, ids_out, weights_out,
-                                                    tokens, top_k, expert_lo, experts_total, my_counts, slot_pos, ctrl, ex);
-  } else if (route_experts <= 128) {
-    moe_count_kernel<4><<<grid, block, 0, stream>>>(logits, route_experts, renormalize, nullptr, ids_out, weights_out,
-                                                    tokens, top_k, expert_lo, experts_total, my_counts, slot_pos, ctrl, ex);
-  } else if (route_experts <= 256) {
-    moe_count_kernel<8><<<grid, block, 0, stream>>>(logits, route_experts, renormalize, nullptr, ids_out, weights_out,
-                                                    tokens, top_k, expert_lo, experts_total, my_counts, slot_pos, ctrl, ex);
-  } else {
-    moe_count_kernel<kRouteMaxPerLane><<<grid, block, 0, stream>>>(logits, route_experts, renormalize, nullptr, ids_out,
-                                                                   weights_out, tokens, top_k, expert_lo, experts_total,
-                                                                   my_counts, slot_pos, ctrl, ex);
-  }
+                 int* slot_pos, int* ctrl, const Exchange& ex, void* zero_fill, size_t zero_fill_bytes,
+                 cudaStream_t stream) {
+  const int tpc = tokens >= 4096 ? kCountTokensPerCta : (tokens >= 1024 ? 16 : 8);
+  const dim3 grid((tokens + tpc - 1) / tpc);
+  const size_t smem = sizeof(int) * 2 * experts_total;
+  uint4* zf = static_cast<uint4*>(zero_fill);
+  const size_t zn = zero_fill_bytes / 16;
+#define B200_COUNT(PL)                                                                                             \
+  moe_count_kernel<PL><<<grid, std::min(count_threads(PL), 32 * tpc), smem, stream>>>(                             \
+      logits, route_experts, renormalize, ids_in, ids_out, weights_out, tokens, top_k, expert_lo, experts_total,    \
+      my_counts, slot_pos, ctrl, ex, tpc, zf, zn)
+  if (logits == nullptr) B200_COUNT(0);
+  else if (route_experts <= 64) B200_COUNT(2);
+  else if (route_experts <= 128) B200_COUNT(4);
+  else if (route_experts <= 256) B200_COUNT(8);
+  else B200_COUNT(kRouteMaxPerLane);
+#undef B200_COUNT
   return check_cuda(cudaGetLastError(), "moe_count_kernel launch");
 }
 
@@ -731,17 +732,12 @@ int launch_place(const void* x, const int* ids, const int* slot_pos, const Excha
                  int top_k, int expert_lo, int experts_total, int max_m_blocks, int rows_per_block, int* slot_row,
                  int* num_m_blocks, int* m_block_expert, int* m_block_rows, int* ctrl, int* status,
                  cudaStream_t stream) {
-  const int grid = std::max(1, std::min(tokens, 8 * sm_count_of_current_device()));
+  // eight warps per CTA, one token per warp at a time; enough CTAs that every SM holds several
+  const int grid = std::max(1, std::min((tokens + 7) / 8, 6 * sm_count_of_current_device()));
   const size_t smem = sizeof(int) * 3 * experts_total;
-  if (hidden >= 4096) {
-    moe_quant_place_kernel<256><<<grid, 256, smem, stream>>>(
-        static_cast<const __nv_bfloat16*>(x), ids, slot_pos, ex, tokens, hidden, top_k, expert_lo, experts_total,
-        max_m_blocks, rows_per_block, slot_row, num_m_blocks, m_block_expert, m_block_rows, ctrl, status);
-  } else {
-    moe_quant_place_kernel<128><<<grid, 128, smem, stream>>>(
-        static_cast<const __nv_bfloat16*>(x), ids, slot_pos, ex, tokens, hidden, top_k, expert_lo, experts_total,
-        max_m_blocks, rows_per_block, slot_row, num_m_blocks, m_block_expert, m_block_rows, ctrl, status);
-  }
+  moe_quant_place_kernel<256><<<grid, 256, smem, stream>>>(
+      static_cast<const __nv_bfloat16*>(x), ids, slot_pos, ex, tokens, hidden, top_k, expert_lo, experts_total,
+      max_m_blocks, rows_per_block, slot_row, num_m_blocks, m_block_expert, m_block_rows, ctrl, status);
   return check_cuda(cudaGetLastError(), "moe_quant_place_kernel launch");
 }
 
@@ -815,8 +811,8 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
   const int max_rows = ws.max_m_blocks * 128;
   const int few_rows = moe_few_rows(tokens, top_k);
 
-  B200_CUDA(cudaMemsetAsync(ws.xq_sf, 0, ws.xq_sf_bytes, stream));      // rows that only pad a block read as zero
   if (slots <= 1024) {
+    B200_CUDA(cudaMemsetAsync(ws.xq_sf, 0, ws.xq_sf_bytes, stream));    // rows that only pad a block read as zero
     // few slots: one CTA counts, scans and assigns rows in slot order; quantisation splits a token's columns
     // over several CTAs (a decode step is mostly the latency of these small kernels)
     if (logits != nullptr) {
@@ -842,7 +838,7 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
     ex.world = 1;
     ex.experts_local = experts;
     int rc = launch_count(logits, route_experts, renormalize, ids, ids, route_w, static_cast<int>(tokens), top_k,
-                          expert_lo, experts, ws.my_counts, ws.slot_pos, ws.ctrl, ex, stream);
+                          expert_lo, experts, ws.my_counts, ws.slot_pos, ws.ctrl, ex, ws.xq_sf, ws.xq_sf_bytes, stream);
     if (rc) return rc;
     rc = launch_place(x, ids, ws.slot_pos, ex, static_cast<int>(tokens), hidden, top_k, expert_lo, experts,
                       ws.max_m_blocks, 128, ws.h.slot_row, ws.h.num_m_blocks, ws.h.m_block_expert, ws.h.m_block_rows,
@@ -907,7 +903,7 @@ int gemm_moe_fc2_push(const void* act_codes, const void* act_sf, const void* w2,
                       const int* row_tag, const PeerPtrs& peers, size_t recv_off, const int* abort_flag,
                       const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
                       const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int few_rows,
-                      int* status, cudaStream_t stream);
+                      int* status, cudaStream_t stream, const PeerSync* peer);
 
 namespace {
 
@@ -964,15 +960,6 @@ __global__ void ep_wait_kernel(Exchange ex, int phase, int* ctrl, int* status, i
   __shared__ int s_ok;
   const bool ok = wait_all_ranks(ex, phase, ctrl, status, &s_ok);
   if (!ok && threadIdx.x == 0 && num_m_blocks != nullptr) *num_m_blocks = 0;
-}
-
-// one warp, launched behind kernels that wrote to peer memory: raise `phase` at every peer
-__global__ void ep_signal_kernel(Exchange ex, int phase, int* ctrl) {
-  if (threadIdx.x < ex.world && threadIdx.x != ex.rank && *reinterpret_cast<volatile int*>(ctrl + kCtrlAbort) == 0) {
-    __threadfence_system();
-    const int epoch = *reinterpret_cast<volatile int*>(ctrl + kCtrlEpoch) + 1;
-    st_release_sys(reinterpret_cast<int*>(ex.peers.p[threadIdx.x] + ex.flags) + phase * kMaxPeers + ex.rank, epoch);
-  }
 }
 
 // Weighted sum of the k rows that arrived for each local token (this rank's own memory).  kFew: CTA (token,
@@ -1139,11 +1126,11 @@ int moe_ep_dispatch(const void* x, const int* ids, const float* logits, int rout
   int* ids_buf = reinterpret_cast<int*>(b + L.ids);
   float* w_buf = reinterpret_cast<float*>(b + L.weights);
   if (phases & 1) {
-    // rows that only pad a block must read as zero; peers write into this memory only after this rank's signal 0
-    B200_CUDA(cudaMemsetAsync(b + L.xq_sf, 0, L.xq_sf_bytes, stream));
+    // the count kernel also clears the scale tiles of the FC1 operand (rows that only pad a block must read as
+    // zero); peers write into that memory only after this rank's signal 0, which the same kernel raises at its end
     rc = launch_count(logits, route_experts, renormalize, ids, ids_buf, w_buf, static_cast<int>(tokens_local), top_k, 0,
                       experts_total, reinterpret_cast<int*>(b + L.my_counts), reinterpret_cast<int*>(b + L.slot_pos),
-                      ctrl, ex, stream);
+                      ctrl, ex, b + L.xq_sf, L.xq_sf_bytes, stream);
     if (rc) return rc;
   }
   if (phases & 2) {
@@ -1171,26 +1158,31 @@ int moe_ep_compute(const void* const* peer_buffers, int rank, int world, const v
   if (rc) return rc;
   uint8_t* b = ex.peers.p[rank];
   int* ctrl = reinterpret_cast<int*>(b + L.ctrl);
-  int* num_m_blocks = reinterpret_cast<int*>(b + L.num_m_blocks);
+  const int* num_m_blocks = reinterpret_cast<const int*>(b + L.num_m_blocks);
   const int* m_block_expert = reinterpret_cast<const int*>(b + L.m_block_expert);
   const int* m_block_rows = reinterpret_cast<const int*>(b + L.m_block_rows);
-  if (world > 1) {
-    ep_wait_kernel<<<1, 32, 0, stream>>>(ex, 1, ctrl, status, num_m_blocks);
-    B200_CUDA(cudaGetLastError());
-  }
   const int few_rows = L.rows_per_block == 32;
+  // FC1 waits (inside the kernel, bounded) for the "rows placed" signal of every rank; FC2's last CTA raises
+  // "output rows delivered" at every rank
+  PeerSync sync{};
+  sync.ctrl = ctrl;
+  sync.wait_ns = ex.wait_ns;
+  sync.rank = rank;
+  sync.world = world;
+  sync.flags_off = L.flags;
+  sync.peers = ex.peers;
+  PeerSync fc1_sync = sync;
+  fc1_sync.wait_flags = reinterpret_cast<const int*>(b + L.flags) + 1 * kMaxPeers;
+  PeerSync fc2_sync = sync;
+  fc2_sync.signal_phase = 2;
+  fc2_sync.ticket = kCtrlTicketGemm;
   rc = gemm_moe_fc1(b + L.xq, b + L.xq_sf, w1, w1_sf, b + L.act, b + L.act_sf, w1_alpha, fc2_input_scale, num_m_blocks,
-                    m_block_expert, m_block_rows, L.max_m_blocks, hidden, inter, experts_local, few_rows, status, stream);
+                    m_block_expert, m_block_rows, L.max_m_blocks, hidden, inter, experts_local, few_rows, status, stream,
+                    &fc1_sync);
   if (rc) return rc;
-  rc = gemm_moe_fc2_push(b + L.act, b + L.act_sf, w2, w2_sf, reinterpret_cast<const int*>(b + L.row_tag), ex.peers,
-                         L.recv, ctrl + kCtrlAbort, w2_alpha, num_m_blocks, m_block_expert, m_block_rows,
-                         L.max_m_blocks, hidden, inter, experts_local, few_rows, status, stream);
-  if (rc) return rc;
-  if (world > 1) {
-    ep_signal_kernel<<<1, 32, 0, stream>>>(ex, 2, ctrl);
-    B200_CUDA(cudaGetLastError());
-  }
-  return kOk;
+  return gemm_moe_fc2_push(b + L.act, b + L.act_sf, w2, w2_sf, reinterpret_cast<const int*>(b + L.row_tag), ex.peers,
+                           L.recv, ctrl + kCtrlAbort, w2_alpha, num_m_blocks, m_block_expert, m_block_rows,
+                           L.max_m_blocks, hidden, inter, experts_local, few_rows, status, stream, &fc2_sync);
 }
 
 // ids / weights: the routing of the local tokens; null = what the dispatch computed from logits

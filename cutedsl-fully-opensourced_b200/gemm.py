@@ -95,7 +95,7 @@ def nvfp4_gemm(a: torch.Tensor, b: torch.Tensor, sfa: torch.Tensor, sfb: torch.T
         raise ValueError(f"c must be [{m}, {n}] (x{l}) in float16, bfloat16 or float32")
     if alpha is not None and (alpha.dtype != torch.float32 or not alpha.is_cuda):
         raise ValueError("alpha must be a float32 CUDA tensor")
-    with torch.cuda.device(a.device):
+    with _lib.on_device(a.device):
         _lib.check(_lib.lib.b200fp4_nvfp4_gemm(
             a3.data_ptr(), b3.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), out3.data_ptr(), _lib.ptr(alpha),
             m, n, k, l, _C_CODES[out.dtype], tile_n, _lib.current_stream_ptr(a.device)))

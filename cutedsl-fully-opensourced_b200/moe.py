@@ -65,7 +65,7 @@ def topk_route(router_logits: torch.Tensor, top_k: int, renormalize: bool = True
     t, e = logits.shape
     ids = torch.empty(t, top_k, dtype=torch.int32, device=logits.device)
     w = torch.empty(t, top_k, dtype=torch.float32, device=logits.device)
-    with torch.cuda.device(logits.device):
+    with _lib.on_device(logits.device):
         _lib.check(_lib.lib.b200fp4_topk_route(logits.data_ptr(), ids.data_ptr(), w.data_ptr(), t, e, top_k,
                                                1 if renormalize else 0, _lib.current_stream_ptr(logits.device)))
     return ids, w
@@ -181,7 +181,7 @@ def b12x_fused_moe(
     tail = (_lib.ptr(w1_alpha), _lib.ptr(w2_alpha), _lib.ptr(fc2_input_scale), output.data_ptr(), tokens, hidden,
             inter, local, top_k, int(local_expert_offset), 1 if accumulate else 0, out_code, ws.data_ptr(),
             ws.numel() * ws.element_size(), _lib.current_stream_ptr(dev))
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         if router_logits is None:
             _lib.check(_lib.lib.b200fp4_moe_fused(x.data_ptr(), w1.data_ptr(), s1.data_ptr(), w2.data_ptr(),
                                                   s2.data_ptr(), ids.data_ptr(), scales.data_ptr(), *tail))

@@ -105,7 +105,7 @@ def rmsnorm_fp4quant(
         raise ValueError("global_scale must be a float32 tensor on the input's device")
     if rows == 0:
         return y_fp4, block_scale
-    with torch.cuda.device(input.device):
+    with _lib.on_device(input.device):
         _lib.check(_lib.lib.b200fp4_rmsnorm_fp4quant(
             x2.data_ptr(), weight.contiguous().data_ptr(), y_fp4.data_ptr(), block_scale.data_ptr(), None,
             gs.data_ptr(), float(eps), rows, hidden, x2.stride(0) if rows > 1 else hidden, _DTYPES[input.dtype],
@@ -157,7 +157,7 @@ def add_rmsnorm_fp4quant(
         raise ValueError("global_scale must be a float32 tensor on the input's device")
     if rows == 0:
         return (y_fp4, block_scale, block_scale_unswizzled) if output_both_sf_layouts else (y_fp4, block_scale)
-    with torch.cuda.device(input.device):
+    with _lib.on_device(input.device):
         _lib.check(_lib.lib.b200fp4_add_rmsnorm_fp4quant(
             x2.data_ptr(), r2.data_ptr(), weight.contiguous().data_ptr(), y_fp4.data_ptr(), block_scale.data_ptr(),
             _lib.ptr(block_scale_unswizzled), gs.data_ptr(), float(eps), rows, hidden,

@@ -174,7 +174,7 @@ class PeerExpertParallelMoE:
         """Clear signals, counters and the abort mark (collective: every rank of the group calls it)."""
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
-        with torch.cuda.device(self.device):
+        with self._lib.on_device(self.device):
             self._lib.check(self._lib.lib.b200fp4_moe_ep_reset(self._own_ptr, *self._shape, self.world,
                                                                self._lib.current_stream_ptr(self.device)))
         torch.cuda.synchronize(self.device)
@@ -221,7 +221,7 @@ class PeerExpertParallelMoE:
         stream = self._lib.current_stream_ptr(x.device)
         ms = self.wait_timeout_ms
         routed = router_logits is not None
-        with torch.cuda.device(x.device):
+        with self._lib.on_device(x.device):
             chk(lib.b200fp4_moe_ep_dispatch(
                 x.data_ptr(), None if routed else ids.data_ptr(), self._lib.ptr(router_logits),
                 1 if renormalize else 0, self._peer_array, self.rank, self.world, *self._shape, ms, stream))
@@ -240,7 +240,7 @@ class PeerExpertParallelMoE:
         """(ids, scales) that the last ``forward(..., router_logits=...)`` computed on the GPU."""
         ids = torch.empty(self.tokens_local, self.top_k, dtype=torch.int32, device=self.device)
         w = torch.empty(self.tokens_local, self.top_k, dtype=torch.float32, device=self.device)
-        with torch.cuda.device(self.device):
+        with self._lib.on_device(self.device):
             self._lib.check(self._lib.lib.b200fp4_moe_ep_routing(
                 self._own_ptr, ids.data_ptr(), w.data_ptr(), *self._shape, self.world,
                 self._lib.current_stream_ptr(self.device)))
