@@ -124,6 +124,26 @@ int make_sf_map(CUtensorMap* map, const void* base, int64_t total_bytes) {
   return kOk;
 }
 
+// Row-major scale factors of A: [rows][k / 16] bytes, `pitch` bytes between rows; boxes of 128 rows x 16 bytes (the
+// scale bytes of one 256-wide K step).  Columns beyond k / 16 read as zero.
+int make_sfa_rows_map(CUtensorMap* map, const void* base, int64_t rows, int k, int64_t pitch) {
+  const MapKey key{4, reinterpret_cast<uint64_t>(base), static_cast<uint64_t>(rows), static_cast<uint64_t>(k),
+                   static_cast<uint64_t>(pitch), 0};
+  if (cached_map(key, map)) return kOk;
+  EncodeTiledFn enc = encode_tiled_fn();
+  if (enc == nullptr) return fail(kCudaError, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(k / 16), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch)};
+  cuuint32_t box[2] = {16, 128};
+  cuuint32_t elem[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(kCudaError, "cuTensorMapEncodeTiled (scale rows) failed with CUresult %d", static_cast<int>(r));
+  remember_map(key, *map);
+  return kOk;
+}
+
 std::mutex g_status_mutex;
 int* g_status_word[64] = {};
 
@@ -364,7 +384,9 @@ int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, v
 int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* w1_sf, void* act_codes, void* act_sf,
                  const float* w1_alpha, const float* fc2_input_scale, const int* num_m_blocks_dev,
                  const int* m_block_expert, const int* m_block_rows, int max_m_blocks, int hidden, int inter,
-                 int experts, int few_rows, int* status, cudaStream_t stream, const PeerSync* peer) {
+                 int experts, int few_rows, int* status, cudaStream_t stream, const PeerSync* peer,
+                 int sfa_row_pitch) {
+  // sfa_row_pitch: 0 = xq_sf holds 128x4 tiles; else plain rows of scale bytes with that pitch
   // few_rows: no row block holds more than 32 rows (the caller knows: at most 32 tokens) -> stages of 32 rows of A
   // Tile width: [up 128 | gate 128] tiles by default.  They have one accumulator, but the epilogue hands it back
   // as soon as it has read its columns (before the SwiGLU arithmetic), and they need half the MMA instructions
@@ -400,13 +422,19 @@ int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* 
   p.status = status;
   p.row_block_major = 1;
   if (peer != nullptr) p.peer = *peer;
+  CUtensorMap tsfa{};
+  if (sfa_row_pitch != 0) {
+    rc = make_sfa_rows_map(&tsfa, xq_sf, static_cast<int64_t>(max_m_blocks) * 128, hidden, sfa_row_pitch);
+    if (rc) return rc;
+    p.sfa_row_major = 1;
+  }
   EpilogueSwiglu epi{static_cast<uint8_t*>(act_codes), static_cast<uint8_t*>(act_sf), w1_alpha, fc2_input_scale, inter};
   if (narrow) {
     p.num_n_blocks = inter / 64;
-    return launch_gemm<128, true>(ta, tb, CUtensorMap{}, p, epi, max_m_blocks * p.num_n_blocks, stream);
+    return launch_gemm<128, true>(ta, tb, tsfa, p, epi, max_m_blocks * p.num_n_blocks, stream);
   }
-  if (small_a) return launch_gemm<256, true, 32>(ta, tb, CUtensorMap{}, p, epi, max_m_blocks * p.num_n_blocks, stream);
-  return launch_gemm<256, true>(ta, tb, CUtensorMap{}, p, epi, max_m_blocks * p.num_n_blocks, stream);
+  if (small_a) return launch_gemm<256, true, 32>(ta, tb, tsfa, p, epi, max_m_blocks * p.num_n_blocks, stream);
+  return launch_gemm<256, true>(ta, tb, tsfa, p, epi, max_m_blocks * p.num_n_blocks, stream);
 }
 
 // Epilogue warps of the 128-wide FC2 tiles (short reductions: three K steps per tile at the prefill shape, so the

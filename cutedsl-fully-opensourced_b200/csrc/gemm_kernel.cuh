@@ -90,6 +90,11 @@ struct GemmParams {
   // and the column blocks of their groups -- for the grouped GEMMs that keeps an expert's weights and its
   // rows in L2 for exactly as long as they are needed.
   int row_block_major;
+  // Scale factors of A as plain rows instead of 128x4 tiles: byte [row][k / 16] with sfa_row_pitch bytes between
+  // rows, fetched per stage as a box of 128 rows x 16 bytes through the kernel's third tensor map (tmap_aux, which
+  // is the output map in the variants that store through TMA -- never both).  The MoE front end writes them this
+  // way: a row's scale bytes are then one contiguous run for the writer instead of 4-byte pieces 512 bytes apart.
+  int sfa_row_major;
   // Expert-parallel launches synchronise with the other ranks inside the kernel instead of through extra
   // launches.  peer.wait_flags != null: every CTA's producer thread waits (bounded) until the signal words of all
   // ranks have reached this step before it issues its first load -- the operand rows were written by peers.
@@ -506,7 +511,7 @@ struct EpilogueSwiglu {
 template <int kBlockN, bool kSwigluB, typename Epilogue, int kARows = 128, int kEpi = 0>
 __global__ void __launch_bounds__(gemm_threads(kBlockN, kSwigluB, kEpi), 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                  const __grid_constant__ CUtensorMap tmap_c, const GemmParams p, const Epilogue epi) {
+                  const __grid_constant__ CUtensorMap tmap_aux, const GemmParams p, const Epilogue epi) {
   static_assert(kARows == 128 || (kBlockN == 256 && kARows == 32), "few-row stages exist for 256-wide tiles");
   constexpr SmemLayout L = smem_layout<kBlockN, kSwigluB, Epilogue::kOutBytes, kARows>();
   constexpr int kStages = L.stages;
@@ -556,7 +561,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     ptx::fence_mbar_init();
     ptx::prefetch_tensormap(&tmap_a);
     ptx::prefetch_tensormap(&tmap_b);
-    if (L.epi_stage_bytes != 0 && Epilogue::kUsesOutputMap) ptx::prefetch_tensormap(&tmap_c);
+    if ((L.epi_stage_bytes != 0 && Epilogue::kUsesOutputMap) || p.sfa_row_major) ptx::prefetch_tensormap(&tmap_aux);
   }
   if (warp == 0) {
     __syncwarp();
@@ -625,8 +630,13 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           // the scale slabs go first and report to their own barrier: the movers carry them into tensor
           // memory while the operand tiles are still on their way
           const uint32_t sbar = sf_loaded_bar(st.stage);
-          ptx::mbar_expect_tx(sbar, sf_bytes * (1 + kBPieces));
-          ptx::bulk_load(ssfa, p.sfa + (static_cast<int64_t>(m_blk) * p.rk + 4 * kt) * 512, sf_bytes, sbar);
+          if (p.sfa_row_major) {
+            ptx::mbar_expect_tx(sbar, 2048u + sf_bytes * kBPieces);     // a box always delivers its full size
+            ptx::tma_load_2d(ssfa, &tmap_aux, kt * 16, m_blk * kBlockM, sbar);
+          } else {
+            ptx::mbar_expect_tx(sbar, sf_bytes * (1 + kBPieces));
+            ptx::bulk_load(ssfa, p.sfa + (static_cast<int64_t>(m_blk) * p.rk + 4 * kt) * 512, sf_bytes, sbar);
+          }
 #pragma unroll
           for (int i = 0; i < kBPieces; ++i) {
             const int64_t tile_idx = static_cast<int64_t>(group) * p.b_row_tiles + (b_row[i] >> 7);
@@ -717,10 +727,19 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         const uint8_t* slab = smem_gen + st.stage * L.stage_bytes + L.a_bytes + L.b_bytes + lane * 16;
         const uint32_t t_sf = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + kSfaCol + st.stage * kSfSetCols;
         uint32_t ra[16];
+        if (p.sfa_row_major) {
+          // stage holds [128 rows][16 bytes]: the words of row 32 c + lane are K blocks 0..3 of row group c
 #pragma unroll
-        for (int kb = 0; kb < 4; ++kb) {
-          const uint4 v = *reinterpret_cast<const uint4*>(slab + 512 * kb);
-          ra[4 * kb] = v.x, ra[4 * kb + 1] = v.y, ra[4 * kb + 2] = v.z, ra[4 * kb + 3] = v.w;
+          for (int c = 0; c < 4; ++c) {
+            const uint4 v = *reinterpret_cast<const uint4*>(slab + 512 * c);
+            ra[c] = v.x, ra[4 + c] = v.y, ra[8 + c] = v.z, ra[12 + c] = v.w;
+          }
+        } else {
+#pragma unroll
+          for (int kb = 0; kb < 4; ++kb) {
+            const uint4 v = *reinterpret_cast<const uint4*>(slab + 512 * kb);
+            ra[4 * kb] = v.x, ra[4 * kb + 1] = v.y, ra[4 * kb + 2] = v.z, ra[4 * kb + 3] = v.w;
+          }
         }
         ptx::tmem_st_32x16(t_sf, ra);
         const uint8_t* slab_b = slab + L.sfa_bytes;
@@ -802,7 +821,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                                            ptx::tc_fence_before_sync();
                                            ptx::mbar_arrive(acc_empty_bar(acc.stage));
                                          },
-                                         stage, &tmap_c);
+                                         stage, &tmap_aux);
       } else {
         ptx::tc_fence_before_sync();
         ptx::mbar_arrive(acc_empty_bar(acc.stage));

@@ -25,7 +25,8 @@ namespace b200fp4 {
 int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* w1_sf, void* act_codes, void* act_sf,
                  const float* w1_alpha, const float* fc2_input_scale, const int* num_m_blocks_dev,
                  const int* m_block_expert, const int* m_block_rows, int max_m_blocks, int hidden, int inter,
-                 int experts, int few_rows, int* status, cudaStream_t stream, const PeerSync* peer = nullptr);
+                 int experts, int few_rows, int* status, cudaStream_t stream, const PeerSync* peer = nullptr,
+                 int sfa_row_pitch = 0);
 int gemm_moe_fc2(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, void* partial,
                  int rows_bf16, const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
                  const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int few_rows,
@@ -155,6 +156,7 @@ struct Exchange {
   PeerPtrs peers;
   size_t flags, counts_all, xq, xq_sf, row_tag;      // offsets inside a rank's buffer (written by peers)
   int rank, world, experts_local;
+  int xq_sf_pitch;            // bytes between the rows of scale bytes of the FC1 operand (plain rows, see place)
   unsigned long long wait_ns;
 };
 
@@ -213,13 +215,8 @@ __global__ void __launch_bounds__(count_threads(kPerLane))
 moe_count_kernel(const float* __restrict__ logits, int route_experts, int renormalize, const int* __restrict__ ids_in,
                  int* __restrict__ ids_out, float* __restrict__ weights_out, int tokens, int top_k, int expert_lo,
                  int experts_total, int* my_counts, int* __restrict__ slot_pos, int* ctrl, Exchange ex,
-                 int tokens_per_cta, uint4* zero_fill, size_t zero_fill_vec16) {
+                 int tokens_per_cta) {
   const int kCountThreads = blockDim.x;
-  // scale bytes of rows that only pad a 128-row block must read as zero: clear the scale tiles of the FC1 operand
-  // (nobody writes them before this kernel has finished: the place kernels wait for its signal)
-  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < zero_fill_vec16;
-       i += static_cast<size_t>(gridDim.x) * blockDim.x)
-    zero_fill[i] = make_uint4(0u, 0u, 0u, 0u);
   extern __shared__ int s_dyn[];
   int* s_hist = s_dyn;
   int* s_base = s_dyn + experts_total;
@@ -375,7 +372,6 @@ moe_quant_place_kernel(const __nv_bfloat16* __restrict__ x, const int* __restric
   }
 
   const int groups = hidden >> 6;            // groups of four 16-element blocks
-  const int rk = groups;                     // 64-wide K tiles of the scale layout
   for (int token = blockIdx.x * kWarps + warp; token < tokens; token += gridDim.x * kWarps) {
     __syncwarp();
     for (int j = lane; j < top_k; j += 32) {
@@ -416,7 +412,9 @@ moe_quant_place_kernel(const __nv_bfloat16* __restrict__ x, const int* __restric
         if (row < 0) continue;
         uint8_t* base = ex.peers.p[s_dst[warp][j]];
         st_32B(base + ex.xq + static_cast<int64_t>(row) * (hidden >> 1) + g * 32, codes);
-        *reinterpret_cast<uint32_t*>(base + ex.xq_sf + sf_swizzled_offset(row, 4 * g, rk)) = quad;
+        // scale bytes as plain rows: a warp's 32 groups are 128 contiguous bytes (one write instead of 32 pieces
+        // 512 bytes apart, which is what the 128x4 tiles would ask for; FC1 fetches these rows as they are)
+        *reinterpret_cast<uint32_t*>(base + ex.xq_sf + static_cast<int64_t>(row) * ex.xq_sf_pitch + 4 * g) = quad;
       }
     }
   }
@@ -649,6 +647,17 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 // gets several blocks instead of wrong results.
 inline bool moe_few_rows(int64_t tokens, int top_k) { return tokens <= 32 && tokens * top_k <= 1024; }
 
+// Scale bytes of the FC1 operand.  The general front end writes them as plain rows, sf_row_pitch(hidden) bytes
+// apart (a multiple of 16, as the tensor map wants); the few-slot front end writes 128x4 tiles.  The buffer fits
+// either.  Rows that only pad a 128-row block are never written and never cleared: a row of the accumulator
+// depends on its own row of A and of its scale bytes only, and rows without data are never read back.
+inline int sf_row_pitch(int hidden) { return ((hidden / 16) + 15) / 16 * 16; }
+inline size_t xq_sf_buffer_bytes(int64_t blocks, int hidden) {
+  const size_t tiled = static_cast<size_t>(blocks) * ((hidden + 63) / 64) * 512;
+  const size_t rows = static_cast<size_t>(blocks) * 128 * sf_row_pitch(hidden);
+  return std::max(tiled, rows);
+}
+
 struct MoeWorkspace {
   MoeHeader h;
   int* ctrl;               // [kCtrlWords] + my_counts [experts] right behind it: cleared together at every call
@@ -694,7 +703,7 @@ MoeWorkspace carve(void* base, int64_t tokens, int hidden, int inter, int expert
   w.counts_all = reinterpret_cast<int*>(take(sizeof(int) * experts));
   w.slot_pos = reinterpret_cast<int*>(take(sizeof(int) * slots));
   w.row_tag = reinterpret_cast<int*>(take(sizeof(int) * rows));
-  w.xq_sf_bytes = static_cast<size_t>(blocks) * ((hidden + 63) / 64) * 512;
+  w.xq_sf_bytes = xq_sf_buffer_bytes(blocks, hidden);
   w.xq_sf = take(w.xq_sf_bytes);
   w.xq = take(static_cast<size_t>(rows) * (hidden / 2));
   w.act_sf = take(static_cast<size_t>(blocks) * ((inter + 63) / 64) * 512);
@@ -708,17 +717,14 @@ MoeWorkspace carve(void* base, int64_t tokens, int hidden, int inter, int expert
 // result), else the caller's ids
 int launch_count(const float* logits, int route_experts, int renormalize, const int* ids_in, int* ids_out,
                  float* weights_out, int tokens, int top_k, int expert_lo, int experts_total, int* my_counts,
-                 int* slot_pos, int* ctrl, const Exchange& ex, void* zero_fill, size_t zero_fill_bytes,
-                 cudaStream_t stream) {
+                 int* slot_pos, int* ctrl, const Exchange& ex, cudaStream_t stream) {
   const int tpc = tokens >= 4096 ? kCountTokensPerCta : (tokens >= 1024 ? 16 : 8);
   const dim3 grid((tokens + tpc - 1) / tpc);
   const size_t smem = sizeof(int) * 2 * experts_total;
-  uint4* zf = static_cast<uint4*>(zero_fill);
-  const size_t zn = zero_fill_bytes / 16;
 #define B200_COUNT(PL)                                                                                             \
   moe_count_kernel<PL><<<grid, std::min(count_threads(PL), 32 * tpc), smem, stream>>>(                             \
       logits, route_experts, renormalize, ids_in, ids_out, weights_out, tokens, top_k, expert_lo, experts_total,    \
-      my_counts, slot_pos, ctrl, ex, tpc, zf, zn)
+      my_counts, slot_pos, ctrl, ex, tpc)
   if (logits == nullptr) B200_COUNT(0);
   else if (route_experts <= 64) B200_COUNT(2);
   else if (route_experts <= 128) B200_COUNT(4);
@@ -833,12 +839,13 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
     ex.counts_all = reinterpret_cast<uint8_t*>(ws.counts_all) - base;
     ex.xq = ws.xq - base;
     ex.xq_sf = ws.xq_sf - base;
+    ex.xq_sf_pitch = sf_row_pitch(hidden);
     ex.row_tag = reinterpret_cast<uint8_t*>(ws.row_tag) - base;
     ex.rank = 0;
     ex.world = 1;
     ex.experts_local = experts;
     int rc = launch_count(logits, route_experts, renormalize, ids, ids, route_w, static_cast<int>(tokens), top_k,
-                          expert_lo, experts, ws.my_counts, ws.slot_pos, ws.ctrl, ex, ws.xq_sf, ws.xq_sf_bytes, stream);
+                          expert_lo, experts, ws.my_counts, ws.slot_pos, ws.ctrl, ex, stream);
     if (rc) return rc;
     rc = launch_place(x, ids, ws.slot_pos, ex, static_cast<int>(tokens), hidden, top_k, expert_lo, experts,
                       ws.max_m_blocks, 128, ws.h.slot_row, ws.h.num_m_blocks, ws.h.m_block_expert, ws.h.m_block_rows,
@@ -848,7 +855,7 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
   B200_CUDA(cudaGetLastError());
   int rc = gemm_moe_fc1(ws.xq, ws.xq_sf, w1, w1_sf, ws.act, ws.act_sf, w1_alpha, fc2_input_scale, ws.h.num_m_blocks,
                         ws.h.m_block_expert, ws.h.m_block_rows, ws.max_m_blocks, hidden, inter, experts, few_rows,
-                        status, stream);
+                        status, stream, nullptr, slots <= 1024 ? 0 : sf_row_pitch(hidden));
   if (rc) return rc;
   rc = gemm_moe_fc2(ws.act, ws.act_sf, w2, w2_sf, ws.partial, rows_bf16, w2_alpha, ws.h.num_m_blocks, ws.h.m_block_expert,
                     ws.h.m_block_rows, ws.max_m_blocks, hidden, inter, experts, few_rows, status, stream);
@@ -913,7 +920,7 @@ struct EpLayout {
   // private to the rank
   size_t ctrl, my_counts, slot_pos, ids, weights, num_m_blocks, m_block_expert, m_block_rows, act_sf, act;
   size_t xq_sf_bytes, total;
-  int max_m_blocks, rows_per_block;
+  int max_m_blocks, rows_per_block, xq_sf_pitch;
 };
 
 EpLayout ep_layout(int64_t tokens_local, int hidden, int inter, int experts_local, int top_k, int world) {
@@ -934,7 +941,8 @@ EpLayout ep_layout(int64_t tokens_local, int hidden, int inter, int experts_loca
   };
   L.flags = take(sizeof(int) * kSignalPhases * kMaxPeers);
   L.counts_all = take(sizeof(int) * world * experts_total);
-  L.xq_sf_bytes = static_cast<size_t>(blocks) * ((hidden + 63) / 64) * 512;
+  L.xq_sf_pitch = sf_row_pitch(hidden);
+  L.xq_sf_bytes = xq_sf_buffer_bytes(blocks, hidden);
   L.xq_sf = take(L.xq_sf_bytes);
   L.xq = take(static_cast<size_t>(rows) * (hidden / 2));
   L.row_tag = take(sizeof(int) * rows);
@@ -1065,6 +1073,7 @@ int ep_exchange(const void* const* peer_buffers, int rank, int world, int expert
   ex->counts_all = L.counts_all;
   ex->xq = L.xq;
   ex->xq_sf = L.xq_sf;
+  ex->xq_sf_pitch = L.xq_sf_pitch;
   ex->row_tag = L.row_tag;
   ex->rank = rank;
   ex->world = world;
@@ -1126,11 +1135,9 @@ int moe_ep_dispatch(const void* x, const int* ids, const float* logits, int rout
   int* ids_buf = reinterpret_cast<int*>(b + L.ids);
   float* w_buf = reinterpret_cast<float*>(b + L.weights);
   if (phases & 1) {
-    // the count kernel also clears the scale tiles of the FC1 operand (rows that only pad a block must read as
-    // zero); peers write into that memory only after this rank's signal 0, which the same kernel raises at its end
     rc = launch_count(logits, route_experts, renormalize, ids, ids_buf, w_buf, static_cast<int>(tokens_local), top_k, 0,
                       experts_total, reinterpret_cast<int*>(b + L.my_counts), reinterpret_cast<int*>(b + L.slot_pos),
-                      ctrl, ex, b + L.xq_sf, L.xq_sf_bytes, stream);
+                      ctrl, ex, stream);
     if (rc) return rc;
   }
   if (phases & 2) {
@@ -1178,7 +1185,7 @@ int moe_ep_compute(const void* const* peer_buffers, int rank, int world, const v
   fc2_sync.ticket = kCtrlTicketGemm;
   rc = gemm_moe_fc1(b + L.xq, b + L.xq_sf, w1, w1_sf, b + L.act, b + L.act_sf, w1_alpha, fc2_input_scale, num_m_blocks,
                     m_block_expert, m_block_rows, L.max_m_blocks, hidden, inter, experts_local, few_rows, status, stream,
-                    &fc1_sync);
+                    &fc1_sync, L.xq_sf_pitch);
   if (rc) return rc;
   return gemm_moe_fc2_push(b + L.act, b + L.act_sf, w2, w2_sf, reinterpret_cast<const int*>(b + L.row_tag), ex.peers,
                            L.recv, ctrl + kCtrlAbort, w2_alpha, num_m_blocks, m_block_expert, m_block_rows,
