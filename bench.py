@@ -19,7 +19,8 @@ seeded synthetic inputs that are already resident in HBM, and prints ONE JSON li
 A "step" is one pass of a part over its batch.  Steps are timed one by one with CUDA events on the launching
 stream (median / p10 / p90 / min are reported; the value uses the mean), after >= 3 warm-up steps, as the
 maximum over ranks.  ``e2e`` is the same step through the public Python API with host buffers: the host->device
-copy of the inputs and the device->host copy of the result are inside the timed region.  ``roofline`` compares
+copy of the inputs and the device->host copy of the result are inside the timed region (two buffer sets, so that
+the copies of neighbouring steps overlap the kernels of the current one, as in a serving loop).  ``roofline`` compares
 algorithmic bytes (or flops) per step with the measured peaks of MEASURED_PEAKS.json.  ``cpu_baseline`` is the
 oracle port of the reference's CPU golden path timed on the host cores over a bounded sample.
 ``--impl reference`` prints that CPU arm alone, for the same parts.
@@ -236,21 +237,24 @@ class NormPart(Part):
         import torch
         self.hx = self.xs[0].cpu().pin_memory()
         self.hr = self.r0.cpu().pin_memory()
-        self.hy = torch.empty(self.ys[0].shape, dtype=torch.uint8).pin_memory()
-        self.hsf = torch.empty(self.sfs[0].shape, dtype=torch.uint8).pin_memory()
-        self.hres = torch.empty(self.rs[0].shape, dtype=torch.bfloat16).pin_memory()
+        self.hy = [torch.empty(self.ys[0].shape, dtype=torch.uint8).pin_memory() for _ in range(2)]
+        self.hsf = [torch.empty(self.sfs[0].shape, dtype=torch.uint8).pin_memory() for _ in range(2)]
+        self.hres = [torch.empty(self.rs[0].shape, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
         self.h2d = self.hx.numel() * 2 + self.hr.numel() * 2
-        self.d2h = self.hy.numel() + self.hsf.numel() + self.hres.numel() * 2
+        self.d2h = self.hy[0].numel() + self.hsf[0].numel() + self.hres[0].numel() * 2
 
-    def step_e2e(self):
-        x, r, y, sf = self.xs[0], self.rs[0], self.ys[0], self.sfs[0]
-        x.copy_(self.hx, non_blocking=True)
-        r.copy_(self.hr, non_blocking=True)
-        self.pkg.add_rmsnorm_fp4quant(x, r, self.w, y, sf, global_scale=self.gs, eps=1e-6, block_size=16,
-                                      is_sf_swizzled_layout=True)
-        self.hy.copy_(y, non_blocking=True)
-        self.hsf.copy_(sf, non_blocking=True)
-        self.hres.copy_(r, non_blocking=True)
+    def e2e_h2d(self, b):
+        self.xs[b].copy_(self.hx, non_blocking=True)
+        self.rs[b].copy_(self.hr, non_blocking=True)
+
+    def e2e_compute(self, b):
+        self.pkg.add_rmsnorm_fp4quant(self.xs[b], self.rs[b], self.w, self.ys[b], self.sfs[b], global_scale=self.gs,
+                                      eps=1e-6, block_size=16, is_sf_swizzled_layout=True)
+
+    def e2e_d2h(self, b):
+        self.hy[b].copy_(self.ys[b], non_blocking=True)
+        self.hsf[b].copy_(self.sfs[b], non_blocking=True)
+        self.hres[b].copy_(self.rs[b], non_blocking=True)
 
     def roofline_extra(self):
         return {"traffic": int(self.traffic_per_element * self.rows * self.hidden)}
@@ -342,16 +346,20 @@ class GemmPart(Part):
         import torch
         aq, bq, sfa, sfb, alpha, c = self.ops[0]
         self.h = [t.cpu().pin_memory() for t in (aq, bq, sfa, sfb)]
-        self.hc = torch.empty(c.shape, dtype=c.dtype).pin_memory()
+        self.hc = [torch.empty(c.shape, dtype=c.dtype).pin_memory() for _ in range(2)]
         self.h2d = sum(t.numel() * t.element_size() for t in self.h)
-        self.d2h = self.hc.numel() * 2
+        self.d2h = self.hc[0].numel() * 2
 
-    def step_e2e(self):
-        aq, bq, sfa, sfb, alpha, c = self.ops[0]
-        for d, h in zip((aq, bq, sfa, sfb), self.h):
+    def e2e_h2d(self, b):
+        for d, h in zip(self.ops[b][:4], self.h):
             d.copy_(h, non_blocking=True)
+
+    def e2e_compute(self, b):
+        aq, bq, sfa, sfb, alpha, c = self.ops[b]
         self.pkg.nvfp4_gemm(aq, bq, sfa, sfb, alpha=alpha, out=c, tile_n=self.tile_n)
-        self.hc.copy_(c, non_blocking=True)
+
+    def e2e_d2h(self, b):
+        self.hc[b].copy_(self.ops[b][5], non_blocking=True)
 
     def roofline_extra(self):
         return {"traffic": None}
@@ -478,28 +486,38 @@ class MoePart(Part):
             self.wrapper = pkg.B12xMoEWrapper(e, k, h, i, max_num_tokens=t)
         self.flush = _flush_buffer()
 
-    def step(self):
+    def step(self, x=None, logits=None, out=None):
         w = self.weights
+        x = self.x if x is None else x
+        logits = self.logits if logits is None else logits
+        out = self.out if out is None else out
         if self.ep is not None:
-            self.ep.forward(self.x, None, None, self.ep_weights, out=self.out, router_logits=self.logits)
+            self.ep.forward(x, None, None, self.ep_weights, out=out, router_logits=logits)
             return
-        self.wrapper.run(self.x, w["w1"], w["w1_sf"], w["w2"], w["w2_sf"], router_logits=self.logits,
+        self.wrapper.run(x, w["w1"], w["w1_sf"], w["w2"], w["w2_sf"], router_logits=logits,
                          w1_alpha=w["w1_alpha"], w2_alpha=w["w2_alpha"], fc2_input_scale=w["fc2_input_scale"],
-                         output=self.out)
+                         output=out)
 
     def setup_e2e(self):
         import torch
         self.hx = self.x.cpu().pin_memory()
         self.hl = self.logits.cpu().pin_memory()
-        self.ho = torch.empty(self.out.shape, dtype=torch.bfloat16).pin_memory()
+        self.ho = [torch.empty(self.out.shape, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        self.ex = [self.x, torch.empty_like(self.x)]
+        self.el = [self.logits, torch.empty_like(self.logits)]
+        self.eo = [self.out, torch.empty_like(self.out)]
         self.h2d = self.hx.numel() * 2 + self.hl.numel() * 4
-        self.d2h = self.ho.numel() * 2
+        self.d2h = self.ho[0].numel() * 2
 
-    def step_e2e(self):
-        self.x.copy_(self.hx, non_blocking=True)
-        self.logits.copy_(self.hl, non_blocking=True)
-        self.step()
-        self.ho.copy_(self.out, non_blocking=True)
+    def e2e_h2d(self, b):
+        self.ex[b].copy_(self.hx, non_blocking=True)
+        self.el[b].copy_(self.hl, non_blocking=True)
+
+    def e2e_compute(self, b):
+        self.step(self.ex[b], self.el[b], self.eo[b])
+
+    def e2e_d2h(self, b):
+        self.ho[b].copy_(self.eo[b], non_blocking=True)
 
     def roofline_extra(self):
         return {"traffic": None, "active_experts": self.active_experts,
@@ -593,13 +611,13 @@ class MoePart(Part):
                                    f"oracle port (numpy+torch), {threads} threads")
 
 
-def make_parts(rank, world, wanted):
+def make_parts(rank, world, wanted, nk=8192):
     table = [
         ("moe_prefill", lambda: MoePart(rank, world, "prefill")),
         ("norm_quant", lambda: NormPart(rank, world)),
-        ("gemm_8192", lambda: GemmPart(rank, world, 8192)),
-        ("gemm_m1024", lambda: GemmPart(rank, 1, 1024)),
-        ("gemm_m128", lambda: GemmPart(rank, 1, 128)),
+        ("gemm_8192", lambda: GemmPart(rank, world, nk, nk, nk)),
+        ("gemm_m1024", lambda: GemmPart(rank, 1, 1024, nk, nk)),
+        ("gemm_m128", lambda: GemmPart(rank, 1, 128, nk, nk)),
         ("moe_decode_t64", lambda: MoePart(rank, world, "decode", 64)),
         ("moe_decode_t8", lambda: MoePart(rank, world, "decode", 8)),
         ("moe_decode_t1", lambda: MoePart(rank, world, "decode", 1)),
@@ -639,7 +657,7 @@ def cpu_part(part, steps, warmup, budget_s):
 
 def run_reference_arm(args, world):
     """The reference's CPU golden path (restated in oracle/) for every part, timed on the host cores."""
-    parts = make_parts(0, world, args.parts)
+    parts = make_parts(0, world, args.parts, args.nk)
     out, head = {}, None
     for key, part in parts:
         budget = 20.0 if key == "moe_prefill" else 6.0
@@ -668,6 +686,48 @@ def run_reference_arm(args, world):
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
+class E2EPipeline:
+    """The end-to-end leg as a serving loop would run it: every step copies its inputs from pinned host memory,
+    computes through the public API and copies its result back, all inside the timed region; two buffer sets let
+    the copies of neighbouring steps (separate copy streams, both DMA directions) overlap the kernels of the
+    current one.  A step's kernels start only when its own inputs have landed, and a buffer set is reused only
+    when the step that used it two steps earlier has delivered its result."""
+
+    def __init__(self, part):
+        import torch
+        self.torch, self.part, self.i = torch, part, 0
+        self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        self.ev_in = [torch.cuda.Event() for _ in range(2)]
+        self.ev_cmp = [torch.cuda.Event() for _ in range(2)]
+        self.ev_out = [torch.cuda.Event() for _ in range(2)]
+
+    def step(self):
+        torch, part, b = self.torch, self.part, self.i % 2
+        cur = torch.cuda.current_stream()
+        if self.i < 2:
+            self.s_in.wait_stream(cur)
+        with torch.cuda.stream(self.s_in):
+            if self.i >= 2:
+                self.s_in.wait_event(self.ev_cmp[b])      # the kernels that read this input set have finished
+            part.e2e_h2d(b)
+            self.ev_in[b].record(self.s_in)
+        cur.wait_event(self.ev_in[b])
+        if self.i >= 2:
+            cur.wait_event(self.ev_out[b])                # this set's previous result has left the device
+        part.e2e_compute(b)
+        self.ev_cmp[b].record(cur)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(self.ev_cmp[b])
+            part.e2e_d2h(b)
+            self.ev_out[b].record(self.s_out)
+        self.i += 1
+
+    def drain(self):
+        cur = self.torch.cuda.current_stream()
+        for ev in self.ev_out[:min(2, self.i)]:
+            cur.wait_event(ev)
+
+
 def run_part(key, part, pkg, args, rank, world, barrier, sampler, peaks, all_reduce_max):
     import torch
     steps, warmup = max(1, args.steps), max(3, args.warmup)
@@ -718,13 +778,16 @@ def run_part(key, part, pkg, args, rank, world, barrier, sampler, peaks, all_red
     e2e_steps, e2e_ms = min(steps, 10), float("nan")
     if not args.no_e2e:
         part.setup_e2e()
+        pipe = E2EPipeline(part)
         for _ in range(2):
-            part.step_e2e()
+            pipe.step()
+        pipe.drain()
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(e2e_steps):
-            part.step_e2e()
+            pipe.step()
+        pipe.drain()
         e1.record()
         barrier()
         e2e_ms = e0.elapsed_time(e1)
@@ -783,6 +846,8 @@ def main():
     ap.add_argument("--no-checks", action="store_true", help="skip the parity check of the MoE parts")
     ap.add_argument("--no-graph", action="store_true", help="launch the MoE steps eagerly instead of replaying a CUDA graph")
     ap.add_argument("--tile-n", type=int, default=0, help="gemm parts: force a tile variant (64/128/256/512)")
+    ap.add_argument("--nk", type=int, default=8192, help="gemm parts: N = K (and M of gemm_8192); smaller values are "
+                    "for profiler captures of a small case")
     args = ap.parse_args()
     args.parts = [p for p in args.parts.split(",") if p]
 
@@ -835,7 +900,7 @@ def main():
         time.sleep(0.2)
     results = {}
     failed = False
-    for key, part in make_parts(rank, world, args.parts):
+    for key, part in make_parts(rank, world, args.parts, args.nk):
         part.tile_n = args.tile_n
         res = run_part(key, part, pkg, args, rank, world, barrier, sampler, peaks, all_reduce_max)
         if rank == 0:

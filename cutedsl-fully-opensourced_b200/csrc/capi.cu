@@ -31,7 +31,8 @@ int norm_fp4quant_launch(const void* x, void* residual, const void* weight, void
                          cudaStream_t stream);
 
 int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha, int m, int n,
-               int k, int l, int c_dtype, int tile_n, cudaStream_t stream);
+               int k, int l, int c_dtype, int tile_n, void* workspace, size_t workspace_bytes, cudaStream_t stream);
+size_t gemm_workspace_bytes(int m, int n, int k);
 int device_status_word(int** out);
 int route_topk(const float* logits, int* ids, float* weights, int tokens, int experts, int top_k, int renormalize,
                cudaStream_t stream);
@@ -91,7 +92,19 @@ int b200fp4_add_rmsnorm_fp4quant(const void* x, void* residual, const void* weig
 
 int b200fp4_nvfp4_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha,
                        int m, int n, int k, int l, int c_dtype, int tile_n, void* stream) {
-  return gemm_dense(a, b, sfa, sfb, c, alpha, m, n, k, l, c_dtype, tile_n, static_cast<cudaStream_t>(stream));
+  return gemm_dense(a, b, sfa, sfb, c, alpha, m, n, k, l, c_dtype, tile_n, nullptr, 0, static_cast<cudaStream_t>(stream));
+}
+
+size_t b200fp4_nvfp4_gemm_workspace_bytes(int m, int n, int k) {
+  if (m <= 0 || n <= 0 || k <= 0) return 0;
+  return gemm_workspace_bytes(m, n, k);
+}
+
+int b200fp4_nvfp4_gemm_ws(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha,
+                          int m, int n, int k, int l, int c_dtype, int tile_n, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  return gemm_dense(a, b, sfa, sfb, c, alpha, m, n, k, l, c_dtype, tile_n, workspace, workspace_bytes,
+                    static_cast<cudaStream_t>(stream));
 }
 
 int b200fp4_topk_route(const float* logits, int* ids, float* weights, int tokens, int experts, int top_k,

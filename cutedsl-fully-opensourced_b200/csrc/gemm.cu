@@ -1,6 +1,7 @@
 // Host side of the NVFP4 GEMM family: tensor-map construction, launch
 // configuration and argument checks for the dense block-scaled GEMM and the
 // two grouped GEMMs of the fused MoE.  The device code is in gemm_kernel.cuh.
+#include <algorithm>
 #include <atomic>
 #include <cstdlib>
 #include <cstring>
@@ -291,6 +292,84 @@ int gemm_dense_pair(const void* a, const void* b, const void* sfa, const void* s
 }
 
 // ---------------------------------------------------------------------------
+// split-K: few output tiles against a long weight stream (M = 128, N = K = 8192: 32 tiles of 128 x 256 for 148 SMs).
+// The K tiles of every output tile are dealt to `splits` work items that run on different CTAs at the same time and
+// write f32 partial matrices into a caller-provided workspace; this kernel sums them (slice order, so the result
+// does not depend on timing), applies alpha and rounds once.
+// ---------------------------------------------------------------------------
+template <typename OutT>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, int splits, int64_t stride,
+                                     const float* __restrict__ alpha, OutT* __restrict__ c, int64_t n4) {
+  const float scale = alpha == nullptr ? 1.0f : __ldg(alpha);
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    float4 acc = *reinterpret_cast<const float4*>(partial + 4 * i);
+    for (int s = 1; s < splits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(partial + s * stride + 4 * i);
+      acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+    }
+    acc.x *= scale, acc.y *= scale, acc.z *= scale, acc.w *= scale;
+    if constexpr (sizeof(OutT) == 4) {
+      *reinterpret_cast<float4*>(c + 4 * i) = acc;
+    } else {
+      uint2 packed;
+      packed.x = Pair16<OutT>::pack(acc.x, acc.y);
+      packed.y = Pair16<OutT>::pack(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(c + 4 * i) = packed;
+    }
+  }
+}
+
+// number of K slices for an m x n x k problem on 128 x 256 tiles (1 = no split)
+int splitk_slices(int m, int n, int k) {
+  const int sms = sm_count_of_current_device();
+  const int64_t tiles = static_cast<int64_t>((m + 127) / 128) * ((n + 255) / 256);
+  const int k_tiles = (k + kBlockK - 1) / kBlockK;
+  if (n % 4 != 0 || tiles * 2 > sms || k_tiles < 8) return 1;
+  int splits = static_cast<int>(std::min<int64_t>(sms / tiles, 8));
+  splits = std::min(splits, k_tiles / 4);                         // at least four K steps per slice
+  while (splits > 1 && (splits - 1) * ((k_tiles + splits - 1) / splits) >= k_tiles) --splits;   // no empty slice
+  return std::max(splits, 1);
+}
+
+size_t gemm_workspace_bytes(int m, int n, int k) {
+  const int splits = splitk_slices(m, n, k);
+  return splits > 1 ? static_cast<size_t>(splits) * m * n * sizeof(float) : 0;
+}
+
+template <typename OutT>
+int gemm_dense_splitk(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha, int m,
+                      int n, int k, int splits, float* workspace, cudaStream_t stream) {
+  CUtensorMap ta, tb;
+  int rc = make_operand_map(&ta, a, m, k, 0);
+  if (rc) return rc;
+  rc = make_operand_map(&tb, b, n, k, 1);
+  if (rc) return rc;
+  GemmParams p{};
+  p.sfa = static_cast<const uint8_t*>(sfa);
+  p.sfb = static_cast<const uint8_t*>(sfb);
+  p.m_rows = m;
+  p.n_cols = n;
+  p.k = k;
+  p.rk = (k + 63) / 64;
+  p.num_k_tiles = (k + kBlockK - 1) / kBlockK;
+  p.b_row_tiles = (n + 127) / 128;
+  p.num_m_blocks = (m + kBlockM - 1) / kBlockM;
+  p.num_n_blocks = (n + 255) / 256;
+  p.k_splits = splits;
+  rc = device_status_word(&p.status);
+  if (rc) return rc;
+  EpilogueStore<float> epi{workspace, n, nullptr, 0, static_cast<int64_t>(m) * n};
+  rc = launch_gemm<256, false>(ta, tb, CUtensorMap{}, p, epi, p.num_m_blocks * p.num_n_blocks * splits, stream);
+  if (rc) return rc;
+  const int64_t n4 = static_cast<int64_t>(m) * n / 4;
+  const int grid = static_cast<int>(std::min<int64_t>((n4 + 255) / 256, 4 * sm_count_of_current_device()));
+  splitk_reduce_kernel<OutT><<<grid, 256, 0, stream>>>(workspace, splits, static_cast<int64_t>(m) * n, alpha,
+                                                        static_cast<OutT*>(c), n4);
+  return check_cuda(cudaGetLastError(), "splitk_reduce_kernel launch");
+}
+
+// ---------------------------------------------------------------------------
 // dense GEMM: C[l][m][n] = alpha * A[l][m][k] . B[l][n][k]^T
 // ---------------------------------------------------------------------------
 template <typename OutT>
@@ -334,8 +413,10 @@ int gemm_dense_typed(const void* a, const void* b, const void* sfa, const void* 
   return launch_gemm<128, false>(ta, tb, tc, p, epi, p.num_m_blocks * p.num_n_blocks, stream);
 }
 
+// workspace: optional f32 scratch of gemm_workspace_bytes(m, n, k) bytes; with it, problems with few output tiles
+// and a long reduction run split-K (tile_n 0 only).  Without it they run unsplit.
 int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha, int m, int n,
-               int k, int l, int c_dtype, int tile_n, cudaStream_t stream) {
+               int k, int l, int c_dtype, int tile_n, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
   if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || c == nullptr)
     return fail(kInvalidArgument, "null pointer argument");
   if (m <= 0 || n <= 0 || k <= 0 || l <= 0) return fail(kInvalidArgument, "m, n, k, l must be positive");
@@ -349,6 +430,14 @@ int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, v
   if (c_dtype < 0 || c_dtype > 2) return fail(kUnsupported, "c_dtype code %d (0 fp16, 1 bf16, 2 f32)", c_dtype);
   if (tile_n != 0 && tile_n != 64 && tile_n != 128 && tile_n != 256 && tile_n != 512)
     return fail(kInvalidArgument, "tile_n must be 0, 64, 128, 256 or 512 (512 = 256 x 256 tiles on CTA pairs)");
+  int splits = 1;
+  if (tile_n == 0 && workspace != nullptr) {
+    splits = splitk_slices(m, n, k);
+    if (splits > 1 && (workspace_bytes < static_cast<size_t>(splits) * m * n * sizeof(float) ||
+                       (reinterpret_cast<uintptr_t>(workspace) & 15)))
+      return fail(kInvalidArgument, "split-K workspace must hold %zu bytes, 16-byte aligned",
+                  static_cast<size_t>(splits) * m * n * sizeof(float));
+  }
   if (tile_n == 0) {
     // wide tiles halve the operand traffic per flop; keep narrow ones while they are needed to fill the SMs
     const int sms = sm_count_of_current_device();
@@ -369,6 +458,14 @@ int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, v
     const uint8_t* sfbi = static_cast<const uint8_t*>(sfb) + i * n_tiles * rk * 512;
     uint8_t* ci = static_cast<uint8_t*>(c) + static_cast<int64_t>(i) * m * n * c_elem;
     int rc;
+    if (splits > 1) {
+      float* ws = static_cast<float*>(workspace);
+      if (c_dtype == 0) rc = gemm_dense_splitk<__half>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, splits, ws, stream);
+      else if (c_dtype == 1) rc = gemm_dense_splitk<__nv_bfloat16>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, splits, ws, stream);
+      else rc = gemm_dense_splitk<float>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, splits, ws, stream);
+      if (rc) return rc;
+      continue;
+    }
     if (c_dtype == 0) rc = gemm_dense_typed<__half>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, stream);
     else if (c_dtype == 1) rc = gemm_dense_typed<__nv_bfloat16>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, stream);
     else rc = gemm_dense_typed<float>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, stream);

@@ -95,6 +95,11 @@ struct GemmParams {
   // is the output map in the variants that store through TMA -- never both).  The MoE front end writes them this
   // way: a row's scale bytes are then one contiguous run for the writer instead of 4-byte pieces 512 bytes apart.
   int sfa_row_major;
+  // Split-K (dense GEMMs with few tiles, e.g. M = 128 against a large weight matrix): the K tiles of every output
+  // tile are dealt to k_splits work items that run on different CTAs at the same time, so that all SMs pull on the
+  // weight stream; item s of a tile hands its partial sums to the epilogue as "group" s (EpilogueStore adds
+  // group * group_stride to the output pointer) and a small kernel sums the partial matrices afterwards.
+  int k_splits;                // 0 or 1: off
   // Expert-parallel launches synchronise with the other ranks inside the kernel instead of through extra
   // launches.  peer.wait_flags != null: every CTA's producer thread waits (bounded) until the signal words of all
   // ranks have reached this step before it issues its first load -- the operand rows were written by peers.
@@ -174,6 +179,7 @@ struct EpilogueStore {
   int64_t ldc;                  // elements
   const float* alpha;           // one scale, or one per group (alpha_per_group); null = 1
   int alpha_per_group;
+  int64_t group_stride = 0;     // elements between the outputs of consecutive groups (split-K partial matrices)
 
   static constexpr int kOutBytes = static_cast<int>(sizeof(OutT));
   static constexpr bool kUsesOutputMap = true;      // 128-wide tiles leave through TMA stores
@@ -293,7 +299,7 @@ struct EpilogueStore {
     }
     const int64_t grow = static_cast<int64_t>(m_blk) * kBlockM + row;
     const bool row_ok = grow < p.m_rows && row < rows_valid;
-    OutT* crow = c + grow * ldc + static_cast<int64_t>(n_blk) * kBlockN;
+    OutT* crow = c + group * group_stride + grow * ldc + static_cast<int64_t>(n_blk) * kBlockN;
     const int cols_left = p.n_cols - n_blk * kBlockN;
     const int span = kBlockN / parts;
 #pragma unroll 1
@@ -576,9 +582,20 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
   // grouped launches read the number of row blocks from device memory; never trust it beyond the table size
   const int num_m_blocks =
       p.num_m_blocks_dev != nullptr ? max(0, min(__ldg(p.num_m_blocks_dev), p.num_m_blocks)) : p.num_m_blocks;
-  const int num_tiles = num_m_blocks * p.num_n_blocks;
-  auto tile_m = [&](int tile) { return p.row_block_major ? tile / p.num_n_blocks : tile % num_m_blocks; };
-  auto tile_n = [&](int tile) { return p.row_block_major ? tile % p.num_n_blocks : tile / num_m_blocks; };
+  const int num_out_tiles = num_m_blocks * p.num_n_blocks;
+  const int splits = p.k_splits > 1 ? p.k_splits : 1;
+  const int kt_per_split = (p.num_k_tiles + splits - 1) / splits;
+  const int num_tiles = num_out_tiles * splits;               // work items: (output tile, K slice)
+  auto tile_m = [&](int item) {
+    const int tile = item % num_out_tiles;
+    return p.row_block_major ? tile / p.num_n_blocks : tile % num_m_blocks;
+  };
+  auto tile_n = [&](int item) {
+    const int tile = item % num_out_tiles;
+    return p.row_block_major ? tile % p.num_n_blocks : tile / num_m_blocks;
+  };
+  auto tile_kt0 = [&](int item) { return (item / num_out_tiles) * kt_per_split; };
+  auto tile_kt1 = [&](int item) { return min(p.num_k_tiles, (item / num_out_tiles + 1) * kt_per_split); };
 
   if (warp == 0) {
     // =============================== TMA producer ===============================
@@ -615,7 +632,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         }
         if (kARows < kBlockM && p.m_block_rows != nullptr && __ldg(p.m_block_rows + m_blk) > kARows)
           atomicOr(p.status, kStatusRowsExceedTile);      // results of this block are wrong: tell the host
-        for (int kt = 0; kt < p.num_k_tiles; ++kt) {
+        for (int kt = tile_kt0(tile), kt_end = tile_kt1(tile); kt < kt_end; ++kt) {
           if (!wait_bounded(empty_bar(st.stage), st.phase ^ 1u, abort_flag)) {
             atomicOr(p.status, kStatusTimeoutProducer);
             ok = false;
@@ -675,7 +692,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         // (the movers of a SwiGLU tile with 64-row pieces have already picked the right halves)
         const uint32_t sfb_shift = kBlockN >= 128 ? 0u : static_cast<uint32_t>((tile_n(tile) * kBlockN & 127) >> 5);
         const uint32_t sf_t0 = tmem_base + kSfaCol + 16 + sfb_shift;
-        for (int kt = 0; kt < p.num_k_tiles; ++kt) {
+        const int kt_first = tile_kt0(tile);
+        for (int kt = kt_first, kt_end = tile_kt1(tile); kt < kt_end; ++kt) {
           // the slab movers have put this stage's scale factors into its set of TMEM columns (usually long
           // before the operands land), and the operand tiles are in shared memory
           if (!wait_bounded(sf_full_bar(st.stage), st.phase, abort_flag) ||
@@ -691,7 +709,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const uint32_t sfa_t = tmem_base + kSfaCol + st.stage * kSfSetCols;
           const int kblocks = kt + 1 == p.num_k_tiles ? last_kblocks : 4;
           if (ptx::elect_one()) {
-            ptx::mma_mxf4nvf4(d_tmem, da, db, kIdesc, sfa_t, sfb_t, kt != 0 ? 1u : 0u);
+            ptx::mma_mxf4nvf4(d_tmem, da, db, kIdesc, sfa_t, sfb_t, kt != kt_first ? 1u : 0u);
 #pragma unroll
             for (int kb = 1; kb < 4; ++kb) {
               if (kb < kblocks)
@@ -718,7 +736,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
       // 64-row pieces: rows (n_blk * 64) % 128 .. +63 of their slab = its row groups 0-1 or 2-3
       const bool upper_half = kHalfSlabPieces && (tile_n(tile) & 1) != 0;
-      for (int kt = 0; kt < p.num_k_tiles; ++kt) {
+      for (int kt = tile_kt0(tile), kt_end = tile_kt1(tile); kt < kt_end; ++kt) {
         if (!wait_bounded(sf_loaded_bar(st.stage), st.phase, abort_flag)) {
           if (lane == 0) atomicOr(p.status, kStatusTimeoutMma);
           ok = false;
@@ -793,7 +811,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const int m_blk = tile_m(tile);
       const int n_blk = tile_n(tile);
       const int group =
-          p.m_block_group != nullptr ? max(0, min(__ldg(p.m_block_group + m_blk), p.num_groups - 1)) : 0;
+          p.m_block_group != nullptr ? max(0, min(__ldg(p.m_block_group + m_blk), p.num_groups - 1))
+                                     : (splits > 1 ? tile / num_out_tiles : 0);
       if (!wait_bounded<64>(acc_full_bar(acc.stage), acc.phase, abort_flag)) {
         if (lane == 0) atomicOr(p.status, kStatusTimeoutEpilogue);
         break;

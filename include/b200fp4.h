@@ -71,6 +71,18 @@ int b200fp4_add_rmsnorm_fp4quant(const void* x, void* residual, const void* weig
 int b200fp4_nvfp4_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha,
                        int m, int n, int k, int l, int c_dtype, int tile_n, void* stream);
 
+/* The same GEMM with scratch memory for split-K.  Problems with few 128 x 256 output tiles and a long reduction
+ * (M = 128 against an 8192 x 8192 weight matrix: a 40 MB weight stream for 32 tiles) leave most SMs idle; with a
+ * workspace of b200fp4_nvfp4_gemm_workspace_bytes(m, n, k) bytes (0 = this shape does not split; f32, 16-byte aligned,
+ * caller-owned) and tile_n = 0 the K tiles of every output tile are dealt to several CTAs and a second small kernel
+ * sums their partial matrices in slice order, applies alpha and rounds once.  workspace = NULL behaves exactly as
+ * b200fp4_nvfp4_gemm.  (Measured at M = 128, N = K = 8192: the split kernel takes the same 15 us as the unsplit
+ * 64-wide tiles and the reduction adds 4, so nothing selects this by default.)  Same reference interface as above. */
+size_t b200fp4_nvfp4_gemm_workspace_bytes(int m, int n, int k);
+int b200fp4_nvfp4_gemm_ws(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha,
+                          int m, int n, int k, int l, int c_dtype, int tile_n, void* workspace, size_t workspace_bytes,
+                          void* stream);
+
 /* Router: softmax over `experts` logits per token, the top_k largest probabilities (lowest index
  * first among equals), optionally renormalised to sum 1.  logits f32 [tokens, experts] ->
  * ids i32 [tokens, top_k], weights f32 [tokens, top_k].

@@ -242,3 +242,26 @@ def test_two_devices_in_one_process(b200):
             c = b200.nvfp4_gemm(*ops, out_dtype=torch.float32, tile_n=tile_n)
             torch.cuda.synchronize(dev)
             assert torch.equal(c.cpu(), ref)
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 1024, 4096), (200, 520, 2304), (64, 256, 8192)])
+def test_split_k_integer_exact(b200, m, n, k):
+    """Few output tiles and a long reduction: with a workspace the K tiles of every output tile are dealt to several
+    CTAs (split-K, f32 partial matrices in the workspace, summed in slice order).  Integer-valued operands must still
+    give the exact product, equal to the unsplit kernels'."""
+    assert b200.gemm.gemm_workspace_bytes(m, n, k) > 0, "this shape is expected to split"
+    ac, sfa, bc, sfb = O.integer_gemm_operands(m, n, k, seed=m + n + k)
+    ref = O.gemm_nvfp4_ref(ac, sfa, bc, sfb, alpha=0.5)
+    a, b, sa, sb = _dev_operands(ac, sfa, bc, sfb)
+    alpha = torch.tensor([0.5], device="cuda")
+    for out_dtype in (torch.float32, torch.bfloat16):
+        ws = torch.empty(b200.gemm.gemm_workspace_bytes(m, n, k), dtype=torch.uint8, device="cuda")
+        c = b200.nvfp4_gemm(a, b, sa, sb, alpha=alpha, out_dtype=out_dtype, workspace=ws)
+        c2 = b200.nvfp4_gemm(a, b, sa, sb, alpha=alpha, out_dtype=out_dtype)            # unsplit default
+        unsplit = b200.nvfp4_gemm(a, b, sa, sb, alpha=alpha, out_dtype=out_dtype, tile_n=256)
+        torch.cuda.synchronize()
+        _check_status(b200)
+        assert torch.equal(c.cpu().float(), ref.to(out_dtype).float())
+        assert torch.equal(c, c2) and torch.equal(c, unsplit)
+    with pytest.raises(ValueError):
+        b200.nvfp4_gemm(a, b, sa, sb, workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
