@@ -374,7 +374,7 @@ int gemm_dense_splitk(const void* a, const void* b, const void* sfa, const void*
 // ---------------------------------------------------------------------------
 template <typename OutT>
 int gemm_dense_typed(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha, int m,
-                     int n, int k, int tile_n, cudaStream_t stream) {
+                     int n, int k, int tile_n, int sf_vec, cudaStream_t stream) {
   if (tile_n == 512) return gemm_dense_pair<OutT>(a, b, sfa, sfb, c, alpha, m, n, k, stream);
   CUtensorMap ta, tb;
   int rc = make_operand_map(&ta, a, m, k, 0);
@@ -387,7 +387,8 @@ int gemm_dense_typed(const void* a, const void* b, const void* sfa, const void* 
   p.m_rows = m;
   p.n_cols = n;
   p.k = k;
-  p.rk = (k + 63) / 64;
+  p.sf_block32 = sf_vec == 32;
+  p.rk = sf_vec == 32 ? (k + 127) / 128 : (k + 63) / 64;
   p.num_k_tiles = (k + kBlockK - 1) / kBlockK;
   p.b_row_tiles = (n + 127) / 128;
   p.num_m_blocks = (m + kBlockM - 1) / kBlockM;
@@ -415,8 +416,13 @@ int gemm_dense_typed(const void* a, const void* b, const void* sfa, const void* 
 
 // workspace: optional f32 scratch of gemm_workspace_bytes(m, n, k) bytes; with it, problems with few output tiles
 // and a long reduction run split-K (tile_n 0 only).  Without it they run unsplit.
+// sf_vec: 16 = NVFP4 (e4m3 scale per 16 elements), 32 = MXFP4 (ue8m0 scale per 32 elements; single-CTA tiles only)
 int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha, int m, int n,
-               int k, int l, int c_dtype, int tile_n, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+               int k, int l, int c_dtype, int tile_n, void* workspace, size_t workspace_bytes, int sf_vec,
+               cudaStream_t stream) {
+  if (sf_vec != 16 && sf_vec != 32) return fail(kUnsupported, "sf_vec=%d (16 = NVFP4, 32 = MXFP4)", sf_vec);
+  if (sf_vec == 32 && tile_n == 512) return fail(kUnsupported, "MXFP4 runs on single-CTA tiles (tile_n 0, 64, 128, 256)");
+  if (sf_vec == 32) workspace = nullptr;
   if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || c == nullptr)
     return fail(kInvalidArgument, "null pointer argument");
   if (m <= 0 || n <= 0 || k <= 0 || l <= 0) return fail(kInvalidArgument, "m, n, k, l must be positive");
@@ -444,12 +450,12 @@ int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, v
     const int64_t m_blocks = (m + 127) / 128;
     static const bool no_pairs = getenv("B200FP4_NO_PAIRS") != nullptr;
     // a full wave of 256 x 256 tiles on CTA pairs: each CTA fills 38 KB per K step instead of 54 KB
-    if (!no_pairs && ((m + 255) / 256) * static_cast<int64_t>((n + 255) / 256) >= sms / 2 && k >= 1024) tile_n = 512;
+    if (!no_pairs && sf_vec == 16 && ((m + 255) / 256) * static_cast<int64_t>((n + 255) / 256) >= sms / 2 && k >= 1024) tile_n = 512;
     else if (m_blocks * ((n + 255) / 256) >= sms) tile_n = 256;
     else if (m_blocks * ((n + 127) / 128) >= sms) tile_n = 128;
     else tile_n = 64;            // few rows (weight streaming): narrow tiles put more SMs on the stream of B
   }
-  const int64_t m_tiles = (m + 127) / 128, n_tiles = (n + 127) / 128, rk = (k + 63) / 64;
+  const int64_t m_tiles = (m + 127) / 128, n_tiles = (n + 127) / 128, rk = sf_vec == 32 ? (k + 127) / 128 : (k + 63) / 64;
   const size_t c_elem = c_dtype == 2 ? 4 : 2;
   for (int i = 0; i < l; ++i) {
     const uint8_t* ai = static_cast<const uint8_t*>(a) + static_cast<int64_t>(i) * m * (k / 2);
@@ -466,9 +472,9 @@ int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, v
       if (rc) return rc;
       continue;
     }
-    if (c_dtype == 0) rc = gemm_dense_typed<__half>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, stream);
-    else if (c_dtype == 1) rc = gemm_dense_typed<__nv_bfloat16>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, stream);
-    else rc = gemm_dense_typed<float>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, stream);
+    if (c_dtype == 0) rc = gemm_dense_typed<__half>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, sf_vec, stream);
+    else if (c_dtype == 1) rc = gemm_dense_typed<__nv_bfloat16>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, sf_vec, stream);
+    else rc = gemm_dense_typed<float>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, sf_vec, stream);
     if (rc) return rc;
   }
   return kOk;

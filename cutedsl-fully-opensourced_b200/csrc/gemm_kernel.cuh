@@ -100,6 +100,9 @@ struct GemmParams {
   // weight stream; item s of a tile hands its partial sums to the epilogue as "group" s (EpilogueStore adds
   // group * group_stride to the output pointer) and a small kernel sums the partial matrices afterwards.
   int k_splits;                // 0 or 1: off
+  // MXFP4 instead of NVFP4: one ue8m0 scale per 32 K-elements.  The scale tiles keep their 128x4 shape, so a
+  // 512-byte tile spans 128 K-elements (two per 256-wide stage instead of four) and rk counts those.
+  int sf_block32;
   // Expert-parallel launches synchronise with the other ranks inside the kernel instead of through extra
   // launches.  peer.wait_flags != null: every CTA's producer thread waits (bounded) until the signal words of all
   // ranks have reached this step before it issues its first load -- the operand rows were written by peers.
@@ -642,7 +645,8 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const uint32_t sb = sa + L.a_bytes;
           const uint32_t ssfa = sb + L.b_bytes;
           const uint32_t ssfb = ssfa + L.sfa_bytes;
-          const int k_sf_tiles = min(4, p.rk - 4 * kt);                 // 512-byte scale tiles in this stage
+          const int tps = p.sf_block32 ? 2 : 4;                         // 512-byte scale tiles per stage
+          const int k_sf_tiles = min(tps, p.rk - tps * kt);
           const uint32_t sf_bytes = static_cast<uint32_t>(k_sf_tiles) * 512u;
           // the scale slabs go first and report to their own barrier: the movers carry them into tensor
           // memory while the operand tiles are still on their way
@@ -652,12 +656,12 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             ptx::tma_load_2d(ssfa, &tmap_aux, kt * 16, m_blk * kBlockM, sbar);
           } else {
             ptx::mbar_expect_tx(sbar, sf_bytes * (1 + kBPieces));
-            ptx::bulk_load(ssfa, p.sfa + (static_cast<int64_t>(m_blk) * p.rk + 4 * kt) * 512, sf_bytes, sbar);
+            ptx::bulk_load(ssfa, p.sfa + (static_cast<int64_t>(m_blk) * p.rk + tps * kt) * 512, sf_bytes, sbar);
           }
 #pragma unroll
           for (int i = 0; i < kBPieces; ++i) {
             const int64_t tile_idx = static_cast<int64_t>(group) * p.b_row_tiles + (b_row[i] >> 7);
-            ptx::bulk_load(ssfb + i * 2048, p.sfb + (tile_idx * p.rk + 4 * kt) * 512, sf_bytes, sbar);
+            ptx::bulk_load(ssfb + i * 2048, p.sfb + (tile_idx * p.rk + tps * kt) * 512, sf_bytes, sbar);
           }
           const uint32_t bar = full_bar(st.stage);
           ptx::mbar_expect_tx(bar, L.a_bytes + L.b_bytes);
@@ -709,11 +713,22 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const uint32_t sfa_t = tmem_base + kSfaCol + st.stage * kSfSetCols;
           const int kblocks = kt + 1 == p.num_k_tiles ? last_kblocks : 4;
           if (ptx::elect_one()) {
-            ptx::mma_mxf4nvf4(d_tmem, da, db, kIdesc, sfa_t, sfb_t, kt != kt_first ? 1u : 0u);
+            if (p.sf_block32) {
+              // a scale tile serves two instructions (bytes 0-1, then 2-3 of its columns)
 #pragma unroll
-            for (int kb = 1; kb < 4; ++kb) {
-              if (kb < kblocks)
-                ptx::mma_mxf4nvf4(d_tmem, da + 2 * kb, db + 2 * kb, kIdesc, sfa_t + 4 * kb, sfb_t + kSfbColsPerKb * kb, 1u);
+              for (int kb = 0; kb < 4; ++kb) {
+                if (kb < kblocks)
+                  ptx::mma_mxf4_block32(d_tmem, da + 2 * kb, db + 2 * kb, ptx::idesc_mxf4_block32(kBlockN, (kb & 1) * 2),
+                                        sfa_t + 4 * (kb >> 1), sfb_t + kSfbColsPerKb * (kb >> 1),
+                                        (kt != kt_first || kb != 0) ? 1u : 0u);
+              }
+            } else {
+              ptx::mma_mxf4nvf4(d_tmem, da, db, kIdesc, sfa_t, sfb_t, kt != kt_first ? 1u : 0u);
+#pragma unroll
+              for (int kb = 1; kb < 4; ++kb) {
+                if (kb < kblocks)
+                  ptx::mma_mxf4nvf4(d_tmem, da + 2 * kb, db + 2 * kb, kIdesc, sfa_t + 4 * kb, sfb_t + kSfbColsPerKb * kb, 1u);
+              }
             }
             ptx::tc_commit(empty_bar(st.stage));        // stage reusable once these MMAs have read it
           }

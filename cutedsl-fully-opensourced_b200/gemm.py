@@ -76,8 +76,11 @@ def gemm_workspace_bytes(m: int, n: int, k: int) -> int:
 def nvfp4_gemm(a: torch.Tensor, b: torch.Tensor, sfa: torch.Tensor, sfb: torch.Tensor,
                alpha: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                out_dtype: torch.dtype = torch.bfloat16, tile_n: int = 0,
-               workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+               workspace: Optional[torch.Tensor] = None, sf_vec_size: int = 16) -> torch.Tensor:
     """C = alpha * (A*SFA) @ (B*SFB)^T with f32 accumulation on the tensor cores.
+
+    ``sf_vec_size`` 16: NVFP4 (one e4m3 scale byte per 16 K-elements); 32: MXFP4 (one ue8m0 scale byte per 32
+    K-elements, same 128x4 tiles; single-CTA tile variants only).
 
     ``workspace=`` (uint8, ``gemm_workspace_bytes(m, n, k)`` bytes) opts a problem with few output tiles and a long
     reduction into split-K.  It is off by default: at M = 128, N = K = 8192 the split kernel takes the same 15 us as
@@ -92,8 +95,10 @@ def nvfp4_gemm(a: torch.Tensor, b: torch.Tensor, sfa: torch.Tensor, sfb: torch.T
     k = kh * 2
     if k % 32 != 0 or n % 8 != 0:
         raise ValueError("Invalid tensor alignment")
-    need_a = l * swizzled_sf_numel(m, k // 16)
-    need_b = l * swizzled_sf_numel(n, k // 16)
+    if sf_vec_size not in (16, 32):
+        raise NotImplementedError("sf_vec_size must be 16 (NVFP4) or 32 (MXFP4)")
+    need_a = l * swizzled_sf_numel(m, ceil_div(k, sf_vec_size))
+    need_b = l * swizzled_sf_numel(n, ceil_div(k, sf_vec_size))
     if sfa.element_size() != 1 or sfb.element_size() != 1 or sfa.numel() < need_a or sfb.numel() < need_b:
         raise ValueError(f"scale factors must be 1-byte tensors in the 128x4 tiled layout "
                          f"({need_a} and {need_b} bytes)")
@@ -105,6 +110,12 @@ def nvfp4_gemm(a: torch.Tensor, b: torch.Tensor, sfa: torch.Tensor, sfb: torch.T
         raise ValueError(f"c must be [{m}, {n}] (x{l}) in float16, bfloat16 or float32")
     if alpha is not None and (alpha.dtype != torch.float32 or not alpha.is_cuda):
         raise ValueError("alpha must be a float32 CUDA tensor")
+    if sf_vec_size == 32:
+        with _lib.on_device(a.device):
+            _lib.check(_lib.lib.b200fp4_mxfp4_gemm(
+                a3.data_ptr(), b3.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), out3.data_ptr(), _lib.ptr(alpha),
+                m, n, k, l, _C_CODES[out.dtype], tile_n, _lib.current_stream_ptr(a.device)))
+        return out
     ws_ptr, ws_bytes = None, 0
     if workspace is not None and tile_n == 0:
         ws_bytes = gemm_workspace_bytes(m, n, k)
@@ -120,15 +131,15 @@ def nvfp4_gemm(a: torch.Tensor, b: torch.Tensor, sfa: torch.Tensor, sfb: torch.T
 
 
 class Sm120BlockScaledGemmKernel:
-    """Same constructor and call signature as the demo's kernel class.  Only the
-    NVFP4 configuration the reference exercises is implemented: f32 accumulate,
-    sf_vec_size 16 with e4m3 scale factors, K-major A and B, N-major C."""
+    """Same constructor and call signature as the demo's kernel class.  Implemented: f32 accumulate, e2m1 operands
+    with sf_vec_size 16 and e4m3 scale factors (NVFP4, the configuration the reference exercises) or sf_vec_size 32
+    and ue8m0 scale factors (MXFP4), K-major A and B, N-major C."""
 
     def __init__(self, acc_dtype, sf_vec_size: int, tile_shape_mnk: Tuple[int, int, int], epi_tile: Tuple[int, int]):
         if _dtype_token(acc_dtype) is not Float32:
             raise TypeError("Only Float32 accumulation is supported in FP4 mma")
-        if sf_vec_size != 16:
-            raise NotImplementedError("only sf_vec_size=16 (NVFP4, e4m3 scale factors) is implemented")
+        if sf_vec_size not in (16, 32):
+            raise NotImplementedError("sf_vec_size must be 16 (NVFP4, e4m3 scales) or 32 (MXFP4, ue8m0 scales)")
         tm, tn, tk = tile_shape_mnk
         if tm % 128 or tn % 128 or tk % 64:
             raise ValueError("tile_shape_mnk must be multiples of (128, 128, 64)")
@@ -149,7 +160,7 @@ class Sm120BlockScaledGemmKernel:
             stream = torch.cuda.ExternalStream(int(stream))
         ctx = torch.cuda.stream(stream) if stream is not None else torch.cuda.stream(torch.cuda.current_stream())
         with ctx:
-            nvfp4_gemm(a, b, sfa, sfb, out=c, tile_n=self._tile_n)
+            nvfp4_gemm(a, b, sfa, sfb, out=c, tile_n=self._tile_n, sf_vec_size=self.sf_vec_size)
         return c
 
 
@@ -176,11 +187,16 @@ def _integer_operand(rows: int, k: int, l: int, device) -> Tuple[torch.Tensor, t
     return pack_e2m1(codes), vals.float()
 
 
-def _integer_scales(rows: int, k: int, l: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Scale factors in {1, 2}: returns (tiled bytes [L, tiles*512], f32 per element [L, rows, K])."""
-    sf = torch.randint(1, 3, (l, rows, k // 16), device=device, dtype=torch.int32).float()
-    bits = sf.to(torch.float8_e4m3fn).view(torch.uint8)
-    return swizzle_sf(bits), sf.repeat_interleave(16, dim=-1)
+def _integer_scales(rows: int, k: int, l: int, device, sf_vec: int = 16) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Scale factors in {1, 2}: returns (tiled bytes [L, tiles*512], f32 per element [L, rows, K]).
+    sf_vec 16: e4m3 bytes; 32: ue8m0 bytes (127 = 1, 128 = 2)."""
+    blocks = ceil_div(k, sf_vec)
+    sf = torch.randint(1, 3, (l, rows, blocks), device=device, dtype=torch.int32)
+    if sf_vec == 16:
+        bits = sf.float().to(torch.float8_e4m3fn).view(torch.uint8)
+    else:
+        bits = (sf + 126).to(torch.uint8)
+    return swizzle_sf(bits), sf.float().repeat_interleave(sf_vec, dim=-1)[..., :k]
 
 
 def run_bs(mnkl, a_dtype, b_dtype, sf_dtype, sf_vec_size, c_dtype, acc_dtype, a_major, b_major, c_major,
@@ -188,8 +204,10 @@ def run_bs(mnkl, a_dtype, b_dtype, sf_dtype, sf_vec_size, c_dtype, acc_dtype, a_
            use_cold_l2=False, **kwargs) -> float:
     m, n, k, l = mnkl
     a_dtype, b_dtype, sf_dtype, c_dtype = (_dtype_token(d) for d in (a_dtype, b_dtype, sf_dtype, c_dtype))
-    if (a_dtype, b_dtype, sf_dtype, sf_vec_size) != (Float4E2M1FN, Float4E2M1FN, Float8E4M3FN, 16):
-        raise NotImplementedError("only Float4E2M1FN x Float4E2M1FN with Float8E4M3FN scales per 16 is implemented")
+    if (a_dtype, b_dtype, sf_dtype, sf_vec_size) not in ((Float4E2M1FN, Float4E2M1FN, Float8E4M3FN, 16),
+                                                         (Float4E2M1FN, Float4E2M1FN, Float8E8M0FNU, 32)):
+        raise NotImplementedError("implemented: Float4E2M1FN x Float4E2M1FN with Float8E4M3FN scales per 16 (NVFP4) "
+                                  "or Float8E8M0FNU scales per 32 (MXFP4)")
     if (a_major, b_major, c_major) != ("k", "k", "n"):
         raise NotImplementedError("A and B must be K-major and C N-major")
     if c_dtype.torch_dtype not in _C_CODES:
@@ -205,8 +223,8 @@ def run_bs(mnkl, a_dtype, b_dtype, sf_dtype, sf_vec_size, c_dtype, acc_dtype, a_
     def make():
         a, a_ref = _integer_operand(m, k, l, dev)
         b, b_ref = _integer_operand(n, k, l, dev)
-        sfa, sfa_ref = _integer_scales(m, k, l, dev)
-        sfb, sfb_ref = _integer_scales(n, k, l, dev)
+        sfa, sfa_ref = _integer_scales(m, k, l, dev, sf_vec_size)
+        sfb, sfb_ref = _integer_scales(n, k, l, dev, sf_vec_size)
         c = torch.zeros(l, m, n, dtype=c_dtype.torch_dtype, device=dev)
         return (a, b, sfa, sfb, c), (a_ref, b_ref, sfa_ref, sfb_ref)
 

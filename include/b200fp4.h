@@ -83,6 +83,13 @@ int b200fp4_nvfp4_gemm_ws(const void* a, const void* b, const void* sfa, const v
                           int m, int n, int k, int l, int c_dtype, int tile_n, void* workspace, size_t workspace_bytes,
                           void* stream);
 
+/* MXFP4 flavour of the same GEMM (sf_vec_size 32 of the demo): e2m1 codes as above, one ue8m0 scale byte (2^(b-127))
+ * per 32 K-elements, in the same 128x4 tiles ([l][ceil(rows/128)][ceil(k/128)][32][4][4]).  Single-CTA tiles only
+ * (tile_n 0, 64, 128 or 256).  Stands in for the (Float4E2M1FN, Float4E2M1FN, Float8E8M0FNU, 32) configuration of
+ *   .../blockscaled_gemm/blockscaled_gemm_dispatch.py:34-43 and dense_blockscaled_gemm_persistent_cooperative.py:60-68. */
+int b200fp4_mxfp4_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha,
+                       int m, int n, int k, int l, int c_dtype, int tile_n, void* stream);
+
 /* Router: softmax over `experts` logits per token, the top_k largest probabilities (lowest index
  * first among equals), optionally renormalised to sum 1.  logits f32 [tokens, experts] ->
  * ids i32 [tokens, top_k], weights f32 [tokens, top_k].

@@ -262,11 +262,18 @@ def nvfp4_global_scale(values: torch.Tensor) -> float:
 # --------------------------------------------------------------------------
 # NVFP4 block-scaled GEMM
 # --------------------------------------------------------------------------
-def gemm_nvfp4_ref(a_codes, sfa_bits, b_codes, sfb_bits, alpha: float = 1.0) -> torch.Tensor:
+def e8m0_decode(bits) -> np.ndarray:
+    """ue8m0 scale bytes (MXFP4): 2^(b - 127)."""
+    return np.exp2(np.asarray(bits, dtype=np.int32).astype(F32) - F32(127.0)).astype(F32)
+
+
+def gemm_nvfp4_ref(a_codes, sfa_bits, b_codes, sfb_bits, alpha: float = 1.0, sf_vec: int = SF_BLOCK) -> torch.Tensor:
     """C[m,n] = alpha * sum_k (A*SFA)[m,k] * (B*SFB)[n,k]; operands are
-    de-quantised to f32 first and multiplied in f32 (the demo's own check)."""
-    a = torch.from_numpy(e2m1_decode(a_codes) * np.repeat(e4m3_decode(sfa_bits), SF_BLOCK, axis=-1))
-    b = torch.from_numpy(e2m1_decode(b_codes) * np.repeat(e4m3_decode(sfb_bits), SF_BLOCK, axis=-1))
+    de-quantised to f32 first and multiplied in f32 (the demo's own check).
+    sf_vec 16: e4m3 scale bytes per 16 elements (NVFP4); 32: ue8m0 scale bytes per 32 elements (MXFP4)."""
+    decode = e4m3_decode if sf_vec == SF_BLOCK else e8m0_decode
+    a = torch.from_numpy(e2m1_decode(a_codes) * np.repeat(decode(sfa_bits), sf_vec, axis=-1))
+    b = torch.from_numpy(e2m1_decode(b_codes) * np.repeat(decode(sfb_bits), sf_vec, axis=-1))
     c = a @ b.t()
     return c * alpha if alpha != 1.0 else c
 

@@ -122,7 +122,7 @@ def test_alignment_and_argument_errors(b200):
     with pytest.raises(ValueError, match="Invalid tensor alignment"):
         g.run((128, 100, 128, 1), g.Float4E2M1FN, g.Float4E2M1FN, g.Float8E4M3FN, 16, g.Float16)
     with pytest.raises(NotImplementedError):
-        g.run((128, 128, 128, 1), g.Float4E2M1FN, g.Float4E2M1FN, g.Float8E8M0FNU, 32, g.Float16)
+        g.run((128, 128, 128, 1), g.Float8E4M3FN, g.Float8E4M3FN, g.Float8E8M0FNU, 32, g.Float16)      # MXFP8
     a = torch.zeros(128, 64, dtype=torch.uint8, device="cuda")
     sf = torch.zeros(512, dtype=torch.uint8, device="cuda")
     with pytest.raises(ValueError):
@@ -265,3 +265,35 @@ def test_split_k_integer_exact(b200, m, n, k):
         assert torch.equal(c, c2) and torch.equal(c, unsplit)
     with pytest.raises(ValueError):
         b200.nvfp4_gemm(a, b, sa, sb, workspace=torch.empty(16, dtype=torch.uint8, device="cuda"))
+
+
+@pytest.mark.parametrize("m,n,k,tile_n", [(128, 128, 128, 128), (256, 384, 512, 0), (200, 264, 1184, 256), (128, 192, 4096, 64),
+                                          (1024, 1024, 1024, 0)])
+def test_mxfp4_block32_ue8m0(b200, m, n, k, tile_n):
+    """The MXFP4 flavour of the demo (sf_vec_size 32, ue8m0 scales; blockscaled_gemm_dispatch.py:34-43): random e2m1
+    codes with random power-of-two scales per 32 elements.  Every product and every scale is a power of two times a
+    small integer, so f32 sums differ from the oracle's only by summation order: rel-L2 <= 1e-5; integer-valued data
+    through run() must be exact."""
+    rng = np.random.default_rng(m + n + k)
+    ac = rng.integers(0, 16, size=(m, k), dtype=np.uint8)
+    bc = rng.integers(0, 16, size=(n, k), dtype=np.uint8)
+    kb = -(-k // 32)
+    sfa = rng.integers(122, 131, size=(m, kb), dtype=np.uint8)        # 2^-5 .. 2^3
+    sfb = rng.integers(122, 131, size=(n, kb), dtype=np.uint8)
+    ref = O.gemm_nvfp4_ref(ac, sfa, bc, sfb, alpha=0.25, sf_vec=32)
+    a, b, sa, sb = _dev_operands(ac, sfa, bc, sfb)
+    c = b200.nvfp4_gemm(a, b, sa, sb, alpha=torch.tensor([0.25], device="cuda"), out_dtype=torch.float32, tile_n=tile_n,
+                        sf_vec_size=32)
+    torch.cuda.synchronize()
+    _check_status(b200)
+    err = torch.linalg.vector_norm(c.cpu() - ref) / torch.linalg.vector_norm(ref)
+    assert err <= 1e-5, float(err)
+
+
+def test_mxfp4_through_the_demo_entry(b200):
+    torch.manual_seed(0)
+    g = b200.gemm
+    us = g.run((256, 256, 512, 1), g.Float4E2M1FN, g.Float4E2M1FN, g.Float8E8M0FNU, 32, g.Float16, a_major="k",
+               b_major="k", c_major="n", tile_shape_mnk=(128, 128, 128), epi_tile=(128, 128), tolerance=0.1,
+               warmup_iterations=0, iterations=1, skip_ref_check=False)
+    assert us > 0
