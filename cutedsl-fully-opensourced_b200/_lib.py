@@ -27,6 +27,7 @@ SIGNATURES = {
     "b200fp4_nvfp4_gemm_workspace_bytes": (_sz, [_i32, _i32, _i32]),
     "b200fp4_nvfp4_gemm_ws": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),
     "b200fp4_mxfp4_gemm": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
+    "b200fp4_mxfp8_gemm": (_i32, [_vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp]),
     "b200fp4_topk_route": (_i32, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _vp]),
     "b200fp4_moe_workspace_bytes": (_sz, [_i64, _i32, _i32, _i32, _i32]),
     "b200fp4_moe_fused": (_i32, [_vp] * 11 + [_i64, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _sz, _vp]),

@@ -31,7 +31,7 @@ int norm_fp4quant_launch(const void* x, void* residual, const void* weight, void
                          cudaStream_t stream);
 
 int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha, int m, int n,
-               int k, int l, int c_dtype, int tile_n, void* workspace, size_t workspace_bytes, int sf_vec,
+               int k, int l, int c_dtype, int tile_n, void* workspace, size_t workspace_bytes, int sf_vec, int fmt8,
                cudaStream_t stream);
 size_t gemm_workspace_bytes(int m, int n, int k);
 int device_status_word(int** out);
@@ -93,13 +93,18 @@ int b200fp4_add_rmsnorm_fp4quant(const void* x, void* residual, const void* weig
 
 int b200fp4_nvfp4_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha,
                        int m, int n, int k, int l, int c_dtype, int tile_n, void* stream) {
-  return gemm_dense(a, b, sfa, sfb, c, alpha, m, n, k, l, c_dtype, tile_n, nullptr, 0, 16, static_cast<cudaStream_t>(stream));
+  return gemm_dense(a, b, sfa, sfb, c, alpha, m, n, k, l, c_dtype, tile_n, nullptr, 0, 16, -1, static_cast<cudaStream_t>(stream));
 }
 
 int b200fp4_mxfp4_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha,
                        int m, int n, int k, int l, int c_dtype, int tile_n, void* stream) {
-  if (k % 32 != 0) return fail(kInvalidArgument, "Invalid tensor alignment: k=%d is not a multiple of 32", k);
-  return gemm_dense(a, b, sfa, sfb, c, alpha, m, n, k, l, c_dtype, tile_n, nullptr, 0, 32, static_cast<cudaStream_t>(stream));
+  return gemm_dense(a, b, sfa, sfb, c, alpha, m, n, k, l, c_dtype, tile_n, nullptr, 0, 32, -1, static_cast<cudaStream_t>(stream));
+}
+
+int b200fp4_mxfp8_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha,
+                       int m, int n, int k, int l, int c_dtype, int tile_n, int a_e5m2, int b_e5m2, void* stream) {
+  return gemm_dense(a, b, sfa, sfb, c, alpha, m, n, k, l, c_dtype, tile_n, nullptr, 0, 32, (a_e5m2 ? 1 : 0) | (b_e5m2 ? 2 : 0),
+                    static_cast<cudaStream_t>(stream));
 }
 
 size_t b200fp4_nvfp4_gemm_workspace_bytes(int m, int n, int k) {
@@ -110,7 +115,7 @@ size_t b200fp4_nvfp4_gemm_workspace_bytes(int m, int n, int k) {
 int b200fp4_nvfp4_gemm_ws(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha,
                           int m, int n, int k, int l, int c_dtype, int tile_n, void* workspace, size_t workspace_bytes,
                           void* stream) {
-  return gemm_dense(a, b, sfa, sfb, c, alpha, m, n, k, l, c_dtype, tile_n, workspace, workspace_bytes, 16,
+  return gemm_dense(a, b, sfa, sfb, c, alpha, m, n, k, l, c_dtype, tile_n, workspace, workspace_bytes, 16, -1,
                     static_cast<cudaStream_t>(stream));
 }
 

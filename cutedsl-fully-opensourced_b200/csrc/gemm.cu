@@ -67,6 +67,7 @@ void remember_map(const MapKey& key, const CUtensorMap& map) {
 }
 
 // K-major e2m1 operand viewed as bytes: [groups][rows][k/2], boxes of 128 rows x 128 bytes, 128-byte swizzle.
+// (`k` counts e2m1 elements, two per byte; 8-bit operands pass twice their element count)
 int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int k, int64_t groups, int box_rows = 128) {
   const MapKey key{1, reinterpret_cast<uint64_t>(base), static_cast<uint64_t>(rows), static_cast<uint64_t>(k),
                    static_cast<uint64_t>(groups), static_cast<uint64_t>(box_rows)};
@@ -262,6 +263,7 @@ int gemm_dense_pair(const void* a, const void* b, const void* sfa, const void* s
   p.m_rows = m;
   p.n_cols = n;
   p.k = k;
+  p.k_bytes = k / 2;
   p.rk = static_cast<int>(rk);
   p.num_k_tiles = (k + kBlockK - 1) / kBlockK;
   p.num_m_blocks = (m + 255) / 256;
@@ -351,6 +353,7 @@ int gemm_dense_splitk(const void* a, const void* b, const void* sfa, const void*
   p.m_rows = m;
   p.n_cols = n;
   p.k = k;
+  p.k_bytes = k / 2;
   p.rk = (k + 63) / 64;
   p.num_k_tiles = (k + kBlockK - 1) / kBlockK;
   p.b_row_tiles = (n + 127) / 128;
@@ -374,12 +377,14 @@ int gemm_dense_splitk(const void* a, const void* b, const void* sfa, const void*
 // ---------------------------------------------------------------------------
 template <typename OutT>
 int gemm_dense_typed(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha, int m,
-                     int n, int k, int tile_n, int sf_vec, cudaStream_t stream) {
+                     int n, int k, int tile_n, int sf_vec, int fmt8, cudaStream_t stream) {
+  // fmt8 < 0: e2m1 operands; else MXFP8 with operand formats a = fmt8 & 1, b = fmt8 >> 1 (0 e4m3, 1 e5m2)
   if (tile_n == 512) return gemm_dense_pair<OutT>(a, b, sfa, sfb, c, alpha, m, n, k, stream);
   CUtensorMap ta, tb;
-  int rc = make_operand_map(&ta, a, m, k, 0);
+  const int k_nibbles = fmt8 >= 0 ? 2 * k : k;           // operand maps count 4-bit units
+  int rc = make_operand_map(&ta, a, m, k_nibbles, 0);
   if (rc) return rc;
-  rc = make_operand_map(&tb, b, n, k, 1, tile_n == 64 ? 64 : 128);
+  rc = make_operand_map(&tb, b, n, k_nibbles, 1, tile_n == 64 ? 64 : 128);
   if (rc) return rc;
   GemmParams p{};
   p.sfa = static_cast<const uint8_t*>(sfa);
@@ -387,9 +392,12 @@ int gemm_dense_typed(const void* a, const void* b, const void* sfa, const void* 
   p.m_rows = m;
   p.n_cols = n;
   p.k = k;
-  p.sf_block32 = sf_vec == 32;
+  p.k_bytes = fmt8 >= 0 ? k : k / 2;
+  p.sf_block32 = fmt8 >= 0 ? 2 : (sf_vec == 32 ? 1 : 0);
+  p.a_fmt8 = fmt8 >= 0 ? (fmt8 & 1) : 0;
+  p.b_fmt8 = fmt8 >= 0 ? (fmt8 >> 1) : 0;
   p.rk = sf_vec == 32 ? (k + 127) / 128 : (k + 63) / 64;
-  p.num_k_tiles = (k + kBlockK - 1) / kBlockK;
+  p.num_k_tiles = (p.k_bytes + 127) / 128;
   p.b_row_tiles = (n + 127) / 128;
   p.num_m_blocks = (m + kBlockM - 1) / kBlockM;
   rc = device_status_word(&p.status);
@@ -418,17 +426,19 @@ int gemm_dense_typed(const void* a, const void* b, const void* sfa, const void* 
 // and a long reduction run split-K (tile_n 0 only).  Without it they run unsplit.
 // sf_vec: 16 = NVFP4 (e4m3 scale per 16 elements), 32 = MXFP4 (ue8m0 scale per 32 elements; single-CTA tiles only)
 int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha, int m, int n,
-               int k, int l, int c_dtype, int tile_n, void* workspace, size_t workspace_bytes, int sf_vec,
+               int k, int l, int c_dtype, int tile_n, void* workspace, size_t workspace_bytes, int sf_vec, int fmt8,
                cudaStream_t stream) {
-  if (sf_vec != 16 && sf_vec != 32) return fail(kUnsupported, "sf_vec=%d (16 = NVFP4, 32 = MXFP4)", sf_vec);
-  if (sf_vec == 32 && tile_n == 512) return fail(kUnsupported, "MXFP4 runs on single-CTA tiles (tile_n 0, 64, 128, 256)");
+  if (sf_vec != 16 && sf_vec != 32) return fail(kUnsupported, "sf_vec=%d (16 = NVFP4, 32 = MXFP4 / MXFP8)", sf_vec);
+  if (fmt8 >= 0 && (sf_vec != 32 || fmt8 > 3)) return fail(kUnsupported, "8-bit operands take ue8m0 scales per 32 elements");
+  if (sf_vec == 32 && tile_n == 512) return fail(kUnsupported, "the MX flavours run on single-CTA tiles (tile_n 0, 64, 128, 256)");
   if (sf_vec == 32) workspace = nullptr;
   if (a == nullptr || b == nullptr || sfa == nullptr || sfb == nullptr || c == nullptr)
     return fail(kInvalidArgument, "null pointer argument");
   if (m <= 0 || n <= 0 || k <= 0 || l <= 0) return fail(kInvalidArgument, "m, n, k, l must be positive");
   // contiguous dimension of every tensor must cover whole 16-byte units (the reference's
   // is_valid_tensor_alignment rule): 32 e2m1 elements for A/B, 8 (16-bit) or 4 (f32) for C
-  if (k % 32 != 0) return fail(kInvalidArgument, "Invalid tensor alignment: k=%d is not a multiple of 32", k);
+  if (k % (fmt8 >= 0 ? 16 : 32) != 0)
+    return fail(kInvalidArgument, "Invalid tensor alignment: k=%d is not a multiple of %d", k, fmt8 >= 0 ? 16 : 32);
   if (n % 8 != 0) return fail(kInvalidArgument, "Invalid tensor alignment: n=%d is not a multiple of 8", n);
   if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(sfa) |
        reinterpret_cast<uintptr_t>(sfb) | reinterpret_cast<uintptr_t>(c)) & 15)
@@ -450,7 +460,7 @@ int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, v
     const int64_t m_blocks = (m + 127) / 128;
     static const bool no_pairs = getenv("B200FP4_NO_PAIRS") != nullptr;
     // a full wave of 256 x 256 tiles on CTA pairs: each CTA fills 38 KB per K step instead of 54 KB
-    if (!no_pairs && sf_vec == 16 && ((m + 255) / 256) * static_cast<int64_t>((n + 255) / 256) >= sms / 2 && k >= 1024) tile_n = 512;
+    if (!no_pairs && sf_vec == 16 && fmt8 < 0 && ((m + 255) / 256) * static_cast<int64_t>((n + 255) / 256) >= sms / 2 && k >= 1024) tile_n = 512;
     else if (m_blocks * ((n + 255) / 256) >= sms) tile_n = 256;
     else if (m_blocks * ((n + 127) / 128) >= sms) tile_n = 128;
     else tile_n = 64;            // few rows (weight streaming): narrow tiles put more SMs on the stream of B
@@ -458,8 +468,9 @@ int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, v
   const int64_t m_tiles = (m + 127) / 128, n_tiles = (n + 127) / 128, rk = sf_vec == 32 ? (k + 127) / 128 : (k + 63) / 64;
   const size_t c_elem = c_dtype == 2 ? 4 : 2;
   for (int i = 0; i < l; ++i) {
-    const uint8_t* ai = static_cast<const uint8_t*>(a) + static_cast<int64_t>(i) * m * (k / 2);
-    const uint8_t* bi = static_cast<const uint8_t*>(b) + static_cast<int64_t>(i) * n * (k / 2);
+    const int64_t row_bytes = fmt8 >= 0 ? k : k / 2;
+    const uint8_t* ai = static_cast<const uint8_t*>(a) + static_cast<int64_t>(i) * m * row_bytes;
+    const uint8_t* bi = static_cast<const uint8_t*>(b) + static_cast<int64_t>(i) * n * row_bytes;
     const uint8_t* sfai = static_cast<const uint8_t*>(sfa) + i * m_tiles * rk * 512;
     const uint8_t* sfbi = static_cast<const uint8_t*>(sfb) + i * n_tiles * rk * 512;
     uint8_t* ci = static_cast<uint8_t*>(c) + static_cast<int64_t>(i) * m * n * c_elem;
@@ -472,9 +483,9 @@ int gemm_dense(const void* a, const void* b, const void* sfa, const void* sfb, v
       if (rc) return rc;
       continue;
     }
-    if (c_dtype == 0) rc = gemm_dense_typed<__half>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, sf_vec, stream);
-    else if (c_dtype == 1) rc = gemm_dense_typed<__nv_bfloat16>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, sf_vec, stream);
-    else rc = gemm_dense_typed<float>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, sf_vec, stream);
+    if (c_dtype == 0) rc = gemm_dense_typed<__half>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, sf_vec, fmt8, stream);
+    else if (c_dtype == 1) rc = gemm_dense_typed<__nv_bfloat16>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, sf_vec, fmt8, stream);
+    else rc = gemm_dense_typed<float>(ai, bi, sfai, sfbi, ci, alpha, m, n, k, tile_n, sf_vec, fmt8, stream);
     if (rc) return rc;
   }
   return kOk;
@@ -512,6 +523,7 @@ int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* 
   p.m_rows = max_m_blocks * 128;
   p.n_cols = inter;
   p.k = hidden;
+  p.k_bytes = hidden / 2;
   p.rk = (hidden + 63) / 64;
   p.num_k_tiles = (hidden + kBlockK - 1) / kBlockK;
   p.num_n_blocks = inter / 128;
@@ -572,6 +584,7 @@ int gemm_moe_fc2_typed(const void* act_codes, const void* act_sf, const void* w2
   p.m_rows = max_m_blocks * 128;
   p.n_cols = hidden;
   p.k = inter;
+  p.k_bytes = inter / 2;
   p.rk = (inter + 63) / 64;
   p.num_k_tiles = (inter + kBlockK - 1) / kBlockK;
   p.b_row_tiles = (hidden + 127) / 128;
@@ -619,6 +632,7 @@ int gemm_moe_fc2_push(const void* act_codes, const void* act_sf, const void* w2,
   p.m_rows = max_m_blocks * 128;
   p.n_cols = hidden;
   p.k = inter;
+  p.k_bytes = inter / 2;
   p.rk = (inter + 63) / 64;
   p.num_k_tiles = (inter + kBlockK - 1) / kBlockK;
   p.b_row_tiles = (hidden + 127) / 128;

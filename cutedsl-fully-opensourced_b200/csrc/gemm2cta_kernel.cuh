@@ -133,7 +133,7 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       bool ok = true;
       const uint64_t a_desc0 = ptx::smem_desc_sw128(smem_base);
       const uint64_t b_desc0 = ptx::smem_desc_sw128(smem_base + kABytes);
-      const int last_kblocks = ((p.k - (p.num_k_tiles - 1) * kBlockK) + 63) >> 6;
+      const int last_kblocks = ((p.k_bytes - (p.num_k_tiles - 1) * 128) + 31) >> 5;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         if (!wait_bounded(acc_empty_bar, acc_phase ^ 1u, abort_flag)) {
           if (lane == 0) atomicOr(p.status, kStatusTimeoutMma);

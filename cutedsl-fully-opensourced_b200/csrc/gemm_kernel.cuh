@@ -100,9 +100,13 @@ struct GemmParams {
   // weight stream; item s of a tile hands its partial sums to the epilogue as "group" s (EpilogueStore adds
   // group * group_stride to the output pointer) and a small kernel sums the partial matrices afterwards.
   int k_splits;                // 0 or 1: off
-  // MXFP4 instead of NVFP4: one ue8m0 scale per 32 K-elements.  The scale tiles keep their 128x4 shape, so a
-  // 512-byte tile spans 128 K-elements (two per 256-wide stage instead of four) and rk counts those.
+  // Flavour of the block scaling.  0: NVFP4 (e2m1, e4m3 scale per 16 elements: four 512-byte scale tiles per stage).
+  // 1: MXFP4 (e2m1, ue8m0 scale per 32 elements: a tile spans 128 K-elements, two per stage).  2: MXFP8 (8-bit
+  // operands, 128 of them per 128-byte stage row, ue8m0 scale per 32: one tile per stage).  rk counts the tiles
+  // along K of the flavour; every flavour feeds the tensor core 32 bytes of K per row and instruction.
   int sf_block32;
+  int a_fmt8, b_fmt8;          // MXFP8: operand format codes (0 = e4m3, 1 = e5m2)
+  int k_bytes;                 // bytes of K per operand row (k / 2 for e2m1, k for 8-bit operands)
   // Expert-parallel launches synchronise with the other ranks inside the kernel instead of through extra
   // launches.  peer.wait_flags != null: every CTA's producer thread waits (bounded) until the signal words of all
   // ranks have reached this step before it issues its first load -- the operand rows were written by peers.
@@ -645,7 +649,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const uint32_t sb = sa + L.a_bytes;
           const uint32_t ssfa = sb + L.b_bytes;
           const uint32_t ssfb = ssfa + L.sfa_bytes;
-          const int tps = p.sf_block32 ? 2 : 4;                         // 512-byte scale tiles per stage
+          const int tps = 4 >> p.sf_block32;                            // 512-byte scale tiles per stage: 4, 2 or 1
           const int k_sf_tiles = min(tps, p.rk - tps * kt);
           const uint32_t sf_bytes = static_cast<uint32_t>(k_sf_tiles) * 512u;
           // the scale slabs go first and report to their own barrier: the movers carry them into tensor
@@ -684,7 +688,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       bool ok = true;
       const uint64_t a_desc0 = ptx::smem_desc_sw128(smem_base);
       const uint64_t b_desc0 = ptx::smem_desc_sw128(smem_base + L.a_bytes);
-      const int last_kblocks = ((p.k - (p.num_k_tiles - 1) * kBlockK) + 63) >> 6;   // 64-wide steps of the last K tile
+      const int last_kblocks = ((p.k_bytes - (p.num_k_tiles - 1) * 128) + 31) >> 5;   // 32-byte steps of the last K tile
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         if (!wait_bounded(acc_empty_bar(acc.stage), acc.phase ^ 1u, abort_flag)) {
           if (lane == 0) atomicOr(p.status, kStatusTimeoutMma);
@@ -713,7 +717,16 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
           const uint32_t sfa_t = tmem_base + kSfaCol + st.stage * kSfSetCols;
           const int kblocks = kt + 1 == p.num_k_tiles ? last_kblocks : 4;
           if (ptx::elect_one()) {
-            if (p.sf_block32) {
+            if (p.sf_block32 == 2) {
+              // one scale tile per stage; instruction kb reads byte kb of its columns
+#pragma unroll
+              for (int kb = 0; kb < 4; ++kb) {
+                if (kb < kblocks)
+                  ptx::mma_mxf8_block32(d_tmem, da + 2 * kb, db + 2 * kb,
+                                        ptx::idesc_mxf8_block32(kBlockN, p.a_fmt8, p.b_fmt8, kb), sfa_t, sfb_t,
+                                        (kt != kt_first || kb != 0) ? 1u : 0u);
+              }
+            } else if (p.sf_block32 == 1) {
               // a scale tile serves two instructions (bytes 0-1, then 2-3 of its columns)
 #pragma unroll
               for (int kb = 0; kb < 4; ++kb) {

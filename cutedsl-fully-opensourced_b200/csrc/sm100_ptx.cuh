@@ -169,6 +169,24 @@ __device__ __forceinline__ void mma_mxf4_block32(uint32_t d_tmem, uint64_t a_des
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
       : "memory");
 }
+// MXFP8: 8-bit operands (format code 0 = e4m3, 1 = e5m2), one ue8m0 scale per 32 K-elements = per instruction
+// (K = 32); the scale byte of an instruction is byte `sf_id` of its scale column.
+__host__ __device__ constexpr uint32_t idesc_mxf8_block32(int n, int a_fmt, int b_fmt, int sf_id) {
+  return (static_cast<uint32_t>(a_fmt) << 7) | (static_cast<uint32_t>(b_fmt) << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (1u << 23) /* ue8m0 scales */ | (static_cast<uint32_t>(128 >> 4) << 24) | (static_cast<uint32_t>(sf_id) << 29) |
+         (static_cast<uint32_t>(sf_id) << 4);
+}
+__device__ __forceinline__ void mma_mxf8_block32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n"
+      "}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
 // 32 rows x 16 bytes from shared memory, replicated into the four 32-lane quarters of TMEM
 __device__ __forceinline__ void tmem_cp_sf(uint32_t dst_tmem, uint64_t src_desc) {
   asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(dst_tmem), "l"(src_desc) : "memory");

@@ -39,11 +39,12 @@ class _DType:
 
 Float4E2M1FN = _DType("Float4E2M1FN", 4)
 Float8E4M3FN = _DType("Float8E4M3FN", 8, torch.float8_e4m3fn)
+Float8E5M2 = _DType("Float8E5M2", 8, torch.float8_e5m2)
 Float8E8M0FNU = _DType("Float8E8M0FNU", 8)
 Float16 = _DType("Float16", 16, torch.float16)
 BFloat16 = _DType("BFloat16", 16, torch.bfloat16)
 Float32 = _DType("Float32", 32, torch.float32)
-_BY_NAME = {d.name: d for d in (Float4E2M1FN, Float8E4M3FN, Float8E8M0FNU, Float16, BFloat16, Float32)}
+_BY_NAME = {d.name: d for d in (Float4E2M1FN, Float8E4M3FN, Float8E5M2, Float8E8M0FNU, Float16, BFloat16, Float32)}
 _C_CODES = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
 
 
@@ -130,10 +131,47 @@ def nvfp4_gemm(a: torch.Tensor, b: torch.Tensor, sfa: torch.Tensor, sfb: torch.T
     return out
 
 
+def mxfp8_gemm(a: torch.Tensor, b: torch.Tensor, sfa: torch.Tensor, sfb: torch.Tensor,
+               alpha: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+               out_dtype: torch.dtype = torch.bfloat16, tile_n: int = 0) -> torch.Tensor:
+    """MXFP8 flavour: A ``[M, K]`` and B ``[N, K]`` are ``torch.float8_e4m3fn`` or ``torch.float8_e5m2`` (each
+    operand its own format), scale factors ue8m0 bytes, one per 32 K-elements, in the 128x4 tiled layout
+    (``swizzled_sf_numel(rows, ceil(K / 32))`` bytes).  Same kernel family as ``nvfp4_gemm``; single-CTA tiles."""
+    fmts = {torch.float8_e4m3fn: 0, torch.float8_e5m2: 1}
+    if a.dtype not in fmts or b.dtype not in fmts:
+        raise ValueError("a and b must be float8_e4m3fn or float8_e5m2 tensors")
+    if not (a.is_cuda and b.is_cuda and sfa.is_cuda and sfb.is_cuda):
+        raise ValueError("operands must be CUDA tensors (there is no CPU implementation)")
+    a3, b3 = _as_lmk(a.view(torch.uint8), "a"), _as_lmk(b.view(torch.uint8), "b")
+    l, m, k = a3.shape
+    lb, n, kb_ = b3.shape
+    if lb != l or kb_ != k:
+        raise ValueError(f"a {tuple(a3.shape)} and b {tuple(b3.shape)} disagree on batch or K")
+    if k % 16 != 0 or n % 8 != 0:
+        raise ValueError("Invalid tensor alignment")
+    need_a = l * swizzled_sf_numel(m, ceil_div(k, 32))
+    need_b = l * swizzled_sf_numel(n, ceil_div(k, 32))
+    if sfa.element_size() != 1 or sfb.element_size() != 1 or sfa.numel() < need_a or sfb.numel() < need_b:
+        raise ValueError(f"scale factors must be 1-byte tensors in the 128x4 tiled layout ({need_a} and {need_b} bytes)")
+    if out is None:
+        out = torch.empty((m, n) if a.dim() == 2 else (l, m, n), dtype=out_dtype, device=a.device)
+    out3 = _as_lmk(out, "c")
+    if tuple(out3.shape) != (l, m, n) or out.dtype not in _C_CODES:
+        raise ValueError(f"c must be [{m}, {n}] (x{l}) in float16, bfloat16 or float32")
+    if alpha is not None and (alpha.dtype != torch.float32 or not alpha.is_cuda):
+        raise ValueError("alpha must be a float32 CUDA tensor")
+    with _lib.on_device(a.device):
+        _lib.check(_lib.lib.b200fp4_mxfp8_gemm(
+            a3.data_ptr(), b3.data_ptr(), sfa.data_ptr(), sfb.data_ptr(), out3.data_ptr(), _lib.ptr(alpha),
+            m, n, k, l, _C_CODES[out.dtype], tile_n, fmts[a.dtype], fmts[b.dtype], _lib.current_stream_ptr(a.device)))
+    return out
+
+
 class Sm120BlockScaledGemmKernel:
     """Same constructor and call signature as the demo's kernel class.  Implemented: f32 accumulate, e2m1 operands
     with sf_vec_size 16 and e4m3 scale factors (NVFP4, the configuration the reference exercises) or sf_vec_size 32
-    and ue8m0 scale factors (MXFP4), K-major A and B, N-major C."""
+    and ue8m0 scale factors (MXFP4), float8 operands with sf_vec_size 32 and ue8m0 scale factors (MXFP8; the operand
+    flavour is taken from the tensors' dtype), K-major A and B, N-major C."""
 
     def __init__(self, acc_dtype, sf_vec_size: int, tile_shape_mnk: Tuple[int, int, int], epi_tile: Tuple[int, int]):
         if _dtype_token(acc_dtype) is not Float32:
@@ -160,7 +198,12 @@ class Sm120BlockScaledGemmKernel:
             stream = torch.cuda.ExternalStream(int(stream))
         ctx = torch.cuda.stream(stream) if stream is not None else torch.cuda.stream(torch.cuda.current_stream())
         with ctx:
-            nvfp4_gemm(a, b, sfa, sfb, out=c, tile_n=self._tile_n, sf_vec_size=self.sf_vec_size)
+            if a.dtype in (torch.float8_e4m3fn, torch.float8_e5m2):        # MXFP8: 8-bit operands
+                if self.sf_vec_size != 32:
+                    raise NotImplementedError("8-bit operands take ue8m0 scale factors per 32 elements")
+                mxfp8_gemm(a, b, sfa, sfb, out=c, tile_n=self._tile_n)
+            else:
+                nvfp4_gemm(a, b, sfa, sfb, out=c, tile_n=self._tile_n, sf_vec_size=self.sf_vec_size)
         return c
 
 
@@ -179,9 +222,12 @@ def compile(gemm, a, b, sfa, sfb, c, max_active_clusters=None, stream=None):  # 
 _E2M1_OF_INT = {-2: 0xC, -1: 0xA, 0: 0x0, 1: 0x2}      # value -> e2m1 code
 
 
-def _integer_operand(rows: int, k: int, l: int, device) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Values in {-2,-1,0,1} (the demo's integer RANDOM init): returns ([L,rows,K/2] packed, [L,rows,K] f32)."""
+def _integer_operand(rows: int, k: int, l: int, device, dtype: Optional[_DType] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Values in {-2,-1,0,1} (the demo's integer RANDOM init): returns ([L,rows,K/2] packed e2m1 or [L,rows,K]
+    float8, [L,rows,K] f32)."""
     vals = torch.randint(-2, 2, (l, rows, k), device=device, dtype=torch.int32)
+    if dtype is not None and dtype.width == 8:
+        return vals.float().to(dtype.torch_dtype), vals.float()
     lut = torch.tensor([0xC, 0xA, 0x0, 0x2], dtype=torch.uint8, device=device)
     codes = lut[(vals + 2).long()]
     return pack_e2m1(codes), vals.float()
@@ -204,10 +250,13 @@ def run_bs(mnkl, a_dtype, b_dtype, sf_dtype, sf_vec_size, c_dtype, acc_dtype, a_
            use_cold_l2=False, **kwargs) -> float:
     m, n, k, l = mnkl
     a_dtype, b_dtype, sf_dtype, c_dtype = (_dtype_token(d) for d in (a_dtype, b_dtype, sf_dtype, c_dtype))
-    if (a_dtype, b_dtype, sf_dtype, sf_vec_size) not in ((Float4E2M1FN, Float4E2M1FN, Float8E4M3FN, 16),
-                                                         (Float4E2M1FN, Float4E2M1FN, Float8E8M0FNU, 32)):
-        raise NotImplementedError("implemented: Float4E2M1FN x Float4E2M1FN with Float8E4M3FN scales per 16 (NVFP4) "
-                                  "or Float8E8M0FNU scales per 32 (MXFP4)")
+    fp8 = (Float8E4M3FN, Float8E5M2)
+    if not ((a_dtype, b_dtype, sf_dtype, sf_vec_size) in ((Float4E2M1FN, Float4E2M1FN, Float8E4M3FN, 16),
+                                                          (Float4E2M1FN, Float4E2M1FN, Float8E8M0FNU, 32))
+            or (a_dtype in fp8 and b_dtype in fp8 and (sf_dtype, sf_vec_size) == (Float8E8M0FNU, 32))):
+        raise NotImplementedError("implemented: Float4E2M1FN x Float4E2M1FN with Float8E4M3FN scales per 16 (NVFP4) or "
+                                  "Float8E8M0FNU scales per 32 (MXFP4), and Float8E4M3FN / Float8E5M2 operands with "
+                                  "Float8E8M0FNU scales per 32 (MXFP8); mixed 4-bit x 8-bit operands are not")
     if (a_major, b_major, c_major) != ("k", "k", "n"):
         raise NotImplementedError("A and B must be K-major and C N-major")
     if c_dtype.torch_dtype not in _C_CODES:
@@ -221,8 +270,8 @@ def run_bs(mnkl, a_dtype, b_dtype, sf_dtype, sf_vec_size, c_dtype, acc_dtype, a_
     sets = max(1, min(10, iterations)) if use_cold_l2 else 1
 
     def make():
-        a, a_ref = _integer_operand(m, k, l, dev)
-        b, b_ref = _integer_operand(n, k, l, dev)
+        a, a_ref = _integer_operand(m, k, l, dev, a_dtype)
+        b, b_ref = _integer_operand(n, k, l, dev, b_dtype)
         sfa, sfa_ref = _integer_scales(m, k, l, dev, sf_vec_size)
         sfb, sfb_ref = _integer_scales(n, k, l, dev, sf_vec_size)
         c = torch.zeros(l, m, n, dtype=c_dtype.torch_dtype, device=dev)

@@ -90,6 +90,13 @@ int b200fp4_nvfp4_gemm_ws(const void* a, const void* b, const void* sfa, const v
 int b200fp4_mxfp4_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha,
                        int m, int n, int k, int l, int c_dtype, int tile_n, void* stream);
 
+/* MXFP8 flavour: A [l][m][k] and B [l][n][k] are 8-bit floats (e4m3, or e5m2 where a_e5m2 / b_e5m2 != 0), one ue8m0
+ * scale byte per 32 K-elements in 128x4 tiles ([l][ceil(rows/128)][ceil(k/128)][32][4][4]); k a multiple of 16.
+ * Single-CTA tiles only.  Stands in for the (Float8E4M3FN | Float8E5M2, ..., Float8E8M0FNU, 32) configurations of
+ *   .../blockscaled_gemm/blockscaled_gemm_dispatch.py:34-43. */
+int b200fp4_mxfp8_gemm(const void* a, const void* b, const void* sfa, const void* sfb, void* c, const float* alpha,
+                       int m, int n, int k, int l, int c_dtype, int tile_n, int a_e5m2, int b_e5m2, void* stream);
+
 /* Router: softmax over `experts` logits per token, the top_k largest probabilities (lowest index
  * first among equals), optionally renormalised to sum 1.  logits f32 [tokens, experts] ->
  * ids i32 [tokens, top_k], weights f32 [tokens, top_k].

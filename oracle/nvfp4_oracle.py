@@ -267,13 +267,31 @@ def e8m0_decode(bits) -> np.ndarray:
     return np.exp2(np.asarray(bits, dtype=np.int32).astype(F32) - F32(127.0)).astype(F32)
 
 
+def e5m2_decode(bits) -> np.ndarray:
+    """e5m2 bytes -> f32 (an e5m2 byte is the upper half of the IEEE binary16 with the same value)."""
+    return (np.asarray(bits, dtype=np.uint8).astype(np.uint16) << 8).view(np.float16).astype(F32)
+
+
+def gemm_mxfp8_ref(a_bits, sfa_bits, b_bits, sfb_bits, alpha: float = 1.0, a_e5m2: bool = False,
+                   b_e5m2: bool = False) -> torch.Tensor:
+    """MXFP8: 8-bit operands (e4m3 or e5m2 bytes) with one ue8m0 scale per 32 K-elements; de-quantise, f32 product."""
+    a = (e5m2_decode if a_e5m2 else e4m3_decode)(a_bits)
+    b = (e5m2_decode if b_e5m2 else e4m3_decode)(b_bits)
+    k = a.shape[-1]
+    a = torch.from_numpy(a * np.repeat(e8m0_decode(sfa_bits), 32, axis=-1)[..., :k])
+    b = torch.from_numpy(b * np.repeat(e8m0_decode(sfb_bits), 32, axis=-1)[..., :k])
+    c = a @ b.t()
+    return c * alpha if alpha != 1.0 else c
+
+
 def gemm_nvfp4_ref(a_codes, sfa_bits, b_codes, sfb_bits, alpha: float = 1.0, sf_vec: int = SF_BLOCK) -> torch.Tensor:
     """C[m,n] = alpha * sum_k (A*SFA)[m,k] * (B*SFB)[n,k]; operands are
     de-quantised to f32 first and multiplied in f32 (the demo's own check).
     sf_vec 16: e4m3 scale bytes per 16 elements (NVFP4); 32: ue8m0 scale bytes per 32 elements (MXFP4)."""
     decode = e4m3_decode if sf_vec == SF_BLOCK else e8m0_decode
-    a = torch.from_numpy(e2m1_decode(a_codes) * np.repeat(decode(sfa_bits), sf_vec, axis=-1))
-    b = torch.from_numpy(e2m1_decode(b_codes) * np.repeat(decode(sfb_bits), sf_vec, axis=-1))
+    k = np.asarray(a_codes).shape[-1]
+    a = torch.from_numpy(e2m1_decode(a_codes) * np.repeat(decode(sfa_bits), sf_vec, axis=-1)[..., :k])
+    b = torch.from_numpy(e2m1_decode(b_codes) * np.repeat(decode(sfb_bits), sf_vec, axis=-1)[..., :k])
     c = a @ b.t()
     return c * alpha if alpha != 1.0 else c
 

@@ -122,7 +122,9 @@ def test_alignment_and_argument_errors(b200):
     with pytest.raises(ValueError, match="Invalid tensor alignment"):
         g.run((128, 100, 128, 1), g.Float4E2M1FN, g.Float4E2M1FN, g.Float8E4M3FN, 16, g.Float16)
     with pytest.raises(NotImplementedError):
-        g.run((128, 128, 128, 1), g.Float8E4M3FN, g.Float8E4M3FN, g.Float8E8M0FNU, 32, g.Float16)      # MXFP8
+        g.run((128, 128, 128, 1), g.Float4E2M1FN, g.Float8E4M3FN, g.Float8E8M0FNU, 32, g.Float16)      # mixed 4 x 8 bit
+    with pytest.raises(NotImplementedError):
+        g.run((128, 128, 128, 1), g.Float8E4M3FN, g.Float8E4M3FN, g.Float8E4M3FN, 16, g.Float16)
     a = torch.zeros(128, 64, dtype=torch.uint8, device="cuda")
     sf = torch.zeros(512, dtype=torch.uint8, device="cuda")
     with pytest.raises(ValueError):
@@ -297,3 +299,45 @@ def test_mxfp4_through_the_demo_entry(b200):
                b_major="k", c_major="n", tile_shape_mnk=(128, 128, 128), epi_tile=(128, 128), tolerance=0.1,
                warmup_iterations=0, iterations=1, skip_ref_check=False)
     assert us > 0
+
+
+@pytest.mark.parametrize("m,n,k,tile_n", [(128, 128, 128, 128), (256, 384, 512, 0), (200, 264, 1168, 256), (128, 192, 2048, 64)])
+@pytest.mark.parametrize("a_e5m2,b_e5m2", [(False, False), (True, False), (True, True)])
+def test_mxfp8_block32_ue8m0(b200, m, n, k, tile_n, a_e5m2, b_e5m2):
+    """The MXFP8 flavours of the demo (8-bit operands, ue8m0 scale per 32 elements; blockscaled_gemm_dispatch.py:34-43):
+    random finite e4m3 / e5m2 bytes of moderate magnitude with random power-of-two scales; rel-L2 <= 1e-5 against the
+    de-quantised f32 product (summation order is the only difference)."""
+    rng = np.random.default_rng(m + n + k + a_e5m2 + 2 * b_e5m2)
+
+    def operand(rows, e5m2):
+        # exponent fields in the middle of the range (no inf / nan, no overflow of the f32 sums), random sign / mantissa
+        if e5m2:
+            exp = rng.integers(10, 18, size=(rows, k), dtype=np.uint8)
+            return (rng.integers(0, 2, size=(rows, k), dtype=np.uint8) << 7) | (exp << 2) | rng.integers(0, 4, size=(rows, k), dtype=np.uint8)
+        exp = rng.integers(3, 10, size=(rows, k), dtype=np.uint8)
+        return (rng.integers(0, 2, size=(rows, k), dtype=np.uint8) << 7) | (exp << 3) | rng.integers(0, 8, size=(rows, k), dtype=np.uint8)
+
+    ab, bb = operand(m, a_e5m2).astype(np.uint8), operand(n, b_e5m2).astype(np.uint8)
+    kb = -(-k // 32)
+    sfa = rng.integers(122, 131, size=(m, kb), dtype=np.uint8)
+    sfb = rng.integers(122, 131, size=(n, kb), dtype=np.uint8)
+    ref = O.gemm_mxfp8_ref(ab, sfa, bb, sfb, alpha=0.25, a_e5m2=a_e5m2, b_e5m2=b_e5m2)
+    a = torch.from_numpy(ab).cuda().view(torch.float8_e5m2 if a_e5m2 else torch.float8_e4m3fn)
+    b = torch.from_numpy(bb).cuda().view(torch.float8_e5m2 if b_e5m2 else torch.float8_e4m3fn)
+    sa = torch.from_numpy(O.swizzle_sf(sfa)).cuda()
+    sb = torch.from_numpy(O.swizzle_sf(sfb)).cuda()
+    c = b200.mxfp8_gemm(a, b, sa, sb, alpha=torch.tensor([0.25], device="cuda"), out_dtype=torch.float32, tile_n=tile_n)
+    torch.cuda.synchronize()
+    _check_status(b200)
+    err = torch.linalg.vector_norm(c.cpu() - ref) / torch.linalg.vector_norm(ref)
+    assert err <= 1e-5, float(err)
+
+
+def test_mxfp8_through_the_demo_entry(b200):
+    torch.manual_seed(0)
+    g = b200.gemm
+    for a_dt, b_dt in ((g.Float8E4M3FN, g.Float8E4M3FN), (g.Float8E5M2, g.Float8E4M3FN)):
+        us = g.run((256, 256, 512, 1), a_dt, b_dt, g.Float8E8M0FNU, 32, g.BFloat16, a_major="k", b_major="k",
+                   c_major="n", tile_shape_mnk=(128, 128, 128), epi_tile=(128, 128), tolerance=0.1,
+                   warmup_iterations=0, iterations=1, skip_ref_check=False)
+        assert us > 0
