@@ -199,6 +199,10 @@ class NormPart(Part):
         self.units_per_step = float(self.total_rows * self.hidden * self.bytes_per_element)
         per_set = max(1, self.alg_bytes)
         self.sets = max(4, math.ceil(3 * L2_BYTES / per_set) + 1)
+        # a rank's share of the rows takes less device time than an eager launch through Python costs on the host
+        # once the rows are split over several GPUs: those launches are replayed from CUDA graphs (one per set)
+        self.use_graph = self.rows <= 4096
+        self.graph_variants = self.sets
 
     def config(self, world):
         return {"workload": self.name, "rows": self.total_rows, "rows_per_gpu": self.total_rows // world,

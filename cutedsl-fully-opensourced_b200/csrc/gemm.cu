@@ -563,6 +563,15 @@ int fc2_epilogue_warps() {
   return n;
 }
 
+// B200FP4_FC2_WIDE=1 takes the 256-wide single-accumulator tiles for FC2 whatever the reduction length (experiment)
+bool fc2_force_wide() {
+  static const bool v = [] {
+    const char* e = getenv("B200FP4_FC2_WIDE");
+    return e != nullptr && atoi(e) != 0;
+  }();
+  return v;
+}
+
 // FC2: partial[row][h] = (Actq . W2[e]^T) * w2_alpha[e], stored as f32 or (rows_bf16) rounded to bf16.
 // The kernel is bound by what its epilogue can store (an SM writes some 16 bytes per cycle), so the
 // 16-bit rows nearly halve its time and the combine's.
@@ -572,7 +581,7 @@ int gemm_moe_fc2_typed(const void* act_codes, const void* act_sf, const void* w2
                        const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int few_rows,
                        int* status, cudaStream_t stream) {
   CUtensorMap ta, tb;
-  const bool wide = hidden % 256 == 0 && (inter + kBlockK - 1) / kBlockK > 4;
+  const bool wide = hidden % 256 == 0 && ((inter + kBlockK - 1) / kBlockK > 4 || fc2_force_wide());
   const bool small_a = few_rows != 0 && wide;
   int rc = make_operand_map(&ta, act_codes, static_cast<int64_t>(max_m_blocks) * 128, inter, 0, small_a ? 32 : 128);
   if (rc) return rc;
