@@ -549,7 +549,16 @@ int gemm_moe_fc1(const void* xq, const void* xq_sf, const void* w1, const void* 
     return launch_gemm<128, true>(ta, tb, tsfa, p, epi, max_m_blocks * p.num_n_blocks, stream);
   }
   if (small_a) return launch_gemm<256, true, 32>(ta, tb, tsfa, p, epi, max_m_blocks * p.num_n_blocks, stream);
-  return launch_gemm<256, true>(ta, tb, tsfa, p, epi, max_m_blocks * p.num_n_blocks, stream);
+  // Sixteen epilogue warps: each reads its 32 up and 32 gate columns in one go and hands the (single) accumulator
+  // back before any SwiGLU arithmetic, so the next tile's MMAs wait for a tensor-memory read only; with eight
+  // warps half of the arithmetic ran before the release (FC1 of the prefill shape: 104 us with eight, 91 with
+  // sixteen).  B200FP4_FC1_EPI=8 selects the eight-warp variant.
+  static const bool epi8 = [] {
+    const char* e = getenv("B200FP4_FC1_EPI");
+    return e != nullptr && atoi(e) == 8;
+  }();
+  if (epi8) return launch_gemm<256, true>(ta, tb, tsfa, p, epi, max_m_blocks * p.num_n_blocks, stream);
+  return launch_gemm<256, true, 128, 16>(ta, tb, tsfa, p, epi, max_m_blocks * p.num_n_blocks, stream);
 }
 
 // Epilogue warps of the 128-wide FC2 tiles (short reductions: three K steps per tile at the prefill shape, so the

@@ -110,16 +110,17 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
           const uint32_t ssfa = sb + kBBytes;
           const uint32_t ssfb = ssfa + kSfaBytes;
           const uint32_t bar = full_bar(st.stage) & ptx::kPeerBitMask;   // always the even CTA's barrier
-          if (rank == 0) ptx::mbar_expect_tx(full_bar(st.stage), 2 * (kABytes + kBBytes));
-          ptx::tma2_load_2d(sa, &tmap_a, kt * 128, m_tile * 128, bar);
-          ptx::tma2_load_3d(sb, &tmap_b, kt * 128, n_blk * 256 + static_cast<int>(rank) * 128, 0, bar);
-          // the scale slabs are consumed by this CTA's own mover warps: they report to a local barrier
+          // the scale slabs go first: this CTA's own mover warps (local barrier) carry them into tensor memory
+          // while the operand tiles are still on their way
           const uint32_t sbar = sf_loaded_bar(st.stage);
           ptx::mbar_expect_tx(sbar, kSfaBytes + 4096);
           ptx::tma_load_2d(ssfa, &tmap_sfa, 0, (m_tile * p.rk + 4 * kt) * 2, sbar);
 #pragma unroll
           for (int i = 0; i < 2; ++i)
             ptx::tma_load_2d(ssfb + i * 2048, &tmap_sfb, 0, ((n_blk * 2 + i) * p.rk + 4 * kt) * 2, sbar);
+          if (rank == 0) ptx::mbar_expect_tx(full_bar(st.stage), 2 * (kABytes + kBBytes));
+          ptx::tma2_load_2d(sa, &tmap_a, kt * 128, m_tile * 128, bar);
+          ptx::tma2_load_3d(sb, &tmap_b, kt * 128, n_blk * 256 + static_cast<int>(rank) * 128, 0, bar);
           st.advance(kStages);
         }
       }

@@ -36,7 +36,7 @@ constexpr int kBlockM = 128;
 constexpr int kBlockK = 256;                 // e2m1 elements per stage = 128 bytes per row
 // two single-thread roles (TMA, MMA) + the epilogue warps: four for 128-wide tiles (the second
 // accumulator hides the epilogue), eight for 256-wide tiles (one accumulator: drain it twice as fast)
-// (the SwiGLU epilogue is arithmetic-heavy: eight warps at either width)
+// (the SwiGLU epilogue is arithmetic-heavy: eight warps at either width, sixteen on request)
 __host__ __device__ constexpr int epilogue_warps(int block_n, bool swiglu = false, int forced = 0) {
   return forced != 0 ? forced : ((block_n == 256 || swiglu) ? 8 : 4);
 }
@@ -503,8 +503,9 @@ struct EpilogueSwiglu {
       const int kb = (j0 + c0) >> 4;          // even
       *reinterpret_cast<uint16_t*>(sf_tile + (kb & 3) + (kb >> 2) * 512) = static_cast<uint16_t>(sfpair);
     };
-    // (Reading the warp's whole share first -- 128 registers -- and releasing the accumulator before any of the
-    // arithmetic was measured slower: 116 against 103 us for FC1 of the prefill shape.)
+    // The accumulator is released after the warp's last read of it.  With sixteen warps (span = 32) that is
+    // before any arithmetic.  With eight, reading the whole share first -- 128 registers -- to release early was
+    // measured slower (116 against 103 us for FC1 of the prefill shape).
 #pragma unroll 1
     for (int c0 = part * span; c0 < (part + 1) * span; c0 += 32) {
       uint32_t up[32], gate[32];
