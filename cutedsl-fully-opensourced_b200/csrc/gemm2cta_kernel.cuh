@@ -13,9 +13,14 @@
 // tensor memory with tcgen05.st, each CTA for itself; they report to the even CTA).  No TMA multicast is used anywhere: every tile
 // is fetched by the CTA that needs it.  All waits are bounded as in the single-CTA kernel.
 //
-// Measured: no faster than the single-CTA kernel.  The B half that each tensor core reads from its peer's
-// shared memory appears to come through the same SM ingest path as the TMA loads (38 KB + 16 KB per K step
-// again), so without multicast loads the pair saves nothing; the kernel is kept as the tile_n = 512 option.
+// Measured at M = N = K = 8192 (cycle accounting of the MMA-issuing thread, -DB200FP4_ACCT): 720 cycles per K step
+// against 875 for the single-CTA kernel with 128 x 256 tiles (512 would keep the tensor pipe busy).  40 % of the
+// issuing thread's cycles go into issuing MMAs, 15 % into waiting for operand tiles and 26 % into waiting for
+// scale slabs that reach tensor memory after the operands have landed.  Tried against that slab wait, without
+// gain: a second group of mover warps (unchanged: one group keeps up); a slab ring of its own, twice as deep as
+// the operand ring, with the slabs requested five K steps early and held in the movers' registers until the
+// columns are free (slab wait down to 7 %, operand wait up to 45 %, 15 to 25 % slower overall); loading only A
+// (42 % fewer bytes per stage: 7 % faster, so the kernel is not bound by the bytes an SM can take in).
 #pragma once
 
 #include "gemm_kernel.cuh"
@@ -135,13 +140,24 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
       const uint64_t a_desc0 = ptx::smem_desc_sw128(smem_base);
       const uint64_t b_desc0 = ptx::smem_desc_sw128(smem_base + kABytes);
       const int last_kblocks = ((p.k_bytes - (p.num_k_tiles - 1) * 128) + 31) >> 5;
+      B200_ACCT(MmaAcct acct; acct.start();)
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        B200_ACCT(acct.skip();)
         if (!wait_bounded(acc_empty_bar, acc_phase ^ 1u, abort_flag)) {
           if (lane == 0) atomicOr(p.status, kStatusTimeoutMma);
           break;
         }
+        B200_ACCT(acct.mark(acct.acc); ++acct.tiles;)
         ptx::tc_fence_after_sync();
         for (int kt = 0; kt < p.num_k_tiles; ++kt) {
+#ifdef B200FP4_ACCT
+          acct.skip();
+          wait_bounded(full_bar(st.stage), st.phase, abort_flag);
+          acct.mark(acct.full);
+          wait_bounded(sf_full_bar(st.stage), st.phase, abort_flag);
+          acct.mark(acct.sf);
+          ++acct.ksteps;
+#endif
           if (!wait_bounded(sf_full_bar(st.stage), st.phase, abort_flag) ||
               !wait_bounded(full_bar(st.stage), st.phase, abort_flag)) {
             if (lane == 0) atomicOr(p.status, kStatusTimeoutMma);
@@ -164,15 +180,24 @@ nvfp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_
             ptx::tc2_commit_mcast(empty_bar(st.stage), 3);      // frees the stage in both CTAs
           }
           __syncwarp();
+          B200_ACCT(acct.mark(acct.issue);)
           st.advance(kStages);
         }
         if (ok && ptx::elect_one()) ptx::tc2_commit_mcast(acc_full_bar, 3);   // accumulators of both CTAs are complete
         __syncwarp();
         acc_phase ^= 1u;
       }
+#ifdef B200FP4_ACCT
+      if (lane == 0 && (pair == 3 || pair == 50))
+        printf("acct pair %d: tiles %d ksteps %d cycles %lld = accumulator wait %lld + operand wait %lld + slab wait %lld + "
+               "issue %lld + other\n",
+               pair, acct.tiles, acct.ksteps, clock64() - acct.begin, acct.acc, acct.full, acct.sf, acct.issue);
+#endif
     }
   } else if (warp >= 10) {
     // =============================== scale-slab movers (both CTAs) ===============================
+    // (A second group of four mover warps taking every other K step changed nothing: the slabs are late because
+    // the stage's bytes are, not because one group cannot keep up.)
     const int quarter = warp & 3;
     PipeState st;
     bool ok = true;

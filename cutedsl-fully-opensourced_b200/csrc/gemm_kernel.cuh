@@ -27,6 +27,9 @@
 // expiry the kernel raises a flag in the status word and all roles leave.
 #pragma once
 
+#ifdef B200FP4_ACCT
+#include <cstdio>
+#endif
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
@@ -174,6 +177,27 @@ __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity, vola
     }
   }
 }
+
+// Cycle accounting of the MMA-issuing thread (builds with -DB200FP4_ACCT only; two CTAs print one line per launch):
+// where its cycles go -- waiting for a free accumulator, for the operand tiles, for the scale slabs, or issuing.
+// The issue of an MMA blocks while the tensor pipe's queue is full, so "issue" approaches the execution time of
+// the MMAs when they run back to back.
+#ifdef B200FP4_ACCT
+struct MmaAcct {
+  long long acc = 0, full = 0, first = 0, sf = 0, issue = 0, t = 0, begin = 0;
+  int tiles = 0, ksteps = 0;
+  __device__ __forceinline__ void start() { begin = t = clock64(); }
+  __device__ __forceinline__ void mark(long long& bucket) {
+    const long long now = clock64();
+    bucket += now - t;
+    t = now;
+  }
+  __device__ __forceinline__ void skip() { t = clock64(); }
+};
+#define B200_ACCT(x) x
+#else
+#define B200_ACCT(x)
+#endif
 
 // ----------------------------------------------------------------------------
 // Epilogue functors.  operator() is called by the 128 epilogue threads once per
@@ -690,11 +714,14 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
       const uint64_t a_desc0 = ptx::smem_desc_sw128(smem_base);
       const uint64_t b_desc0 = ptx::smem_desc_sw128(smem_base + L.a_bytes);
       const int last_kblocks = ((p.k_bytes - (p.num_k_tiles - 1) * 128) + 31) >> 5;   // 32-byte steps of the last K tile
+      B200_ACCT(MmaAcct acct; acct.start();)
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        B200_ACCT(acct.skip();)
         if (!wait_bounded(acc_empty_bar(acc.stage), acc.phase ^ 1u, abort_flag)) {
           if (lane == 0) atomicOr(p.status, kStatusTimeoutMma);
           break;
         }
+        B200_ACCT(acct.mark(acct.acc); ++acct.tiles;)
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc.stage * kBlockN;
         // a 64-wide tile uses half of a 128-row slab of B scale factors: its row groups start at column 0 or 2
@@ -705,6 +732,20 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
         for (int kt = kt_first, kt_end = tile_kt1(tile); kt < kt_end; ++kt) {
           // the slab movers have put this stage's scale factors into its set of TMEM columns (usually long
           // before the operands land), and the operand tiles are in shared memory
+#ifdef B200FP4_ACCT
+          acct.skip();
+          wait_bounded(full_bar(st.stage), st.phase, abort_flag);
+          if (kt == kt_first) {
+            const long long before = acct.full;
+            acct.mark(acct.full);
+            acct.first += acct.full - before;
+          } else {
+            acct.mark(acct.full);
+          }
+          wait_bounded(sf_full_bar(st.stage), st.phase, abort_flag);
+          acct.mark(acct.sf);
+          ++acct.ksteps;
+#endif
           if (!wait_bounded(sf_full_bar(st.stage), st.phase, abort_flag) ||
               !wait_bounded(full_bar(st.stage), st.phase, abort_flag)) {
             if (lane == 0) atomicOr(p.status, kStatusTimeoutMma);
@@ -747,12 +788,20 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
             ptx::tc_commit(empty_bar(st.stage));        // stage reusable once these MMAs have read it
           }
           __syncwarp();
+          B200_ACCT(acct.mark(acct.issue);)
           st.advance(kStages);
         }
         if (ok && ptx::elect_one()) ptx::tc_commit(acc_full_bar(acc.stage));
         __syncwarp();
         acc.advance(kAccStages);
       }
+#ifdef B200FP4_ACCT
+      if (lane == 0 && (blockIdx.x == 3 || blockIdx.x == 100))
+        printf("acct cta %d tile_n %d swiglu %d epi_warps %d: tiles %d ksteps %d cycles %lld = accumulator wait %lld + "
+               "operand wait %lld (first K step of a tile %lld) + slab wait %lld + issue %lld + other\n",
+               blockIdx.x, kBlockN, kSwigluB ? 1 : 0, kEpiWarps, acct.tiles, acct.ksteps, clock64() - acct.begin, acct.acc,
+               acct.full, acct.first, acct.sf, acct.issue);
+#endif
     }
   } else if (warp >= kFirstSfWarp && warp < kFirstSfWarp + 4) {
     // =============================== scale-slab movers ===============================
