@@ -20,7 +20,10 @@
 // gain: a second group of mover warps (unchanged: one group keeps up); a slab ring of its own, twice as deep as
 // the operand ring, with the slabs requested five K steps early and held in the movers' registers until the
 // columns are free (slab wait down to 7 %, operand wait up to 45 %, 15 to 25 % slower overall); loading only A
-// (42 % fewer bytes per stage: 7 % faster, so the kernel is not bound by the bytes an SM can take in).
+// (42 % fewer bytes per stage: 7 % faster, so the kernel is not bound by the bytes an SM can take in); two groups
+// of movers that each carry two of a stage's four K blocks and report to barriers of their own, the MMAs of
+// blocks 2-3 issued after a second wait (the extra wait, fence and election in the issuing thread cost more than
+// the shorter slab chain saves: 17 % slower).
 #pragma once
 
 #include "gemm_kernel.cuh"
