@@ -425,18 +425,38 @@ moe_quant_place_kernel(const __nv_bfloat16* __restrict__ x, const int* __restric
 // kernels, which is most of a decode step's bookkeeping time.  Rows of an expert go to its slots in slot order.
 // rows_per_block: valid rows that a 128-row block may hold.  128 normally; 32 for the few-row GEMM variants, which
 // load only the first 32 rows of every block (an expert with more rows than that simply gets more blocks).
-__global__ void __launch_bounds__(1024) moe_prepare_small_kernel(const int* __restrict__ ids, int n_slots, int expert_lo,
-                                                                 MoeHeader h, int experts, int max_m_blocks,
-                                                                 int max_rows, int rows_per_block) {
+// kRoutePerLane > 0: the router runs here first (one warp per token, the CTA's 32 warps take the tokens in turn;
+// experts per lane as in route_one_token) and writes its choice to ids / weights -- one launch fewer in a decode
+// step.  0: the ids are inputs.
+template <int kRoutePerLane>
+__global__ void __launch_bounds__(1024)
+moe_prepare_small_kernel(const float* __restrict__ logits, int route_experts, int renormalize, int top_k, int* ids,
+                         float* weights, int n_slots, int expert_lo, MoeHeader h, int experts, int max_m_blocks,
+                         int max_rows, int rows_per_block) {
   __shared__ int s_count[1024];
   __shared__ int s_blocks[1024];
   __shared__ int s_offset[1024];
   __shared__ int s_expert[1024];
   const int t = threadIdx.x;
   s_count[t] = 0;
+  if constexpr (kRoutePerLane > 0) {
+    const int lane = t & 31;
+    for (int token = t >> 5; token * top_k < n_slots; token += 32) {
+      int my_id;
+      float my_w;
+      route_one_token<kRoutePerLane>(logits + static_cast<int64_t>(token) * route_experts, lane, route_experts, top_k,
+                                     renormalize, my_id, my_w);
+      if (lane < top_k) {
+        ids[token * top_k + lane] = my_id;
+        weights[token * top_k + lane] = my_w;
+        s_blocks[token * top_k + lane] = my_id;          // handed to the slot's thread below
+      }
+    }
+    __syncthreads();
+  }
   int e = -1, rank_in_expert = 0;
   if (t < n_slots) {
-    e = ids[t] - expert_lo;
+    e = (kRoutePerLane > 0 ? s_blocks[t] : ids[t]) - expert_lo;
     if (e < 0 || e >= experts) e = -1;
   }
   s_expert[t] = e;
@@ -821,12 +841,25 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
     B200_CUDA(cudaMemsetAsync(ws.xq_sf, 0, ws.xq_sf_bytes, stream));    // rows that only pad a block read as zero
     // few slots: one CTA counts, scans and assigns rows in slot order; quantisation splits a token's columns
     // over several CTAs (a decode step is mostly the latency of these small kernels)
-    if (logits != nullptr) {
+#define B200_PREPARE(PL)                                                                                          \
+  moe_prepare_small_kernel<PL><<<1, 1024, 0, stream>>>(logits, route_experts, renormalize, top_k, ids, route_w, slots, \
+                                                       expert_lo, ws.h, experts, ws.max_m_blocks, max_rows,          \
+                                                       few_rows ? 32 : 128)
+    if (logits == nullptr) {
+      B200_PREPARE(0);
+    } else if (route_experts <= 64) {
+      B200_PREPARE(2);
+    } else if (route_experts <= 128) {
+      B200_PREPARE(4);
+    } else if (route_experts <= 256) {
+      B200_PREPARE(8);
+    } else {
+      // more experts per lane than the 64 registers of a 1024-thread CTA hold: the router keeps its own launch
       int rc = route_topk(logits, ids, route_w, static_cast<int>(tokens), route_experts, top_k, renormalize, stream);
       if (rc) return rc;
+      B200_PREPARE(0);
     }
-    moe_prepare_small_kernel<<<1, 1024, 0, stream>>>(ids, slots, expert_lo, ws.h, experts, ws.max_m_blocks, max_rows,
-                                                     few_rows ? 32 : 128);
+#undef B200_PREPARE
     const int parts = std::max(1, std::min(8, (hidden / 16) / 128));
     moe_scatter_quant_rows_kernel<128><<<dim3(static_cast<unsigned>(tokens), parts), 128, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(x), ws.h.slot_row, ws.xq, ws.xq_sf, hidden, top_k);
