@@ -36,11 +36,11 @@ SIGNATURES = {
     "b200fp4_moe_fused_noalloc": (_i32, [_vp] * 11 + [_i64, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
     "b200fp4_moe_ep_buffer_bytes": (_sz, [_i64, _i32, _i32, _i32, _i32, _i32]),
     "b200fp4_moe_ep_reset": (_i32, [_vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp]),
-    "b200fp4_moe_ep_dispatch": (_i32, [_vp, _vp, _vp, _i32, _vp, _i32, _i32, _i64, _i32, _i32, _i32, _i32, _f64, _vp]),
-    "b200fp4_moe_ep_dispatch_count": (_i32, [_vp, _vp, _vp, _i32, _vp, _i32, _i32, _i64, _i32, _i32, _i32, _i32, _f64, _vp]),
-    "b200fp4_moe_ep_dispatch_place": (_i32, [_vp, _vp, _vp, _i32, _vp, _i32, _i32, _i64, _i32, _i32, _i32, _i32, _f64, _vp]),
-    "b200fp4_moe_ep_compute": (_i32, [_vp, _i32, _i32] + [_vp] * 7 + [_i64, _i32, _i32, _i32, _i32, _f64, _vp]),
-    "b200fp4_moe_ep_combine": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _f64, _vp]),
+    "b200fp4_moe_ep_dispatch": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _i32, _i32, _i64, _i32, _i32, _i32, _i32, _i32, _f64, _vp]),
+    "b200fp4_moe_ep_dispatch_count": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _i32, _i32, _i64, _i32, _i32, _i32, _i32, _i32, _f64, _vp]),
+    "b200fp4_moe_ep_dispatch_place": (_i32, [_vp, _vp, _vp, _vp, _i32, _vp, _i32, _i32, _i64, _i32, _i32, _i32, _i32, _i32, _f64, _vp]),
+    "b200fp4_moe_ep_compute": (_i32, [_vp, _i32, _i32] + [_vp] * 7 + [_i64, _i32, _i32, _i32, _i32, _i32, _f64, _vp]),
+    "b200fp4_moe_ep_combine": (_i32, [_vp, _i32, _i32, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _f64, _vp]),
     "b200fp4_moe_ep_routing": (_i32, [_vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp]),
     "b200fp4_selftest_peer_wait": (_i32, [_vp, _i32, _f64, _i64, _i32, _i32, _i32, _i32, _vp]),
     "b200fp4_selftest_bounded_wait": (_i32, [C.c_longlong, _vp, _vp]),

@@ -48,16 +48,17 @@ int bounded_wait_selftest(long long limit_cycles, int* gave_up_dev, cudaStream_t
 size_t moe_ep_buffer_bytes(int64_t tokens_local, int hidden, int inter, int experts_local, int top_k, int world);
 int moe_ep_reset(void* own_buffer, int64_t tokens_local, int hidden, int inter, int experts_local, int top_k,
                  int world, cudaStream_t stream);
-int moe_ep_dispatch(const void* x, const int* ids, const float* logits, int route_experts, int renormalize,
-                    const void* const* peer_buffers, int rank, int world, int64_t tokens_local, int hidden, int inter,
-                    int experts_local, int top_k, double wait_ms, int phases, int* status, cudaStream_t stream);
+int moe_ep_dispatch(const void* x, const int* ids, const float* weights, const float* logits, int route_experts,
+                    int renormalize, const void* const* peer_buffers, int rank, int world, int64_t tokens_local,
+                    int hidden, int inter, int experts_local, int top_k, int return_mode, double wait_ms, int phases,
+                    int* status, cudaStream_t stream);
 int moe_ep_compute(const void* const* peer_buffers, int rank, int world, const void* w1, const void* w1_sf,
                    const void* w2, const void* w2_sf, const float* w1_alpha, const float* w2_alpha,
                    const float* fc2_input_scale, int64_t tokens_local, int hidden, int inter, int experts_local,
-                   int top_k, double wait_ms, int* status, cudaStream_t stream);
+                   int top_k, int return_mode, double wait_ms, int* status, cudaStream_t stream);
 int moe_ep_combine(const void* const* peer_buffers, int rank, int world, const int* ids, const float* weights,
                    void* out, int64_t tokens_local, int hidden, int inter, int experts_local, int top_k,
-                   double wait_ms, int* status, cudaStream_t stream);
+                   int return_mode, double wait_ms, int* status, cudaStream_t stream);
 int moe_ep_routing(const void* own_buffer, int* ids_out, float* weights_out, int64_t tokens_local, int hidden,
                    int inter, int experts_local, int top_k, int world, cudaStream_t stream);
 int moe_ep_wait_selftest(void* own_buffer, int world, double wait_ms, int64_t tokens_local, int hidden, int inter,
@@ -172,61 +173,67 @@ int b200fp4_moe_ep_reset(void* own_buffer, int64_t tokens_local, int hidden, int
                       static_cast<cudaStream_t>(stream));
 }
 
-static int ep_dispatch_phases(const void* x, const int* ids, const float* logits, int renormalize,
+static int ep_dispatch_phases(const void* x, const int* ids, const float* scales, const float* logits, int renormalize,
                               const void* const* peer_buffers, int rank, int world, int64_t tokens_local, int hidden,
-                              int intermediate, int local_experts, int top_k, double wait_ms, int phases, void* stream) {
+                              int intermediate, int local_experts, int top_k, int return_mode, double wait_ms,
+                              int phases, void* stream) {
   int* status = nullptr;
   int rc = device_status_word(&status);
   if (rc) return rc;
-  return moe_ep_dispatch(x, ids, logits, local_experts * world, renormalize, peer_buffers, rank, world, tokens_local,
-                         hidden, intermediate, local_experts, top_k, wait_ms, phases, status,
+  return moe_ep_dispatch(x, ids, scales, logits, local_experts * world, renormalize, peer_buffers, rank, world,
+                         tokens_local, hidden, intermediate, local_experts, top_k, return_mode, wait_ms, phases, status,
                          static_cast<cudaStream_t>(stream));
 }
 
-int b200fp4_moe_ep_dispatch(const void* x, const int* token_selected_experts, const float* router_logits,
-                            int renormalize, const void* const* peer_buffers, int rank, int world,
+int b200fp4_moe_ep_dispatch(const void* x, const int* token_selected_experts, const float* token_final_scales,
+                            const float* router_logits, int renormalize, const void* const* peer_buffers, int rank, int world,
                             int64_t tokens_local, int hidden, int intermediate, int local_experts, int top_k,
-                            double wait_ms, void* stream) {
-  return ep_dispatch_phases(x, token_selected_experts, router_logits, renormalize, peer_buffers, rank, world,
-                            tokens_local, hidden, intermediate, local_experts, top_k, wait_ms, 3, stream);
+                            int return_mode, double wait_ms, void* stream) {
+  return ep_dispatch_phases(x, token_selected_experts, token_final_scales, router_logits, renormalize, peer_buffers,
+                            rank, world, tokens_local, hidden, intermediate, local_experts, top_k, return_mode, wait_ms,
+                            3, stream);
 }
 
-int b200fp4_moe_ep_dispatch_count(const void* x, const int* token_selected_experts, const float* router_logits,
-                                  int renormalize, const void* const* peer_buffers, int rank, int world,
+int b200fp4_moe_ep_dispatch_count(const void* x, const int* token_selected_experts, const float* token_final_scales,
+                                  const float* router_logits, int renormalize, const void* const* peer_buffers, int rank, int world,
                                   int64_t tokens_local, int hidden, int intermediate, int local_experts, int top_k,
-                                  double wait_ms, void* stream) {
-  return ep_dispatch_phases(x, token_selected_experts, router_logits, renormalize, peer_buffers, rank, world,
-                            tokens_local, hidden, intermediate, local_experts, top_k, wait_ms, 1, stream);
+                                  int return_mode, double wait_ms, void* stream) {
+  return ep_dispatch_phases(x, token_selected_experts, token_final_scales, router_logits, renormalize, peer_buffers,
+                            rank, world, tokens_local, hidden, intermediate, local_experts, top_k, return_mode, wait_ms,
+                            1, stream);
 }
 
-int b200fp4_moe_ep_dispatch_place(const void* x, const int* token_selected_experts, const float* router_logits,
-                                  int renormalize, const void* const* peer_buffers, int rank, int world,
+int b200fp4_moe_ep_dispatch_place(const void* x, const int* token_selected_experts, const float* token_final_scales,
+                                  const float* router_logits, int renormalize, const void* const* peer_buffers, int rank, int world,
                                   int64_t tokens_local, int hidden, int intermediate, int local_experts, int top_k,
-                                  double wait_ms, void* stream) {
-  return ep_dispatch_phases(x, token_selected_experts, router_logits, renormalize, peer_buffers, rank, world,
-                            tokens_local, hidden, intermediate, local_experts, top_k, wait_ms, 2, stream);
+                                  int return_mode, double wait_ms, void* stream) {
+  return ep_dispatch_phases(x, token_selected_experts, token_final_scales, router_logits, renormalize, peer_buffers,
+                            rank, world, tokens_local, hidden, intermediate, local_experts, top_k, return_mode, wait_ms,
+                            2, stream);
 }
 
 int b200fp4_moe_ep_compute(const void* const* peer_buffers, int rank, int world, const void* w1, const void* w1_sf,
                            const void* w2, const void* w2_sf, const float* w1_alpha, const float* w2_alpha,
                            const float* fc2_input_scale, int64_t tokens_local, int hidden, int intermediate,
-                           int local_experts, int top_k, double wait_ms, void* stream) {
+                           int local_experts, int top_k, int return_mode, double wait_ms, void* stream) {
   int* status = nullptr;
   int rc = device_status_word(&status);
   if (rc) return rc;
   return moe_ep_compute(peer_buffers, rank, world, w1, w1_sf, w2, w2_sf, w1_alpha, w2_alpha, fc2_input_scale,
-                        tokens_local, hidden, intermediate, local_experts, top_k, wait_ms, status,
+                        tokens_local, hidden, intermediate, local_experts, top_k, return_mode, wait_ms, status,
                         static_cast<cudaStream_t>(stream));
 }
 
 int b200fp4_moe_ep_combine(const void* const* peer_buffers, int rank, int world, const int* token_selected_experts,
                            const float* token_final_scales, void* out, int64_t tokens_local, int hidden,
-                           int intermediate, int local_experts, int top_k, double wait_ms, void* stream) {
+                           int intermediate, int local_experts, int top_k, int return_mode, double wait_ms,
+                           void* stream) {
   int* status = nullptr;
   int rc = device_status_word(&status);
   if (rc) return rc;
   return moe_ep_combine(peer_buffers, rank, world, token_selected_experts, token_final_scales, out, tokens_local,
-                        hidden, intermediate, local_experts, top_k, wait_ms, status, static_cast<cudaStream_t>(stream));
+                        hidden, intermediate, local_experts, top_k, return_mode, wait_ms, status,
+                        static_cast<cudaStream_t>(stream));
 }
 
 int b200fp4_moe_ep_routing(const void* own_buffer, int* ids_out, float* weights_out, int64_t tokens_local, int hidden,

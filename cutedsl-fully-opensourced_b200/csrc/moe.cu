@@ -155,6 +155,9 @@ struct MoeHeader {           // all int32, contiguous
 struct Exchange {
   PeerPtrs peers;
   size_t flags, counts_all, xq, xq_sf, row_tag;      // offsets inside a rank's buffer (written by peers)
+  // per-rank return (see the expert-parallel section): [source rank][slot] row at this rank (-1: not served
+  // here) and routing weight of every (token, slot) of every rank; 0 = per-slot return, nothing is written
+  size_t inv_row, inv_w;
   int rank, world, experts_local;
   int xq_sf_pitch;            // bytes between the rows of scale bytes of the FC1 operand (plain rows, see place)
   unsigned long long wait_ns;
@@ -297,7 +300,8 @@ __global__ void __launch_bounds__(kThreads)
 moe_quant_place_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ ids,
                        const int* __restrict__ slot_pos, Exchange ex, int tokens, int hidden, int top_k,
                        int expert_lo, int experts_total, int max_m_blocks, int rows_per_block, int* slot_row,
-                       int* num_m_blocks, int* m_block_expert, int* m_block_rows, int* ctrl, int* status) {
+                       int* num_m_blocks, int* m_block_expert, int* m_block_rows, int* ctrl, int* status,
+                       const float* __restrict__ weights) {
   extern __shared__ int s_dyn[];
   int* s_base = s_dyn;                       // blocks before expert e (over all experts, in expert order)
   int* s_myoff = s_dyn + experts_total;      // rows of lower ranks inside expert e's segment
@@ -389,6 +393,13 @@ moe_quant_place_kernel(const __nv_bfloat16* __restrict__ x, const int* __restric
       s_rows[warp][j] = row;
       s_dst[warp][j] = d;
       if (slot_row != nullptr) slot_row[slot] = row;
+      if (ex.inv_row != 0) {
+        // per-rank return: every rank learns which of its rows (if any) holds this slot, the owner also its weight
+        const int64_t idx = static_cast<int64_t>(ex.rank) * tokens * top_k + slot;
+        for (int q = 0; q < ex.world; ++q)
+          reinterpret_cast<int*>(ex.peers.p[q] + ex.inv_row)[idx] = (q == d && row >= 0) ? row : -1;
+        if (row >= 0) reinterpret_cast<float*>(ex.peers.p[d] + ex.inv_w)[idx] = weights[slot];
+      }
     }
     __syncwarp();
     const __nv_bfloat16* xrow = x + static_cast<int64_t>(token) * hidden;
@@ -757,13 +768,13 @@ int launch_count(const float* logits, int route_experts, int renormalize, const 
 int launch_place(const void* x, const int* ids, const int* slot_pos, const Exchange& ex, int tokens, int hidden,
                  int top_k, int expert_lo, int experts_total, int max_m_blocks, int rows_per_block, int* slot_row,
                  int* num_m_blocks, int* m_block_expert, int* m_block_rows, int* ctrl, int* status,
-                 cudaStream_t stream) {
+                 cudaStream_t stream, const float* weights = nullptr) {
   // eight warps per CTA, one token per warp at a time; enough CTAs that every SM holds several
   const int grid = std::max(1, std::min((tokens + 7) / 8, 6 * sm_count_of_current_device()));
   const size_t smem = sizeof(int) * 3 * experts_total;
   moe_quant_place_kernel<256><<<grid, 256, smem, stream>>>(
       static_cast<const __nv_bfloat16*>(x), ids, slot_pos, ex, tokens, hidden, top_k, expert_lo, experts_total,
-      max_m_blocks, rows_per_block, slot_row, num_m_blocks, m_block_expert, m_block_rows, ctrl, status);
+      max_m_blocks, rows_per_block, slot_row, num_m_blocks, m_block_expert, m_block_rows, ctrl, status, weights);
   return check_cuda(cudaGetLastError(), "moe_quant_place_kernel launch");
 }
 
@@ -949,9 +960,9 @@ namespace {
 
 struct EpLayout {
   // written by peers
-  size_t flags, counts_all, xq_sf, xq, row_tag, recv;
+  size_t flags, counts_all, xq_sf, xq, row_tag, recv, inv_row, inv_w;
   // private to the rank
-  size_t ctrl, my_counts, slot_pos, ids, weights, num_m_blocks, m_block_expert, m_block_rows, act_sf, act;
+  size_t ctrl, my_counts, slot_pos, ids, weights, num_m_blocks, m_block_expert, m_block_rows, act_sf, act, partial;
   size_t xq_sf_bytes, total;
   int max_m_blocks, rows_per_block, xq_sf_pitch;
 };
@@ -979,8 +990,12 @@ EpLayout ep_layout(int64_t tokens_local, int hidden, int inter, int experts_loca
   L.xq_sf = take(L.xq_sf_bytes);
   L.xq = take(static_cast<size_t>(rows) * (hidden / 2));
   L.row_tag = take(sizeof(int) * rows);
-  // per-slot output rows cross NVLink and are summed as bf16 rows (f32 accumulation in the combine)
-  L.recv = take(static_cast<size_t>(slots_local) * hidden * sizeof(__nv_bfloat16));
+  // output rows cross NVLink as bf16 rows (f32 accumulation in the combine): one per slot, or one per (token,
+  // rank that serves some of the token's slots)
+  L.recv = take(static_cast<size_t>(std::max<int64_t>(slots_local, tokens_local * world)) * hidden *
+                sizeof(__nv_bfloat16));
+  L.inv_row = take(sizeof(int) * slots);
+  L.inv_w = take(sizeof(float) * slots);
   L.ctrl = take(sizeof(int) * kCtrlWords);
   L.my_counts = take(sizeof(int) * experts_total);
   L.slot_pos = take(sizeof(int) * slots_local);
@@ -991,6 +1006,8 @@ EpLayout ep_layout(int64_t tokens_local, int hidden, int inter, int experts_loca
   L.m_block_rows = take(sizeof(int) * blocks);
   L.act_sf = take(static_cast<size_t>(blocks) * ((inter + 63) / 64) * 512);
   L.act = take(static_cast<size_t>(rows) * (inter / 2));
+  // FC2's rows before they are summed per (source rank, token) (per-rank return only)
+  L.partial = take(static_cast<size_t>(rows) * hidden * sizeof(__nv_bfloat16));
   L.total = off;
   return L;
 }
@@ -1079,6 +1096,126 @@ __global__ void ep_combine_kernel(const __nv_bfloat16* __restrict__ recv, const 
   }
 }
 
+// Per-rank return, expert side.  One warp per (source rank r, token t of r): the rows of this rank that hold slots
+// of that token (inv_row, written by r's place kernel) are summed with their routing weights in f32 in slot order,
+// rounded to bf16 once and stored as ONE row into r's landing zone at [t][this rank] -- over NVLink when r is a
+// peer.  A token whose top_k experts sit on few ranks sends few rows home instead of top_k.  A lane owns eight
+// 16-byte pieces of a 2048-element segment at a time, so eight loads per row are in flight.  Persistent grid: every
+// CTA fences its remote stores once; the last one raises signal 2 at every rank.
+__global__ void __launch_bounds__(256)
+ep_presum_push_kernel(const __nv_bfloat16* __restrict__ partial, const int* __restrict__ inv_row,
+                      const float* __restrict__ inv_w, Exchange ex, size_t recv_off, int tokens_local, int hidden,
+                      int top_k, int* ctrl) {
+  __shared__ int s_flag;
+  const int lane = threadIdx.x & 31;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int pairs = tokens_local * ex.world;
+  const bool live = *reinterpret_cast<volatile int*>(ctrl + kCtrlAbort) == 0;
+  for (int pair = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; pair < pairs && live; pair += warps) {
+    const int r = pair % ex.world;                     // neighbouring warps send to different ranks
+    const int t = pair / ex.world;
+    int row = -1;
+    float w = 0.0f;
+    if (lane < top_k) {
+      const int64_t idx = (static_cast<int64_t>(r) * tokens_local + t) * top_k + lane;
+      row = inv_row[idx];
+      if (row >= 0) w = inv_w[idx];
+    }
+    const unsigned served = __ballot_sync(0xffffffffu, row >= 0);
+    if (served == 0) continue;
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(ex.peers.p[r] + recv_off) +
+                         (static_cast<int64_t>(t) * ex.world + ex.rank) * hidden;
+    for (int seg = 0; seg < hidden; seg += 2048) {
+      float acc[8][8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[q][i] = 0.0f;
+      for (unsigned m = served; m != 0; m &= m - 1) {  // slot order
+        const int j = __ffs(m) - 1;
+        const int rj = __shfl_sync(0xffffffffu, row, j);
+        const float wj = __shfl_sync(0xffffffffu, w, j);
+        const __nv_bfloat16* src = partial + static_cast<int64_t>(rj) * hidden + seg + lane * 8;
+        uint4 u[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          u[q] = seg + q * 256 + lane * 8 < hidden ? *reinterpret_cast<const uint4*>(src + q * 256)
+                                                   : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const uint32_t words[4] = {u[q].x, u[q].y, u[q].z, u[q].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            acc[q][2 * i] = __fadd_rn(acc[q][2 * i], __fmul_rn(wj, Pair16<__nv_bfloat16>::lo(words[i])));
+            acc[q][2 * i + 1] = __fadd_rn(acc[q][2 * i + 1], __fmul_rn(wj, Pair16<__nv_bfloat16>::hi(words[i])));
+          }
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const int c = seg + q * 256 + lane * 8;
+        if (c < hidden) {
+          uint4 o;
+          o.x = Pair16<__nv_bfloat16>::pack(acc[q][0], acc[q][1]);
+          o.y = Pair16<__nv_bfloat16>::pack(acc[q][2], acc[q][3]);
+          o.z = Pair16<__nv_bfloat16>::pack(acc[q][4], acc[q][5]);
+          o.w = Pair16<__nv_bfloat16>::pack(acc[q][6], acc[q][7]);
+          *reinterpret_cast<uint4*>(dst + c) = o;
+        }
+      }
+    }
+  }
+  signal_when_all_ctas_done(ex, 2, ctrl, kCtrlTicketGemm, &s_flag);
+}
+
+// Per-rank return, home side: out[t] = sum over the ranks that serve at least one valid slot of t, in rank
+// order, of the row that rank sent (f32 accumulation, one bf16 rounding).  The last CTA closes the step.
+__global__ void ep_combine_ranks_kernel(const __nv_bfloat16* __restrict__ recv, const int* __restrict__ ids,
+                                        __nv_bfloat16* __restrict__ out, int hidden, int top_k, int experts_total,
+                                        Exchange ex, int* ctrl, int* status) {
+  __shared__ int s_serves[kMaxPeers];
+  __shared__ int s_flag;
+  const bool ok = wait_all_ranks(ex, 2, ctrl, status, &s_flag);
+  const int t = blockIdx.x;
+  if (ok) {
+    if (threadIdx.x < kMaxPeers) s_serves[threadIdx.x] = 0;
+    __syncthreads();
+    if (threadIdx.x < top_k) {
+      const int id = ids[static_cast<int64_t>(t) * top_k + threadIdx.x];
+      if (id >= 0 && id < experts_total) s_serves[id / ex.experts_local] = 1;
+    }
+    __syncthreads();
+    const __nv_bfloat16* rows = recv + static_cast<int64_t>(t) * ex.world * hidden;
+    for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int d = 0; d < ex.world; ++d) {
+        if (!s_serves[d]) continue;
+        const uint4 u = *reinterpret_cast<const uint4*>(rows + static_cast<int64_t>(d) * hidden + c);
+        const uint32_t words[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          acc[2 * i] = __fadd_rn(acc[2 * i], Pair16<__nv_bfloat16>::lo(words[i]));
+          acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], Pair16<__nv_bfloat16>::hi(words[i]));
+        }
+      }
+      uint4 o;
+      o.x = Pair16<__nv_bfloat16>::pack(acc[0], acc[1]);
+      o.y = Pair16<__nv_bfloat16>::pack(acc[2], acc[3]);
+      o.z = Pair16<__nv_bfloat16>::pack(acc[4], acc[5]);
+      o.w = Pair16<__nv_bfloat16>::pack(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(out + static_cast<int64_t>(t) * hidden + c) = o;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(ctrl + kCtrlTicketCombine, 1) == static_cast<int>(gridDim.x) - 1) {
+      ctrl[kCtrlTicketCombine] = 0;
+      if (ok) atomicAdd(ctrl + kCtrlEpoch, 1);
+    }
+  }
+}
+
 int ep_check(int64_t tokens_local, int hidden, int inter, int experts_local, int top_k, int world, int rank) {
   if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
     return fail(kInvalidArgument, "world=%d rank=%d (at most %d ranks)", world, rank, kMaxPeers);
@@ -1093,8 +1230,11 @@ int ep_check(int64_t tokens_local, int hidden, int inter, int experts_local, int
   return kOk;
 }
 
+// return_mode: 0 = FC2's epilogue sends one row per slot home; 1 = rows are summed per (source rank, token) on
+// the expert's rank first and one row per (token, rank) travels
 int ep_exchange(const void* const* peer_buffers, int rank, int world, int experts_local, const EpLayout& L,
-                double wait_ms, Exchange* ex) {
+                double wait_ms, Exchange* ex, int return_mode = 0) {
+  if (return_mode != 0 && return_mode != 1) return fail(kInvalidArgument, "return_mode must be 0 or 1");
   if (peer_buffers == nullptr) return fail(kInvalidArgument, "peer_buffers is null");
   *ex = Exchange{};
   for (int i = 0; i < world; ++i) {
@@ -1108,6 +1248,8 @@ int ep_exchange(const void* const* peer_buffers, int rank, int world, int expert
   ex->xq_sf = L.xq_sf;
   ex->xq_sf_pitch = L.xq_sf_pitch;
   ex->row_tag = L.row_tag;
+  ex->inv_row = return_mode == 1 ? L.inv_row : 0;
+  ex->inv_w = return_mode == 1 ? L.inv_w : 0;
   ex->rank = rank;
   ex->world = world;
   ex->experts_local = experts_local;
@@ -1143,13 +1285,18 @@ int moe_ep_reset(void* own_buffer, int64_t tokens_local, int hidden, int inter, 
 // logits == nullptr: ids (and weights, used by the combine) are the caller's; else they are computed here into
 // the rank's buffer.  phases: bit 0 = the count kernel, bit 1 = the place kernel (the two are separate entry
 // points as well so that a test can interleave the ranks of a group on one stream).
-int moe_ep_dispatch(const void* x, const int* ids, const float* logits, int route_experts, int renormalize,
-                    const void* const* peer_buffers, int rank, int world, int64_t tokens_local, int hidden, int inter,
-                    int experts_local, int top_k, double wait_ms, int phases, int* status, cudaStream_t stream) {
+// return_mode 1 (per-rank return) also needs the routing weights here (`weights`, with ids; from the router
+// otherwise): the place kernel hands them to the ranks that own the experts.
+int moe_ep_dispatch(const void* x, const int* ids, const float* weights, const float* logits, int route_experts,
+                    int renormalize, const void* const* peer_buffers, int rank, int world, int64_t tokens_local,
+                    int hidden, int inter, int experts_local, int top_k, int return_mode, double wait_ms, int phases,
+                    int* status, cudaStream_t stream) {
   int rc = ep_check(tokens_local, hidden, inter, experts_local, top_k, world, rank);
   if (rc) return rc;
   if (x == nullptr || (ids == nullptr && logits == nullptr) || status == nullptr)
     return fail(kInvalidArgument, "null pointer argument");
+  if (return_mode == 1 && logits == nullptr && weights == nullptr)
+    return fail(kInvalidArgument, "the per-rank return needs the routing weights at dispatch");
   if (reinterpret_cast<uintptr_t>(x) & 31) return fail(kInvalidArgument, "x must be 32-byte aligned");
   const int experts_total = experts_local * world;
   if (logits != nullptr) {
@@ -1160,7 +1307,7 @@ int moe_ep_dispatch(const void* x, const int* ids, const float* logits, int rout
   }
   const EpLayout L = ep_layout(tokens_local, hidden, inter, experts_local, top_k, world);
   Exchange ex;
-  rc = ep_exchange(peer_buffers, rank, world, experts_local, L, wait_ms, &ex);
+  rc = ep_exchange(peer_buffers, rank, world, experts_local, L, wait_ms, &ex, return_mode);
   if (rc) return rc;
   if (tokens_local == 0) return fail(kUnsupported, "every rank must hold at least one token");
   uint8_t* b = ex.peers.p[rank];
@@ -1178,7 +1325,7 @@ int moe_ep_dispatch(const void* x, const int* ids, const float* logits, int rout
                       static_cast<int>(tokens_local), hidden, top_k, 0, experts_total, L.max_m_blocks,
                       L.rows_per_block, nullptr, reinterpret_cast<int*>(b + L.num_m_blocks),
                       reinterpret_cast<int*>(b + L.m_block_expert), reinterpret_cast<int*>(b + L.m_block_rows), ctrl,
-                      status, stream);
+                      status, stream, logits != nullptr ? w_buf : weights);
     if (rc) return rc;
   }
   return kOk;
@@ -1187,14 +1334,14 @@ int moe_ep_dispatch(const void* x, const int* ids, const float* logits, int rout
 int moe_ep_compute(const void* const* peer_buffers, int rank, int world, const void* w1, const void* w1_sf,
                    const void* w2, const void* w2_sf, const float* w1_alpha, const float* w2_alpha,
                    const float* fc2_input_scale, int64_t tokens_local, int hidden, int inter, int experts_local,
-                   int top_k, double wait_ms, int* status, cudaStream_t stream) {
+                   int top_k, int return_mode, double wait_ms, int* status, cudaStream_t stream) {
   int rc = ep_check(tokens_local, hidden, inter, experts_local, top_k, world, rank);
   if (rc) return rc;
   if (w1 == nullptr || w1_sf == nullptr || w2 == nullptr || w2_sf == nullptr || status == nullptr)
     return fail(kInvalidArgument, "null pointer argument");
   const EpLayout L = ep_layout(tokens_local, hidden, inter, experts_local, top_k, world);
   Exchange ex;
-  rc = ep_exchange(peer_buffers, rank, world, experts_local, L, wait_ms, &ex);
+  rc = ep_exchange(peer_buffers, rank, world, experts_local, L, wait_ms, &ex, return_mode);
   if (rc) return rc;
   uint8_t* b = ex.peers.p[rank];
   int* ctrl = reinterpret_cast<int*>(b + L.ctrl);
@@ -1220,6 +1367,21 @@ int moe_ep_compute(const void* const* peer_buffers, int rank, int world, const v
                     m_block_expert, m_block_rows, L.max_m_blocks, hidden, inter, experts_local, few_rows, status, stream,
                     &fc1_sync, L.xq_sf_pitch);
   if (rc) return rc;
+  if (return_mode == 1) {
+    // FC2 keeps its rows on this GPU (TMA stores); a second kernel sums them per (source rank, token) and sends
+    // one row per pair home
+    rc = gemm_moe_fc2(b + L.act, b + L.act_sf, w2, w2_sf, b + L.partial, 1, w2_alpha, num_m_blocks, m_block_expert,
+                      m_block_rows, L.max_m_blocks, hidden, inter, experts_local, few_rows, status, stream);
+    if (rc) return rc;
+    if (top_k > 32) return fail(kUnsupported, "the per-rank return serves top_k <= 32");
+    // one warp per (source rank, token); two resident CTAs per SM (128 registers), one system-wide fence per CTA
+    const int64_t pairs = tokens_local * world;
+    const int grid = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>((pairs + 7) / 8, 2 * sm_count_of_current_device())));
+    ep_presum_push_kernel<<<grid, 256, 0, stream>>>(
+        reinterpret_cast<const __nv_bfloat16*>(b + L.partial), reinterpret_cast<const int*>(b + L.inv_row),
+        reinterpret_cast<const float*>(b + L.inv_w), ex, L.recv, static_cast<int>(tokens_local), hidden, top_k, ctrl);
+    return check_cuda(cudaGetLastError(), "ep_presum_push_kernel launch");
+  }
   return gemm_moe_fc2_push(b + L.act, b + L.act_sf, w2, w2_sf, reinterpret_cast<const int*>(b + L.row_tag), ex.peers,
                            L.recv, ctrl + kCtrlAbort, w2_alpha, num_m_blocks, m_block_expert, m_block_rows,
                            L.max_m_blocks, hidden, inter, experts_local, few_rows, status, stream, &fc2_sync);
@@ -1228,14 +1390,14 @@ int moe_ep_compute(const void* const* peer_buffers, int rank, int world, const v
 // ids / weights: the routing of the local tokens; null = what the dispatch computed from logits
 int moe_ep_combine(const void* const* peer_buffers, int rank, int world, const int* ids, const float* weights,
                    void* out, int64_t tokens_local, int hidden, int inter, int experts_local, int top_k,
-                   double wait_ms, int* status, cudaStream_t stream) {
+                   int return_mode, double wait_ms, int* status, cudaStream_t stream) {
   int rc = ep_check(tokens_local, hidden, inter, experts_local, top_k, world, rank);
   if (rc) return rc;
   if (out == nullptr || status == nullptr || (ids == nullptr) != (weights == nullptr))
     return fail(kInvalidArgument, "null pointer argument (ids and weights are given together or not at all)");
   const EpLayout L = ep_layout(tokens_local, hidden, inter, experts_local, top_k, world);
   Exchange ex;
-  rc = ep_exchange(peer_buffers, rank, world, experts_local, L, wait_ms, &ex);
+  rc = ep_exchange(peer_buffers, rank, world, experts_local, L, wait_ms, &ex, return_mode);
   if (rc) return rc;
   if (tokens_local == 0) return kOk;
   uint8_t* b = ex.peers.p[rank];
@@ -1247,6 +1409,11 @@ int moe_ep_combine(const void* const* peer_buffers, int rank, int world, const i
   const __nv_bfloat16* recv = reinterpret_cast<const __nv_bfloat16*>(b + L.recv);
   const int threads = hidden / 4 >= 256 ? 256 : 128;
   const int experts_total = experts_local * world;
+  if (return_mode == 1) {
+    ep_combine_ranks_kernel<<<static_cast<unsigned>(tokens_local), hidden / 8 >= 256 ? 256 : 128, 0, stream>>>(
+        recv, ids, static_cast<__nv_bfloat16*>(out), hidden, top_k, experts_total, ex, ctrl, status);
+    return check_cuda(cudaGetLastError(), "ep_combine_ranks_kernel launch");
+  }
   if (tokens_local <= 256) {
     ep_combine_kernel<true><<<dim3(static_cast<unsigned>(tokens_local), (hidden / 4 + threads - 1) / threads), threads, 0,
                               stream>>>(recv, ids, weights, static_cast<__nv_bfloat16*>(out), hidden, top_k,

@@ -176,6 +176,13 @@ int b200fp4_moe_fused_noalloc(const void* x, const void* w1, const void* w1_sf, 
  * All peer accesses are plain loads / stores of these kernels over NVLink.  Every wait is bounded by wait_ms
  * (0 < wait_ms <= 60000): on expiry the kernel ORs bit 16 into the device status word, marks the buffer as
  * aborted and returns; later kernels of the group then touch no peer memory until b200fp4_moe_ep_reset.
+ * return_mode (the same value in all calls of a step, on all ranks): 0 = as above, one row per (token, slot)
+ * travels home and the results are bit-identical to b200fp4_moe_fused; 1 = FC2 keeps its rows on the expert's
+ * GPU, a second kernel sums them per (source rank, token) with the routing weights (f32, slot order, one bf16
+ * rounding) and sends ONE row per (token, rank that serves some of its slots); the combine adds those rows in
+ * rank order.  Fewer bytes cross NVLink (a token's top_k experts sit on at most `world` ranks); the sum is
+ * grouped by rank, so results differ from mode 0 by bf16 roundings of the partial sums.  Mode 1 needs
+ * token_final_scales at dispatch when ids are given.
  * Routing: either token_selected_experts (global ids) is given, or router_logits f32
  * [tokens_local, world*local_experts] and the dispatch routes on the GPU (then pass NULL ids / scales to the
  * combine, and fetch the routing with b200fp4_moe_ep_routing if it is wanted).
@@ -188,29 +195,30 @@ size_t b200fp4_moe_ep_buffer_bytes(int64_t tokens_local, int hidden, int interme
  * rank (host-side barrier before and after). */
 int b200fp4_moe_ep_reset(void* own_buffer, int64_t tokens_local, int hidden, int intermediate, int local_experts,
                          int top_k, int world, void* stream);
-int b200fp4_moe_ep_dispatch(const void* x, const int* token_selected_experts, const float* router_logits,
-                            int renormalize, const void* const* peer_buffers, int rank, int world,
-                            int64_t tokens_local, int hidden, int intermediate, int local_experts, int top_k,
-                            double wait_ms, void* stream);
+int b200fp4_moe_ep_dispatch(const void* x, const int* token_selected_experts, const float* token_final_scales,
+                            const float* router_logits, int renormalize, const void* const* peer_buffers, int rank,
+                            int world, int64_t tokens_local, int hidden, int intermediate, int local_experts,
+                            int top_k, int return_mode, double wait_ms, void* stream);
 /* The two halves of the dispatch as separate calls (count + signal 0, then wait + place + signal 1; same
  * arguments).  A harness that emulates several ranks of a group on ONE GPU must issue all ranks' counts before
  * any rank's place, all places before any compute and all computes before any combine, on one stream: then
  * every wait is already satisfied when its kernel starts and no kernel ever waits for a later launch. */
-int b200fp4_moe_ep_dispatch_count(const void* x, const int* token_selected_experts, const float* router_logits,
-                                  int renormalize, const void* const* peer_buffers, int rank, int world,
-                                  int64_t tokens_local, int hidden, int intermediate, int local_experts, int top_k,
-                                  double wait_ms, void* stream);
-int b200fp4_moe_ep_dispatch_place(const void* x, const int* token_selected_experts, const float* router_logits,
-                                  int renormalize, const void* const* peer_buffers, int rank, int world,
-                                  int64_t tokens_local, int hidden, int intermediate, int local_experts, int top_k,
-                                  double wait_ms, void* stream);
+int b200fp4_moe_ep_dispatch_count(const void* x, const int* token_selected_experts, const float* token_final_scales,
+                                  const float* router_logits, int renormalize, const void* const* peer_buffers,
+                                  int rank, int world, int64_t tokens_local, int hidden, int intermediate,
+                                  int local_experts, int top_k, int return_mode, double wait_ms, void* stream);
+int b200fp4_moe_ep_dispatch_place(const void* x, const int* token_selected_experts, const float* token_final_scales,
+                                  const float* router_logits, int renormalize, const void* const* peer_buffers,
+                                  int rank, int world, int64_t tokens_local, int hidden, int intermediate,
+                                  int local_experts, int top_k, int return_mode, double wait_ms, void* stream);
 int b200fp4_moe_ep_compute(const void* const* peer_buffers, int rank, int world, const void* w1, const void* w1_sf,
                            const void* w2, const void* w2_sf, const float* w1_alpha, const float* w2_alpha,
                            const float* fc2_input_scale, int64_t tokens_local, int hidden, int intermediate,
-                           int local_experts, int top_k, double wait_ms, void* stream);
+                           int local_experts, int top_k, int return_mode, double wait_ms, void* stream);
 int b200fp4_moe_ep_combine(const void* const* peer_buffers, int rank, int world, const int* token_selected_experts,
                            const float* token_final_scales, void* out, int64_t tokens_local, int hidden,
-                           int intermediate, int local_experts, int top_k, double wait_ms, void* stream);
+                           int intermediate, int local_experts, int top_k, int return_mode, double wait_ms,
+                           void* stream);
 int b200fp4_moe_ep_routing(const void* own_buffer, int* ids_out, float* weights_out, int64_t tokens_local, int hidden,
                            int intermediate, int local_experts, int top_k, int world, void* stream);
 

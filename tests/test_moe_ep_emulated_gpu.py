@@ -42,8 +42,8 @@ def _dev_weights(w, sl):
 
 
 class EmulatedGroup:
-    def __init__(self, lib, check, world, tokens_local, hidden, inter, experts, top_k):
-        self.lib, self.check, self.world = lib, check, world
+    def __init__(self, lib, check, world, tokens_local, hidden, inter, experts, top_k, mode=0):
+        self.lib, self.check, self.world, self.mode = lib, check, world, mode
         self.shape = (tokens_local, hidden, inter, experts // world, top_k)
         nbytes = lib.b200fp4_moe_ep_buffer_bytes(*self.shape, world)
         assert nbytes > 0
@@ -61,17 +61,17 @@ class EmulatedGroup:
         for fn in (lib.b200fp4_moe_ep_dispatch_count, lib.b200fp4_moe_ep_dispatch_place):
             for r in range(w):
                 check(fn(xs[r].data_ptr(), None if routed else ids[r].data_ptr(),
-                         logits[r].data_ptr() if routed else None, 1, self.peers, r, w, *self.shape, WAIT_MS,
-                         self.stream))
+                         None if routed else wts[r].data_ptr(), logits[r].data_ptr() if routed else None, 1,
+                         self.peers, r, w, *self.shape, self.mode, WAIT_MS, self.stream))
         for r in range(w):
             d = weights[r]
             check(lib.b200fp4_moe_ep_compute(self.peers, r, w, d["w1"].data_ptr(), d["s1"].data_ptr(),
                                              d["w2"].data_ptr(), d["s2"].data_ptr(), d["a1"].data_ptr(), None, None,
-                                             *self.shape, WAIT_MS, self.stream))
+                                             *self.shape, self.mode, WAIT_MS, self.stream))
         for r in range(w):
             check(lib.b200fp4_moe_ep_combine(self.peers, r, w, None if routed else ids[r].data_ptr(),
                                              None if routed else wts[r].data_ptr(), outs[r].data_ptr(), *self.shape,
-                                             WAIT_MS, self.stream))
+                                             self.mode, WAIT_MS, self.stream))
         return outs
 
 
@@ -82,7 +82,10 @@ class EmulatedGroup:
     (8, 64, 32, 2304, 1280, 8, True),        # decode-like: few tokens per rank, long reductions (256-wide FC2 tiles)
     (2, 24, 4, 2304, 1280, 2, False),        # at most 32 tokens in total: the few-row tiles
 ])
-def test_emulated_ranks_match_single_gpu_bit_for_bit(b200, world, tokens, experts, hidden, inter, top_k, hot):
+@pytest.mark.parametrize("mode", [0, 1], ids=["per_slot", "per_rank"])
+def test_emulated_ranks_match_single_gpu(b200, world, tokens, experts, hidden, inter, top_k, hot, mode):
+    """Per-slot return: bit for bit the single-GPU operator.  Per-rank return: the same sum grouped by serving
+    rank with one bf16 rounding per partial sum (bound on the difference: a few bf16 ulps, rel-L2 4e-3)."""
     lib, check = b200._lib.lib, b200._lib.check
     w, x, logits, ids, wts = _problem(tokens, experts, hidden, inter, top_k, seed=world * 7 + tokens, hot=hot)
     ids = ids.clone()
@@ -91,7 +94,7 @@ def test_emulated_ranks_match_single_gpu_bit_for_bit(b200, world, tokens, expert
         ids[3, 0] = experts + 5              # an id outside the group's experts
     t = tokens // world
     el = experts // world
-    g = EmulatedGroup(lib, check, world, t, hidden, inter, experts, top_k)
+    g = EmulatedGroup(lib, check, world, t, hidden, inter, experts, top_k, mode)
     xs = [x[r * t:(r + 1) * t].contiguous().cuda() for r in range(world)]
     idr = [ids[r * t:(r + 1) * t].contiguous().cuda() for r in range(world)]
     wtr = [wts[r * t:(r + 1) * t].contiguous().cuda() for r in range(world)]
@@ -104,7 +107,15 @@ def test_emulated_ranks_match_single_gpu_bit_for_bit(b200, world, tokens, expert
         torch.cuda.synchronize()
         assert b200._lib.device_status() == 0, "a wait expired"
         got = torch.cat(outs)
-        assert torch.equal(got, single), f"step {step}: expert-parallel result differs from the single-GPU operator"
+        if mode == 0:
+            assert torch.equal(got, single), f"step {step}: expert-parallel result differs from the single-GPU operator"
+        else:
+            assert bool(torch.isfinite(got.float()).all())
+            diff = torch.linalg.vector_norm(got.float() - single.float()) / torch.linalg.vector_norm(single.float())
+            assert diff <= 4e-3, f"step {step}: rel-L2 {float(diff)} against the single-GPU operator"
+            if step == 0:
+                first = got.clone()
+            assert torch.equal(got, first), "the per-rank sums are taken in a fixed order: same bits every step"
     valid = (ids >= 0) & (ids < experts)
     ref = O.moe_ref(x, *w, torch.where(valid, ids, torch.zeros_like(ids)), torch.where(valid, wts, torch.zeros_like(wts)),
                     np.full(experts, 0.02, np.float32))
@@ -112,12 +123,13 @@ def test_emulated_ranks_match_single_gpu_bit_for_bit(b200, world, tokens, expert
     assert err <= 1e-2
 
 
-def test_emulated_ranks_route_from_logits_inside_the_dispatch(b200):
+@pytest.mark.parametrize("mode", [0, 1], ids=["per_slot", "per_rank"])
+def test_emulated_ranks_route_from_logits_inside_the_dispatch(b200, mode):
     lib, check = b200._lib.lib, b200._lib.check
     world, tokens, experts, hidden, inter, top_k = 4, 128, 16, 512, 256, 4
     w, x, logits, ids, wts = _problem(tokens, experts, hidden, inter, top_k, seed=99)
     t, el = tokens // world, experts // world
-    g = EmulatedGroup(lib, check, world, t, hidden, inter, experts, top_k)
+    g = EmulatedGroup(lib, check, world, t, hidden, inter, experts, top_k, mode)
     xs = [x[r * t:(r + 1) * t].contiguous().cuda() for r in range(world)]
     lg = [logits[r * t:(r + 1) * t].contiguous().cuda() for r in range(world)]
     weights = [_dev_weights(w, slice(r * el, (r + 1) * el)) for r in range(world)]
@@ -137,10 +149,15 @@ def test_emulated_ranks_route_from_logits_inside_the_dispatch(b200):
     single = b200.b12x_fused_moe(x.cuda(), full["w1"], full["s1"], full["w2"], full["s2"], ids_d, w_d, experts, top_k,
                                  w1_alpha=full["a1"])
     torch.cuda.synchronize()
-    assert torch.equal(torch.cat(outs), single)
+    if mode == 0:
+        assert torch.equal(torch.cat(outs), single)
+    else:
+        got = torch.cat(outs).float()
+        assert float(torch.linalg.vector_norm(got - single.float()) / torch.linalg.vector_norm(single.float())) <= 4e-3
 
 
-def test_wait_for_a_rank_that_never_signals_gives_up_and_reports(b200):
+@pytest.mark.parametrize("mode", [0, 1], ids=["per_slot", "per_rank"])
+def test_wait_for_a_rank_that_never_signals_gives_up_and_reports(b200, mode):
     """A group of two whose second rank never runs: rank 0's place kernel waits for counts that nobody publishes.
     The wait gives up after its bound, the kernels that follow touch nothing, the status word carries bit 16 and
     the host raises; after a reset the same buffers work again."""
@@ -148,7 +165,7 @@ def test_wait_for_a_rank_that_never_signals_gives_up_and_reports(b200):
     world, tokens, experts, hidden, inter, top_k = 2, 32, 4, 512, 256, 2
     w, x, logits, ids, wts = _problem(tokens, experts, hidden, inter, top_k, seed=5)
     t, el = tokens // world, experts // world
-    g = EmulatedGroup(lib, check, world, t, hidden, inter, experts, top_k)
+    g = EmulatedGroup(lib, check, world, t, hidden, inter, experts, top_k, mode)
     xs = [x[r * t:(r + 1) * t].contiguous().cuda() for r in range(world)]
     idr = [ids[r * t:(r + 1) * t].contiguous().cuda() for r in range(world)]
     wtr = [wts[r * t:(r + 1) * t].contiguous().cuda() for r in range(world)]
@@ -157,12 +174,13 @@ def test_wait_for_a_rank_that_never_signals_gives_up_and_reports(b200):
     out = torch.zeros(t, hidden, dtype=torch.bfloat16, device="cuda")
     d = weights[0]
     short = 2.0                                                      # milliseconds
-    check(lib.b200fp4_moe_ep_dispatch(xs[0].data_ptr(), idr[0].data_ptr(), None, 1, g.peers, 0, world, *g.shape,
-                                      short, g.stream))
+    check(lib.b200fp4_moe_ep_dispatch(xs[0].data_ptr(), idr[0].data_ptr(), wtr[0].data_ptr(), None, 1, g.peers, 0,
+                                      world, *g.shape, mode, short, g.stream))
     check(lib.b200fp4_moe_ep_compute(g.peers, 0, world, d["w1"].data_ptr(), d["s1"].data_ptr(), d["w2"].data_ptr(),
-                                     d["s2"].data_ptr(), d["a1"].data_ptr(), None, None, *g.shape, short, g.stream))
+                                     d["s2"].data_ptr(), d["a1"].data_ptr(), None, None, *g.shape, mode, short,
+                                     g.stream))
     check(lib.b200fp4_moe_ep_combine(g.peers, 0, world, idr[0].data_ptr(), wtr[0].data_ptr(), out.data_ptr(),
-                                     *g.shape, short, g.stream))
+                                     *g.shape, mode, short, g.stream))
     with pytest.raises(b200.B200Fp4Error, match="another rank"):
         b200.synchronize()
     assert b200._lib.device_status() == 0                            # reading cleared it
@@ -175,7 +193,11 @@ def test_wait_for_a_rank_that_never_signals_gives_up_and_reports(b200):
     single = b200.b12x_fused_moe(x.cuda(), full["w1"], full["s1"], full["w2"], full["s2"], ids.cuda(), wts.cuda(),
                                  experts, top_k, w1_alpha=full["a1"])
     torch.cuda.synchronize()
-    assert torch.equal(torch.cat(outs), single)
+    if mode == 0:
+        assert torch.equal(torch.cat(outs), single)
+    else:
+        got = torch.cat(outs).float()
+        assert float(torch.linalg.vector_norm(got - single.float()) / torch.linalg.vector_norm(single.float())) <= 4e-3
 
 
 def test_peer_wait_selftest_sets_the_status_bit(b200):

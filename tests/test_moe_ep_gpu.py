@@ -49,11 +49,12 @@ def _worker(rank, world, port, result_dir):
         dev = torch.device("cuda", rank)
         t = x.shape[0] // world
         mine = slice(rank * t, (rank + 1) * t)
-        for kind in ("collective", "peer"):
+        for kind in ("collective", "peer", "peer_rank"):
             if kind == "collective":
                 ep = b200.parallel.ExpertParallelMoE(experts, top_k)
             else:
-                ep = b200.parallel.PeerExpertParallelMoE(experts, top_k, t, x.shape[1], w2c.shape[2])
+                ep = b200.parallel.PeerExpertParallelMoE(experts, top_k, t, x.shape[1], w2c.shape[2],
+                                                         return_rows="per_slot" if kind == "peer" else "per_rank")
             sl = slice(ep.expert_lo, ep.expert_lo + ep.local_experts)
             w = _dev_weights(w1c, w1s, w2c, w2s, sl, dev)
             for _ in range(3):          # several steps: buffers are reused
@@ -89,14 +90,15 @@ def test_expert_parallel_two_gpus_matches_single_gpu(b200, tmp_path):
     parts = [torch.load(os.path.join(tmp_path, f"routed{r}.pt")) for r in range(world)]
     assert torch.equal(torch.cat([p[1] for p in parts]), ids_g.cpu())
     assert torch.equal(torch.cat([p[0] for p in parts]), single_routed)
-    for kind in ("collective", "peer"):
+    for kind in ("collective", "peer", "peer_rank"):
         got = torch.cat([torch.load(os.path.join(tmp_path, f"out_{kind}{r}.pt")) for r in range(world)])
         if kind == "peer":
             # same bf16 per-slot rows, same slot order, same single rounding as on one GPU
             assert torch.equal(got, single), "peer-memory expert parallelism differs from the single-GPU result"
         else:
-            # bf16 rows both ways, f32 weighted sum by torch: only the summation order may differ
+            # collective: bf16 rows both ways, f32 weighted sum by torch: only the summation order may differ.
+            # peer_rank: the sum is grouped by serving rank, one bf16 rounding per partial sum.
             base = single.float()
             err = torch.linalg.vector_norm(got.float() - base) / torch.linalg.vector_norm(base)
-            assert err <= 2e-3, float(err)
+            assert err <= (4e-3 if kind == "peer_rank" else 2e-3), float(err)
         assert torch.linalg.vector_norm(got.float() - ref.float()) / torch.linalg.vector_norm(ref.float()) <= 1e-2
