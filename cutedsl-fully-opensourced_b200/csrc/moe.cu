@@ -943,6 +943,12 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
 //   combine    wait for signal 2 of every rank; sum the k rows of each local token in f32 in slot
 //              order, one bf16 rounding
 //
+// Per-rank return (return_mode 1) changes the second half: the place kernel also hands every rank the row index
+// (or -1) and the routing weight of every (token, slot) it serves; FC2 keeps its rows on this GPU; a pre-sum kernel
+// adds the rows of every (source rank, token) with their weights and stores ONE row per pair into the owner's
+// landing zone -> signal 2; the combine adds a token's rows (one per serving rank) in rank order.  Fewer bytes
+// cross NVLink; the sum is grouped by rank, so its bf16 roundings differ from the single-GPU operator's.
+//
 // The signals carry a step counter, so the three of them also separate consecutive steps (a rank can
 // only run ahead of a peer by less than one phase of the same kind); there is no other barrier.
 // Every wait is bounded (Exchange::wait_ns).  The reference has no multi-GPU path; this is the
