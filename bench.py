@@ -425,6 +425,8 @@ class MoePart(Part):
         return {"workload": self.name, "tokens": self.tokens, "tokens_per_gpu": self.tokens // world,
                 "hidden": self.hidden, "experts": self.experts, "experts_per_gpu": self.experts // world,
                 "top_k": self.top_k, "intermediate": self.inter, "slot_rows": "bf16",
+                "return_rows": ("n/a" if world == 1 else getattr(getattr(self, "ep", None), "return_rows",
+                                                                  os.environ.get("B200FP4_EP_RETURN", "auto"))),
                 "parallelism": ("single GPU" if world == 1 else
                                 f"experts x{world}, tokens x{world}; dispatch / combine as NVLink peer stores inside "
                                 "the kernels, three bounded in-kernel signals per step (no NCCL call in a step)"),
