@@ -414,9 +414,9 @@ class MoePart(Part):
         self.expert_lo = rank * self.local_experts
         self.units_per_step = float(self.tokens)
         self.expert_bytes = 3 * self.hidden * self.inter // 2 + 3 * self.hidden * self.inter // 16
-        # kernels of this library per step: count(+route), place, FC1, FC2, sum; few slots: route, prepare, quantise,
-        # FC1, FC2, sum; expert-parallel: count(+route), place, wait, FC1, FC2, signal, sum
-        self.launches_per_step = 7 if world > 1 else (5 if self.tokens * self.top_k > 1024 else 6)
+        # kernels of this library per step: count(+route), place, FC1, FC2, sum; few slots: prepare(+route), quantise,
+        # FC1, FC2, sum; expert-parallel: the same five, plus the pre-sum kernel with the per-rank return (set in setup)
+        self.launches_per_step = 5
 
     def supported(self, world):
         return self.tokens % world == 0 and self.experts % world == 0 and self.tokens >= world
@@ -486,6 +486,7 @@ class MoePart(Part):
         if self.world > 1:
             self.ep = pkg.parallel.PeerExpertParallelMoE(
                 e, k, t, h, i, return_rows=os.environ.get("B200FP4_EP_RETURN", "auto"))
+            self.launches_per_step = 6 if self.ep.return_rows == "per_rank" else 5
             self.ep_weights = {"w1": self.weights["w1"], "w1_sf": self.weights["w1_sf"], "w2": self.weights["w2"],
                                "w2_sf": self.weights["w2_sf"], "w1_alpha": self.weights["w1_alpha"],
                                "w2_alpha": self.weights["w2_alpha"], "fc2_input_scale": self.weights["fc2_input_scale"]}
