@@ -234,7 +234,7 @@ template <int kBlockN, bool kSwigluB, int kARows = 128, int kEpi = 0, typename E
 int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, const GemmParams& p,
                 const Epilogue& epi, int max_tiles, cudaStream_t stream) {
   auto kern = nvfp4_gemm_kernel<kBlockN, kSwigluB, Epilogue, kARows, kEpi>;
-  constexpr SmemLayout L = smem_layout<kBlockN, kSwigluB, Epilogue::kOutBytes, kARows>();
+  constexpr SmemLayout L = smem_layout<kBlockN, kSwigluB, Epilogue::kOutBytes, kARows, Epilogue::kParkWide>();
   static std::atomic<bool> configured[kMaxDevices];      // per instantiation and device
   int rc_cfg = configure_smem_once(configured, kern, static_cast<int>(L.total));
   if (rc_cfg) return rc_cfg;
@@ -590,7 +590,16 @@ int gemm_moe_fc2_typed(const void* act_codes, const void* act_sf, const void* w2
                        const int* m_block_rows, int max_m_blocks, int hidden, int inter, int experts, int few_rows,
                        int* status, cudaStream_t stream) {
   CUtensorMap ta, tb;
-  const bool wide = hidden % 256 == 0 && ((inter + kBlockK - 1) / kBlockK > 4 || fc2_force_wide());
+  // Short reductions with 16-bit rows: 256-wide tiles whose rows leave through TMA stores (EpilogueStoreWide, three
+  // stages).  FC2 of the prefill shape: 128-wide tiles with TMA stores 67 us, 256-wide with register stores 64,
+  // 256-wide with TMA stores 53.  B200FP4_FC2_PARK=0 keeps the 128-wide tiles.
+  static const bool park_allowed = [] {
+    const char* e = getenv("B200FP4_FC2_PARK");
+    return e == nullptr || atoi(e) != 0;
+  }();
+  const int k_tiles = (inter + kBlockK - 1) / kBlockK;
+  const bool park = sizeof(RowT) == 2 && hidden % 256 == 0 && few_rows == 0 && k_tiles <= 4 && park_allowed;
+  const bool wide = hidden % 256 == 0 && (k_tiles > 4 || fc2_force_wide() || park);
   const bool small_a = few_rows != 0 && wide;
   int rc = make_operand_map(&ta, act_codes, static_cast<int64_t>(max_m_blocks) * 128, inter, 0, small_a ? 32 : 128);
   if (rc) return rc;
@@ -623,6 +632,12 @@ int gemm_moe_fc2_typed(const void* act_codes, const void* act_sf, const void* w2
   if (wide) {
     p.num_n_blocks = hidden / 256;
     if (small_a) return launch_gemm<256, false, 32>(ta, tb, tc, p, epi, max_m_blocks * p.num_n_blocks, stream);
+    if constexpr (sizeof(RowT) == 2) {
+      if (park) {
+        EpilogueStoreWide wepi{w2_alpha};
+        return launch_gemm<256, false>(ta, tb, tc, p, wepi, max_m_blocks * p.num_n_blocks, stream);
+      }
+    }
     return launch_gemm<256, false>(ta, tb, tc, p, epi, max_m_blocks * p.num_n_blocks, stream);
   }
   p.num_n_blocks = (hidden + 127) / 128;

@@ -130,7 +130,9 @@ constexpr uint32_t kBarrierBytes = 512;
 // kARows: rows of A that a stage holds.  Below 128 (256-wide tiles of launches whose row blocks all hold that few
 // rows: decode) the MMA still reads 128 rows -- the rest of its A operand is whatever follows in the stage, times
 // scale factors that are zero for rows without data -- and the shared memory saved buys another stage of B.
-template <int kBlockN, bool kSwigluB = false, int kOutBytes = 0, int kARows = 128>
+// kParkWide: 256-wide plain tiles whose 16-bit rows leave through TMA stores as well: every epilogue warp parks one
+// box of 32 rows x 64 columns at a time (two passes over its 128 columns); the parking space costs a stage
+template <int kBlockN, bool kSwigluB = false, int kOutBytes = 0, int kARows = 128, bool kParkWide = false>
 __host__ __device__ constexpr SmemLayout smem_layout() {
   SmemLayout s{};
   s.a_bytes = kARows * 128;
@@ -140,7 +142,8 @@ __host__ __device__ constexpr SmemLayout smem_layout() {
   s.sfb_bytes = (kSwigluB ? 2 : (kBlockN >= 128 ? kBlockN / 128 : 1)) * 2048;
   s.stage_bytes = s.a_bytes + s.b_bytes + s.sfa_bytes + s.sfb_bytes;
   s.epi_stage_bytes = (kBlockN == 128 && !kSwigluB) ? 32u * 128u * kOutBytes : 0u;
-  s.stages = kBlockN == 256 ? (kARows <= 32 ? 5 : 4) : (kBlockN == 128 ? (kSwigluB ? 5 : (kOutBytes == 0 ? 6 : (kOutBytes == 4 ? 4 : 5))) : 7);
+  if (kBlockN == 256 && kParkWide) s.epi_stage_bytes = 2u * 4096u;      // per tensor-memory quarter: two warps, one box each
+  s.stages = kBlockN == 256 ? (kARows <= 32 ? 5 : (kParkWide ? 3 : 4)) : (kBlockN == 128 ? (kSwigluB ? 5 : (kOutBytes == 0 ? 6 : (kOutBytes == 4 ? 4 : 5))) : 7);
   s.total = s.stages * s.stage_bytes + 1024 /*alignment slack*/ + kBarrierBytes +
             (s.epi_stage_bytes != 0 ? 1024 + 4 * s.epi_stage_bytes : 0);
   return s;
@@ -214,6 +217,7 @@ struct EpilogueStore {
 
   static constexpr int kOutBytes = static_cast<int>(sizeof(OutT));
   static constexpr bool kUsesOutputMap = true;      // 128-wide tiles leave through TMA stores
+  static constexpr bool kParkWide = false;
 
   // The warp parks its 32 rows of the tile in shared memory (boxes of 32 rows x 128 bytes in the 128-byte
   // swizzle of the tensor map) and one lane hands them to TMA stores: the accumulator is free as soon as it has
@@ -380,6 +384,73 @@ struct EpilogueStore {
   }
 };
 
+// 256-wide plain tiles with bf16 rows that leave through TMA stores (FC2 of the MoE with short reductions).  The
+// tile has one accumulator, so what counts is how soon it is handed back: each of the eight epilogue warps owns 128
+// columns of its 32 rows as two 32 x 64 boxes and has 4 KB of parking space: it reads and packs the first box into
+// registers, reads the second straight into the parking space, releases the accumulator, stores the second box by
+// TMA and, once that store has read the space, parks and stores the first.  Register stores of the same tile take
+// 64 KB through lanes that each write another row (about 12 bytes per cycle and SM).
+struct EpilogueStoreWide {
+  static constexpr int kOutBytes = 2;
+  static constexpr bool kUsesOutputMap = true;
+  static constexpr bool kParkWide = true;
+  const float* alpha;           // one scale per group, or null
+  template <int kBlockN, typename Loader, typename Release>
+  __device__ __forceinline__ void operator()(const GemmParams& p, int m_blk, int n_blk, int group, int row,
+                                             int /*rows_valid*/, int part, int parts, Loader&& load, Release&& release,
+                                             uint8_t* stage = nullptr, const CUtensorMap* cmap = nullptr) const {
+    static_assert(kBlockN == 256, "wide parking serves 256-wide tiles");
+    const float scale = alpha == nullptr ? 1.0f : __ldg(alpha + group);
+    const int lane = row & 31;
+    uint8_t* box = stage + lane * 128;
+    const int y = m_blk * kBlockM + (row & ~31);
+    const int b0 = part * (4 / parts);                 // first 64-column box of this warp (it owns two: parts == 2)
+    auto pack8 = [&](const uint32_t (&r)[32], int q) {
+      uint4 v;
+      v.x = Pair16<__nv_bfloat16>::pack(__uint_as_float(r[8 * q]) * scale, __uint_as_float(r[8 * q + 1]) * scale);
+      v.y = Pair16<__nv_bfloat16>::pack(__uint_as_float(r[8 * q + 2]) * scale, __uint_as_float(r[8 * q + 3]) * scale);
+      v.z = Pair16<__nv_bfloat16>::pack(__uint_as_float(r[8 * q + 4]) * scale, __uint_as_float(r[8 * q + 5]) * scale);
+      v.w = Pair16<__nv_bfloat16>::pack(__uint_as_float(r[8 * q + 6]) * scale, __uint_as_float(r[8 * q + 7]) * scale);
+      return v;
+    };
+    auto store_box = [&](int b) {
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        const int col = n_blk * kBlockN + b * 64;
+        if (col < p.n_cols && y < p.m_rows) ptx::tma_store_2d(cmap, col * 2, y, ptx::smem_u32(stage));
+        ptx::bulk_commit_group();
+      }
+    };
+    // the first box waits in registers while the second is read, so the accumulator goes back without any wait for a
+    // store in between
+    uint4 first[8];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t r[32];
+      load(b0 * 64 + 32 * h, r);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) first[4 * h + q] = pack8(r, q);
+    }
+    if (lane == 0) ptx::bulk_wait_group_read0();       // the previous tile's last store has read the box
+    __syncwarp();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t r[32];
+      load((b0 + 1) * 64 + 32 * h, r);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(box + (((4 * h + q) ^ (lane & 7)) << 4)) = pack8(r, q);
+    }
+    release();                                         // the accumulator has been read
+    store_box(b0 + 1);
+    if (lane == 0) ptx::bulk_wait_group_read0();
+    __syncwarp();
+#pragma unroll
+    for (int c = 0; c < 8; ++c) *reinterpret_cast<uint4*>(box + ((c ^ (lane & 7)) << 4)) = first[c];
+    store_box(b0);
+  }
+};
+
 // FC2 of the expert-parallel MoE: every output row goes straight to the GPU that owns its token.  `row_tag[r]`
 // names the destination of expert-major row r as (rank << 24 | slot), slot = token * top_k + j at that rank; the
 // row lands at recv[slot][0..hidden) (bf16) in that rank's exchange buffer.  All remote accesses are plain
@@ -389,6 +460,7 @@ struct EpilogueStore {
 struct EpiloguePushRows {
   static constexpr int kOutBytes = 2;
   static constexpr bool kUsesOutputMap = false;
+  static constexpr bool kParkWide = false;
   const int* row_tag;           // [rows] destination of every expert-major row
   PeerPtrs peers;               // exchange buffer of every rank as mapped into this process
   size_t recv_off;              // offset of the landing zone inside an exchange buffer
@@ -484,6 +556,7 @@ struct EpiloguePushRows {
 struct EpilogueSwiglu {
   static constexpr int kOutBytes = 0;     // stores from registers
   static constexpr bool kUsesOutputMap = false;
+  static constexpr bool kParkWide = false;
   uint8_t* act_codes;           // [m_rows, inter/2]
   uint8_t* act_sf;              // tiled [m_tiles][rk2][512], rk2 = ceil(inter/64)
   const float* w1_alpha;        // per group
@@ -551,7 +624,7 @@ __global__ void __launch_bounds__(gemm_threads(kBlockN, kSwigluB, kEpi), 1)
 nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ CUtensorMap tmap_aux, const GemmParams p, const Epilogue epi) {
   static_assert(kARows == 128 || (kBlockN == 256 && kARows == 32), "few-row stages exist for 256-wide tiles");
-  constexpr SmemLayout L = smem_layout<kBlockN, kSwigluB, Epilogue::kOutBytes, kARows>();
+  constexpr SmemLayout L = smem_layout<kBlockN, kSwigluB, Epilogue::kOutBytes, kARows, Epilogue::kParkWide>();
   constexpr int kStages = L.stages;
   constexpr int kAccStages = kBlockN == 256 ? 1 : 2;
   constexpr int kBPieces = kSwigluB ? 2 : (kBlockN >= 128 ? kBlockN / 128 : 1);
