@@ -582,8 +582,8 @@ bool fc2_force_wide() {
 }
 
 // FC2: partial[row][h] = (Actq . W2[e]^T) * w2_alpha[e], stored as f32 or (rows_bf16) rounded to bf16.
-// The kernel is bound by what its epilogue can store (an SM writes some 16 bytes per cycle), so the
-// 16-bit rows nearly halve its time and the combine's.
+// The kernel is sensitive to how its rows leave (an SM writes some 12-16 bytes per cycle when every lane stores to
+// another row), so the 16-bit rows nearly halve its time and the combine's, and they leave through TMA stores.
 template <typename RowT>
 int gemm_moe_fc2_typed(const void* act_codes, const void* act_sf, const void* w2, const void* w2_sf, RowT* partial,
                        const float* w2_alpha, const int* num_m_blocks_dev, const int* m_block_expert,
