@@ -666,7 +666,7 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
     }
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(acc_full_bar(s), 1);
-      ptx::mbar_init(acc_empty_bar(s), 32 * kEpiWarps);
+      ptx::mbar_init(acc_empty_bar(s), kEpiWarps);           // one arrival per epilogue warp
     }
     *abort_flag = 0;
     ptx::fence_mbar_init();
@@ -987,14 +987,16 @@ nvfp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_const
                                            ptx::tmem_ld_32x32(t_acc + c0, r);
                                            ptx::tmem_ld_wait();
                                          },
-                                         [&]() {
+                                         [&]() {        // called by all lanes of the warp together
                                            ptx::tc_fence_before_sync();
-                                           ptx::mbar_arrive(acc_empty_bar(acc.stage));
+                                           __syncwarp();
+                                           if (lane == 0) ptx::mbar_arrive(acc_empty_bar(acc.stage));
                                          },
                                          stage, &tmap_aux);
       } else {
         ptx::tc_fence_before_sync();
-        ptx::mbar_arrive(acc_empty_bar(acc.stage));
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(acc_empty_bar(acc.stage));
       }
       acc.advance(kAccStages);
     }
