@@ -669,6 +669,62 @@ __global__ void moe_combine_few_kernel(const RowT* __restrict__ partial, const i
   }
 }
 
+// The same sum for bf16 rows and a bf16 output with 16-byte accesses: one CTA per token, a thread owns 8 columns and
+// keeps the loads of four rows in flight.  Same arithmetic as moe_combine_kernel (f32, slot order, one product and
+// one sum per slot, one rounding).
+__global__ void moe_combine_bf16x8_kernel(const __nv_bfloat16* __restrict__ partial, const int* __restrict__ slot_row,
+                                          const float* __restrict__ weights, __nv_bfloat16* __restrict__ out,
+                                          int hidden, int top_k, int accumulate) {
+  __shared__ int s_rows[64];
+  __shared__ float s_w[64];
+  const int token = blockIdx.x;
+  if (threadIdx.x < top_k) {
+    s_rows[threadIdx.x] = slot_row[static_cast<int64_t>(token) * top_k + threadIdx.x];
+    s_w[threadIdx.x] = weights[static_cast<int64_t>(token) * top_k + threadIdx.x];
+  }
+  __syncthreads();
+  for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j0 = 0; j0 < top_k; j0 += 4) {
+      uint4 u[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int row = j0 + k < top_k ? s_rows[j0 + k] : -1;
+        u[k] = row >= 0 ? *reinterpret_cast<const uint4*>(partial + static_cast<int64_t>(row) * hidden + c)
+                        : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (j0 + k < top_k && s_rows[j0 + k] >= 0) {
+          const float w = s_w[j0 + k];
+          const uint32_t words[4] = {u[k].x, u[k].y, u[k].z, u[k].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            acc[2 * i] = __fadd_rn(acc[2 * i], __fmul_rn(w, Pair16<__nv_bfloat16>::lo(words[i])));
+            acc[2 * i + 1] = __fadd_rn(acc[2 * i + 1], __fmul_rn(w, Pair16<__nv_bfloat16>::hi(words[i])));
+          }
+        }
+      }
+    }
+    __nv_bfloat16* o = out + static_cast<int64_t>(token) * hidden + c;
+    if (accumulate) {
+      const uint4 prev = *reinterpret_cast<const uint4*>(o);
+      const uint32_t words[4] = {prev.x, prev.y, prev.z, prev.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[2 * i] += Pair16<__nv_bfloat16>::lo(words[i]);
+        acc[2 * i + 1] += Pair16<__nv_bfloat16>::hi(words[i]);
+      }
+    }
+    uint4 v;
+    v.x = Pair16<__nv_bfloat16>::pack(acc[0], acc[1]);
+    v.y = Pair16<__nv_bfloat16>::pack(acc[2], acc[3]);
+    v.z = Pair16<__nv_bfloat16>::pack(acc[4], acc[5]);
+    v.w = Pair16<__nv_bfloat16>::pack(acc[6], acc[7]);
+    *reinterpret_cast<uint4*>(o) = v;
+  }
+}
+
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // With at most 32 tokens (and few enough slots for the single-CTA bookkeeping kernel) the wide GEMM variants keep
@@ -914,7 +970,10 @@ int moe_fused(const void* x, const void* w1, const void* w1_sf, const void* w2, 
     moe_combine_kernel<float, float><<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
         ws.partial, ws.h.slot_row, route_w, static_cast<float*>(out), hidden, top_k, accumulate);
   } else if (rows_bf16) {
-    moe_combine_kernel<__nv_bfloat16, __nv_bfloat16><<<static_cast<unsigned>(tokens), threads, 0, stream>>>(
+    // hidden is a multiple of 64 (checked above): whole 16-byte pieces (32.8 -> 27.9 us at the prefill shape against
+    // 8-byte accesses with one row in flight)
+    const int t8 = hidden / 8 >= 256 ? 256 : 128;
+    moe_combine_bf16x8_kernel<<<static_cast<unsigned>(tokens), t8, 0, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(ws.partial), ws.h.slot_row, route_w, static_cast<__nv_bfloat16*>(out),
         hidden, top_k, accumulate);
   } else {
