@@ -577,22 +577,30 @@ struct EpilogueSwiglu {
     uint8_t* sf_tile = act_sf + static_cast<int64_t>(m_blk) * rk2 * 512 + (row & 31) * 16 + (row >> 5) * 4;
     const int span = kHalf / parts;
     // one 32-column group: silu(gate) * up -> bf16 -> NVFP4 (two 16-element blocks), codes and scale bytes out
+    // The arithmetic runs on the packed f32x2 instructions where it can (scaling, 1 + e, the product, the bf16
+    // round trip): every operation is the same IEEE f32 operation as in scalar form, two per instruction -- the
+    // fewer instructions the epilogue issues, the less it holds up the warps that feed the tensor pipe.
+    const uint64_t a1_2 = f32x2_pack(a1, a1);
+    const uint64_t one_2 = f32x2_pack(1.0f, 1.0f);
     auto finish = [&](int c0, const uint32_t (&up)[32], const uint32_t (&gate)[32]) {
       if (j0 + c0 >= inter) return;
       uint32_t sfpair = 0;
       uint32_t codes[4];
 #pragma unroll
       for (int b = 0; b < 2; ++b) {
-        float v[16];
+        uint64_t v2[8];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float u = __uint_as_float(up[16 * b + i]) * a1;
-          const float g = __uint_as_float(gate[16 * b + i]) * a1;
-          const float s = __fdividef(g, 1.0f + __expf(-g));       // silu in f32 (a few ulp; rounded to bf16 next)
-          v[i] = __bfloat162float(__float2bfloat16_rn(__fmul_rn(s, u)));
+        for (int i = 0; i < 8; ++i) {
+          const uint64_t u2 = f32x2_mul(f32x2_pack(__uint_as_float(up[16 * b + 2 * i]), __uint_as_float(up[16 * b + 2 * i + 1])), a1_2);
+          const uint64_t g2 = f32x2_mul(f32x2_pack(__uint_as_float(gate[16 * b + 2 * i]), __uint_as_float(gate[16 * b + 2 * i + 1])), a1_2);
+          const float g0 = f32x2_lo(g2), g1 = f32x2_hi(g2);
+          const uint64_t d2 = f32x2_add(one_2, f32x2_pack(__expf(-g0), __expf(-g1)));
+          // silu in f32 (a few ulp; rounded to bf16 next)
+          const uint64_t s2 = f32x2_pack(__fdividef(g0, f32x2_lo(d2)), __fdividef(g1, f32x2_hi(d2)));
+          v2[i] = pair16_to_f32x2<__nv_bfloat16>(f32x2_to_pair16<__nv_bfloat16>(f32x2_mul(s2, u2)));
         }
         uint32_t sfb;
-        quantize_block16<true>(v, gs, codes[2 * b], codes[2 * b + 1], sfb);
+        quantize_block16<true>(v2, gs, codes[2 * b], codes[2 * b + 1], sfb);
         sfpair |= sfb << (8 * b);
       }
       *reinterpret_cast<uint4*>(act_codes + grow * (inter >> 1) + ((j0 + c0) >> 1)) =
